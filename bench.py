@@ -1,0 +1,383 @@
+#!/usr/bin/env python
+"""Benchmark of the GGUF quantized-linear hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl kq|reference]
+
+Workload (N=1): decode GEMV at 27B-class shapes - a stack of LAYERS distinct MLP blocks, each with
+gate and up projections in Q4_K (K=5120, N=17408) and a down projection in Q6_K (K=17408, N=5120),
+seeded synthetic blocks, bf16 N(0,1) activations.  One STEP is one pass over the whole stack for every
+M in {1, 2, 8, 16}; the stack (2.8 GB at 16 layers) is far larger than the 126 MB L2, so every weight byte
+comes from HBM.  The op called per matrix follows the reference's own regime dispatch
+(quantization/linear.py:40-63): ggml_mul_mat_vec_a8 for small M, ggml_mul_mat_a8 above.
+
+value     whole-job algorithmic GB/s, activations and weights resident in HBM, calls made through the
+          C ABI and replayed as one CUDA graph per step (the reference serves under CUDA graphs too)
+e2e       same metric through the plugin-facing op API (kaillm_b200.linear.fused_mul_mat_gguf ->
+          torch.ops._C_gguf.*) with HOST activations/outputs: pinned host -> device copy of every call's
+          input and device -> host read of every call's output inside the timed region
+roofline  the dominant kernel alone (the Q4_K GEMV over all Q4_K matrices and all M, activations already
+          quantized), algorithmic bytes / CUDA-event time against the measured HBM copy bandwidth
+With N > 1 the weights are row-sharded over the ranks and every call ends with an all-gather of the
+output slices over NCCL (total work fixed: strong scaling).
+
+--impl reference times the reference's CPU path (gguf-reader style dequantize + torch matmul) on the host
+cores, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+Q4_K, Q6_K = 12, 14
+K_HID, N_FF = 5120, 17408
+MS = (1, 2, 8, 16)
+
+
+def algorithmic_bytes(qt: int, n: int, k: int, m: int, esize: int = 2) -> int:
+    blk, nb = {12: (256, 144), 14: (256, 210)}[qt]
+    return n * (k // blk) * nb + m * k * esize + m * n * esize
+
+
+def use_mmq(m: int, n: int) -> bool:
+    """The reference's choice for K-quant types (quantization/linear.py:43-54)."""
+    return m > (2 if n > 5120 else 6)
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        self.t.join(timeout=2)
+        sm, smax, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                smax.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7),
+                              ("sw_power_cap", 8)):
+                if len(r) > col and r[col].lower() == "active":
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------- reference arm
+def reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import numpy as np
+    import torch
+
+    from kaillm_b200 import synth
+    from oracle import gguf_oracle as O
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    m = 16
+    rows_q4, rows_q6 = 17408 // 8, 5120 // 8          # a 1/8 row slice of each matrix keeps a step to seconds
+    wq4 = synth.wire_numpy(Q4_K, rows_q4, K_HID, seed=1)
+    wq6 = synth.wire_numpy(Q6_K, rows_q6, N_FF, seed=2)
+    x1 = torch.from_numpy(synth.activations_numpy(m, K_HID, seed=3, dtype="bf16"))
+    x2 = torch.from_numpy(synth.activations_numpy(m, N_FF, seed=4, dtype="bf16"))
+    bytes_step = 2 * algorithmic_bytes(Q4_K, rows_q4, K_HID, m) + algorithmic_bytes(Q6_K, rows_q6, N_FF, m)
+
+    def step():
+        for w, qt, x in ((wq4, Q4_K, x1), (wq4, Q4_K, x1), (wq6, Q6_K, x2)):
+            W = torch.from_numpy(O.dequantize_f32(w, qt, iq3s_top=60))
+            torch.matmul(x, W.T)
+
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    val = bytes_step / dt / 1e9
+    sample = (f"1/8 row slice of one MLP block at M={m}: Q4_K gate+up {rows_q4}x{K_HID}, Q6_K down {rows_q6}x{N_FF}; "
+              "numpy dequantize (gguf-reader arithmetic) + torch.matmul fp32")
+    print(json.dumps({
+        "impl": "reference", "metric": "quantized GEMV HBM GB/s", "value": val, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "27B-class decode GEMV, Q4_K gate/up + Q6_K down", "M": [m], "sample": "1/8 rows"},
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ---------------------------------------------------------------------------------------------- our arm
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="kq", choices=["kq", "reference"])
+    ap.add_argument("--layers", type=int, default=16, help="distinct MLP blocks in the stack")
+    ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--small", action="store_true", help="2-layer stack, for profiler captures")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "kq" and not args.small:
+        args.warmup = 3
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+    if args.small:
+        args.layers = 2
+
+    import torch
+
+    from kaillm_b200 import capi, linear, synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the GGUF kernels have no CPU fallback)")
+    dev = torch.device(f"cuda:{local}")
+    torch.cuda.set_device(dev)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    # ---- the stack: per layer gate, up (Q4_K) and down (Q6_K); rows sharded over ranks
+    def make(qt, n, k, seed):
+        w = synth.wire_torch(qt, n, k, seed, dev)
+        if world > 1:
+            per = n // world
+            w = w[rank * per:(rank + 1) * per].contiguous()
+        return w
+
+    mats = []  # (W, qt, n_full, k)
+    for layer in range(args.layers):
+        mats.append((make(Q4_K, N_FF, K_HID, 10 * layer + 1), Q4_K, N_FF, K_HID))
+        mats.append((make(Q4_K, N_FF, K_HID, 10 * layer + 2), Q4_K, N_FF, K_HID))
+        mats.append((make(Q6_K, K_HID, N_FF, 10 * layer + 3), Q6_K, K_HID, N_FF))
+    g = torch.Generator(device=dev)
+    g.manual_seed(1234)
+    xs = {(m, k): torch.randn((m, k), device=dev, generator=g).to(torch.bfloat16) for m in MS for k in (K_HID, N_FF)}
+    ys = {(m, n): torch.empty((m, n // world), dtype=torch.bfloat16, device=dev) for m in MS for n in (K_HID, N_FF)}
+    yg = {(m, n): torch.empty((world, m, n // world), dtype=torch.bfloat16, device=dev) for m in MS for n in (K_HID, N_FF)}
+    ws = max(capi.workspace_bytes(qt, 16, n // world, k) for _, qt, n, k in mats)
+    scratch = torch.empty(ws, dtype=torch.uint8, device=dev)
+    bytes_step = sum(algorithmic_bytes(qt, n, k, m) for m in MS for _, qt, n, k in mats)
+    calls_step = len(MS) * len(mats)
+
+    def step():
+        for m in MS:
+            for W, qt, n, k in mats:
+                y = capi.mul_mat(W, xs[(m, k)], qt, mmq=use_mmq(m, n), out=ys[(m, n)], scratch=scratch, n=n // world)
+                if world > 1:
+                    dist.all_gather_into_tensor(yg[(m, n)], y)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    stream = torch.cuda.Stream(device=dev)
+    graph = None
+    with torch.cuda.stream(stream):
+        l0 = capi.get_option("launch_count")
+        step()
+        launches_step = capi.get_option("launch_count") - l0
+        torch.cuda.synchronize()
+        if not args.no_graph:
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    step()
+            except Exception as e:  # noqa: BLE001 - report and fall back to eager launches
+                print(f"[bench] CUDA graph capture failed ({e!r}); running eagerly", file=sys.stderr)
+                graph = None
+        run = graph.replay if graph is not None else step
+        for _ in range(args.warmup):
+            run()
+        barrier()
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record(stream)
+        for _ in range(args.steps):
+            run()
+        e1.record(stream)
+        barrier()
+        ms_total = e0.elapsed_time(e1)
+        clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms_total], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    value = bytes_step / (ms_step * 1e-3) / 1e9
+
+    # ---- roofline of the dominant kernel: Q4_K GEMV alone, activations already quantized
+    q4 = [(W, n, k) for W, qt, n, k in mats if qt == Q4_K]
+    roof = None
+    with torch.cuda.stream(stream):
+        def q4_region():
+            for m in MS:
+                capi.prepare_q8(xs[(m, K_HID)], Q4_K, N_FF // world, scratch)
+                for W, n, k in q4:
+                    capi.mul_mat_prepared(W, Q4_K, m, k, ys[(m, n)], scratch, mmq=use_mmq(m, n))
+        q4_region()
+        torch.cuda.synchronize()
+        g4 = None
+        if not args.no_graph:
+            try:
+                g4 = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g4, stream=stream):
+                    q4_region()
+            except Exception:  # noqa: BLE001
+                g4 = None
+        run4 = g4.replay if g4 is not None else q4_region
+        for _ in range(3):
+            run4()
+        torch.cuda.synchronize()
+        reps = 10
+        e0.record(stream)
+        for _ in range(reps):
+            run4()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        n_launch = len(MS) * len(q4)
+        us = e0.elapsed_time(e1) * 1e3 / (reps * n_launch)
+        alg = sum(algorithmic_bytes(Q4_K, N_FF // world, K_HID, m) for m in MS) / len(MS)
+        peak, how = measured_peaks()
+        ach = alg / (us * 1e-6) / 1e9
+        roof = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+                "kernel": "Q4_K decode GEMV (gate/up 17408x5120), mean over M=1,2,8,16", "us_per_launch": us,
+                "algorithmic_bytes_per_launch": alg, "peak_source": f"of {how} (MEASURED_PEAKS.json hbm_gbs)",
+                "note": "region = 4 q8_1 quantize launches + %d GEMV launches, divided by the GEMV launches" % n_launch}
+
+    # ---- end to end through the op API with host buffers
+    e2e = None
+    with torch.cuda.stream(stream):
+        hx = {key: v.cpu().pin_memory() for key, v in xs.items()}
+        hy = {(m, n): torch.empty((m, n // world), dtype=torch.bfloat16).pin_memory() for m in MS for n in (K_HID, N_FF)}
+        h2d = sum(hx[(m, k)].numel() * 2 for m in MS for _, _, _, k in mats)
+        d2h = sum(hy[(m, n)].numel() * 2 for m in MS for _, _, n, _ in mats)
+        dx = {key: torch.empty_like(v) for key, v in xs.items()}
+
+        def e2e_step():
+            for m in MS:
+                for W, qt, n, k in mats:
+                    dx[(m, k)].copy_(hx[(m, k)], non_blocking=True)
+                    y = linear.fused_mul_mat_gguf(dx[(m, k)], W, qt)
+                    if world > 1:
+                        dist.all_gather_into_tensor(yg[(m, n)], y)
+                    hy[(m, n)].copy_(y, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        esteps = max(2, min(args.steps, 5))
+        e0.record(stream)
+        for _ in range(esteps):
+            e2e_step()
+        e1.record(stream)
+        barrier()
+        t2 = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+        ms_e2e = float(t2.item()) / esteps
+        e2e = {"value": bytes_step / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e,
+               "api": "kaillm_b200.linear.fused_mul_mat_gguf -> torch.ops._C_gguf.ggml_mul_mat_{vec_,}a8, eager"}
+
+    # ---- CPU baseline (oracle port of the reference's CPU path) on rank 0, bounded sample
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        import numpy as np
+
+        from oracle import gguf_oracle as O
+        cores = os.cpu_count() or 1
+        torch.set_num_threads(cores)
+        m = 16
+        r4, r6 = N_FF // 4, K_HID // 4
+        w4 = synth.wire_numpy(Q4_K, r4, K_HID, seed=1)
+        w6 = synth.wire_numpy(Q6_K, r6, N_FF, seed=2)
+        x1 = torch.from_numpy(synth.activations_numpy(m, K_HID, seed=3, dtype="bf16"))
+        x2 = torch.from_numpy(synth.activations_numpy(m, N_FF, seed=4, dtype="bf16"))
+        t0 = time.perf_counter()
+        for w, qt, x in ((w4, Q4_K, x1), (w4, Q4_K, x1), (w6, Q6_K, x2)):
+            Wd = torch.from_numpy(O.dequantize_f32(w, qt, iq3s_top=60))
+            torch.matmul(x, Wd.T)
+        dt = time.perf_counter() - t0
+        b = 2 * algorithmic_bytes(Q4_K, r4, K_HID, m) + algorithmic_bytes(Q6_K, r6, N_FF, m)
+        cpu = {"value": b / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": "port", "seconds": dt,
+               "sample": f"1/4 row slice of one MLP block at M={m} (Q4_K gate+up {r4}x{K_HID}, Q6_K down {r6}x{N_FF}): "
+                         "numpy dequantize with gguf-reader arithmetic + torch.matmul fp32"}
+
+    if rank == 0:
+        out = {
+            "metric": "quantized GEMV HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": "27B-class decode GEMV: Q4_K gate/up (K=5120,N=17408) + Q6_K down (K=17408,N=5120)",
+                       "layers": args.layers, "M": list(MS), "activations": "bf16 N(0,1)",
+                       "calls_per_step": calls_step, "bytes_per_step": bytes_step,
+                       "l2": "stack of %.2f GB per rank >> 126 MB L2, no flush needed" % (sum(w.numel() for w, *_ in mats) / 1e9),
+                       "launch": "cuda graph replay" if graph is not None else "eager",
+                       "parallelism": f"row-sharded x{world} + all-gather" if world > 1 else "single GPU"},
+            "frac_of_measured_hbm": value / measured_peaks()[0], "frac_of_nominal_8tbs": value / 8000.0,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches_step * args.steps,
+            "roofline": roof, "cpu_baseline": cpu,
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,133 @@
+/*
+ * kq_gguf.h - C ABI of libkq: GGUF block-quantized linear kernels for NVIDIA B200 (sm_100a).
+ *
+ * This is the boundary a host runtime binds (ctypes / cgo / a torch extension).  Every entry point
+ *   - takes plain device pointers and sizes, never a framework type;
+ *   - allocates nothing (except where a comment says otherwise) and never synchronises: work is
+ *     enqueued on `stream` (a cudaStream_t passed as void*, NULL = the legacy default stream) of the
+ *     CURRENT device, and all scratch memory is the caller's;
+ *   - returns 0 on success or a KQ_E* code; kq_last_error() then gives a thread-local message.
+ *     (Same convention as the reference's own C-ABI bridges: `int status` + `current_direct_error()`,
+ *     vllm_gguf_plugin/native/kernels/current_ggml_direct.cu:32,174.)
+ *
+ * Each function names the reference interface it replaces (paths inside the kaiLLM source tree).
+ *
+ * Weight tensors are GGUF wire bytes: uint8 [n, k/blk * block_bytes], rows contiguous, blocks
+ * consecutive along k (vllm_gguf_plugin/csrc/gguf/ggml-common.h:20-150).  Supported GGML type ids:
+ * 2 (Q4_0), 8 (Q8_0), 10 (Q2_K), 12 (Q4_K), 14 (Q6_K), 21 (IQ3_S); any other id is KQ_EUNSUPPORTED.
+ */
+#ifndef KQ_GGUF_H
+#define KQ_GGUF_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KQ_OK 0
+#define KQ_EINVAL 1        /* bad argument (null pointer, negative size, k not a multiple of the block, ...) */
+#define KQ_EUNSUPPORTED 2  /* GGML type id or dtype outside the supported set */
+#define KQ_ESCRATCH 3      /* scratch buffer missing, misaligned or too small */
+#define KQ_ECUDA 4         /* a CUDA runtime call or launch failed; message holds cudaGetErrorString */
+#define KQ_ELIMIT 5        /* size beyond a stated maximum of the entry point */
+
+/* element types of activations / outputs */
+#define KQ_F32 0
+#define KQ_F16 1
+#define KQ_BF16 2
+
+/* GGML type ids (gguf-reader/gguf/constants.py:5763-5799) */
+#define KQ_TYPE_Q4_0 2
+#define KQ_TYPE_Q8_0 8
+#define KQ_TYPE_Q2_K 10
+#define KQ_TYPE_Q4_K 12
+#define KQ_TYPE_Q6_K 14
+#define KQ_TYPE_IQ3_S 21
+
+/* Thread-local text of the last error returned on this thread ("" if none). */
+const char* kq_last_error(void);
+
+/* ABI version of this header (bumped on incompatible change). */
+int kq_abi_version(void);
+
+/* Weights per block and bytes per block of a GGML type
+ * (gguf-reader/gguf/constants.py:5958 GGML_QUANT_SIZES).  KQ_EUNSUPPORTED for other ids. */
+int kq_block_geometry(int type, int* weights_per_block, int* bytes_per_block);
+
+/* Bytes of caller-provided scratch kq_mul_mat_vec_a8 / kq_mul_mat_a8 need for these sizes
+ * (quantized activations + split-K partials).  The scratch pointer must be 256-byte aligned.
+ * Replaces the `quant_X` allocation in vllm_gguf_plugin/csrc/gguf/gguf_kernel.cu:114-115. */
+size_t kq_workspace_bytes(int type, int64_t m, int64_t n, int64_t k);
+
+/* q8_1 activation quantizer, reference scratch layout.
+ * x: [m, k] row-major with row stride `stride_x` elements, dtype x_dtype.
+ * out: m * (kpad/32) blocks of 36 bytes {fp16 d, fp16 sum, int8 q[32]}, kpad = ceil(k/512)*512,
+ * positions >= k quantize as zeros.
+ * Replaces quantize_row_q8_1_cuda, vllm_gguf_plugin/csrc/gguf/gguf_kernel.cu:32-85. */
+int kq_quantize_q8_1(const void* x, int x_dtype, int64_t m, int64_t k, int64_t stride_x,
+                     void* out_blocks, void* stream);
+
+/* y[m, n] = q8_1(x)[m, k] . W[n, k]^T with the arithmetic of the reference's MMVQ kernels.
+ * y has row stride `stride_y` elements and dtype y_dtype (the reference uses x's dtype).
+ * Any m >= 1 is accepted; the kernel variant is chosen inside by m.
+ * Replaces ggml_mul_mat_vec_a8, vllm_gguf_plugin/csrc/gguf/gguf_kernel.cu:104-218
+ * (kernels: csrc/gguf/mmvq.cuh:2-41, csrc/gguf/vecdotq.cuh). */
+int kq_mul_mat_vec_a8(const void* W, int type, int64_t n, int64_t k,
+                      const void* x, int x_dtype, int64_t m, int64_t stride_x,
+                      void* y, int y_dtype, int64_t stride_y,
+                      void* scratch, size_t scratch_bytes, void* stream);
+
+/* Same contract with the arithmetic of the reference's MMQ kernels (Q4_K's min term uses the fp16
+ * block sum of the raw activations).  IQ3_S is KQ_EUNSUPPORTED here, as in the reference.
+ * Replaces ggml_mul_mat_a8, vllm_gguf_plugin/csrc/gguf/gguf_kernel.cu:220-290
+ * (kernels: csrc/gguf/mmq.cuh:2-104). */
+int kq_mul_mat_a8(const void* W, int type, int64_t n, int64_t k,
+                  const void* x, int x_dtype, int64_t m, int64_t stride_x,
+                  void* y, int y_dtype, int64_t stride_y,
+                  void* scratch, size_t scratch_bytes, void* stream);
+
+/* The two halves of the mul_mat entry points, for layers that share one activation (q/k/v, gate/up):
+ * kq_prepare_q8 quantizes x into `scratch`; kq_mul_mat_prepared multiplies any number of weight tensors
+ * against the activations already held there (mmq != 0 selects the MMQ arithmetic).  n passed to
+ * kq_prepare_q8 must be >= every n used with that scratch (it sizes the split-K area).
+ * Replace the quantize_row_q8_1_cuda call and the kernel launch inside ggml_mul_mat_vec_a8 /
+ * ggml_mul_mat_a8, vllm_gguf_plugin/csrc/gguf/gguf_kernel.cu:116-118 and 119-215, 232-287; the
+ * reference's production path shares the preparation the same way
+ * (vllm_gguf_plugin/quantization/native_fused.py:282-347). */
+int kq_prepare_q8(int type, int64_t n, int64_t k, const void* x, int x_dtype, int64_t m, int64_t stride_x,
+                  void* scratch, size_t scratch_bytes, void* stream);
+int kq_mul_mat_prepared(const void* W, int type, int64_t n, int64_t k, int64_t m,
+                        void* y, int y_dtype, int64_t stride_y, int mmq,
+                        void* scratch, size_t scratch_bytes, void* stream);
+
+/* Dense dequantization of `count` weights (count a multiple of the block size) to out_dtype, with
+ * the reference kernels' fp16 intermediate roundings.
+ * Replaces ggml_dequantize, vllm_gguf_plugin/csrc/gguf/gguf_kernel.cu:87-102
+ * (kernels: csrc/gguf/dequantize.cuh:3-16,69-121,156-196,232-256,334-353). */
+int kq_dequantize(const void* W, int type, int64_t count, void* out, int out_dtype, void* stream);
+
+/* Test hook: exact integer dot products per weight scale group.
+ * dots: int32 [m, n, k/G] with G = 32 (Q4_0, Q8_0, Q4_K, IQ3_S) or 16 (Q2_K, Q6_K);
+ * sums: int32 [m, k/G] = sum of the activation codes of each group (may be NULL).
+ * Uses the same scratch as the mul_mat entry points.  No counterpart in the reference (its kernels
+ * never materialise the integer dots); exists so the bit-exactness of the integer path can be
+ * checked through the ABI. */
+int kq_debug_group_dots(const void* W, int type, int64_t n, int64_t k,
+                        const void* x, int x_dtype, int64_t m, int64_t stride_x,
+                        int32_t* dots, int32_t* sums,
+                        void* scratch, size_t scratch_bytes, void* stream);
+
+/* Runtime knobs for tests and profiling (process-wide, not thread-safe against concurrent launches):
+ *   "gemv_impl"   0 = choose by shape (default), 1 = force the dp4a kernel, 2 = force the tensor-core kernel
+ *   "half_fma"    1 = K-quant dequantize contracts fp16 mul+sub into one fma (default), 0 = two roundings
+ * Returns KQ_EINVAL for an unknown name. */
+int kq_set_option(const char* name, int value);
+/* kq_get_option additionally answers "launch_count": kernels launched by the library so far. */
+int kq_get_option(const char* name, int* value);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KQ_GGUF_H */

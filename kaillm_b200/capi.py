@@ -1,0 +1,162 @@
+"""ctypes binding of libkq's C ABI (include/kq_gguf.h).
+
+The wrappers take torch tensors only to obtain device pointers, strides and the current stream; every
+call goes through the `extern "C"` entry points, so tests and benchmarks that use this module exercise
+exactly what a cgo/JNI/ctypes host of the reference would bind.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libkq.so")
+
+KQ_OK, KQ_EINVAL, KQ_EUNSUPPORTED, KQ_ESCRATCH, KQ_ECUDA, KQ_ELIMIT = 0, 1, 2, 3, 4, 5
+KQ_F32, KQ_F16, KQ_BF16 = 0, 1, 2
+_DT = {torch.float32: KQ_F32, torch.float16: KQ_F16, torch.bfloat16: KQ_BF16}
+
+EXPORTS = (
+    "kq_last_error", "kq_abi_version", "kq_block_geometry", "kq_workspace_bytes", "kq_quantize_q8_1",
+    "kq_mul_mat_vec_a8", "kq_mul_mat_a8", "kq_dequantize", "kq_debug_group_dots", "kq_set_option",
+    "kq_get_option", "kq_prepare_q8", "kq_mul_mat_prepared",
+)
+
+
+class KqError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"libkq error {code}: {msg}")
+        self.code = code
+
+
+def _load() -> ctypes.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m kaillm_b200._build` "
+            "(there is no CPU fallback for the GGUF kernels)")
+    lib = ctypes.CDLL(LIB_PATH)
+    vp, i32, i64, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_size_t
+    lib.kq_last_error.restype = ctypes.c_char_p
+    lib.kq_last_error.argtypes = []
+    lib.kq_abi_version.restype = i32
+    lib.kq_block_geometry.argtypes = [i32, ctypes.POINTER(i32), ctypes.POINTER(i32)]
+    lib.kq_workspace_bytes.restype = sz
+    lib.kq_workspace_bytes.argtypes = [i32, i64, i64, i64]
+    lib.kq_quantize_q8_1.argtypes = [vp, i32, i64, i64, i64, vp, vp]
+    mm = [vp, i32, i64, i64, vp, i32, i64, i64, vp, i32, i64, vp, sz, vp]
+    lib.kq_mul_mat_vec_a8.argtypes = mm
+    lib.kq_mul_mat_a8.argtypes = mm
+    lib.kq_prepare_q8.argtypes = [i32, i64, i64, vp, i32, i64, i64, vp, sz, vp]
+    lib.kq_mul_mat_prepared.argtypes = [vp, i32, i64, i64, i64, vp, i32, i64, i32, vp, sz, vp]
+    lib.kq_dequantize.argtypes = [vp, i32, i64, vp, i32, vp]
+    lib.kq_debug_group_dots.argtypes = [vp, i32, i64, i64, vp, i32, i64, i64, vp, vp, vp, sz, vp]
+    lib.kq_set_option.argtypes = [ctypes.c_char_p, i32]
+    lib.kq_get_option.argtypes = [ctypes.c_char_p, ctypes.POINTER(i32)]
+    return lib
+
+
+lib = _load()
+
+
+def _check(rc: int) -> None:
+    if rc != KQ_OK:
+        raise KqError(rc, lib.kq_last_error().decode())
+
+
+def _stream(dev) -> int:
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+def block_geometry(qtype: int) -> tuple[int, int]:
+    a, b = ctypes.c_int(), ctypes.c_int()
+    _check(lib.kq_block_geometry(qtype, ctypes.byref(a), ctypes.byref(b)))
+    return a.value, b.value
+
+
+def workspace_bytes(qtype: int, m: int, n: int, k: int) -> int:
+    return int(lib.kq_workspace_bytes(qtype, m, n, k))
+
+
+def set_option(name: str, value: int) -> None:
+    _check(lib.kq_set_option(name.encode(), value))
+
+
+def get_option(name: str) -> int:
+    v = ctypes.c_int()
+    _check(lib.kq_get_option(name.encode(), ctypes.byref(v)))
+    return v.value
+
+
+def quantize_q8_1(x: torch.Tensor) -> torch.Tensor:
+    """x [m,k] -> uint8 [m, kpad/32, 36] in the reference's block_q8_1 layout."""
+    m, k = x.shape
+    kpad = (k + 511) // 512 * 512
+    out = torch.empty((m, kpad // 32, 36), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        _check(lib.kq_quantize_q8_1(x.data_ptr(), _DT[x.dtype], m, k, x.stride(0), out.data_ptr(), _stream(x.device)))
+    return out
+
+
+def _k_of(W: torch.Tensor, qtype: int) -> int:
+    blk, nb = block_geometry(qtype)
+    return W.shape[1] // nb * blk
+
+
+def mul_mat(W: torch.Tensor, x: torch.Tensor, qtype: int, *, mmq: bool = False, out_dtype=None,
+            out: torch.Tensor | None = None, scratch: torch.Tensor | None = None, n: int | None = None) -> torch.Tensor:
+    """y[m,n] through kq_mul_mat_vec_a8 (mmq=False) or kq_mul_mat_a8 (mmq=True)."""
+    m, k = x.shape
+    n = W.shape[0] if n is None else n
+    odt = out_dtype or x.dtype
+    if out is None:
+        out = torch.empty((m, n), dtype=odt, device=x.device)
+    ws = workspace_bytes(qtype, m, n, k)
+    if scratch is None:
+        scratch = torch.empty(ws, dtype=torch.uint8, device=x.device)
+    fn = lib.kq_mul_mat_a8 if mmq else lib.kq_mul_mat_vec_a8
+    with torch.cuda.device(x.device):
+        _check(fn(W.data_ptr(), qtype, n, k, x.data_ptr(), _DT[x.dtype], m, x.stride(0), out.data_ptr(),
+                  _DT[out.dtype], out.stride(0), scratch.data_ptr(), scratch.numel(), _stream(x.device)))
+    return out
+
+
+def prepare_q8(x: torch.Tensor, qtype: int, n: int, scratch: torch.Tensor) -> None:
+    """Quantize x [m,k] into `scratch` (kq_prepare_q8)."""
+    m, k = x.shape
+    with torch.cuda.device(x.device):
+        _check(lib.kq_prepare_q8(qtype, n, k, x.data_ptr(), _DT[x.dtype], m, x.stride(0), scratch.data_ptr(),
+                                 scratch.numel(), _stream(x.device)))
+
+
+def mul_mat_prepared(W: torch.Tensor, qtype: int, m: int, k: int, out: torch.Tensor, scratch: torch.Tensor,
+                     *, mmq: bool = False) -> torch.Tensor:
+    """y = activations held in `scratch` times W (kq_mul_mat_prepared)."""
+    n = W.shape[0]
+    with torch.cuda.device(W.device):
+        _check(lib.kq_mul_mat_prepared(W.data_ptr(), qtype, n, k, m, out.data_ptr(), _DT[out.dtype], out.stride(0),
+                                       int(mmq), scratch.data_ptr(), scratch.numel(), _stream(W.device)))
+    return out
+
+
+def dequantize(W: torch.Tensor, qtype: int, count: int, dtype=torch.float16) -> torch.Tensor:
+    out = torch.empty(count, dtype=dtype, device=W.device)
+    with torch.cuda.device(W.device):
+        _check(lib.kq_dequantize(W.data_ptr(), qtype, count, out.data_ptr(), _DT[dtype], _stream(W.device)))
+    return out
+
+
+def debug_group_dots(W: torch.Tensor, x: torch.Tensor, qtype: int):
+    m, k = x.shape
+    n = W.shape[0]
+    g = 16 if qtype in (10, 14) else 32
+    dots = torch.empty((m, n, k // g), dtype=torch.int32, device=x.device)
+    sums = torch.empty((m, k // g), dtype=torch.int32, device=x.device)
+    ws = workspace_bytes(qtype, m, n, k)
+    scratch = torch.empty(ws, dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        _check(lib.kq_debug_group_dots(W.data_ptr(), qtype, n, k, x.data_ptr(), _DT[x.dtype], m, x.stride(0),
+                                       dots.data_ptr(), sums.data_ptr(), scratch.data_ptr(), scratch.numel(),
+                                       _stream(x.device)))
+    return dots, sums

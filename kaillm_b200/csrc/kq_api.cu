@@ -1,0 +1,191 @@
+// C ABI of libkq (see include/kq_gguf.h): argument validation, scratch carving, kernel selection.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "kq_common.cuh"
+
+namespace kq {
+
+static thread_local char t_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(t_err, sizeof(t_err), fmt, ap);
+  va_end(ap);
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  set_error("CUDA error %d (%s) at %s", (int)e, cudaGetErrorString(e), what);
+  return KQ_ECUDA;
+}
+
+Options& options() {
+  static Options o = {0, 1, 0};
+  return o;
+}
+
+static bool dtype_ok(int dt) { return dt == KQ_F32 || dt == KQ_F16 || dt == KQ_BF16; }
+static size_t dtype_size(int dt) { return dt == KQ_F32 ? 4 : 2; }
+
+struct Problem {
+  int blk, bytes;
+  int64_t rowbytes;
+  Q8Layout L;
+};
+
+// need_w / need_x: the prepare / prepared entry points pass only one of the two operands
+static int validate(const char* fn, const void* W, int type, int64_t n, int64_t k, const void* x, int x_dtype,
+                    int64_t m, int64_t stride_x, const void* scratch, size_t scratch_bytes, Problem& p,
+                    bool need_w = true, bool need_x = true) {
+  if (!type_geometry(type, &p.blk, &p.bytes)) {
+    set_error("%s: GGML type %d is not supported (supported: 2 Q4_0, 8 Q8_0, 10 Q2_K, 12 Q4_K, 14 Q6_K, 21 IQ3_S)", fn, type);
+    return KQ_EUNSUPPORTED;
+  }
+  if (need_x && !dtype_ok(x_dtype)) { set_error("%s: unsupported activation dtype %d", fn, x_dtype); return KQ_EUNSUPPORTED; }
+  if (n <= 0 || k <= 0 || m <= 0) { set_error("%s: n, k, m must be positive (n=%lld k=%lld m=%lld)", fn, (long long)n, (long long)k, (long long)m); return KQ_EINVAL; }
+  if (k % p.blk) { set_error("%s: k=%lld is not a multiple of the block size %d", fn, (long long)k, p.blk); return KQ_EINVAL; }
+  if (n > 0x7fffffff / 2 || k > (1 << 24) || m > (1 << 20)) { set_error("%s: size out of range", fn); return KQ_ELIMIT; }
+  if ((need_w && !W) || (need_x && !x)) { set_error("%s: null pointer", fn); return KQ_EINVAL; }
+  if (need_x && stride_x < k) { set_error("%s: stride_x=%lld < k=%lld", fn, (long long)stride_x, (long long)k); return KQ_EINVAL; }
+  const uintptr_t wa = (uintptr_t)W;
+  const int need = (p.bytes % 4 == 0) ? 4 : 2;
+  if (wa % need) { set_error("%s: weight pointer must be %d-byte aligned for this type", fn, need); return KQ_EINVAL; }
+  if (need_x && (uintptr_t)x % dtype_size(x_dtype)) { set_error("%s: misaligned activation pointer", fn); return KQ_EINVAL; }
+  p.rowbytes = k / p.blk * p.bytes;
+  p.L = q8_layout(m, n, k);
+  if (!scratch || (uintptr_t)scratch % 256) { set_error("%s: scratch must be non-null and 256-byte aligned", fn); return KQ_ESCRATCH; }
+  if (scratch_bytes < p.L.total) { set_error("%s: scratch too small (%zu < %zu)", fn, scratch_bytes, p.L.total); return KQ_ESCRATCH; }
+  return KQ_OK;
+}
+
+static int mul_mat(const char* fn, bool mmq, const void* W, int type, int64_t n, int64_t k, const void* x,
+                   int x_dtype, int64_t m, int64_t stride_x, void* y, int y_dtype, int64_t stride_y, void* scratch,
+                   size_t scratch_bytes, void* stream, bool need_w = true, bool need_x = true) {
+  t_err[0] = 0;
+  Problem p;
+  int rc = validate(fn, W, type, n, k, x, x_dtype, m, stride_x, scratch, scratch_bytes, p, need_w, need_x);
+  if (rc) return rc;
+  if (!need_w) {
+    return launch_quantize(x, x_dtype, m, k, stride_x, (uint8_t*)scratch + p.L.off_ds, (uint8_t*)scratch + p.L.off_qs,
+                           nullptr, p.L.kpad, (cudaStream_t)stream);
+  }
+  if (mmq && type == KQ_TYPE_IQ3_S) { set_error("%s: IQ3_S has no MMQ kernel (use dequantize + matmul or mul_mat_vec)", fn); return KQ_EUNSUPPORTED; }
+  if (!dtype_ok(y_dtype)) { set_error("%s: unsupported output dtype %d", fn, y_dtype); return KQ_EUNSUPPORTED; }
+  if (!y || stride_y < n) { set_error("%s: bad output (null or stride_y < n)", fn); return KQ_EINVAL; }
+  if ((uintptr_t)y % dtype_size(y_dtype)) { set_error("%s: misaligned output pointer", fn); return KQ_EINVAL; }
+  cudaStream_t st = (cudaStream_t)stream;
+  uint8_t* s = (uint8_t*)scratch;
+  if (x) {
+    rc = launch_quantize(x, x_dtype, m, k, stride_x, s + p.L.off_ds, s + p.L.off_qs, nullptr, p.L.kpad, st);
+    if (rc) return rc;
+  }
+  if (!W) return KQ_OK;  // prepare only
+  return launch_gemv_dp4a(W, type, n, k, s + p.L.off_ds, s + p.L.off_qs, p.L.kpad, m, y, y_dtype, stride_y, mmq,
+                          nullptr, nullptr, st);
+}
+
+}  // namespace kq
+
+using namespace kq;
+
+extern "C" {
+
+const char* kq_last_error(void) { return t_err; }
+int kq_abi_version(void) { return 1; }
+
+int kq_block_geometry(int type, int* weights_per_block, int* bytes_per_block) {
+  int b, s;
+  if (!type_geometry(type, &b, &s)) { set_error("kq_block_geometry: GGML type %d is not supported", type); return KQ_EUNSUPPORTED; }
+  if (weights_per_block) *weights_per_block = b;
+  if (bytes_per_block) *bytes_per_block = s;
+  return KQ_OK;
+}
+
+size_t kq_workspace_bytes(int type, int64_t m, int64_t n, int64_t k) {
+  int b, s;
+  if (!type_geometry(type, &b, &s) || m <= 0 || n <= 0 || k <= 0) return 0;
+  return q8_layout(m, n, k).total;
+}
+
+int kq_quantize_q8_1(const void* x, int x_dtype, int64_t m, int64_t k, int64_t stride_x, void* out_blocks, void* stream) {
+  t_err[0] = 0;
+  if (!x || !out_blocks) { set_error("kq_quantize_q8_1: null pointer"); return KQ_EINVAL; }
+  if (m <= 0 || k <= 0 || stride_x < k) { set_error("kq_quantize_q8_1: bad sizes"); return KQ_EINVAL; }
+  if (!dtype_ok(x_dtype)) { set_error("kq_quantize_q8_1: unsupported dtype %d", x_dtype); return KQ_EUNSUPPORTED; }
+  if ((uintptr_t)out_blocks % 4) { set_error("kq_quantize_q8_1: output must be 4-byte aligned"); return KQ_EINVAL; }
+  const int64_t kpad = (k + 511) / 512 * 512;
+  return launch_quantize(x, x_dtype, m, k, stride_x, nullptr, nullptr, out_blocks, kpad, (cudaStream_t)stream);
+}
+
+int kq_mul_mat_vec_a8(const void* W, int type, int64_t n, int64_t k, const void* x, int x_dtype, int64_t m,
+                      int64_t stride_x, void* y, int y_dtype, int64_t stride_y, void* scratch, size_t scratch_bytes,
+                      void* stream) {
+  return mul_mat("kq_mul_mat_vec_a8", false, W, type, n, k, x, x_dtype, m, stride_x, y, y_dtype, stride_y, scratch,
+                 scratch_bytes, stream);
+}
+
+int kq_mul_mat_a8(const void* W, int type, int64_t n, int64_t k, const void* x, int x_dtype, int64_t m,
+                  int64_t stride_x, void* y, int y_dtype, int64_t stride_y, void* scratch, size_t scratch_bytes,
+                  void* stream) {
+  return mul_mat("kq_mul_mat_a8", true, W, type, n, k, x, x_dtype, m, stride_x, y, y_dtype, stride_y, scratch,
+                 scratch_bytes, stream);
+}
+
+int kq_prepare_q8(int type, int64_t n, int64_t k, const void* x, int x_dtype, int64_t m, int64_t stride_x,
+                  void* scratch, size_t scratch_bytes, void* stream) {
+  return mul_mat("kq_prepare_q8", false, nullptr, type, n, k, x, x_dtype, m, stride_x, nullptr, KQ_F32, n, scratch,
+                 scratch_bytes, stream, false, true);
+}
+
+int kq_mul_mat_prepared(const void* W, int type, int64_t n, int64_t k, int64_t m, void* y, int y_dtype,
+                        int64_t stride_y, int mmq, void* scratch, size_t scratch_bytes, void* stream) {
+  return mul_mat("kq_mul_mat_prepared", mmq != 0, W, type, n, k, nullptr, KQ_F32, m, k, y, y_dtype, stride_y, scratch,
+                 scratch_bytes, stream, true, false);
+}
+
+int kq_dequantize(const void* W, int type, int64_t count, void* out, int out_dtype, void* stream) {
+  t_err[0] = 0;
+  int b, s;
+  if (!type_geometry(type, &b, &s)) { set_error("kq_dequantize: GGML type %d is not supported", type); return KQ_EUNSUPPORTED; }
+  if (!dtype_ok(out_dtype)) { set_error("kq_dequantize: unsupported output dtype %d", out_dtype); return KQ_EUNSUPPORTED; }
+  if (count < 0 || count % b) { set_error("kq_dequantize: count=%lld is not a multiple of the block size %d", (long long)count, b); return KQ_EINVAL; }
+  if (count == 0) return KQ_OK;
+  if (!W || !out) { set_error("kq_dequantize: null pointer"); return KQ_EINVAL; }
+  if ((uintptr_t)W % 2 || (uintptr_t)out % 16) { set_error("kq_dequantize: W must be 2-byte and out 16-byte aligned"); return KQ_EINVAL; }
+  return launch_dequantize(W, type, count, out, out_dtype, (cudaStream_t)stream);
+}
+
+int kq_debug_group_dots(const void* W, int type, int64_t n, int64_t k, const void* x, int x_dtype, int64_t m,
+                        int64_t stride_x, int32_t* dots, int32_t* sums, void* scratch, size_t scratch_bytes,
+                        void* stream) {
+  t_err[0] = 0;
+  Problem p;
+  int rc = validate("kq_debug_group_dots", W, type, n, k, x, x_dtype, m, stride_x, scratch, scratch_bytes, p);
+  if (rc) return rc;
+  if (!dots) { set_error("kq_debug_group_dots: null dots"); return KQ_EINVAL; }
+  cudaStream_t st = (cudaStream_t)stream;
+  uint8_t* s = (uint8_t*)scratch;
+  rc = launch_quantize(x, x_dtype, m, k, stride_x, s + p.L.off_ds, s + p.L.off_qs, nullptr, p.L.kpad, st);
+  if (rc) return rc;
+  return launch_gemv_dp4a(W, type, n, k, s + p.L.off_ds, s + p.L.off_qs, p.L.kpad, m, nullptr, KQ_F32, n, false, dots,
+                          sums, st);
+}
+
+int kq_set_option(const char* name, int value) {
+  if (name && !strcmp(name, "gemv_impl")) { options().gemv_impl = value; return KQ_OK; }
+  if (name && !strcmp(name, "half_fma")) { options().half_fma = value; return KQ_OK; }
+  set_error("kq_set_option: unknown option");
+  return KQ_EINVAL;
+}
+
+int kq_get_option(const char* name, int* value) {
+  if (name && value && !strcmp(name, "gemv_impl")) { *value = options().gemv_impl; return KQ_OK; }
+  if (name && value && !strcmp(name, "half_fma")) { *value = options().half_fma; return KQ_OK; }
+  if (name && value && !strcmp(name, "launch_count")) { *value = (int)(options().launches & 0x7fffffff); return KQ_OK; }
+  set_error("kq_get_option: unknown option");
+  return KQ_EINVAL;
+}
+
+}  // extern "C"

@@ -1,0 +1,225 @@
+// Shared definitions of libkq: GGUF block geometry, error plumbing, q8 scratch layout and the
+// per-format decode of one 32-weight sub-block into dp4a/MMA-ready int8 words.
+//
+// Block layouts follow vllm_gguf_plugin/csrc/gguf/ggml-common.h:20-150 of the reference tree.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/kq_gguf.h"
+
+namespace kq {
+
+// ------------------------------------------------------------------ host side plumbing
+void set_error(const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);
+#define KQ_CUDA_TRY(expr)                                  \
+  do {                                                     \
+    cudaError_t _e = (expr);                               \
+    if (_e != cudaSuccess) return ::kq::cuda_fail(_e, #expr); \
+  } while (0)
+
+struct Options {
+  int gemv_impl;       // 0 auto, 1 dp4a, 2 tensor-core
+  int half_fma;        // 1: fp16 mul+sub contracted in K-quant dequantize
+  long long launches;  // kernels launched by this library so far (host-side count)
+};
+Options& options();
+
+// ------------------------------------------------------------------ formats
+template <int QT> struct Fmt;
+template <> struct Fmt<KQ_TYPE_Q4_0> { static constexpr int BLK = 32, BYTES = 18, GROUP = 32; static constexpr bool HAS_MIN = true; };
+template <> struct Fmt<KQ_TYPE_Q8_0> { static constexpr int BLK = 32, BYTES = 34, GROUP = 32; static constexpr bool HAS_MIN = false; };
+template <> struct Fmt<KQ_TYPE_Q2_K> { static constexpr int BLK = 256, BYTES = 84, GROUP = 16; static constexpr bool HAS_MIN = true; };
+template <> struct Fmt<KQ_TYPE_Q4_K> { static constexpr int BLK = 256, BYTES = 144, GROUP = 32; static constexpr bool HAS_MIN = true; };
+template <> struct Fmt<KQ_TYPE_Q6_K> { static constexpr int BLK = 256, BYTES = 210, GROUP = 16; static constexpr bool HAS_MIN = false; };
+template <> struct Fmt<KQ_TYPE_IQ3_S> { static constexpr int BLK = 256, BYTES = 110, GROUP = 32; static constexpr bool HAS_MIN = false; };
+
+inline bool type_geometry(int type, int* blk, int* bytes) {
+  switch (type) {
+    case KQ_TYPE_Q4_0: *blk = 32; *bytes = 18; return true;
+    case KQ_TYPE_Q8_0: *blk = 32; *bytes = 34; return true;
+    case KQ_TYPE_Q2_K: *blk = 256; *bytes = 84; return true;
+    case KQ_TYPE_Q4_K: *blk = 256; *bytes = 144; return true;
+    case KQ_TYPE_Q6_K: *blk = 256; *bytes = 210; return true;
+    case KQ_TYPE_IQ3_S: *blk = 256; *bytes = 110; return true;
+    default: return false;
+  }
+}
+inline int type_group(int type) { return (type == KQ_TYPE_Q2_K || type == KQ_TYPE_Q6_K) ? 16 : 32; }
+
+// ------------------------------------------------------------------ quantized activation scratch
+// Activations are quantized to q8_1 (gguf_kernel.cu:32-69 of the reference) into a split layout:
+//   ds   half2 [m][kpad/32]   {d, raw fp32 block sum rounded to fp16}
+//   qs   int8  [m][kpad]      codes, token-major
+//   part float [..]           split-K partial sums (tensor-core GEMV only)
+//   cnt  int   [..]           split-K arrival counters (self-resetting)
+struct Q8Layout {
+  int64_t kpad;
+  size_t off_ds, off_qs, off_part, off_cnt, total;
+};
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+inline Q8Layout q8_layout(int64_t m, int64_t n, int64_t k) {
+  Q8Layout L;
+  L.kpad = (k + 511) / 512 * 512;
+  size_t p = 0;
+  L.off_ds = p;   p = align_up(p + (size_t)m * (L.kpad / 32) * 4, 256);
+  L.off_qs = p;   p = align_up(p + (size_t)m * L.kpad, 256);
+  L.off_part = p; p = align_up(p + (size_t)8 * m * n * 4, 256);       // up to 8 K-splits
+  L.off_cnt = p;  p = align_up(p + (size_t)((n + 7) / 8 + 64) * 4, 256);
+  L.total = p;
+  return L;
+}
+
+// kernels (defined in the .cu files)
+int launch_quantize(const void* x, int x_dtype, int64_t m, int64_t k, int64_t stride_x,
+                    void* ds, void* qs, void* wire36, int64_t kpad, cudaStream_t st);
+int launch_gemv_dp4a(const void* W, int type, int64_t n, int64_t k, const void* ds, const void* qs,
+                     int64_t kpad, int64_t m, void* y, int y_dtype, int64_t stride_y, bool mmq,
+                     int32_t* dbg_dots, int32_t* dbg_sums, cudaStream_t st);
+int launch_dequantize(const void* W, int type, int64_t count, void* out, int out_dtype, cudaStream_t st);
+
+#ifdef __CUDACC__
+// ------------------------------------------------------------------ device helpers
+__device__ __forceinline__ uint32_t ld_u16x2(const uint8_t* p) {
+  // 32 bits from a 2-byte aligned address (wire blocks of 18/34/110/210 bytes are only 2-aligned)
+  const uint16_t* q = reinterpret_cast<const uint16_t*>(p);
+  return (uint32_t)q[0] | ((uint32_t)q[1] << 16);
+}
+__device__ __forceinline__ uint32_t ld_u32(const uint8_t* p) { return *reinterpret_cast<const uint32_t*>(p); }
+__device__ __forceinline__ float ld_h(const uint8_t* p) {
+  return __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(p)));
+}
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// per-byte (v - 32) for bytes in 0..63, no carries between bytes
+__device__ __forceinline__ uint32_t sub32_bytes(uint32_t v) {
+  return ((v | 0x80808080u) - 0x20202020u) ^ 0x80808080u;
+}
+// bits 0..3 of `nib` -> 0xFF in byte j if bit j is set
+__device__ __forceinline__ uint32_t nibble_to_bytemask(uint32_t nib) {
+  uint32_t m = (nib * 0x01010101u) & 0x08040201u;
+  uint32_t hb = ((m | 0x80808080u) - 0x01010101u) & 0x80808080u;
+  return (hb >> 7) * 0xFFu;
+}
+// negate the bytes of g (each 4..62) selected by mask (0xFF / 0x00 per byte)
+__device__ __forceinline__ uint32_t negate_bytes(uint32_t g, uint32_t mask) {
+  return (g ^ mask) + (mask & 0x01010101u);
+}
+__device__ __forceinline__ uint32_t iq3s_expand(uint32_t code, uint32_t top) {
+  // 12-bit code (4 levels x 3 bits) -> 4 grid bytes: level l<7 -> 8l+4, level 7 -> top
+  uint32_t r = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t l = (code >> (3 * j)) & 7u;
+    uint32_t b = (l == 7u) ? top : (8u * l + 4u);
+    r |= b << (8 * j);
+  }
+  return r;
+}
+#ifndef KQ_IQ3S_TOP
+#define KQ_IQ3S_TOP 62  // top magnitude byte of the codebook as the reference's CUDA table has it
+#endif
+
+// One 32-weight sub-block in the integer-dot domain.
+//   v[8]   int8x4 words, word i = weights 4i..4i+3 of the sub-block (same order as the activations)
+//   wa[h]  scale of group h (h = 0 for 32-weight groups; h = 0,1 for 16-weight groups = words 0-3 / 4-7)
+//   wb[h]  min coefficient of group h (types with HAS_MIN)
+// contribution to y:  sum_h  wa[h] * d8 * I_h  -  wb[h] * z_h
+//   z_h = d8 * S_h (sum of activation codes) or, for Q4_0 and MMQ-flavoured Q4_K, the fp16 raw sum.
+struct SubBlock {
+  uint32_t v[8];
+  float wa[2];
+  float wb[2];
+};
+
+// row: first byte of the weight row; sb: 32-weight sub-block index along k; grid: 512-entry IQ3_S table
+template <int QT>
+__device__ __forceinline__ void decode_subblock(const uint8_t* __restrict__ row, int sb,
+                                                const uint32_t* __restrict__ grid, SubBlock& o) {
+  if constexpr (QT == KQ_TYPE_Q4_0) {
+    const uint8_t* b = row + (size_t)sb * 18;
+    const float d = ld_h(b);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint32_t w = ld_u16x2(b + 2 + 4 * i);
+      o.v[i] = w & 0x0F0F0F0Fu;
+      o.v[i + 4] = (w >> 4) & 0x0F0F0F0Fu;
+    }
+    o.wa[0] = d; o.wb[0] = 8.0f * d; o.wa[1] = 0.f; o.wb[1] = 0.f;
+  } else if constexpr (QT == KQ_TYPE_Q8_0) {
+    const uint8_t* b = row + (size_t)sb * 34;
+    const float d = ld_h(b);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o.v[i] = ld_u16x2(b + 2 + 4 * i);
+    o.wa[0] = d; o.wb[0] = 0.f; o.wa[1] = 0.f; o.wb[1] = 0.f;
+  } else if constexpr (QT == KQ_TYPE_Q2_K) {
+    const uint8_t* b = row + (size_t)(sb >> 3) * 84;
+    const int j = sb & 7, n = j >> 2, jj = j & 3;
+    const float d = ld_h(b + 80), dmin = ld_h(b + 82);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o.v[i] = (ld_u32(b + 16 + 32 * n + 4 * i) >> (2 * jj)) & 0x03030303u;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t s = b[2 * j + h];
+      o.wa[h] = d * (float)(s & 15u);
+      o.wb[h] = dmin * (float)(s >> 4);
+    }
+  } else if constexpr (QT == KQ_TYPE_Q4_K) {
+    const uint8_t* b = row + (size_t)(sb >> 3) * 144;
+    const int j = sb & 7, il = j >> 1, e = j & 1;
+    const float d = ld_h(b), dmin = ld_h(b + 2);
+    const uint8_t* q = b + 4;
+    uint32_t sc, mn;
+    if (j < 4) { sc = q[j] & 63u; mn = q[j + 4] & 63u; }
+    else { sc = (q[j + 4] & 15u) | ((q[j - 4] >> 6) << 4); mn = (q[j + 4] >> 4) | ((q[j] >> 6) << 4); }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o.v[i] = (ld_u32(b + 16 + 32 * il + 4 * i) >> (4 * e)) & 0x0F0F0F0Fu;
+    o.wa[0] = d * (float)sc; o.wb[0] = dmin * (float)mn; o.wa[1] = 0.f; o.wb[1] = 0.f;
+  } else if constexpr (QT == KQ_TYPE_Q6_K) {
+    const uint8_t* b = row + (size_t)(sb >> 3) * 210;
+    const int j = sb & 7, ip = j >> 2, q4 = j & 3;
+    const float d = ld_h(b + 208);
+    const uint8_t* ql = b + 64 * ip + 32 * (q4 & 1);
+    const uint8_t* qh = b + 128 + 32 * ip;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      uint32_t lo = (ld_u16x2(ql + 4 * i) >> (4 * (q4 >> 1))) & 0x0F0F0F0Fu;
+      uint32_t hi = (ld_u16x2(qh + 4 * i) >> (2 * q4)) & 0x03030303u;
+      o.v[i] = sub32_bytes(lo | (hi << 4));
+    }
+    const int8_t* sc = reinterpret_cast<const int8_t*>(b + 192 + 8 * ip + 2 * q4);
+    o.wa[0] = d * (float)sc[0]; o.wa[1] = d * (float)sc[1]; o.wb[0] = 0.f; o.wb[1] = 0.f;
+  } else if constexpr (QT == KQ_TYPE_IQ3_S) {
+    const uint8_t* b = row + (size_t)(sb >> 3) * 110;
+    const int ib = sb & 7;
+    const float d = ld_h(b);
+    const uint8_t* qs = b + 2 + 8 * ib;
+    const uint32_t qh = b[66 + ib];
+    const uint8_t* sg = b + 74 + 4 * ib;
+#pragma unroll
+    for (int il = 0; il < 4; ++il) {
+      const uint32_t i1 = qs[2 * il] | ((qh << (8 - 2 * il)) & 256u);
+      const uint32_t i2 = qs[2 * il + 1] | ((qh << (7 - 2 * il)) & 256u);
+      const uint32_t s = sg[il];
+      o.v[2 * il] = negate_bytes(grid[i1], nibble_to_bytemask(s & 15u));
+      o.v[2 * il + 1] = negate_bytes(grid[i2], nibble_to_bytemask(s >> 4));
+    }
+    const uint32_t s4 = (b[106 + (ib >> 1)] >> (4 * (ib & 1))) & 15u;
+    o.wa[0] = d * (0.5f + (float)s4) * 0.5f; o.wb[0] = 0.f; o.wa[1] = 0.f; o.wb[1] = 0.f;
+  }
+}
+#endif  // __CUDACC__
+
+}  // namespace kq

@@ -1,0 +1,155 @@
+// ggml_dequantize: wire bytes -> dense half / bfloat16 / float.
+//
+// The reference's K-quant and legacy kernels form each weight in fp16 and only then convert to the
+// output type (vllm_gguf_plugin/csrc/gguf/dequantize.cuh:3-16, 69-78, 101-121, 156-196, 232-256); IQ3_S is
+// formed in fp32 (dequantize.cuh:334-353).  The same operation order is kept here so results are
+// bit-identical; `fma` selects whether a dependent fp16 multiply-subtract pair is contracted into one
+// fused operation, which the CUDA compiler is free to do to the reference's `__hsub(__hmul(a,b),c)`
+// (fma = 0: two roundings; 1: the first product is fused; 2: Q2_K's second product is fused instead).
+//
+// One thread produces 8 consecutive weights (16 bytes of fp16 output), so a warp writes 512 contiguous bytes.
+#include "kq_common.cuh"
+
+namespace kq {
+
+__constant__ uint16_t c_iq3s_codes_dq[512] = {
+#include "kq_iq3s_codes.inc"
+};
+
+template <typename OutT> __device__ __forceinline__ OutT half_to_out(__half v);
+template <> __device__ __forceinline__ __half half_to_out<__half>(__half v) { return v; }
+template <> __device__ __forceinline__ float half_to_out<float>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 half_to_out<__nv_bfloat16>(__half v) {
+  return __float2bfloat16_rn(__half2float(v));
+}
+
+__device__ __forceinline__ __half mul_sub(__half a, __half b, __half c, int fma) {
+  // a*b - c : one rounding if contracted, two otherwise
+  return fma ? __hfma(a, b, __hneg(c)) : __hsub_rn(__hmul_rn(a, b), c);
+}
+
+template <int QT, typename OutT>
+__global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restrict__ W, int64_t count,
+                                                         OutT* __restrict__ out, int fma) {
+  using F = Fmt<QT>;
+  const int64_t e0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (e0 >= count) return;
+  const uint8_t* b = W + (e0 / F::BLK) * F::BYTES;
+  const int r0 = (int)(e0 % F::BLK);
+  OutT res[8];
+  if constexpr (QT == KQ_TYPE_Q4_0) {
+    const __half d = __ushort_as_half(*reinterpret_cast<const uint16_t*>(b));
+    const __half eight = __float2half_rn(8.0f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int e = r0 + j;
+      const int q = e < 16 ? (b[2 + e] & 15) : (b[2 + e - 16] >> 4);
+      res[j] = half_to_out<OutT>(__hmul_rn(__hsub_rn(__int2half_rn(q), eight), d));
+    }
+  } else if constexpr (QT == KQ_TYPE_Q8_0) {
+    const __half d = __ushort_as_half(*reinterpret_cast<const uint16_t*>(b));
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int q = (int8_t)b[2 + r0 + j];
+      res[j] = half_to_out<OutT>(__hmul_rn(__int2half_rn(q), d));
+    }
+  } else if constexpr (QT == KQ_TYPE_Q2_K) {
+    const __half dall = __ushort_as_half(*reinterpret_cast<const uint16_t*>(b + 80));
+    const __half dmin = __ushort_as_half(*reinterpret_cast<const uint16_t*>(b + 82));
+    const int n = r0 >> 7, j4 = (r0 >> 5) & 3, l0 = r0 & 31;
+    const int s = b[8 * n + 2 * j4 + (l0 >> 4)];
+    const __half mpart = __hmul_rn(dmin, __int2half_rn(s >> 4));
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int q = (b[16 + 32 * n + l0 + j] >> (2 * j4)) & 3;
+      const __half xq = __int2half_rn((s & 15) * q);
+      res[j] = half_to_out<OutT>(fma == 2 ? __hfma(__hneg(dmin), __int2half_rn(s >> 4), __hmul_rn(dall, xq))
+                                          : mul_sub(dall, xq, mpart, fma));
+    }
+  } else if constexpr (QT == KQ_TYPE_Q4_K) {
+    const __half dall = __ushort_as_half(*reinterpret_cast<const uint16_t*>(b));
+    const __half dmin = __ushort_as_half(*reinterpret_cast<const uint16_t*>(b + 2));
+    const int il = r0 >> 6, hi = (r0 >> 5) & 1, l0 = r0 & 31;
+    const int jj = 2 * il + hi;
+    const uint8_t* q = b + 4;
+    int sc, mn;
+    if (jj < 4) { sc = q[jj] & 63; mn = q[jj + 4] & 63; }
+    else { sc = (q[jj + 4] & 15) | ((q[jj - 4] >> 6) << 4); mn = (q[jj + 4] >> 4) | ((q[jj] >> 6) << 4); }
+    const __half d1 = __hmul_rn(dall, __int2half_rn(sc));
+    const __half m1 = __hmul_rn(dmin, __int2half_rn(mn));
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int byte = b[16 + 32 * il + l0 + j];
+      const int qq = hi ? (byte >> 4) : (byte & 15);
+      res[j] = half_to_out<OutT>(mul_sub(d1, __int2half_rn(qq), m1, fma));
+    }
+  } else if constexpr (QT == KQ_TYPE_Q6_K) {
+    const __half d = __ushort_as_half(*reinterpret_cast<const uint16_t*>(b + 208));
+    const int ip = r0 >> 7, q4 = (r0 >> 5) & 3, l0 = r0 & 31;
+    const int sc = (int8_t)b[192 + 8 * ip + 2 * q4 + (l0 >> 4)];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int lo = b[64 * ip + 32 * (q4 & 1) + l0 + j];
+      const int nib = (q4 < 2) ? (lo & 15) : (lo >> 4);
+      const int hb = (b[128 + 32 * ip + l0 + j] >> (2 * q4)) & 3;
+      const int code = (nib | (hb << 4)) - 32;
+      res[j] = half_to_out<OutT>(__hmul_rn(d, __int2half_rn(sc * code)));
+    }
+  } else if constexpr (QT == KQ_TYPE_IQ3_S) {
+    const float dh = ld_h(b);
+    const int ib = r0 >> 5, il = (r0 >> 3) & 3;
+    const uint32_t qh = b[66 + ib];
+    const uint32_t i1 = b[2 + 8 * ib + 2 * il] | ((qh << (8 - 2 * il)) & 256u);
+    const uint32_t i2 = b[2 + 8 * ib + 2 * il + 1] | ((qh << (7 - 2 * il)) & 256u);
+    const uint32_t g1 = iq3s_expand(c_iq3s_codes_dq[i1], KQ_IQ3S_TOP);
+    const uint32_t g2 = iq3s_expand(c_iq3s_codes_dq[i2], KQ_IQ3S_TOP);
+    const uint32_t signs = b[74 + 4 * ib + il];
+    const uint32_t s4 = (b[106 + (ib >> 1)] >> (4 * (ib & 1))) & 15u;
+    const float d = __fmul_rn(__fmul_rn(dh, 0.5f + (float)s4), 0.5f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t gb = ((j < 4 ? g1 : g2) >> (8 * (j & 3))) & 0xFFu;
+      const float mag = __fmul_rn(d, (float)gb);
+      res[j] = from_f32<OutT>((signs >> j) & 1u ? -mag : mag);
+    }
+  }
+  // 8 outputs = 16 (half/bf16) or 32 (float) contiguous, aligned bytes
+  if constexpr (sizeof(OutT) == 2) {
+    *reinterpret_cast<uint4*>(out + e0) = *reinterpret_cast<const uint4*>(res);
+  } else {
+    reinterpret_cast<uint4*>(out + e0)[0] = reinterpret_cast<const uint4*>(res)[0];
+    reinterpret_cast<uint4*>(out + e0)[1] = reinterpret_cast<const uint4*>(res)[1];
+  }
+}
+
+template <int QT>
+static int run(const void* W, int64_t count, void* out, int out_dtype, int fma, cudaStream_t st) {
+  const int64_t threads = count / 8;
+  const unsigned grid = (unsigned)((threads + 255) / 256);
+  if (grid == 0) return KQ_OK;
+  switch (out_dtype) {
+    case KQ_F16: dequantize_kernel<QT, __half><<<grid, 256, 0, st>>>((const uint8_t*)W, count, (__half*)out, fma); break;
+    case KQ_BF16: dequantize_kernel<QT, __nv_bfloat16><<<grid, 256, 0, st>>>((const uint8_t*)W, count, (__nv_bfloat16*)out, fma); break;
+    case KQ_F32: dequantize_kernel<QT, float><<<grid, 256, 0, st>>>((const uint8_t*)W, count, (float*)out, fma); break;
+    default: set_error("unsupported output dtype %d", out_dtype); return KQ_EUNSUPPORTED;
+  }
+  options().launches += 1;
+  KQ_CUDA_TRY(cudaGetLastError());
+  return KQ_OK;
+}
+
+int launch_dequantize(const void* W, int type, int64_t count, void* out, int out_dtype, cudaStream_t st) {
+  const int fma = options().half_fma;
+  switch (type) {
+    case KQ_TYPE_Q4_0: return run<KQ_TYPE_Q4_0>(W, count, out, out_dtype, fma, st);
+    case KQ_TYPE_Q8_0: return run<KQ_TYPE_Q8_0>(W, count, out, out_dtype, fma, st);
+    case KQ_TYPE_Q2_K: return run<KQ_TYPE_Q2_K>(W, count, out, out_dtype, fma, st);
+    case KQ_TYPE_Q4_K: return run<KQ_TYPE_Q4_K>(W, count, out, out_dtype, fma, st);
+    case KQ_TYPE_Q6_K: return run<KQ_TYPE_Q6_K>(W, count, out, out_dtype, fma, st);
+    case KQ_TYPE_IQ3_S: return run<KQ_TYPE_IQ3_S>(W, count, out, out_dtype, fma, st);
+  }
+  set_error("unsupported GGML type %d", type);
+  return KQ_EUNSUPPORTED;
+}
+
+}  // namespace kq

@@ -1,0 +1,224 @@
+"""GPU parity tests proper: the CUDA path, called through the C ABI, against the CPU oracle.
+
+Bars: q8_1 activation bytes and integer group dots bit-exact; `ggml_dequantize` bit-exact; fp32 outputs
+within rel-L2 1e-3 of the q8_1-semantics oracle (asserted two orders tighter, at 2e-5, so that a wrong
+arithmetic flavour - MMVQ vs MMQ differ by ~1e-3 on Q4_K - cannot hide inside the gate).
+"""
+import numpy as np
+import pytest
+import torch
+
+from kaillm_b200 import capi
+from oracle import gguf_oracle as O
+from tests.gpu_util import TDT, act, dev, rel_l2, to_np, wire
+
+pytestmark = pytest.mark.gpu
+
+QT = O.QTYPES
+GATE = 1e-3      # the contract
+TIGHT = 2e-5     # what fp32 accumulation of exact integer dots should give
+
+
+# ------------------------------------------------------------------ q8_1
+@pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("m,k", [(1, 2048), (16, 5120), (3, 700), (2, 17408), (80, 512), (1, 32)])
+def test_q8_1_bit_exact(dt, m, k):
+    x, xt = act(m, k, seed=m * 7 + k, dt=dt)
+    got = capi.quantize_q8_1(xt).cpu().numpy()
+    want = O.q8_1_wire(O.quantize_q8_1(x))
+    np.testing.assert_array_equal(got, want)
+
+
+def test_q8_1_special_values():
+    x = np.zeros((4, 512), np.float32)
+    x[0, 32:64] = np.linspace(-127, 127, 32)
+    x[0, 33], x[0, 34] = 2.5, -2.5                  # ties round away from zero
+    x[1, :] = 1e-7                                  # tiny: d underflows towards fp16 subnormals
+    x[2, :64] = 3000.0                              # fp16 block sum overflows to inf (reference behaviour)
+    x[3, ::2] = 65504.0
+    x[3, 1::2] = -1e-3
+    xt = torch.from_numpy(x).to(dev())
+    got = capi.quantize_q8_1(xt).cpu().numpy()
+    np.testing.assert_array_equal(got, O.q8_1_wire(O.quantize_q8_1(x)))
+
+
+def test_q8_1_strided_rows():
+    x, _ = act(5, 1024, seed=3, dt="bf16")
+    big = torch.zeros((5, 1500), dtype=torch.bfloat16, device=dev())
+    big[:, :1024] = torch.from_numpy(x).to(torch.bfloat16)
+    got = capi.quantize_q8_1(big[:, :1024]).cpu().numpy()
+    np.testing.assert_array_equal(got, O.q8_1_wire(O.quantize_q8_1(x)))
+
+
+# ------------------------------------------------------------------ integer dots
+@pytest.mark.parametrize("qt", QT)
+@pytest.mark.parametrize("n,k,m", [(33, 1024, 3), (8, 256, 1), (64, 2048, 16)])
+def test_group_dots_bit_exact(qt, n, k, m):
+    w, wt = wire(qt, n, k, seed=qt)
+    x, xt = act(m, k, seed=11, dt="bf16")
+    dots, sums = capi.debug_group_dots(wt, xt, qt)
+    _, _, I, S = O.mul_mat(w, qt, x, "mmvq", return_parts=True)
+    np.testing.assert_array_equal(dots.cpu().numpy().astype(np.int64), I)
+    np.testing.assert_array_equal(sums.cpu().numpy().astype(np.int64), S)
+
+
+# ------------------------------------------------------------------ mul_mat, fp32 outputs
+SHAPES = [(64, 512, 1), (33, 1024, 5), (130, 2048, 16), (17, 256, 2), (256, 5120, 8)]
+
+
+@pytest.mark.parametrize("qt", QT)
+@pytest.mark.parametrize("n,k,m", SHAPES)
+@pytest.mark.parametrize("impl", [1, 0])
+def test_mul_mat_vec_fp32(qt, n, k, m, impl):
+    w, wt = wire(qt, n, k, seed=qt + n)
+    x, xt = act(m, k, seed=k + m, dt="bf16")
+    capi.set_option("gemv_impl", impl)
+    try:
+        y = capi.mul_mat(wt, xt, qt, mmq=False, out_dtype=torch.float32)
+    finally:
+        capi.set_option("gemv_impl", 0)
+    want = O.mul_mat(w, qt, x, "mmvq")
+    r = rel_l2(to_np(y), want)
+    assert r < TIGHT < GATE, r
+
+
+@pytest.mark.parametrize("qt", [2, 8, 10, 12, 14])
+@pytest.mark.parametrize("n,k,m", SHAPES)
+@pytest.mark.parametrize("impl", [1, 0])
+def test_mul_mat_a8_fp32(qt, n, k, m, impl):
+    w, wt = wire(qt, n, k, seed=qt + n)
+    x, xt = act(m, k, seed=k + m, dt="f16")
+    capi.set_option("gemv_impl", impl)
+    try:
+        y = capi.mul_mat(wt, xt, qt, mmq=True, out_dtype=torch.float32)
+    finally:
+        capi.set_option("gemv_impl", 0)
+    want = O.mul_mat(w, qt, x, "mmq")
+    r = rel_l2(to_np(y), want)
+    assert r < TIGHT < GATE, r
+
+
+@pytest.mark.parametrize("qt", QT)
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+def test_mul_mat_low_precision_output(qt, dt):
+    n, k, m = 96, 1024, 4
+    w, wt = wire(qt, n, k, seed=5)
+    x, xt = act(m, k, seed=6, dt=dt)
+    y = capi.mul_mat(wt, xt, qt)                           # output dtype = activation dtype, as the reference
+    assert y.dtype == TDT[dt]
+    want = O.round_to_dtype(O.mul_mat(w, qt, x, "mmvq"), dt)
+    got = to_np(y)
+    assert rel_l2(got, want) < GATE
+    assert (got == want).mean() > 0.98                     # only rounding-boundary cases may differ
+
+
+# ------------------------------------------------------------------ BASELINE.json configurations
+def test_config1_q4_0_single_linear():
+    """Q4_0 N=8192 K=2048, fp32 activation [1,2048], seed 0."""
+    w, wt = wire(2, 8192, 2048, seed=0)
+    x, xt = act(1, 2048, seed=0, dt="f32")
+    y = capi.mul_mat(wt, xt, 2, out_dtype=torch.float32)
+    assert rel_l2(to_np(y), O.mul_mat(w, 2, x, "mmvq")) < TIGHT
+
+
+@pytest.mark.parametrize("qt,n,k", [(12, 17408, 5120), (14, 5120, 17408)])
+@pytest.mark.parametrize("m", [1, 2, 8, 16])
+def test_config2_27b_shapes(qt, n, k, m):
+    """Full-size launch; the oracle checks the first and last 96 rows (rows are independent)."""
+    _, wt = wire(qt, n, k, seed=qt)
+    x, xt = act(m, k, seed=m, dt="bf16")
+    w = wt.cpu().numpy()
+    rows = np.r_[0:96, n - 96:n]
+    for mmq in (False, True):
+        y = to_np(capi.mul_mat(wt, xt, qt, mmq=mmq, out_dtype=torch.float32))
+        want = O.mul_mat(w[rows], qt, x, "mmq" if mmq else "mmvq")
+        assert rel_l2(y[:, rows], want) < TIGHT
+        assert np.isfinite(y).all()
+
+
+@pytest.mark.parametrize("qt", [21, 10])
+@pytest.mark.parametrize("n,k", [(8192, 2048), (17408, 5120)])
+@pytest.mark.parametrize("m", [1, 16, 80])
+def test_config5_lowbit_and_verify_shapes(qt, n, k, m):
+    _, wt = wire(qt, n, k, seed=qt + 1)
+    x, xt = act(m, k, seed=m + 2, dt="bf16")
+    w = wt.cpu().numpy()
+    rows = np.r_[0:64, n - 64:n]
+    y = to_np(capi.mul_mat(wt, xt, qt, out_dtype=torch.float32))
+    assert rel_l2(y[:, rows], O.mul_mat(w[rows], qt, x, "mmvq")) < TIGHT
+
+
+# ------------------------------------------------------------------ edge cases
+@pytest.mark.parametrize("qt", QT)
+def test_edge_shapes(qt):
+    blk = O.BLOCK[qt][0]
+    for n, k, m in [(1, blk, 1), (3, blk, 7), (5, 3 * blk, 80), (1, 2 * blk, 17)]:
+        w, wt = wire(qt, n, k, seed=n + k)
+        x, xt = act(m, k, seed=9, dt="f32")
+        y = capi.mul_mat(wt, xt, qt, out_dtype=torch.float32)
+        assert rel_l2(to_np(y), O.mul_mat(w, qt, x, "mmvq")) < TIGHT
+
+
+@pytest.mark.parametrize("qt", [12, 14])
+def test_strided_output_and_canaries(qt):
+    n, k, m = 40, 1024, 6
+    w, wt = wire(qt, n, k, seed=1)
+    x, xt = act(m, k, seed=2, dt="bf16")
+    ybuf = torch.full((m, n + 24), 777.0, dtype=torch.float32, device=dev())
+    ws = capi.workspace_bytes(qt, m, n, k)
+    sbuf = torch.full((ws + 512,), 0xAB, dtype=torch.uint8, device=dev())
+    wpad = torch.full((wt.numel() + 512,), 0xCD, dtype=torch.uint8, device=dev())
+    wpad[256:256 + wt.numel()] = wt.flatten()
+    wv = wpad[256:256 + wt.numel()].view(n, -1)
+    capi.mul_mat(wv, xt, qt, out=ybuf[:, :n], scratch=sbuf[:ws])
+    got = to_np(ybuf)
+    assert rel_l2(got[:, :n], O.mul_mat(w, qt, x, "mmvq")) < TIGHT
+    assert (got[:, n:] == 777.0).all()                       # output padding untouched
+    assert (sbuf[ws:] == 0xAB).all()                         # nothing written past the scratch
+    assert (wpad[:256] == 0xCD).all() and (wpad[256 + wt.numel():] == 0xCD).all()   # weights never mutated around
+    assert torch.equal(wv, wt)
+
+
+@pytest.mark.parametrize("qt", QT)
+def test_repeated_launches_are_deterministic(qt):
+    w, wt = wire(qt, 512, 2048, seed=4)
+    _, xt = act(16, 2048, seed=4, dt="bf16")
+    a = capi.mul_mat(wt, xt, qt, out_dtype=torch.float32)
+    b = capi.mul_mat(wt, xt, qt, out_dtype=torch.float32)
+    c = capi.mul_mat(wt, xt, qt, out_dtype=torch.float32)
+    assert torch.equal(a, b) and torch.equal(a, c)
+
+
+def test_unsupported_type_raises_on_gpu_too():
+    _, wt = wire(12, 8, 256, seed=0)
+    _, xt = act(1, 256, seed=0, dt="f32")
+    with pytest.raises(capi.KqError) as e:
+        capi.mul_mat(wt, xt, 13)
+    assert e.value.code == capi.KQ_EUNSUPPORTED
+
+
+# ------------------------------------------------------------------ dequantize
+@pytest.mark.parametrize("qt", QT)
+@pytest.mark.parametrize("dt", ["f16", "bf16", "f32"])
+def test_dequantize_bit_exact(qt, dt):
+    n, k = 48, 1024
+    w, wt = wire(qt, n, k, seed=qt * 3)
+    got = to_np(capi.dequantize(wt, qt, n * k, TDT[dt])).reshape(n, k)
+    want = O.dequantize(w, qt, dt, half_fma=capi.get_option("half_fma"))
+    np.testing.assert_array_equal(got, want)
+
+
+@pytest.mark.parametrize("qt", [10, 12])
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_dequantize_rounding_modes_match_oracle(qt, mode):
+    if qt == 12 and mode == 2:
+        mode = 1
+    n, k = 16, 512
+    w, wt = wire(qt, n, k, seed=77)
+    old = capi.get_option("half_fma")
+    capi.set_option("half_fma", mode)
+    try:
+        got = to_np(capi.dequantize(wt, qt, n * k, torch.float16)).reshape(n, k)
+    finally:
+        capi.set_option("half_fma", old)
+    np.testing.assert_array_equal(got, O.dequantize(w, qt, "f16", half_fma=mode))
