@@ -119,6 +119,12 @@ int kq_debug_group_dots(const void* W, int type, int64_t n, int64_t k,
                         int32_t* dots, int32_t* sums,
                         void* scratch, size_t scratch_bytes, void* stream);
 
+/* Diagnostics: copies the device-side status word of a scratch buffer to the host (SYNCHRONISES with the
+ * device; not for the serving path).  0 = every kernel that used the scratch finished normally; non-zero = a
+ * bounded wait inside a kernel gave up and the kernel returned early (its outputs are then undefined).
+ * The sizes must be the ones the scratch was used with.  No counterpart in the reference. */
+int kq_read_status(int type, int64_t m, int64_t n, int64_t k, const void* scratch, size_t scratch_bytes, int* status);
+
 /* Runtime knobs for tests and profiling (process-wide, not thread-safe against concurrent launches):
  *   "gemv_impl"   0 = choose by shape (default), 1 = force the dp4a kernel, 2 = force the tensor-core kernel
  *   "half_fma"    1 = K-quant dequantize contracts fp16 mul+sub into one fma (default), 0 = two roundings

@@ -21,7 +21,7 @@ _DT = {torch.float32: KQ_F32, torch.float16: KQ_F16, torch.bfloat16: KQ_BF16}
 EXPORTS = (
     "kq_last_error", "kq_abi_version", "kq_block_geometry", "kq_workspace_bytes", "kq_quantize_q8_1",
     "kq_mul_mat_vec_a8", "kq_mul_mat_a8", "kq_dequantize", "kq_debug_group_dots", "kq_set_option",
-    "kq_get_option", "kq_prepare_q8", "kq_mul_mat_prepared",
+    "kq_get_option", "kq_prepare_q8", "kq_mul_mat_prepared", "kq_read_status",
 )
 
 
@@ -51,6 +51,7 @@ def _load() -> ctypes.CDLL:
     lib.kq_prepare_q8.argtypes = [i32, i64, i64, vp, i32, i64, i64, vp, sz, vp]
     lib.kq_mul_mat_prepared.argtypes = [vp, i32, i64, i64, i64, vp, i32, i64, i32, vp, sz, vp]
     lib.kq_dequantize.argtypes = [vp, i32, i64, vp, i32, vp]
+    lib.kq_read_status.argtypes = [i32, i64, i64, i64, vp, sz, ctypes.POINTER(i32)]
     lib.kq_debug_group_dots.argtypes = [vp, i32, i64, i64, vp, i32, i64, i64, vp, vp, vp, sz, vp]
     lib.kq_set_option.argtypes = [ctypes.c_char_p, i32]
     lib.kq_get_option.argtypes = [ctypes.c_char_p, ctypes.POINTER(i32)]
@@ -138,6 +139,14 @@ def mul_mat_prepared(W: torch.Tensor, qtype: int, m: int, k: int, out: torch.Ten
         _check(lib.kq_mul_mat_prepared(W.data_ptr(), qtype, n, k, m, out.data_ptr(), _DT[out.dtype], out.stride(0),
                                        int(mmq), scratch.data_ptr(), scratch.numel(), _stream(W.device)))
     return out
+
+
+def read_status(qtype: int, m: int, n: int, k: int, scratch: torch.Tensor) -> int:
+    """Device-side status word of a scratch buffer (synchronises)."""
+    v = ctypes.c_int()
+    with torch.cuda.device(scratch.device):
+        _check(lib.kq_read_status(qtype, m, n, k, scratch.data_ptr(), scratch.numel(), ctypes.byref(v)))
+    return v.value
 
 
 def dequantize(W: torch.Tensor, qtype: int, count: int, dtype=torch.float16) -> torch.Tensor:

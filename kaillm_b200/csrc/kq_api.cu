@@ -68,22 +68,24 @@ static int mul_mat(const char* fn, bool mmq, const void* W, int type, int64_t n,
   int rc = validate(fn, W, type, n, k, x, x_dtype, m, stride_x, scratch, scratch_bytes, p, need_w, need_x);
   if (rc) return rc;
   if (!need_w) {
-    return launch_quantize(x, x_dtype, m, k, stride_x, (uint8_t*)scratch + p.L.off_ds, (uint8_t*)scratch + p.L.off_qs,
-                           nullptr, p.L.kpad, (cudaStream_t)stream);
+    const Q8Ptrs P = q8_ptrs(scratch, p.L, n);
+    return launch_quantize(x, x_dtype, m, k, stride_x, &P, nullptr, p.L.kpad, (cudaStream_t)stream);
   }
   if (mmq && type == KQ_TYPE_IQ3_S) { set_error("%s: IQ3_S has no MMQ kernel (use dequantize + matmul or mul_mat_vec)", fn); return KQ_EUNSUPPORTED; }
   if (!dtype_ok(y_dtype)) { set_error("%s: unsupported output dtype %d", fn, y_dtype); return KQ_EUNSUPPORTED; }
   if (!y || stride_y < n) { set_error("%s: bad output (null or stride_y < n)", fn); return KQ_EINVAL; }
   if ((uintptr_t)y % dtype_size(y_dtype)) { set_error("%s: misaligned output pointer", fn); return KQ_EINVAL; }
   cudaStream_t st = (cudaStream_t)stream;
-  uint8_t* s = (uint8_t*)scratch;
+  const Q8Ptrs P = q8_ptrs(scratch, p.L, n);
   if (x) {
-    rc = launch_quantize(x, x_dtype, m, k, stride_x, s + p.L.off_ds, s + p.L.off_qs, nullptr, p.L.kpad, st);
+    rc = launch_quantize(x, x_dtype, m, k, stride_x, &P, nullptr, p.L.kpad, st);
     if (rc) return rc;
   }
-  if (!W) return KQ_OK;  // prepare only
-  return launch_gemv_dp4a(W, type, n, k, s + p.L.off_ds, s + p.L.off_qs, p.L.kpad, m, y, y_dtype, stride_y, mmq,
-                          nullptr, nullptr, st);
+  const int impl = options().gemv_impl;
+  if (impl != 1 && gemv_mma_supported(W, type, n, k))
+    return launch_gemv_mma(W, type, n, k, P, m, y, y_dtype, stride_y, mmq, st);
+  if (impl == 2) { set_error("%s: the tensor-core GEMV does not cover this type/shape/alignment", fn); return KQ_EUNSUPPORTED; }
+  return launch_gemv_dp4a(W, type, n, k, P.ds, P.qs, p.L.kpad, m, y, y_dtype, stride_y, mmq, nullptr, nullptr, st);
 }
 
 }  // namespace kq
@@ -116,7 +118,7 @@ int kq_quantize_q8_1(const void* x, int x_dtype, int64_t m, int64_t k, int64_t s
   if (!dtype_ok(x_dtype)) { set_error("kq_quantize_q8_1: unsupported dtype %d", x_dtype); return KQ_EUNSUPPORTED; }
   if ((uintptr_t)out_blocks % 4) { set_error("kq_quantize_q8_1: output must be 4-byte aligned"); return KQ_EINVAL; }
   const int64_t kpad = (k + 511) / 512 * 512;
-  return launch_quantize(x, x_dtype, m, k, stride_x, nullptr, nullptr, out_blocks, kpad, (cudaStream_t)stream);
+  return launch_quantize(x, x_dtype, m, k, stride_x, nullptr, out_blocks, kpad, (cudaStream_t)stream);
 }
 
 int kq_mul_mat_vec_a8(const void* W, int type, int64_t n, int64_t k, const void* x, int x_dtype, int64_t m,
@@ -166,11 +168,20 @@ int kq_debug_group_dots(const void* W, int type, int64_t n, int64_t k, const voi
   if (rc) return rc;
   if (!dots) { set_error("kq_debug_group_dots: null dots"); return KQ_EINVAL; }
   cudaStream_t st = (cudaStream_t)stream;
-  uint8_t* s = (uint8_t*)scratch;
-  rc = launch_quantize(x, x_dtype, m, k, stride_x, s + p.L.off_ds, s + p.L.off_qs, nullptr, p.L.kpad, st);
+  const Q8Ptrs P = q8_ptrs(scratch, p.L, n);
+  rc = launch_quantize(x, x_dtype, m, k, stride_x, &P, nullptr, p.L.kpad, st);
   if (rc) return rc;
-  return launch_gemv_dp4a(W, type, n, k, s + p.L.off_ds, s + p.L.off_qs, p.L.kpad, m, nullptr, KQ_F32, n, false, dots,
-                          sums, st);
+  return launch_gemv_dp4a(W, type, n, k, P.ds, P.qs, p.L.kpad, m, nullptr, KQ_F32, n, false, dots, sums, st);
+}
+
+int kq_read_status(int type, int64_t m, int64_t n, int64_t k, const void* scratch, size_t scratch_bytes, int* status) {
+  t_err[0] = 0;
+  int b, sz;
+  if (!type_geometry(type, &b, &sz) || m <= 0 || n <= 0 || k <= 0 || !scratch || !status) { set_error("kq_read_status: bad argument"); return KQ_EINVAL; }
+  const Q8Layout L = q8_layout(m, n, k);
+  if (scratch_bytes < L.total) { set_error("kq_read_status: scratch too small"); return KQ_ESCRATCH; }
+  KQ_CUDA_TRY(cudaMemcpy(status, (const uint8_t*)scratch + L.off_status, sizeof(int), cudaMemcpyDeviceToHost));
+  return KQ_OK;
 }
 
 int kq_set_option(const char* name, int value) {

@@ -53,33 +53,68 @@ inline int type_group(int type) { return (type == KQ_TYPE_Q2_K || type == KQ_TYP
 
 // ------------------------------------------------------------------ quantized activation scratch
 // Activations are quantized to q8_1 (gguf_kernel.cu:32-69 of the reference) into a split layout:
-//   ds   half2 [m][kpad/32]   {d, raw fp32 block sum rounded to fp16}
-//   qs   int8  [m][kpad]      codes, token-major
-//   part float [..]           split-K partial sums (tensor-core GEMV only)
-//   cnt  int   [..]           split-K arrival counters (self-resetting)
+//   ds    half2 [m][kpad/32]        {d, raw fp32 block sum rounded to fp16}
+//   qs    int8  [m][kpad]           codes, token-major
+// and, for the tensor-core GEMV, per-token scale tables transposed to [token tile][block][16 tokens]
+// (tokens beyond m hold zeros) so a K-range of them is one contiguous bulk copy into shared memory:
+//   dT    float [mt][kpad/32][16]   d as fp32
+//   z32   float [mt][kpad/32][16]   d * (sum of the 32 codes)      (min term, MMVQ flavour)
+//   zs8   float [mt][kpad/32][16]   the fp16 raw sum as fp32        (min term of Q4_0 and MMQ-flavoured Q4_K)
+//   z16   float [mt][kpad/16][16]   d * (sum of 16 codes)           (min term of Q2_K)
+//   part  float [4][16][n]          split-K partial sums of one 16-token pass
+//   cnt   int   [ceil(n/16)]        split-K arrival counters (zeroed by the quantizer, self-resetting)
+//   status int  [64]                device-side error word (bounded waits that gave up)
 struct Q8Layout {
-  int64_t kpad;
-  size_t off_ds, off_qs, off_part, off_cnt, total;
+  int64_t kpad, mt;
+  size_t off_ds, off_qs, off_dT, off_z32, off_zs8, off_z16, off_part, off_cnt, off_status, total;
 };
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 inline Q8Layout q8_layout(int64_t m, int64_t n, int64_t k) {
   Q8Layout L;
   L.kpad = (k + 511) / 512 * 512;
+  L.mt = (m + 15) / 16;
+  const size_t nb = (size_t)L.kpad / 32;
   size_t p = 0;
-  L.off_ds = p;   p = align_up(p + (size_t)m * (L.kpad / 32) * 4, 256);
-  L.off_qs = p;   p = align_up(p + (size_t)m * L.kpad, 256);
-  L.off_part = p; p = align_up(p + (size_t)8 * m * n * 4, 256);       // up to 8 K-splits
-  L.off_cnt = p;  p = align_up(p + (size_t)((n + 7) / 8 + 64) * 4, 256);
+  L.off_ds = p;     p = align_up(p + (size_t)m * nb * 4, 256);
+  L.off_qs = p;     p = align_up(p + (size_t)m * L.kpad, 256);
+  L.off_dT = p;     p = align_up(p + (size_t)L.mt * nb * 64, 256);
+  L.off_z32 = p;    p = align_up(p + (size_t)L.mt * nb * 64, 256);
+  L.off_zs8 = p;    p = align_up(p + (size_t)L.mt * nb * 64, 256);
+  L.off_z16 = p;    p = align_up(p + (size_t)L.mt * nb * 128, 256);
+  L.off_part = p;   p = align_up(p + (size_t)4 * 16 * n * 4, 256);
+  L.off_cnt = p;    p = align_up(p + (size_t)((n + 15) / 16) * 4, 256);
+  L.off_status = p; p = align_up(p + 256, 256);
   L.total = p;
   return L;
 }
 
+struct Q8Ptrs {  // device pointers into one scratch buffer
+  __half2* ds; int8_t* qs; float *dT, *z32, *zs8, *z16, *part; int *cnt, *status;
+  int64_t kpad; int ntiles;
+};
+inline Q8Ptrs q8_ptrs(void* scratch, const Q8Layout& L, int64_t n) {
+  uint8_t* s = (uint8_t*)scratch;
+  Q8Ptrs P;
+  P.ds = (__half2*)(s + L.off_ds); P.qs = (int8_t*)(s + L.off_qs);
+  P.dT = (float*)(s + L.off_dT); P.z32 = (float*)(s + L.off_z32); P.zs8 = (float*)(s + L.off_zs8);
+  P.z16 = (float*)(s + L.off_z16); P.part = (float*)(s + L.off_part);
+  P.cnt = (int*)(s + L.off_cnt); P.status = (int*)(s + L.off_status);
+  P.kpad = L.kpad; P.ntiles = (int)((n + 15) / 16);
+  return P;
+}
+
 // kernels (defined in the .cu files)
+// P may be null (then only the reference 36-byte block layout `wire36` is written)
 int launch_quantize(const void* x, int x_dtype, int64_t m, int64_t k, int64_t stride_x,
-                    void* ds, void* qs, void* wire36, int64_t kpad, cudaStream_t st);
+                    const Q8Ptrs* P, void* wire36, int64_t kpad, cudaStream_t st);
 int launch_gemv_dp4a(const void* W, int type, int64_t n, int64_t k, const void* ds, const void* qs,
                      int64_t kpad, int64_t m, void* y, int y_dtype, int64_t stride_y, bool mmq,
                      int32_t* dbg_dots, int32_t* dbg_sums, cudaStream_t st);
+// tensor-core GEMV; returns KQ_EUNSUPPORTED (without setting an error) when the shape/alignment is not
+// covered, so the caller can fall back to the dp4a kernel
+bool gemv_mma_supported(const void* W, int type, int64_t n, int64_t k);
+int launch_gemv_mma(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m, void* y,
+                    int y_dtype, int64_t stride_y, bool mmq, cudaStream_t st);
 int launch_dequantize(const void* W, int type, int64_t count, void* out, int out_dtype, cudaStream_t st);
 
 #ifdef __CUDACC__

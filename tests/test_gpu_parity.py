@@ -112,6 +112,50 @@ def test_mul_mat_low_precision_output(qt, dt):
     assert (got == want).mean() > 0.98                     # only rounding-boundary cases may differ
 
 
+# ------------------------------------------------------------------ tensor-core GEMV specifically
+@pytest.mark.parametrize("qt", [12, 14])
+@pytest.mark.parametrize("n,k,m", [(16, 256, 1), (17, 512, 3), (100, 1024, 8), (2368, 2048, 9), (4736, 5120, 16),
+                                   (333, 4352, 16), (64, 17408, 5), (48, 768, 33)])
+@pytest.mark.parametrize("mmq", [False, True])
+def test_tensor_core_gemv_matches_oracle_and_dp4a(qt, n, k, m, mmq):
+    w, wt = wire(qt, n, k, seed=n + k)
+    x, xt = act(m, k, seed=m, dt="bf16")
+    ws = capi.workspace_bytes(qt, m, n, k)
+    scratch = torch.empty(ws, dtype=torch.uint8, device=dev())
+    capi.set_option("gemv_impl", 2)
+    try:
+        y2 = capi.mul_mat(wt, xt, qt, mmq=mmq, out_dtype=torch.float32, scratch=scratch)
+        assert capi.read_status(qt, m, n, k, scratch) == 0
+        y2b = capi.mul_mat(wt, xt, qt, mmq=mmq, out_dtype=torch.float32, scratch=scratch)   # counters self-reset
+        capi.set_option("gemv_impl", 1)
+        y1 = capi.mul_mat(wt, xt, qt, mmq=mmq, out_dtype=torch.float32)
+    finally:
+        capi.set_option("gemv_impl", 0)
+    want = O.mul_mat(w, qt, x, "mmq" if mmq else "mmvq")
+    assert rel_l2(to_np(y2), want) < TIGHT
+    assert torch.equal(y2, y2b)
+    assert rel_l2(to_np(y2), to_np(y1)) < TIGHT
+
+
+def test_tensor_core_gemv_declines_unaligned_weights():
+    qt, n, k = 14, 32, 512
+    _, wt = wire(qt, n, k, seed=1)
+    _, xt = act(2, k, seed=1, dt="bf16")
+    buf = torch.zeros(wt.numel() + 64, dtype=torch.uint8, device=dev())
+    buf[2:2 + wt.numel()] = wt.flatten()
+    wv = buf[2:2 + wt.numel()].view(n, -1)            # 2-byte aligned only
+    ref = capi.mul_mat(wt, xt, qt, out_dtype=torch.float32)
+    got = capi.mul_mat(wv, xt, qt, out_dtype=torch.float32)     # auto: falls back to the general kernel
+    assert rel_l2(to_np(got), to_np(ref)) < TIGHT
+    capi.set_option("gemv_impl", 2)
+    try:
+        with pytest.raises(capi.KqError) as e:
+            capi.mul_mat(wv, xt, qt, out_dtype=torch.float32)
+        assert e.value.code == capi.KQ_EUNSUPPORTED
+    finally:
+        capi.set_option("gemv_impl", 0)
+
+
 # ------------------------------------------------------------------ BASELINE.json configurations
 def test_config1_q4_0_single_linear():
     """Q4_0 N=8192 K=2048, fp32 activation [1,2048], seed 0."""
@@ -129,11 +173,21 @@ def test_config2_27b_shapes(qt, n, k, m):
     x, xt = act(m, k, seed=m, dt="bf16")
     w = wt.cpu().numpy()
     rows = np.r_[0:96, n - 96:n]
+    scratch = torch.empty(capi.workspace_bytes(qt, m, n, k), dtype=torch.uint8, device=dev())
     for mmq in (False, True):
-        y = to_np(capi.mul_mat(wt, xt, qt, mmq=mmq, out_dtype=torch.float32))
+        yt = capi.mul_mat(wt, xt, qt, mmq=mmq, out_dtype=torch.float32, scratch=scratch)
+        assert capi.read_status(qt, m, n, k, scratch) == 0
+        y = to_np(yt)
         want = O.mul_mat(w[rows], qt, x, "mmq" if mmq else "mmvq")
         assert rel_l2(y[:, rows], want) < TIGHT
         assert np.isfinite(y).all()
+        # every row, against the general kernel (rows are independent, so this covers the middle of the matrix)
+        capi.set_option("gemv_impl", 1)
+        try:
+            y1 = to_np(capi.mul_mat(wt, xt, qt, mmq=mmq, out_dtype=torch.float32))
+        finally:
+            capi.set_option("gemv_impl", 0)
+        assert rel_l2(y, y1) < TIGHT
 
 
 @pytest.mark.parametrize("qt", [21, 10])
