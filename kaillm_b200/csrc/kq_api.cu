@@ -22,7 +22,7 @@ int cuda_fail(cudaError_t e, const char* what) {
 }
 
 Options& options() {
-  static Options o = {0, 1, 0};
+  static Options o = {0, 8, 1, 0};
   return o;
 }
 
@@ -84,7 +84,7 @@ static int mul_mat(const char* fn, bool mmq, const void* W, int type, int64_t n,
   const int impl = options().gemv_impl;
   if (impl != 1 && gemv_mma_supported(W, type, n, k))
     return launch_gemv_mma(W, type, n, k, P, m, y, y_dtype, stride_y, mmq, st);
-  if (impl == 2) { set_error("%s: the tensor-core GEMV does not cover this type/shape/alignment", fn); return KQ_EUNSUPPORTED; }
+  if (impl >= 2) { set_error("%s: the streaming GEMV does not cover this shape/alignment", fn); return KQ_EUNSUPPORTED; }
   return launch_gemv_dp4a(W, type, n, k, P.ds, P.qs, p.L.kpad, m, y, y_dtype, stride_y, mmq, nullptr, nullptr, st);
 }
 
@@ -187,6 +187,7 @@ int kq_read_status(int type, int64_t m, int64_t n, int64_t k, const void* scratc
 int kq_set_option(const char* name, int value) {
   if (name && !strcmp(name, "gemv_impl")) { options().gemv_impl = value; return KQ_OK; }
   if (name && !strcmp(name, "half_fma")) { options().half_fma = value; return KQ_OK; }
+  if (name && !strcmp(name, "tc_min_m")) { options().tc_min_m = value; return KQ_OK; }
   set_error("kq_set_option: unknown option");
   return KQ_EINVAL;
 }
@@ -194,6 +195,7 @@ int kq_set_option(const char* name, int value) {
 int kq_get_option(const char* name, int* value) {
   if (name && value && !strcmp(name, "gemv_impl")) { *value = options().gemv_impl; return KQ_OK; }
   if (name && value && !strcmp(name, "half_fma")) { *value = options().half_fma; return KQ_OK; }
+  if (name && value && !strcmp(name, "tc_min_m")) { *value = options().tc_min_m; return KQ_OK; }
   if (name && value && !strcmp(name, "launch_count")) { *value = (int)(options().launches & 0x7fffffff); return KQ_OK; }
   set_error("kq_get_option: unknown option");
   return KQ_EINVAL;

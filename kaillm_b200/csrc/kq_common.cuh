@@ -23,7 +23,8 @@ int cuda_fail(cudaError_t e, const char* what);
   } while (0)
 
 struct Options {
-  int gemv_impl;       // 0 auto, 1 dp4a, 2 tensor-core
+  int gemv_impl;       // 0 auto, 1 general dp4a kernel, 2 streaming tensor-core, 3 streaming dp4a
+  int tc_min_m;        // auto mode: smallest token count that goes to the tensor-core consumers
   int half_fma;        // 1: fp16 mul+sub contracted in K-quant dequantize
   long long launches;  // kernels launched by this library so far (host-side count)
 };
@@ -61,12 +62,15 @@ inline int type_group(int type) { return (type == KQ_TYPE_Q2_K || type == KQ_TYP
 //   z32   float [mt][kpad/32][16]   d * (sum of the 32 codes)      (min term, MMVQ flavour)
 //   zs8   float [mt][kpad/32][16]   the fp16 raw sum as fp32        (min term of Q4_0 and MMQ-flavoured Q4_K)
 //   z16   float [mt][kpad/16][16]   d * (sum of 16 codes)           (min term of Q2_K)
+//   z32r  float [m][kpad/32]        same values as z32, token-major (row-streaming kernel)
+//   z16r  float [m][kpad/16]        same values as z16, token-major
 //   part  float [4][16][n]          split-K partial sums of one 16-token pass
-//   cnt   int   [ceil(n/16)]        split-K arrival counters (zeroed by the quantizer, self-resetting)
+//   cnt   int   [n]                 split-K arrival counters, per row or per 16-row tile (zeroed by the
+//                                   quantizer, reset by the kernel that used them)
 //   status int  [64]                device-side error word (bounded waits that gave up)
 struct Q8Layout {
   int64_t kpad, mt;
-  size_t off_ds, off_qs, off_dT, off_z32, off_zs8, off_z16, off_part, off_cnt, off_status, total;
+  size_t off_ds, off_qs, off_dT, off_z32, off_zs8, off_z16, off_z32r, off_z16r, off_part, off_cnt, off_status, total;
 };
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 inline Q8Layout q8_layout(int64_t m, int64_t n, int64_t k) {
@@ -81,25 +85,28 @@ inline Q8Layout q8_layout(int64_t m, int64_t n, int64_t k) {
   L.off_z32 = p;    p = align_up(p + (size_t)L.mt * nb * 64, 256);
   L.off_zs8 = p;    p = align_up(p + (size_t)L.mt * nb * 64, 256);
   L.off_z16 = p;    p = align_up(p + (size_t)L.mt * nb * 128, 256);
+  L.off_z32r = p;   p = align_up(p + (size_t)m * nb * 4, 256);
+  L.off_z16r = p;   p = align_up(p + (size_t)m * nb * 8, 256);
   L.off_part = p;   p = align_up(p + (size_t)4 * 16 * n * 4, 256);
-  L.off_cnt = p;    p = align_up(p + (size_t)((n + 15) / 16) * 4, 256);
+  L.off_cnt = p;    p = align_up(p + (size_t)n * 4, 256);
   L.off_status = p; p = align_up(p + 256, 256);
   L.total = p;
   return L;
 }
 
 struct Q8Ptrs {  // device pointers into one scratch buffer
-  __half2* ds; int8_t* qs; float *dT, *z32, *zs8, *z16, *part; int *cnt, *status;
-  int64_t kpad; int ntiles;
+  __half2* ds; int8_t* qs; float *dT, *z32, *zs8, *z16, *z32r, *z16r, *part; int *cnt, *status;
+  int64_t kpad; int ncnt;
 };
 inline Q8Ptrs q8_ptrs(void* scratch, const Q8Layout& L, int64_t n) {
   uint8_t* s = (uint8_t*)scratch;
   Q8Ptrs P;
   P.ds = (__half2*)(s + L.off_ds); P.qs = (int8_t*)(s + L.off_qs);
   P.dT = (float*)(s + L.off_dT); P.z32 = (float*)(s + L.off_z32); P.zs8 = (float*)(s + L.off_zs8);
-  P.z16 = (float*)(s + L.off_z16); P.part = (float*)(s + L.off_part);
+  P.z16 = (float*)(s + L.off_z16); P.z32r = (float*)(s + L.off_z32r); P.z16r = (float*)(s + L.off_z16r);
+  P.part = (float*)(s + L.off_part);
   P.cnt = (int*)(s + L.off_cnt); P.status = (int*)(s + L.off_status);
-  P.kpad = L.kpad; P.ntiles = (int)((n + 15) / 16);
+  P.kpad = L.kpad; P.ncnt = (int)n;
   return P;
 }
 

@@ -33,14 +33,19 @@ namespace kq {
 
 namespace {
 
-constexpr int NW = 8;                     // consumer warps
-constexpr int THREADS = (NW + 1) * 32;
 constexpr int TILE_ROWS = 16;
+// consumer warps: tensor-core mode 8 (a warp owns a tile); dp4a mode 16 (a warp owns one row of every tile)
+__host__ __device__ constexpr int consumer_warps(int mode) { return mode == 0 ? 8 : 16; }
+__host__ __device__ constexpr int cta_threads(int mode) { return (consumer_warps(mode) + 1) * 32; }
 constexpr uint32_t MAGIC_I = 0x4B400000u;  // bits of 12582912.0f: adding an int |v| < 2^22 gives the float 12582912+v
 constexpr float MAGIC_F = 12582912.0f;
 constexpr long long WAIT_LIMIT = 1ll << 27;   // ~70 ms at 1.9 GHz; a healthy wait lasts microseconds
 constexpr int SMEM_HEADER = 1024;
 constexpr int MAX_STAGES = 32;
+
+__constant__ uint16_t c_iq3s_codes_s[512] = {
+#include "kq_iq3s_codes.inc"
+};
 
 struct MmaParams {
   const uint8_t* W;
@@ -280,14 +285,18 @@ __device__ __forceinline__ void chunk_q6k(const uint8_t* pg, const uint8_t* ph, 
 }
 
 // ---------------------------------------------------------------------------------------------- kernel
-template <int QT, int NT, typename OutT>
-__global__ void __launch_bounds__(THREADS, 1) gemv_mma_kernel(const MmaParams p) {
+// tensor-core consumers; NT = n-tiles of 8 tokens (MODE is always 0: the small-M path is gemv_rows_kernel)
+template <int QT, int MODE, int NT, typename OutT>
+__global__ void __launch_bounds__(cta_threads(MODE), 1) gemv_stream_kernel(const MmaParams p) {
   using F = Fmt<QT>;
+  constexpr int NW = consumer_warps(MODE);
+  constexpr int THREADS = cta_threads(MODE);
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem + SMEM_HEADER - 8);
   volatile int* s_issued = reinterpret_cast<volatile int*>(smem + SMEM_HEADER - 16);   // stages issued so far
-  uint8_t* sA = smem + SMEM_HEADER;
+  uint32_t* s_grid = reinterpret_cast<uint32_t*>(smem + SMEM_HEADER);   // IQ3_S codebook (2 KB) when needed
+  uint8_t* sA = smem + SMEM_HEADER + (QT == KQ_TYPE_IQ3_S ? 2048 : 0);
   float* sD = reinterpret_cast<float*>(sA + p.a_bytes);
   float* sZ = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sD) + p.d_bytes);
   uint8_t* ring = reinterpret_cast<uint8_t*>(sZ) + p.z_bytes;
@@ -310,6 +319,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_mma_kernel(const MmaParams p)
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
+  if constexpr (QT == KQ_TYPE_IQ3_S) {
+    for (int i = threadIdx.x; i < 512; i += THREADS) s_grid[i] = iq3s_expand(c_iq3s_codes_s[i], KQ_IQ3S_TOP);
+  }
   __syncthreads();
 
   if (warp == NW) {
@@ -317,7 +329,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_mma_kernel(const MmaParams p)
     const int k0 = blk0 * F::BLK, klen = (blk1 - blk0) * F::BLK;
     const int b32_0 = k0 >> 5, nb32 = klen >> 5;
     const int tt = p.m0 >> 4;
-    const int ntok = p.mcount < 8 * NT ? p.mcount : 8 * NT;
+    constexpr int TOKCAP = 8 * NT;
+    const int ntok = p.mcount < TOKCAP ? p.mcount : TOKCAP;
+    const int mrow0 = p.m0;
     if (lane == 0) {
       uint32_t total = (uint32_t)ntok * klen + (uint32_t)nb32 * 64u;
       if (p.zT != nullptr) total += (uint32_t)nb32 * p.zpb * 64u;
@@ -325,7 +339,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_mma_kernel(const MmaParams p)
     }
     __syncwarp();
     if (lane < ntok)
-      bulk_g2s(smem_u32(sA + lane * p.a_stride), p.qs + (size_t)(p.m0 + lane) * p.kpad + k0, (uint32_t)klen, bar_act);
+      bulk_g2s(smem_u32(sA + lane * p.a_stride), p.qs + (size_t)(mrow0 + lane) * p.kpad + k0, (uint32_t)klen, bar_act);
     if (lane == 16) bulk_g2s(smem_u32(sD), p.dT + ((size_t)tt * p.nb32tot + b32_0) * 16, (uint32_t)nb32 * 64u, bar_act);
     if (lane == 17 && p.zT != nullptr)
       bulk_g2s(smem_u32(sZ), p.zT + ((size_t)tt * p.nb32tot + b32_0) * p.zpb * 16, (uint32_t)nb32 * p.zpb * 64u, bar_act);
@@ -367,84 +381,257 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_mma_kernel(const MmaParams p)
   }
 
   // -------------------------------------------------------------------- consumers
-  const int g = lane >> 2, t = lane & 3;
   if (!mbar_wait(bar_act, 0, s_abort)) { if (lane == 0) atomicExch(p.status, 2); return; }
   ActView A{sA, p.a_stride, sD, sZ};
-  for (int idx = warp; rt0 + idx < rt1; idx += NW) {
-    const int rt = rt0 + idx, row0 = rt * TILE_ROWS;
-    float acc[NT][4];
+  OutT* y = reinterpret_cast<OutT*>(p.y);
+  const int tok0 = p.m0 & 15;                     // first token of this pass inside its 16-token tile
+
+  if constexpr (MODE == 0) {
+    // ---- a warp owns whole tiles
+    const int g = lane >> 2, t = lane & 3;
+    for (int idx = warp; rt0 + idx < rt1; idx += NW) {
+      const int rt = rt0 + idx, row0 = rt * TILE_ROWS;
+      float acc[NT][4];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
+      for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
-    const size_t rbg = (size_t)(row0 + g) * p.rowbytes, rbh = (size_t)(row0 + g + 8) * p.rowbytes;
-    for (int c = 0; c < nchunks; ++c) {
-      const int q = idx * nchunks + c, slot = q % S;
-      if (*s_issued <= q) {   // not issued yet: the slot's barrier may still show an older generation
-        const long long t0 = clock64();
-        while (*s_issued <= q) {
-          if (*s_abort || clock64() - t0 > WAIT_LIMIT) { *s_abort = 1; if (lane == 0) atomicExch(p.status, 4); return; }
+        for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
+      const size_t rbg = (size_t)(row0 + g) * p.rowbytes, rbh = (size_t)(row0 + g + 8) * p.rowbytes;
+      for (int c = 0; c < nchunks; ++c) {
+        const int q = idx * nchunks + c, slot = q % S;
+        if (*s_issued <= q) {   // not issued yet: the slot's barrier may still show an older generation
+          const long long t0 = clock64();
+          while (*s_issued <= q) {
+            if (*s_abort || clock64() - t0 > WAIT_LIMIT) { *s_abort = 1; if (lane == 0) atomicExch(p.status, 4); return; }
+          }
         }
+        if (!mbar_wait(bar_full + 8 * slot, (uint32_t)((q / S) & 1), s_abort)) { if (lane == 0) atomicExch(p.status, 3); return; }
+        const int blk_a = blk0 + c * p.cb;
+        const int nb_c = (blk1 - blk_a) < p.cb ? (blk1 - blk_a) : p.cb;
+        const uint8_t* st = ring + (size_t)slot * p.stage_bytes;
+        const uint32_t offg = (uint32_t)(((uintptr_t)p.W + rbg + (size_t)blk_a * F::BYTES) & 15);
+        const uint32_t offh = (uint32_t)(((uintptr_t)p.W + rbh + (size_t)blk_a * F::BYTES) & 15);
+        const uint8_t* pg = st + (size_t)g * p.slot_stride + offg;
+        const uint8_t* ph = st + (size_t)(g + 8) * p.slot_stride + offh;
+        const int b0 = (blk_a - blk0) * (F::BLK / 32);
+        if constexpr (QT == KQ_TYPE_Q4_K) chunk_q4k<NT>(pg, ph, nb_c, b0, A, g, t, acc);
+        if constexpr (QT == KQ_TYPE_Q6_K) chunk_q6k<NT>(pg, ph, nb_c, b0, A, g, t, acc);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_empty + 8 * slot);
       }
-      if (!mbar_wait(bar_full + 8 * slot, (uint32_t)((q / S) & 1), s_abort)) { if (lane == 0) atomicExch(p.status, 3); return; }
-      const int blk_a = blk0 + c * p.cb;
-      const int nb_c = (blk1 - blk_a) < p.cb ? (blk1 - blk_a) : p.cb;
-      const uint8_t* st = ring + (size_t)slot * p.stage_bytes;
-      const uint32_t offg = (uint32_t)(((uintptr_t)p.W + rbg + (size_t)blk_a * F::BYTES) & 15);
-      const uint32_t offh = (uint32_t)(((uintptr_t)p.W + rbh + (size_t)blk_a * F::BYTES) & 15);
-      const uint8_t* pg = st + (size_t)g * p.slot_stride + offg;
-      const uint8_t* ph = st + (size_t)(g + 8) * p.slot_stride + offh;
-      const int b0 = (blk_a - blk0) * (F::BLK / 32);
-      if constexpr (QT == KQ_TYPE_Q4_K) chunk_q4k<NT>(pg, ph, nb_c, b0, A, g, t, acc);
-      if constexpr (QT == KQ_TYPE_Q6_K) chunk_q6k<NT>(pg, ph, nb_c, b0, A, g, t, acc);
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_empty + 8 * slot);
-    }
-    // ---- outputs of this tile: lane holds rows g (i=0,1) and g+8 (i=2,3), tokens 8nt+2t (+1)
-    OutT* y = reinterpret_cast<OutT*>(p.y);
-    if (p.ks == 1) {
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int row = row0 + g + ((i >> 1) << 3), tl = 8 * nt + 2 * t + (i & 1);
-          if (row < p.n && tl < p.mcount) y[(size_t)(p.m0 + tl) * p.stride_y + row] = from_f32<OutT>(acc[nt][i]);
-        }
-    } else {
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int row = row0 + g + ((i >> 1) << 3), tl = 8 * nt + 2 * t + (i & 1);
-          if (row < p.n && tl < p.mcount) __stcg(p.part + ((size_t)ks * 16 + tl) * p.n + row, acc[nt][i]);
-        }
-      __threadfence();
-      __syncwarp();
-      int old = 0;
-      if (lane == 0) old = atomicAdd(p.cnt + rt, 1);
-      old = __shfl_sync(0xffffffffu, old, 0);
-      if (old == p.ks - 1) {   // every split of this tile has published: add them in split order
-        __threadfence();
+      // lane holds rows g (i=0,1) and g+8 (i=2,3), tokens 8nt+2t (+1)
+      if (p.ks == 1) {
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const int row = row0 + g + ((i >> 1) << 3), tl = 8 * nt + 2 * t + (i & 1);
-            if (row < p.n && tl < p.mcount) {
-              float s = 0.f;
-              for (int sp = 0; sp < p.ks; ++sp) s += __ldcg(p.part + ((size_t)sp * 16 + tl) * p.n + row);
-              y[(size_t)(p.m0 + tl) * p.stride_y + row] = from_f32<OutT>(s);
-            }
+            if (row < p.n && tl < p.mcount) y[(size_t)(p.m0 + tl) * p.stride_y + row] = from_f32<OutT>(acc[nt][i]);
           }
-        if (lane == 0) p.cnt[rt] = 0;   // ready for the next launch on this scratch
+      } else {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int row = row0 + g + ((i >> 1) << 3), tl = 8 * nt + 2 * t + (i & 1);
+            if (row < p.n && tl < p.mcount) __stcg(p.part + ((size_t)ks * 16 + tl) * p.n + row, acc[nt][i]);
+          }
+        __threadfence();
+        __syncwarp();
+        int old = 0;
+        if (lane == 0) old = atomicAdd(p.cnt + rt, 1);
+        old = __shfl_sync(0xffffffffu, old, 0);
+        if (old == p.ks - 1) {   // every split of this tile has published: add them in split order
+          __threadfence();
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int row = row0 + g + ((i >> 1) << 3), tl = 8 * nt + 2 * t + (i & 1);
+              if (row < p.n && tl < p.mcount) {
+                float sum = 0.f;
+                for (int sp = 0; sp < p.ks; ++sp) sum += __ldcg(p.part + ((size_t)sp * 16 + tl) * p.n + row);
+                y[(size_t)(p.m0 + tl) * p.stride_y + row] = from_f32<OutT>(sum);
+              }
+            }
+          if (lane == 0) p.cnt[rt] = 0;   // ready for the next launch on this scratch
+        }
       }
     }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- row-streaming dp4a kernel
+// Small M (1..8 tokens per pass).  A CTA owns a contiguous range of weight rows, so the split over the 148 SMs is
+// balanced to one row and needs no split-K.  The producer fetches R whole consecutive rows per stage with ONE
+// bulk copy (the copy engine handles of the order of ten million requests per second and SM, so requests must
+// be >= ~5 KB to keep up with HBM; row segments of a K-split are far too small).  Row i of the CTA belongs to
+// consumer warp i % 16; its 32 lanes take the row's 32-weight sub-blocks round-robin, decode each once and dot
+// it against the MT tokens, and one butterfly at the end of the row forms the sum.  Warps only meet at the
+// stage barriers: a stage is released when the warps owning its R rows have each arrived.
+struct RowParams {
+  const uint8_t* W;
+  int64_t rowbytes;
+  int n, nsb;               // rows, 32-weight sub-blocks per row
+  int rows_per_stage, stages, stage_bytes;
+  int a_stride, a_bytes, d_bytes, z_bytes;
+  const int8_t* qs;
+  const __half2* ds;        // [m][kpad/32] {d, raw block sum}
+  const float* zr;          // [m][kpad/32 * zpb] token-major min-term table (zmode 2, 3) or nullptr
+  int zmode;                // min term: 0 none, 1 raw block sum from ds, 2 zr[b], 3 zr[2b], zr[2b+1]
+  int zpb, kpad, nb32tot, klen;
+  int m0, mcount;
+  void* y;
+  int64_t stride_y;
+  int* status;
+};
+
+constexpr int ROW_WARPS = 16;
+constexpr int ROW_THREADS = (ROW_WARPS + 1) * 32;
+
+template <int QT, int MT, typename OutT>
+__global__ void __launch_bounds__(ROW_THREADS, 1) gemv_rows_kernel(const RowParams p) {
+  using F = Fmt<QT>;
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(smem + SMEM_HEADER - 8);
+  volatile int* s_issued = reinterpret_cast<volatile int*>(smem + SMEM_HEADER - 16);
+  uint32_t* s_grid = reinterpret_cast<uint32_t*>(smem + SMEM_HEADER);
+  uint8_t* sA = smem + SMEM_HEADER + (QT == KQ_TYPE_IQ3_S ? 2048 : 0);
+  __half2* sDS = reinterpret_cast<__half2*>(sA + p.a_bytes);                              // [MT][nb32tot]
+  float* sZ = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sDS) + p.d_bytes);      // [MT][nb32tot*zpb]
+  uint8_t* ring = reinterpret_cast<uint8_t*>(sZ) + p.z_bytes;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int S = p.stages, R = p.rows_per_stage;
+  const int r0 = (int)((int64_t)blockIdx.x * p.n / gridDim.x), r1 = (int)((int64_t)(blockIdx.x + 1) * p.n / gridDim.x);
+  if (r0 >= r1) return;
+  const int nstages = (r1 - r0 + R - 1) / R;
+  const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + MAX_STAGES), bar_act = smem_u32(bars + 2 * MAX_STAGES);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, R); }
+    mbar_init(bar_act, 1);
+    *s_abort = 0;
+    *s_issued = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if constexpr (QT == KQ_TYPE_IQ3_S) {
+    for (int i = threadIdx.x; i < 512; i += ROW_THREADS) s_grid[i] = iq3s_expand(c_iq3s_codes_s[i], KQ_IQ3S_TOP);
+  }
+  __syncthreads();
+
+  if (warp == ROW_WARPS) {
+    // ------------------------------------------------------------------ producer (one lane is enough)
+    if (lane == 0) {
+      const int ntok = p.mcount < MT ? p.mcount : MT;
+      const uint32_t dsb = (uint32_t)p.nb32tot * 4u, zb = (uint32_t)p.nb32tot * p.zpb * 4u;   // multiples of 64 bytes
+      uint32_t total = (uint32_t)ntok * ((uint32_t)p.klen + dsb + (p.zr != nullptr ? zb : 0u));
+      mbar_expect_tx(bar_act, total);
+      for (int t = 0; t < ntok; ++t) {
+        bulk_g2s(smem_u32(sA + t * p.a_stride), p.qs + (size_t)(p.m0 + t) * p.kpad, (uint32_t)p.klen, bar_act);
+        bulk_g2s(smem_u32(sDS + (size_t)t * p.nb32tot), p.ds + (size_t)(p.m0 + t) * p.nb32tot, dsb, bar_act);
+        if (p.zr != nullptr)
+          bulk_g2s(smem_u32(sZ + (size_t)t * p.nb32tot * p.zpb), p.zr + (size_t)(p.m0 + t) * p.nb32tot * p.zpb, zb, bar_act);
+      }
+      bool ok = true;
+      int q = 0;
+      for (; q < nstages; ++q) {
+        const int slot = q % S;
+        if (q >= S) ok = mbar_wait(bar_empty + 8 * slot, (uint32_t)((q / S - 1) & 1), s_abort);
+        if (!ok) break;
+        const int ra = r0 + q * R;
+        const int rb = (ra + R) < r1 ? (ra + R) : r1;
+        const uintptr_t ga = (uintptr_t)(p.W + (size_t)ra * p.rowbytes);
+        const uintptr_t ge = (uintptr_t)(p.W + (size_t)rb * p.rowbytes);
+        const uintptr_t a0 = ga & ~(uintptr_t)15;
+        const uint32_t bytes = (uint32_t)(((ge + 15) & ~(uintptr_t)15) - a0);
+        mbar_expect_tx(bar_full + 8 * slot, bytes);
+        bulk_g2s(smem_u32(ring + (size_t)slot * p.stage_bytes), (const void*)a0, bytes, bar_full + 8 * slot);
+        __threadfence_block();
+        *s_issued = q + 1;
+      }
+      const int first = q > S ? q - S : 0;
+      for (int qq = first; qq < q; ++qq) mbar_wait(bar_full + 8 * (qq % S), (uint32_t)((qq / S) & 1), s_abort);
+      if (!ok) atomicExch(p.status, 1);
+    }
+    return;
+  }
+
+  // -------------------------------------------------------------------- consumers
+  if (!mbar_wait(bar_act, 0, s_abort)) { if (lane == 0) atomicExch(p.status, 2); return; }
+  OutT* y = reinterpret_cast<OutT*>(p.y);
+  constexpr int NG = 32 / F::GROUP;
+  const int zmode = p.zmode;
+  for (int i = warp; r0 + i < r1; i += ROW_WARPS) {
+    const int row = r0 + i;
+    const int q = i / R, slot = q % S;
+    if (*s_issued <= q) {   // the slot's barrier may still show an older generation until stage q is issued
+      const long long t0 = clock64();
+      while (*s_issued <= q) {
+        if (*s_abort || clock64() - t0 > WAIT_LIMIT) { *s_abort = 1; if (lane == 0) atomicExch(p.status, 4); return; }
+      }
+    }
+    if (!mbar_wait(bar_full + 8 * slot, (uint32_t)((q / S) & 1), s_abort)) { if (lane == 0) atomicExch(p.status, 3); return; }
+    const uint32_t off = (uint32_t)((uintptr_t)(p.W + (size_t)(r0 + q * R) * p.rowbytes) & 15);
+    const uint8_t* prow = ring + (size_t)slot * p.stage_bytes + off + (size_t)(i - q * R) * p.rowbytes;
+    float acc[MT];
+#pragma unroll
+    for (int t = 0; t < MT; ++t) acc[t] = 0.f;
+    const int swz = (lane >> 2) & 1;
+    for (int sb = lane; sb < p.nsb; sb += 32) {
+      SubBlock s;
+      decode_subblock<QT>(prow, sb, s_grid, s);
+#pragma unroll
+      for (int t = 0; t < MT; ++t) {
+        const uint8_t* ap = sA + (size_t)t * p.a_stride + sb * 32;
+        const uint4 ua = *reinterpret_cast<const uint4*>(ap + 16 * swz);
+        const uint4 ub = *reinterpret_cast<const uint4*>(ap + 16 * (swz ^ 1));
+        const uint4 u0 = swz ? ub : ua, u1 = swz ? ua : ub;
+        const uint32_t u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+        const float2 dsf = __half22float2(sDS[(size_t)t * p.nb32tot + sb]);
+        const float d8 = dsf.x;
+        int I[2] = {0, 0};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int hh = (NG == 2) ? (j >> 2) : 0;
+          I[hh] = __dp4a((int)s.v[j], (int)u[j], I[hh]);
+        }
+        float c;
+        if constexpr (NG == 1) {
+          c = s.wa[0] * (d8 * (float)I[0]);
+          if constexpr (F::HAS_MIN) c -= s.wb[0] * (zmode == 1 ? dsf.y : sZ[(size_t)t * p.nb32tot + sb]);
+        } else {
+          c = d8 * (s.wa[0] * (float)I[0] + s.wa[1] * (float)I[1]);
+          if constexpr (F::HAS_MIN) {
+            const float2 z = *reinterpret_cast<const float2*>(sZ + ((size_t)t * p.nb32tot + sb) * 2);
+            c -= s.wb[0] * z.x + s.wb[1] * z.y;
+          }
+        }
+        acc[t] += c;
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_empty + 8 * slot);   // this row's bytes are no longer needed
+#pragma unroll
+    for (int t = 0; t < MT; ++t) {
+#pragma unroll
+      for (int mask = 16; mask > 0; mask >>= 1) acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], mask);
+    }
+    float mine = 0.f;
+#pragma unroll
+    for (int t = 0; t < MT; ++t) if (lane == t) mine = acc[t];
+    if (lane < MT && lane < p.mcount) y[(size_t)(p.m0 + lane) * p.stride_y + row] = from_f32<OutT>(mine);
   }
 }
 
 // ---------------------------------------------------------------------------------------------- host
 struct Config {
   int ks, cb, stages, slot_stride, stage_bytes, a_stride, a_bytes, d_bytes, z_bytes, smem, grid;
+};
+struct RowConfig {
+  int rows_per_stage, stages, stage_bytes, a_stride, a_bytes, d_bytes, z_bytes, smem, grid;
 };
 
 int sm_count() {
@@ -456,22 +643,28 @@ int sm_count() {
   return n;
 }
 
+int z_per_block(int type) {
+  return (type == KQ_TYPE_Q2_K) ? 2 : ((type == KQ_TYPE_Q4_K || type == KQ_TYPE_Q4_0) ? 1 : 0);
+}
+
+constexpr int SMEM_LIMIT = 227 * 1024;
+
+// tensor-core kernel: mtok = token rows of the activation slice kept in shared memory (8 or 16)
 bool make_config(int type, int64_t n, int64_t k, int mtok, Config& c) {
   int blk, bytes;
   if (!type_geometry(type, &blk, &bytes)) return false;
   const int nblk = (int)(k / blk);
   const int ntiles = (int)((n + 15) / 16);
   const int sms = sm_count();
-  const int zpb = (type == KQ_TYPE_Q2_K) ? 2 : ((type == KQ_TYPE_Q4_K || type == KQ_TYPE_Q4_0) ? 1 : 0);
-  const int mp = mtok > 8 ? 16 : 8;
+  const int zpb = z_per_block(type);
   c.cb = 12288 / (16 * bytes);
   if (c.cb < 1) c.cb = 1;
-  const int wide = (type == KQ_TYPE_Q4_K) ? 32 : 16;   // residue of the row-slot stride mod 128: spreads rows over banks
+  const int resid = type == KQ_TYPE_Q4_K ? 32 : 16;   // row-slot stride mod 128: spreads the 16 rows over the banks
   int slot = ((c.cb * bytes + 16 + 15) / 16) * 16;
-  while (slot % 128 != wide) slot += 16;
+  while (slot % 128 != resid) slot += 16;
   c.slot_stride = slot;
   c.stage_bytes = 16 * slot;
-  const int limit = 227 * 1024;
+  const int header = SMEM_HEADER + (type == KQ_TYPE_IQ3_S ? 2048 : 0);
   double best = 1e30;
   bool found = false;
   for (int ks = 1; ks <= 4; ks *= 2) {
@@ -480,11 +673,11 @@ bool make_config(int type, int64_t n, int64_t k, int mtok, Config& c) {
     const int ngrp = grid / ks;
     const int klen = ((nblk + ks - 1) / ks) * blk;
     const int a_stride = klen + 32;
-    const int a_bytes = (mp * a_stride + 127) / 128 * 128;
+    const int a_bytes = (mtok * a_stride + 127) / 128 * 128;
     const int d_bytes = ((klen / 32) * 64 + 127) / 128 * 128;
     const int z_bytes = ((klen / 32) * 64 * zpb + 127) / 128 * 128;
-    const int fixed = SMEM_HEADER + a_bytes + d_bytes + z_bytes;
-    int stages = (limit - fixed) / c.stage_bytes;
+    const int fixed = header + a_bytes + d_bytes + z_bytes;
+    int stages = (SMEM_LIMIT - fixed) / c.stage_bytes;
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     if (stages < 4) continue;
     const int per = (ntiles + ngrp - 1) / ngrp;
@@ -498,31 +691,89 @@ bool make_config(int type, int64_t n, int64_t k, int mtok, Config& c) {
   return found;
 }
 
+// row-streaming kernel: whole rows per stage, the full K of `mt` tokens resident in shared memory
+bool make_row_config(int type, int64_t n, int64_t k, int mt, RowConfig& c) {
+  int blk, bytes;
+  if (!type_geometry(type, &blk, &bytes)) return false;
+  const int64_t rowbytes = k / blk * bytes;
+  const int zpb = z_per_block(type);
+  int R = (int)(16384 / rowbytes);
+  if (R < 1) R = 1;
+  if (R > 16) R = 16;
+  c.rows_per_stage = R;
+  c.stage_bytes = (int)((R * rowbytes + 32 + 127) / 128 * 128);
+  const int64_t kpad = (k + 511) / 512 * 512;
+  const bool zr = type == KQ_TYPE_Q2_K || type == KQ_TYPE_Q4_K;   // types whose min term may need the zr table
+  c.a_stride = (int)k + 32;
+  c.a_bytes = (mt * c.a_stride + 127) / 128 * 128;
+  c.d_bytes = (int)((mt * (kpad / 32) * 4 + 127) / 128 * 128);
+  c.z_bytes = zr ? (int)((mt * (kpad / 32) * 4 * zpb + 127) / 128 * 128) : 0;
+  const int fixed = SMEM_HEADER + (type == KQ_TYPE_IQ3_S ? 2048 : 0) + c.a_bytes + c.d_bytes + c.z_bytes;
+  if (fixed + 3 * (int64_t)c.stage_bytes > SMEM_LIMIT) return false;
+  int stages = (SMEM_LIMIT - fixed) / c.stage_bytes;
+  if (stages > MAX_STAGES) stages = MAX_STAGES;
+  c.stages = stages;
+  c.smem = fixed + stages * c.stage_bytes;
+  const int sms = sm_count();
+  c.grid = n < sms ? (int)n : sms;
+  return true;
+}
+
 template <int QT, int NT, typename OutT>
-int launch_one(const MmaParams& p, const Config& c, cudaStream_t st) {
-  auto kern = gemv_mma_kernel<QT, NT, OutT>;
-  static int attr_set = 0;
-  if (attr_set < c.smem) {
-    KQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    attr_set = 227 * 1024;
+int launch_tc(const MmaParams& p, const Config& c, cudaStream_t st) {
+  auto kern = gemv_stream_kernel<QT, 0, NT, OutT>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    KQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT));
+    attr_set = true;
   }
-  kern<<<c.grid, THREADS, c.smem, st>>>(p);
+  kern<<<c.grid, cta_threads(0), c.smem, st>>>(p);
+  options().launches += 1;
+  KQ_CUDA_TRY(cudaGetLastError());
+  return KQ_OK;
+}
+
+template <int QT, int MT, typename OutT>
+int launch_rows(const RowParams& p, const RowConfig& c, cudaStream_t st) {
+  auto kern = gemv_rows_kernel<QT, MT, OutT>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    KQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT));
+    attr_set = true;
+  }
+  kern<<<c.grid, ROW_THREADS, c.smem, st>>>(p);
   options().launches += 1;
   KQ_CUDA_TRY(cudaGetLastError());
   return KQ_OK;
 }
 
 template <int QT, typename OutT>
-int launch_nt(const MmaParams& p, const Config& c, cudaStream_t st) {
-  return p.mcount > 8 ? launch_one<QT, 2, OutT>(p, c, st) : launch_one<QT, 1, OutT>(p, c, st);
+int launch_tc_nt(const MmaParams& p, const Config& c, int nt, cudaStream_t st) {
+  if constexpr (QT == KQ_TYPE_Q4_K || QT == KQ_TYPE_Q6_K) {
+    return nt == 2 ? launch_tc<QT, 2, OutT>(p, c, st) : launch_tc<QT, 1, OutT>(p, c, st);
+  } else {
+    set_error("tensor-core GEMV: type not covered");
+    return KQ_EUNSUPPORTED;
+  }
+}
+
+template <int QT, typename OutT>
+int launch_rows_mt(const RowParams& p, const RowConfig& c, int mt, cudaStream_t st) {
+  switch (mt) {
+    case 1: return launch_rows<QT, 1, OutT>(p, c, st);
+    case 2: return launch_rows<QT, 2, OutT>(p, c, st);
+    case 4: return launch_rows<QT, 4, OutT>(p, c, st);
+    default: return launch_rows<QT, 8, OutT>(p, c, st);
+  }
 }
 
 template <int QT>
-int launch_typed(const MmaParams& p, const Config& c, int y_dtype, cudaStream_t st) {
+int launch_typed(const MmaParams* pt, const Config* ct, const RowParams* pr, const RowConfig* cr, int nt, int y_dtype,
+                 cudaStream_t st) {
   switch (y_dtype) {
-    case KQ_F32: return launch_nt<QT, float>(p, c, st);
-    case KQ_F16: return launch_nt<QT, __half>(p, c, st);
-    case KQ_BF16: return launch_nt<QT, __nv_bfloat16>(p, c, st);
+    case KQ_F32: return pt ? launch_tc_nt<QT, float>(*pt, *ct, nt, st) : launch_rows_mt<QT, float>(*pr, *cr, nt, st);
+    case KQ_F16: return pt ? launch_tc_nt<QT, __half>(*pt, *ct, nt, st) : launch_rows_mt<QT, __half>(*pr, *cr, nt, st);
+    case KQ_BF16: return pt ? launch_tc_nt<QT, __nv_bfloat16>(*pt, *ct, nt, st) : launch_rows_mt<QT, __nv_bfloat16>(*pr, *cr, nt, st);
   }
   set_error("unsupported output dtype %d", y_dtype);
   return KQ_EUNSUPPORTED;
@@ -530,33 +781,76 @@ int launch_typed(const MmaParams& p, const Config& c, int y_dtype, cudaStream_t 
 
 }  // namespace
 
+// The streaming kernels fetch weights in 16-byte units and (Q4_K tensor-core mode) read 64-bit words, so they
+// need a 16-byte aligned weight pointer; anything else goes to the general dp4a kernel.
 bool gemv_mma_supported(const void* W, int type, int64_t n, int64_t k) {
-  if (type != KQ_TYPE_Q4_K && type != KQ_TYPE_Q6_K) return false;
-  if ((uintptr_t)W % 16) return false;   // row segments are fetched in 16-byte units; Q4_K also reads 64-bit words
-  Config c;
-  return make_config(type, n, k, 16, c);
+  if ((uintptr_t)W % 16) return false;
+  RowConfig c;
+  return make_row_config(type, n, k, 1, c);
 }
 
+// impl: 0 = choose by m, 2 = tensor cores wherever the type has them, 3 = row-streaming dp4a
 int launch_gemv_mma(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m, void* y, int y_dtype,
                     int64_t stride_y, bool mmq, cudaStream_t st) {
   int blk, bytes;
   type_geometry(type, &blk, &bytes);
-  for (int64_t m0 = 0; m0 < m; m0 += 16) {
-    const int mcount = (int)((m - m0) < 16 ? (m - m0) : 16);
+  const int impl = options().gemv_impl;
+  const bool has_tc = (type == KQ_TYPE_Q4_K || type == KQ_TYPE_Q6_K);
+  if (impl == 2 && !has_tc) { set_error("tensor-core GEMV: type %d not covered", type); return KQ_EUNSUPPORTED; }
+  const float* zT = nullptr;
+  if (type == KQ_TYPE_Q4_K) zT = mmq ? P.zs8 : P.z32;
+  if (type == KQ_TYPE_Q4_0) zT = P.zs8;
+  if (type == KQ_TYPE_Q2_K) zT = P.z16;
+  const int zpb = z_per_block(type) ? z_per_block(type) : 1;
+  int64_t m0 = 0;
+  while (m0 < m) {
+    const int64_t left = m - m0;
+    const bool tile_start = (m0 % 16) == 0;
+    int rc, mcount;
     Config c;
-    if (!make_config(type, n, k, mcount, c)) { set_error("tensor-core GEMV: no configuration for this shape"); return KQ_EUNSUPPORTED; }
-    MmaParams p;
-    p.W = (const uint8_t*)W; p.rowbytes = k / blk * bytes; p.n = (int)n; p.nblk = (int)(k / blk); p.ks = c.ks;
-    p.ntiles = (int)((n + 15) / 16); p.cb = c.cb; p.stages = c.stages; p.slot_stride = c.slot_stride;
-    p.stage_bytes = c.stage_bytes; p.a_stride = c.a_stride; p.a_bytes = c.a_bytes; p.d_bytes = c.d_bytes;
-    p.z_bytes = c.z_bytes; p.qs = P.qs; p.dT = P.dT; p.kpad = (int)P.kpad; p.nb32tot = (int)(P.kpad / 32);
-    p.zT = nullptr; p.zpb = 1;
-    if (type == KQ_TYPE_Q4_K) p.zT = mmq ? P.zs8 : P.z32;
-    p.m0 = (int)m0; p.mcount = mcount; p.y = y; p.stride_y = stride_y; p.part = P.part; p.cnt = P.cnt; p.status = P.status;
-    int rc;
-    if (type == KQ_TYPE_Q4_K) rc = launch_typed<KQ_TYPE_Q4_K>(p, c, y_dtype, st);
-    else rc = launch_typed<KQ_TYPE_Q6_K>(p, c, y_dtype, st);
+    if (has_tc && tile_start && impl != 3 && (impl == 2 || left >= options().tc_min_m) &&
+        make_config(type, n, k, left > 8 ? 16 : 8, c)) {
+      mcount = (int)(left < 16 ? left : 16);
+      const int nt = mcount > 8 ? 2 : 1;
+      MmaParams p;
+      p.W = (const uint8_t*)W; p.rowbytes = k / blk * bytes; p.n = (int)n; p.nblk = (int)(k / blk); p.ks = c.ks;
+      p.ntiles = (int)((n + 15) / 16); p.cb = c.cb; p.stages = c.stages; p.slot_stride = c.slot_stride;
+      p.stage_bytes = c.stage_bytes; p.a_stride = c.a_stride; p.a_bytes = c.a_bytes; p.d_bytes = c.d_bytes;
+      p.z_bytes = c.z_bytes; p.qs = P.qs; p.dT = P.dT; p.kpad = (int)P.kpad; p.nb32tot = (int)(P.kpad / 32);
+      p.zT = zT; p.zpb = zpb;
+      p.m0 = (int)m0; p.mcount = mcount; p.y = y; p.stride_y = stride_y; p.part = P.part; p.cnt = P.cnt; p.status = P.status;
+      rc = type == KQ_TYPE_Q4_K ? launch_typed<KQ_TYPE_Q4_K>(&p, &c, nullptr, nullptr, nt, y_dtype, st)
+                                : launch_typed<KQ_TYPE_Q6_K>(&p, &c, nullptr, nullptr, nt, y_dtype, st);
+    } else {
+      if (impl == 2) { set_error("tensor-core GEMV: no configuration for this shape"); return KQ_EUNSUPPORTED; }
+      const int room = 16 - (int)(m0 % 16);          // a pass never crosses a 16-token tile of the scale tables
+      const int cap = (int)(left < room ? left : room);
+      int mt = cap >= 8 ? 8 : (cap >= 4 ? 4 : (cap >= 2 ? 2 : 1));
+      RowConfig rcg;
+      while (mt > 1 && !make_row_config(type, n, k, mt, rcg)) mt >>= 1;   // fewer tokens per pass if K is long
+      if (!make_row_config(type, n, k, mt, rcg)) { set_error("row-streaming GEMV: no configuration for this shape"); return KQ_EUNSUPPORTED; }
+      mcount = mt;
+      RowParams p;
+      p.W = (const uint8_t*)W; p.rowbytes = k / blk * bytes; p.n = (int)n; p.nsb = (int)(k / 32);
+      p.rows_per_stage = rcg.rows_per_stage; p.stages = rcg.stages; p.stage_bytes = rcg.stage_bytes;
+      p.a_stride = rcg.a_stride; p.a_bytes = rcg.a_bytes; p.d_bytes = rcg.d_bytes; p.z_bytes = rcg.z_bytes;
+      p.qs = P.qs; p.ds = P.ds; p.zpb = zpb; p.kpad = (int)P.kpad; p.nb32tot = (int)(P.kpad / 32); p.klen = (int)k;
+      p.zr = nullptr; p.zmode = 0;
+      if (type == KQ_TYPE_Q4_0 || (type == KQ_TYPE_Q4_K && mmq)) p.zmode = 1;
+      else if (type == KQ_TYPE_Q4_K) { p.zmode = 2; p.zr = P.z32r; }
+      else if (type == KQ_TYPE_Q2_K) { p.zmode = 3; p.zr = P.z16r; }
+      p.m0 = (int)m0; p.mcount = mcount; p.y = y; p.stride_y = stride_y; p.status = P.status;
+      switch (type) {
+        case KQ_TYPE_Q4_0: rc = launch_typed<KQ_TYPE_Q4_0>(nullptr, nullptr, &p, &rcg, mt, y_dtype, st); break;
+        case KQ_TYPE_Q8_0: rc = launch_typed<KQ_TYPE_Q8_0>(nullptr, nullptr, &p, &rcg, mt, y_dtype, st); break;
+        case KQ_TYPE_Q2_K: rc = launch_typed<KQ_TYPE_Q2_K>(nullptr, nullptr, &p, &rcg, mt, y_dtype, st); break;
+        case KQ_TYPE_Q4_K: rc = launch_typed<KQ_TYPE_Q4_K>(nullptr, nullptr, &p, &rcg, mt, y_dtype, st); break;
+        case KQ_TYPE_Q6_K: rc = launch_typed<KQ_TYPE_Q6_K>(nullptr, nullptr, &p, &rcg, mt, y_dtype, st); break;
+        default: rc = launch_typed<KQ_TYPE_IQ3_S>(nullptr, nullptr, &p, &rcg, mt, y_dtype, st); break;
+      }
+    }
     if (rc) return rc;
+    m0 += mcount;
   }
   return KQ_OK;
 }

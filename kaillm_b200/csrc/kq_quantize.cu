@@ -19,7 +19,7 @@ __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const T* __restrict_
   const int lane = threadIdx.x & 31;
   const int nb = kpad >> 5;
   const int64_t gthread = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (P.cnt != nullptr && gthread < P.ntiles) P.cnt[gthread] = 0;   // split-K counters start at zero
+  if (P.cnt != nullptr && gthread < P.ncnt) P.cnt[gthread] = 0;   // split-K counters start at zero
   if (P.status != nullptr && gthread == 0) P.status[0] = 0;
   const int64_t blk = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);  // global 32-block index over padded tokens
   if (blk >= mpad * nb) return;
@@ -61,6 +61,9 @@ __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const T* __restrict_
       const int64_t t16 = ((row >> 4) * 2 * nb + 2 * b) * 16 + (row & 15);
       P.z16[t16] = df * (float)s16;
       P.z16[t16 + 16] = df * (float)s16b;
+      P.z32r[row * nb + b] = df * (float)(s16 + s16b);
+      P.z16r[(row * nb + b) * 2] = df * (float)s16;
+      P.z16r[(row * nb + b) * 2 + 1] = df * (float)s16b;
     }
   }
   if (lane == 0) {
@@ -73,12 +76,12 @@ __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const T* __restrict_
 int launch_quantize(const void* x, int x_dtype, int64_t m, int64_t k, int64_t stride_x, const Q8Ptrs* Pp,
                     void* wire36, int64_t kpad, cudaStream_t st) {
   Q8Ptrs P;
-  if (Pp) P = *Pp; else { P = Q8Ptrs(); P.ds = nullptr; P.qs = nullptr; P.dT = P.z32 = P.zs8 = P.z16 = P.part = nullptr; P.cnt = P.status = nullptr; P.kpad = kpad; P.ntiles = 0; }
+  if (Pp) P = *Pp; else { P = Q8Ptrs(); P.ds = nullptr; P.qs = nullptr; P.dT = P.z32 = P.zs8 = P.z16 = P.z32r = P.z16r = P.part = nullptr; P.cnt = P.status = nullptr; P.kpad = kpad; P.ncnt = 0; }
   const int64_t mpad = Pp ? (m + 15) / 16 * 16 : m;
   const int64_t nblk = mpad * (kpad / 32);
   if (nblk == 0) return KQ_OK;
   int64_t gridl = (nblk + 7) / 8;
-  if (gridl * 256 < P.ntiles) gridl = (P.ntiles + 255) / 256;
+  if (gridl * 256 < P.ncnt) gridl = (P.ncnt + 255) / 256;
   const unsigned grid = (unsigned)gridl;
   switch (x_dtype) {
     case KQ_F32:

@@ -68,7 +68,7 @@ SHAPES = [(64, 512, 1), (33, 1024, 5), (130, 2048, 16), (17, 256, 2), (256, 5120
 
 @pytest.mark.parametrize("qt", QT)
 @pytest.mark.parametrize("n,k,m", SHAPES)
-@pytest.mark.parametrize("impl", [1, 0])
+@pytest.mark.parametrize("impl", [1, 0, 3])
 def test_mul_mat_vec_fp32(qt, n, k, m, impl):
     w, wt = wire(qt, n, k, seed=qt + n)
     x, xt = act(m, k, seed=k + m, dt="bf16")
@@ -135,6 +135,25 @@ def test_tensor_core_gemv_matches_oracle_and_dp4a(qt, n, k, m, mmq):
     assert rel_l2(to_np(y2), want) < TIGHT
     assert torch.equal(y2, y2b)
     assert rel_l2(to_np(y2), to_np(y1)) < TIGHT
+
+
+@pytest.mark.parametrize("qt", QT)
+@pytest.mark.parametrize("n,k,m", [(16, 512, 1), (17, 1024, 2), (100, 2048, 3), (2368, 2048, 5), (1200, 5120, 9),
+                                   (333, 4352, 17), (64, 17408, 4), (48, 768, 33), (5, 256, 80)])
+def test_streaming_dp4a_gemv_matches_oracle(qt, n, k, m):
+    w, wt = wire(qt, n, k, seed=n + k + qt)
+    x, xt = act(m, k, seed=m, dt="bf16")
+    ws = capi.workspace_bytes(qt, m, n, k)
+    scratch = torch.empty(ws, dtype=torch.uint8, device=dev())
+    capi.set_option("gemv_impl", 3)
+    try:
+        y = capi.mul_mat(wt, xt, qt, out_dtype=torch.float32, scratch=scratch)
+        assert capi.read_status(qt, m, n, k, scratch) == 0
+        yb = capi.mul_mat(wt, xt, qt, out_dtype=torch.float32, scratch=scratch)
+    finally:
+        capi.set_option("gemv_impl", 0)
+    assert rel_l2(to_np(y), O.mul_mat(w, qt, x, "mmvq")) < TIGHT
+    assert torch.equal(y, yb)
 
 
 def test_tensor_core_gemv_declines_unaligned_weights():
