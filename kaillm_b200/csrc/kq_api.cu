@@ -22,7 +22,7 @@ int cuda_fail(cudaError_t e, const char* what) {
 }
 
 Options& options() {
-  static Options o = {0, 8, 1, 0};
+  static Options o = {0, 8, 33, 1, 0};
   return o;
 }
 
@@ -68,7 +68,8 @@ static int mul_mat(const char* fn, bool mmq, const void* W, int type, int64_t n,
   int rc = validate(fn, W, type, n, k, x, x_dtype, m, stride_x, scratch, scratch_bytes, p, need_w, need_x);
   if (rc) return rc;
   if (!need_w) {
-    const Q8Ptrs P = q8_ptrs(scratch, p.L, n);
+    Q8Ptrs P = q8_ptrs(scratch, p.L, n);
+    if (m < options().gemm_min_m) P.xh = nullptr;
     return launch_quantize(x, x_dtype, m, k, stride_x, &P, nullptr, p.L.kpad, (cudaStream_t)stream);
   }
   if (mmq && type == KQ_TYPE_IQ3_S) { set_error("%s: IQ3_S has no MMQ kernel (use dequantize + matmul or mul_mat_vec)", fn); return KQ_EUNSUPPORTED; }
@@ -76,12 +77,15 @@ static int mul_mat(const char* fn, bool mmq, const void* W, int type, int64_t n,
   if (!y || stride_y < n) { set_error("%s: bad output (null or stride_y < n)", fn); return KQ_EINVAL; }
   if ((uintptr_t)y % dtype_size(y_dtype)) { set_error("%s: misaligned output pointer", fn); return KQ_EINVAL; }
   cudaStream_t st = (cudaStream_t)stream;
-  const Q8Ptrs P = q8_ptrs(scratch, p.L, n);
+  Q8Ptrs P = q8_ptrs(scratch, p.L, n);
+  const int impl = options().gemv_impl;
+  const bool gemm = impl == 0 && m >= options().gemm_min_m && gemm_tc_supported(W, type, n, k);
+  if (!gemm && need_x) P.xh = nullptr;   // the fp16 copy of the activations is only written for the GEMM
   if (x) {
     rc = launch_quantize(x, x_dtype, m, k, stride_x, &P, nullptr, p.L.kpad, st);
     if (rc) return rc;
   }
-  const int impl = options().gemv_impl;
+  if (gemm) return launch_gemm_tc(W, type, n, k, P, m, y, y_dtype, stride_y, mmq, st);
   if (impl != 1 && gemv_mma_supported(W, type, n, k))
     return launch_gemv_mma(W, type, n, k, P, m, y, y_dtype, stride_y, mmq, st);
   if (impl >= 2) { set_error("%s: the streaming GEMV does not cover this shape/alignment", fn); return KQ_EUNSUPPORTED; }
@@ -168,7 +172,8 @@ int kq_debug_group_dots(const void* W, int type, int64_t n, int64_t k, const voi
   if (rc) return rc;
   if (!dots) { set_error("kq_debug_group_dots: null dots"); return KQ_EINVAL; }
   cudaStream_t st = (cudaStream_t)stream;
-  const Q8Ptrs P = q8_ptrs(scratch, p.L, n);
+  Q8Ptrs P = q8_ptrs(scratch, p.L, n);
+  P.xh = nullptr;
   rc = launch_quantize(x, x_dtype, m, k, stride_x, &P, nullptr, p.L.kpad, st);
   if (rc) return rc;
   return launch_gemv_dp4a(W, type, n, k, P.ds, P.qs, p.L.kpad, m, nullptr, KQ_F32, n, false, dots, sums, st);
@@ -188,6 +193,7 @@ int kq_set_option(const char* name, int value) {
   if (name && !strcmp(name, "gemv_impl")) { options().gemv_impl = value; return KQ_OK; }
   if (name && !strcmp(name, "half_fma")) { options().half_fma = value; return KQ_OK; }
   if (name && !strcmp(name, "tc_min_m")) { options().tc_min_m = value; return KQ_OK; }
+  if (name && !strcmp(name, "gemm_min_m")) { options().gemm_min_m = value; return KQ_OK; }
   set_error("kq_set_option: unknown option");
   return KQ_EINVAL;
 }
@@ -196,6 +202,7 @@ int kq_get_option(const char* name, int* value) {
   if (name && value && !strcmp(name, "gemv_impl")) { *value = options().gemv_impl; return KQ_OK; }
   if (name && value && !strcmp(name, "half_fma")) { *value = options().half_fma; return KQ_OK; }
   if (name && value && !strcmp(name, "tc_min_m")) { *value = options().tc_min_m; return KQ_OK; }
+  if (name && value && !strcmp(name, "gemm_min_m")) { *value = options().gemm_min_m; return KQ_OK; }
   if (name && value && !strcmp(name, "launch_count")) { *value = (int)(options().launches & 0x7fffffff); return KQ_OK; }
   set_error("kq_get_option: unknown option");
   return KQ_EINVAL;

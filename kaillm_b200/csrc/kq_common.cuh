@@ -25,6 +25,7 @@ int cuda_fail(cudaError_t e, const char* what);
 struct Options {
   int gemv_impl;       // 0 auto, 1 general dp4a kernel, 2 streaming tensor-core, 3 streaming dp4a
   int tc_min_m;        // auto mode: smallest token count that goes to the tensor-core consumers
+  int gemm_min_m;      // smallest token count that goes to the tcgen05 GEMM
   int half_fma;        // 1: fp16 mul+sub contracted in K-quant dequantize
   long long launches;  // kernels launched by this library so far (host-side count)
 };
@@ -62,6 +63,10 @@ inline int type_group(int type) { return (type == KQ_TYPE_Q2_K || type == KQ_TYP
 //   z32   float [mt][kpad/32][16]   d * (sum of the 32 codes)      (min term, MMVQ flavour)
 //   zs8   float [mt][kpad/32][16]   the fp16 raw sum as fp32        (min term of Q4_0 and MMQ-flavoured Q4_K)
 //   z16   float [mt][kpad/16][16]   d * (sum of 16 codes)           (min term of Q2_K)
+//   qsp   int8  [m][kpad/64][80]    the codes again, 16 bytes of padding after every 64 (bank-conflict-free
+//                                   16-byte reads by lanes that are 64 codes apart)
+//   xh    half  [m][kpad]           d * code rounded to fp16: the B operand of the tensor-core GEMM
+//   s8h   half  [m][kpad/32]        the fp16 raw block sums alone (second B operand of the GEMM)
 //   z32r  float [m][kpad/32]        same values as z32, token-major (row-streaming kernel)
 //   z16r  float [m][kpad/16]        same values as z16, token-major
 //   part  float [4][16][n]          split-K partial sums of one 16-token pass
@@ -70,7 +75,7 @@ inline int type_group(int type) { return (type == KQ_TYPE_Q2_K || type == KQ_TYP
 //   status int  [64]                device-side error word (bounded waits that gave up)
 struct Q8Layout {
   int64_t kpad, mt;
-  size_t off_ds, off_qs, off_dT, off_z32, off_zs8, off_z16, off_z32r, off_z16r, off_part, off_cnt, off_status, total;
+  size_t off_ds, off_qs, off_qsp, off_xh, off_s8h, off_dT, off_z32, off_zs8, off_z16, off_z32r, off_z16r, off_part, off_cnt, off_status, total;
 };
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 inline Q8Layout q8_layout(int64_t m, int64_t n, int64_t k) {
@@ -81,6 +86,9 @@ inline Q8Layout q8_layout(int64_t m, int64_t n, int64_t k) {
   size_t p = 0;
   L.off_ds = p;     p = align_up(p + (size_t)m * nb * 4, 256);
   L.off_qs = p;     p = align_up(p + (size_t)m * L.kpad, 256);
+  L.off_qsp = p;    p = align_up(p + (size_t)m * (L.kpad / 64) * 80, 256);
+  L.off_xh = p;     p = align_up(p + (size_t)m * L.kpad * 2, 1024);
+  L.off_s8h = p;    p = align_up(p + (size_t)m * nb * 2, 1024);
   L.off_dT = p;     p = align_up(p + (size_t)L.mt * nb * 64, 256);
   L.off_z32 = p;    p = align_up(p + (size_t)L.mt * nb * 64, 256);
   L.off_zs8 = p;    p = align_up(p + (size_t)L.mt * nb * 64, 256);
@@ -95,13 +103,13 @@ inline Q8Layout q8_layout(int64_t m, int64_t n, int64_t k) {
 }
 
 struct Q8Ptrs {  // device pointers into one scratch buffer
-  __half2* ds; int8_t* qs; float *dT, *z32, *zs8, *z16, *z32r, *z16r, *part; int *cnt, *status;
+  __half2* ds; int8_t* qs; int8_t* qsp; __half* xh; __half* s8h; float *dT, *z32, *zs8, *z16, *z32r, *z16r, *part; int *cnt, *status;
   int64_t kpad; int ncnt;
 };
 inline Q8Ptrs q8_ptrs(void* scratch, const Q8Layout& L, int64_t n) {
   uint8_t* s = (uint8_t*)scratch;
   Q8Ptrs P;
-  P.ds = (__half2*)(s + L.off_ds); P.qs = (int8_t*)(s + L.off_qs);
+  P.ds = (__half2*)(s + L.off_ds); P.qs = (int8_t*)(s + L.off_qs); P.qsp = (int8_t*)(s + L.off_qsp); P.xh = (__half*)(s + L.off_xh); P.s8h = (__half*)(s + L.off_s8h);
   P.dT = (float*)(s + L.off_dT); P.z32 = (float*)(s + L.off_z32); P.zs8 = (float*)(s + L.off_zs8);
   P.z16 = (float*)(s + L.off_z16); P.z32r = (float*)(s + L.off_z32r); P.z16r = (float*)(s + L.off_z16r);
   P.part = (float*)(s + L.off_part);
@@ -122,6 +130,9 @@ int launch_gemv_dp4a(const void* W, int type, int64_t n, int64_t k, const void* 
 bool gemv_mma_supported(const void* W, int type, int64_t n, int64_t k);
 int launch_gemv_mma(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m, void* y,
                     int y_dtype, int64_t stride_y, bool mmq, cudaStream_t st);
+bool gemm_tc_supported(const void* W, int type, int64_t n, int64_t k);
+int launch_gemm_tc(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m, void* y, int y_dtype,
+                   int64_t stride_y, bool mmq, cudaStream_t st);
 int launch_dequantize(const void* W, int type, int64_t count, void* out, int out_dtype, cudaStream_t st);
 
 #ifdef __CUDACC__

@@ -1,0 +1,485 @@
+// Prefill GEMM (M >= ~32 tokens): dequantize-on-the-fly + tcgen05 (5th-gen tensor core) MMA with TMEM accumulators.
+//
+//   y[tok, row] = sum_k  w^[row, k] * x^[tok, k]   (+ sum_b c[row, b] * s8[tok, b])
+//   w^ = the weight dequantized to fp16 with the op order of ggml_dequantize
+//        (vllm_gguf_plugin/csrc/gguf/dequantize.cuh:156-196 etc.), x^ = fp16(d8 * q8) of the q8_1-quantized
+//        activation (gguf_kernel.cu:32-69).  fp16 operands, fp32 accumulation in TMEM: rel-L2 ~3e-4 to the
+//        integer-dot arithmetic of the reference's MMQ kernels (bf16 operands would give 2e-3).
+//   The reference forms Q4_0's "-8" offset and MMQ-flavoured Q4_K's min term from the fp16 sum of the RAW
+//   activations of each 32-block (s8), not from the quantized codes (vecdotq.cuh:46-66, 353-379); a dense
+//   product cannot express that, and the difference (1e-2 for Q4_0, 1e-3 for Q4_K) would break the 1e-3 gate.
+//   For those cases w^ is formed without the offset/min and extra K steps multiply the per-block coefficient
+//   c[row, b] (-8*d, or -dmin*m) with s8[tok, b] into the same accumulator.
+//
+//   CTA tile  128 weight rows (UMMA M, one TMEM lane per row) x BN = 128 tokens (UMMA N)
+//   warps 0-3 thread = weight row: reads its row's wire blocks straight from global/L2, dequantizes 64 weights at a
+//             time to packed fp16 registers and writes them to TMEM with tcgen05.st - the A operand never touches
+//             shared memory.  After the K loop the same threads read the accumulators back (tcgen05.ld) and
+//             store y (lanes = consecutive rows: coalesced).
+//   warp 4    one lane fetches the x^ tile [BN x 256] of each K step with four TMA tiled loads (128-byte swizzle)
+//   warp 5    one lane issues the MMAs: per K step (one 256-weight super-block) 16 x tcgen05.mma.kind::f16
+//             (128 x BN x 16), A from TMEM, B through a shared-memory descriptor; tcgen05.commit signals
+//             "buffers free" and, at the end, "accumulator complete".
+//   Two A buffers in TMEM (2 x 128 columns) and two B stages in shared memory (2 x 64 KB) overlap dequantization,
+//   loads and MMAs.  Every mbarrier wait is bounded; on give-up a status word is set, TMEM is released and the
+//   CTA returns.
+#include <cuda.h>
+
+#include "kq_common.cuh"
+
+namespace kq {
+namespace {
+
+constexpr int BM = 128;         // weight rows per CTA = UMMA M
+constexpr int BN = 128;         // tokens per CTA = UMMA N
+constexpr int KSTEP = 256;      // k per pipeline step
+constexpr int ATOM = 64;        // k per 128-byte swizzle atom (fp16)
+constexpr int NBUF = 2;
+constexpr int GEMM_THREADS = 192;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t TMEM_D = 0;                 // accumulator: columns [0, BN)
+constexpr uint32_t TMEM_A = 256;               // A buffers: 2 x 128 columns (256 k of fp16 pairs each)
+constexpr int B_STAGE_BYTES = BN * KSTEP * 2;  // 64 KB
+constexpr long long GEMM_WAIT_LIMIT = 1ll << 28;
+
+__constant__ uint16_t c_iq3s_codes_g[512] = {
+#include "kq_iq3s_codes.inc"
+};
+
+struct GemmParams {
+  const uint8_t* W;
+  int64_t rowbytes;
+  int n, k, m;
+  int ntok_tiles;
+  int ncorr;          // extra K steps over the 32-block raw-sum table (0 = none)
+  int nb32;           // k / 32
+  void* y;
+  int64_t stride_y;
+  int* status;
+  int half_fma;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (*abort_flag) return false;
+    if (clock64() - t0 > GEMM_WAIT_LIMIT) { *abort_flag = 1; return false; }
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&a)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
+      "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(a[4]), "r"(a[5]), "r"(a[6]), "r"(a[7]), "r"(a[8]),
+        "r"(a[9]), "r"(a[10]), "r"(a[11]), "r"(a[12]), "r"(a[13]), "r"(a[14]), "r"(a[15]), "r"(a[16]), "r"(a[17]), "r"(a[18]),
+        "r"(a[19]), "r"(a[20]), "r"(a[21]), "r"(a[22]), "r"(a[23]), "r"(a[24]), "r"(a[25]), "r"(a[26]), "r"(a[27]), "r"(a[28]),
+        "r"(a[29]), "r"(a[30]), "r"(a[31]) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
+      "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t h2_bits(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
+__device__ __forceinline__ __half2 bits_h2(uint32_t v) { return *reinterpret_cast<__half2*>(&v); }
+
+// ------------------------------------------------------------------------------------------------ dequantization
+// 64 consecutive weights (k = 64*atom .. +63 of the 256-weight block or of 8 consecutive 32-weight blocks at `blk`)
+// -> 32 packed fp16 pairs, with the fp16 operation order of ggml_dequantize.
+__device__ __forceinline__ __half mul_sub_h(__half a, __half b, __half c, int fma) {
+  return fma ? __hfma(a, b, __hneg(c)) : __hsub_rn(__hmul_rn(a, b), c);
+}
+
+// coefficient of the raw block sum for 32-block b of this row: Q4_0 -8*d, Q4_K -dmin*m (both fp16)
+template <int QT>
+__device__ __forceinline__ __half corr_coef(const uint8_t* __restrict__ wrow, int b) {
+  if constexpr (QT == KQ_TYPE_Q4_0) {
+    return __hmul_rn(__float2half_rn(-8.0f), __ushort_as_half(*reinterpret_cast<const uint16_t*>(wrow + (size_t)b * 18)));
+  } else if constexpr (QT == KQ_TYPE_Q4_K) {
+    const uint8_t* blk = wrow + (size_t)(b >> 3) * 144;
+    const int j = b & 7;
+    const uint8_t* q = blk + 4;
+    const int mn = j < 4 ? (q[j + 4] & 63) : ((q[j + 4] >> 4) | ((q[j] >> 6) << 4));
+    const __half dmin = __ushort_as_half(*reinterpret_cast<const uint16_t*>(blk + 2));
+    return __hneg(__hmul_rn(dmin, __int2half_rn(mn)));
+  } else {
+    return __float2half_rn(0.f);
+  }
+}
+
+template <int QT>
+__device__ __forceinline__ void corr_atom(const uint8_t* __restrict__ wrow, int atom, int nb32, uint32_t (&out)[32]) {
+#pragma unroll 4
+  for (int i = 0; i < 32; ++i) {
+    const int b = atom * 64 + 2 * i;
+    const __half c0 = b < nb32 ? corr_coef<QT>(wrow, b) : __float2half_rn(0.f);
+    const __half c1 = b + 1 < nb32 ? corr_coef<QT>(wrow, b + 1) : __float2half_rn(0.f);
+    out[i] = h2_bits(__halves2half2(c0, c1));
+  }
+}
+
+// CORR: leave the offset (Q4_0) / min (Q4_K) out of w^; it is applied through corr_atom steps instead
+template <int QT, bool CORR>
+__device__ __forceinline__ void dequant_atom(const uint8_t* __restrict__ blk, int atom, const uint32_t* grid, int fma,
+                                             uint32_t (&out)[32]) {
+  if constexpr (QT == KQ_TYPE_Q4_K) {
+    // atom a = sub-blocks 2a (low nibbles of qs[32a..32a+31]) and 2a+1 (high nibbles); 16-byte aligned block
+    const uint4 hdr = *reinterpret_cast<const uint4*>(blk);
+    const __half2 dm = bits_h2(hdr.x);
+    const uint32_t scw = atom < 2 ? (hdr.y & 0x3F3F3F3Fu) : ((hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u));
+    const uint32_t mnw = atom < 2 ? (hdr.z & 0x3F3F3F3Fu) : (((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u));
+    const int sh = 16 * (atom & 1);
+    const __half d1 = __hmul_rn(__low2half(dm), __int2half_rn((int)((scw >> sh) & 0xFFu)));
+    const __half d2 = __hmul_rn(__low2half(dm), __int2half_rn((int)((scw >> (sh + 8)) & 0xFFu)));
+    const __half m1 = __hmul_rn(__high2half(dm), __int2half_rn((int)((mnw >> sh) & 0xFFu)));
+    const __half m2 = __hmul_rn(__high2half(dm), __int2half_rn((int)((mnw >> (sh + 8)) & 0xFFu)));
+    const __half2 d1v = __half2half2(d1), d2v = __half2half2(d2);
+    const __half2 nm1 = __half2half2(__hneg(m1)), nm2 = __half2half2(__hneg(m2));
+    const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
+    const uint4 w0 = *reinterpret_cast<const uint4*>(blk + 16 + 32 * atom);
+    const uint4 w1 = *reinterpret_cast<const uint4*>(blk + 32 + 32 * atom);
+    const uint32_t wq[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t lo = wq[i] & 0x0F0F0F0Fu, hi = (wq[i] >> 4) & 0x0F0F0F0Fu;
+      // bytes (n0, n1) -> half2 (1024+n0, 1024+n1), minus 1024: exact small integers in fp16
+      const __half2 l01 = __hsub2(bits_h2(__byte_perm(lo, 0x64646464u, 0x4140)), k1024);
+      const __half2 l23 = __hsub2(bits_h2(__byte_perm(lo, 0x64646464u, 0x4342)), k1024);
+      const __half2 h01 = __hsub2(bits_h2(__byte_perm(hi, 0x64646464u, 0x4140)), k1024);
+      const __half2 h23 = __hsub2(bits_h2(__byte_perm(hi, 0x64646464u, 0x4342)), k1024);
+      if constexpr (CORR) {
+        out[2 * i] = h2_bits(__hmul2_rn(d1v, l01));
+        out[2 * i + 1] = h2_bits(__hmul2_rn(d1v, l23));
+        out[16 + 2 * i] = h2_bits(__hmul2_rn(d2v, h01));
+        out[16 + 2 * i + 1] = h2_bits(__hmul2_rn(d2v, h23));
+      } else if (fma) {
+        out[2 * i] = h2_bits(__hfma2(d1v, l01, nm1));
+        out[2 * i + 1] = h2_bits(__hfma2(d1v, l23, nm1));
+        out[16 + 2 * i] = h2_bits(__hfma2(d2v, h01, nm2));
+        out[16 + 2 * i + 1] = h2_bits(__hfma2(d2v, h23, nm2));
+      } else {
+        out[2 * i] = h2_bits(__hadd2_rn(__hmul2_rn(d1v, l01), nm1));
+        out[2 * i + 1] = h2_bits(__hadd2_rn(__hmul2_rn(d1v, l23), nm1));
+        out[16 + 2 * i] = h2_bits(__hadd2_rn(__hmul2_rn(d2v, h01), nm2));
+        out[16 + 2 * i + 1] = h2_bits(__hadd2_rn(__hmul2_rn(d2v, h23), nm2));
+      }
+    }
+  } else {
+    // general formats: decode two 32-weight sub-blocks to integer codes, then apply the fp16 op sequence per weight
+    using F = Fmt<QT>;
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int sb = 2 * atom + e;   // sub-block index relative to `blk` (for 32-weight blocks: block index)
+      SubBlock s;
+      decode_subblock<QT>(blk, sb, grid, s);
+      // scale fields again, as fp16
+      __half d = __float2half_rn(0.f), dmin = d;
+      int sc[2] = {0, 0}, mn[2] = {0, 0};
+      float fsc = 0.f;
+      if constexpr (QT == KQ_TYPE_Q4_0) { d = __ushort_as_half(*reinterpret_cast<const uint16_t*>(blk + (size_t)sb * 18)); }
+      if constexpr (QT == KQ_TYPE_Q8_0) { d = __ushort_as_half(*reinterpret_cast<const uint16_t*>(blk + (size_t)sb * 34)); }
+      if constexpr (QT == KQ_TYPE_Q2_K) {
+        d = __ushort_as_half(*reinterpret_cast<const uint16_t*>(blk + 80));
+        dmin = __ushort_as_half(*reinterpret_cast<const uint16_t*>(blk + 82));
+        for (int h = 0; h < 2; ++h) { const int v = blk[2 * sb + h]; sc[h] = v & 15; mn[h] = v >> 4; }
+      }
+      if constexpr (QT == KQ_TYPE_Q6_K) {
+        d = __ushort_as_half(*reinterpret_cast<const uint16_t*>(blk + 208));
+        const int ip = sb >> 2, q4 = sb & 3;
+        for (int h = 0; h < 2; ++h) sc[h] = (int8_t)blk[192 + 8 * ip + 2 * q4 + h];
+      }
+      if constexpr (QT == KQ_TYPE_IQ3_S) {
+        const float dh = ld_h(blk);
+        const uint32_t s4 = (blk[106 + (sb >> 1)] >> (4 * (sb & 1))) & 15u;
+        fsc = __fmul_rn(__fmul_rn(dh, 0.5f + (float)s4), 0.5f);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        __half r[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int h = (F::GROUP == 16) ? (i >> 2) : 0;
+          const int code = (QT == KQ_TYPE_Q4_0 || QT == KQ_TYPE_Q2_K) ? (int)((s.v[i] >> (8 * j)) & 0xFFu)
+                                                                      : (int)(int8_t)(s.v[i] >> (8 * j));
+          if constexpr (QT == KQ_TYPE_Q4_0) r[j] = __hmul_rn(__int2half_rn(code), d);   // offset applied via corr steps
+          if constexpr (QT == KQ_TYPE_Q8_0) r[j] = __hmul_rn(__int2half_rn(code), d);
+          if constexpr (QT == KQ_TYPE_Q2_K) {
+            const __half xq = __int2half_rn(sc[h] * code);
+            const __half mp = __hmul_rn(dmin, __int2half_rn(mn[h]));
+            r[j] = fma == 2 ? __hfma(__hneg(dmin), __int2half_rn(mn[h]), __hmul_rn(d, xq)) : mul_sub_h(d, xq, mp, fma);
+          }
+          if constexpr (QT == KQ_TYPE_Q6_K) r[j] = __hmul_rn(d, __int2half_rn(sc[h] * code));
+          if constexpr (QT == KQ_TYPE_IQ3_S) r[j] = __float2half_rn(__fmul_rn(fsc, (float)code));
+        }
+        out[16 * e + 2 * i] = h2_bits(__halves2half2(r[0], r[1]));
+        out[16 * e + 2 * i + 1] = h2_bits(__halves2half2(r[2], r[3]));
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ kernel
+template <int QT, bool CORR, typename OutT>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap smap) {
+  using F = Fmt<QT>;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* sB = smem;                                            // NBUF x 64 KB, each atom [BN rows x 128 B] swizzled
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + NBUF * B_STAGE_BYTES);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 17);
+  uint32_t* s_grid = reinterpret_cast<uint32_t*>(bars + 32);     // IQ3_S codebook (2 KB)
+  const uint32_t bar_bfull = smem_u32(bars), bar_afull = smem_u32(bars + 2), bar_empty = smem_u32(bars + 4),
+                 bar_dfull = smem_u32(bars + 6);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int row_tile = blockIdx.x / p.ntok_tiles, tok_tile = blockIdx.x % p.ntok_tiles;
+  const int nmain = p.k / KSTEP;
+  const int nsteps = nmain + (CORR ? p.ncorr : 0);
+
+  if (tid == 0) {
+    for (int i = 0; i < NBUF; ++i) {
+      mbar_init(bar_bfull + 8 * i, 1);
+      mbar_init(bar_afull + 8 * i, 4);     // one arrival per producer warp
+      mbar_init(bar_empty + 8 * i, 1);     // tcgen05.commit
+    }
+    mbar_init(bar_dfull, 1);
+    *s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if constexpr (QT == KQ_TYPE_IQ3_S) {
+    for (int i = tid; i < 512; i += GEMM_THREADS) s_grid[i] = iq3s_expand(c_iq3s_codes_g[i], KQ_IQ3S_TOP);
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tbase = *tmem_slot;
+
+  if (warp == 4) {
+    // -------------------------------------------------------------------------- activation loader (TMA)
+    if (lane == 0) {
+      for (int s = 0; s < nsteps; ++s) {
+        const int buf = s & 1;
+        if (s >= NBUF && !mbar_wait(bar_empty + 8 * buf, (uint32_t)(((s >> 1) - 1) & 1), s_abort)) break;
+        mbar_expect_tx(bar_bfull + 8 * buf, B_STAGE_BYTES);
+#pragma unroll
+        for (int a = 0; a < KSTEP / ATOM; ++a) {
+          const uint32_t dst = smem_u32(sB + buf * B_STAGE_BYTES + a * (BN * 128));
+          if (s < nmain) tma_load_2d(dst, &xmap, s * KSTEP + a * ATOM, tok_tile * BN, bar_bfull + 8 * buf);
+          else tma_load_2d(dst, &smap, (s - nmain) * KSTEP + a * ATOM, tok_tile * BN, bar_bfull + 8 * buf);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // -------------------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      // instruction descriptor: D = f32, A = B = f16, both K-major, N >> 3 at bit 17, M >> 4 at bit 24
+      const uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      bool ok = true;
+      for (int s = 0; s < nsteps && ok; ++s) {
+        const int buf = s & 1;
+        const uint32_t par = (uint32_t)((s >> 1) & 1);
+        ok = mbar_wait(bar_bfull + 8 * buf, par, s_abort) && mbar_wait(bar_afull + 8 * buf, par, s_abort);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int a = 0; a < KSTEP / ATOM; ++a) {
+          // shared-memory descriptor: addr >> 4, LBO (unused with swizzle), SBO = 1024 B, version 1, 128-byte swizzle
+          const uint32_t baddr = smem_u32(sB + buf * B_STAGE_BYTES + a * (BN * 128));
+          const uint64_t bdesc = (uint64_t)((baddr & 0x3FFFF) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) |
+                                 (1ull << 46) | (2ull << 61);
+#pragma unroll
+          for (int kk = 0; kk < ATOM / 16; ++kk) {
+            const uint32_t ta = tbase + TMEM_A + buf * 128 + a * 32 + kk * 8;
+            const uint32_t accum = (s > 0 || a > 0 || kk > 0) ? 1u : 0u;
+            asm volatile(
+                "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                ::"r"(tbase + TMEM_D), "r"(ta), "l"(bdesc + (uint64_t)((kk * 32) >> 4)), "r"(idesc), "r"(accum) : "memory");
+          }
+        }
+        // completion of everything issued so far frees this step's A buffer and B stage
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_empty + 8 * buf) : "memory");
+      }
+      if (ok) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_dfull) : "memory");
+    }
+  } else {
+    // -------------------------------------------------------------------------- dequantizers (thread = weight row)
+    int row = row_tile * BM + tid;
+    const bool row_ok = row < p.n;
+    if (!row_ok) row = p.n - 1;                       // clamp: loads stay in bounds, the store is skipped
+    const uint8_t* wrow = p.W + (size_t)row * p.rowbytes;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    bool ok = true;
+    for (int s = 0; s < nsteps && ok; ++s) {
+      const int buf = s & 1;
+      if (s >= NBUF) ok = mbar_wait(bar_empty + 8 * buf, (uint32_t)(((s >> 1) - 1) & 1), s_abort);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint8_t* blk = wrow + (size_t)s * (KSTEP / F::BLK) * F::BYTES;
+#pragma unroll 1
+      for (int a = 0; a < KSTEP / ATOM; ++a) {
+        uint32_t v[32];
+        if (s < nmain) dequant_atom<QT, CORR>(blk, a, s_grid, p.half_fma, v);
+        else corr_atom<QT>(wrow, (s - nmain) * (KSTEP / ATOM) + a, p.nb32, v);
+        tmem_st32(tbase + TMEM_A + lane_base + buf * 128 + a * 32, v);
+      }
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_afull + 8 * buf);
+    }
+    // -------------------------------------------------------------------------- epilogue
+    if (ok && mbar_wait(bar_dfull, 0, s_abort)) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      OutT* y = reinterpret_cast<OutT*>(p.y);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(tbase + TMEM_D + lane_base + c0, r);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int tok = tok_tile * BN + c0 + j;
+          if (row_ok && tok < p.m) y[(size_t)tok * p.stride_y + row] = from_f32<OutT>(__uint_as_float(r[j]));
+        }
+      }
+    }
+  }
+  if (*s_abort && tid == 0) atomicExch(p.status, 16);
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tbase), "r"(TMEM_COLS));
+}
+
+// ------------------------------------------------------------------------------------------------ host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+template <int QT, bool CORR, typename OutT>
+int launch(const GemmParams& p, const CUtensorMap& map, const CUtensorMap& smap, int grid, cudaStream_t st) {
+  auto kern = gemm_tc_kernel<QT, CORR, OutT>;
+  const int smem = NBUF * B_STAGE_BYTES + 4096;
+  static bool attr_set = false;
+  if (!attr_set) {
+    KQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    attr_set = true;
+  }
+  kern<<<grid, GEMM_THREADS, smem, st>>>(p, map, smap);
+  options().launches += 1;
+  KQ_CUDA_TRY(cudaGetLastError());
+  return KQ_OK;
+}
+
+template <int QT, bool CORR>
+int launch_out(const GemmParams& p, const CUtensorMap& map, const CUtensorMap& smap, int grid, int y_dtype, cudaStream_t st) {
+  switch (y_dtype) {
+    case KQ_F32: return launch<QT, CORR, float>(p, map, smap, grid, st);
+    case KQ_F16: return launch<QT, CORR, __half>(p, map, smap, grid, st);
+    case KQ_BF16: return launch<QT, CORR, __nv_bfloat16>(p, map, smap, grid, st);
+  }
+  set_error("unsupported output dtype %d", y_dtype);
+  return KQ_EUNSUPPORTED;
+}
+
+}  // namespace
+
+// The tensor-core GEMM needs whole 256-weight K steps and 16-byte aligned Q4_K blocks; everything else is general.
+bool gemm_tc_supported(const void* W, int type, int64_t n, int64_t k) {
+  if (k % KSTEP) return false;
+  if (type == KQ_TYPE_Q4_K && ((uintptr_t)W % 16)) return false;
+  return encode_fn() != nullptr;
+}
+
+// xh: fp16 [m][kpad] dequantized activations (written by the quantizer)
+int launch_gemm_tc(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m, void* y, int y_dtype,
+                   int64_t stride_y, bool mmq, cudaStream_t st) {
+  int blk, bytes;
+  type_geometry(type, &blk, &bytes);
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) { set_error("tensor-core GEMM: cuTensorMapEncodeTiled is not available"); return KQ_ECUDA; }
+  CUtensorMap map;
+  const cuuint64_t gdim[2] = {(cuuint64_t)k, (cuuint64_t)m};
+  const cuuint64_t gstr[1] = {(cuuint64_t)P.kpad * 2};
+  const cuuint32_t box[2] = {ATOM, BN};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)P.xh, gdim, gstr, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("tensor-core GEMM: cuTensorMapEncodeTiled failed (%d)", (int)r); return KQ_ECUDA; }
+  // raw block sums s8 as fp16 [m][kpad/32]; columns past k/32 read as zero (tensor-map bounds)
+  CUtensorMap smap;
+  const cuuint64_t sdim[2] = {(cuuint64_t)(k / 32), (cuuint64_t)m};
+  const cuuint64_t sstr[1] = {(cuuint64_t)(P.kpad / 32) * 2};
+  const CUresult r2 = enc(&smap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)P.s8h, sdim, sstr, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r2 != CUDA_SUCCESS) { set_error("tensor-core GEMM: cuTensorMapEncodeTiled failed (%d)", (int)r2); return KQ_ECUDA; }
+  const bool corr = type == KQ_TYPE_Q4_0 || (type == KQ_TYPE_Q4_K && mmq);
+  GemmParams p;
+  p.ncorr = corr ? (int)((k / 32 + KSTEP - 1) / KSTEP) : 0;
+  p.nb32 = (int)(k / 32);
+  p.W = (const uint8_t*)W; p.rowbytes = k / blk * bytes; p.n = (int)n; p.k = (int)k; p.m = (int)m;
+  p.ntok_tiles = (int)((m + BN - 1) / BN);
+  p.y = y; p.stride_y = stride_y; p.status = P.status; p.half_fma = options().half_fma;
+  const int grid = (int)((n + BM - 1) / BM) * p.ntok_tiles;
+  switch (type) {
+    case KQ_TYPE_Q4_0: return launch_out<KQ_TYPE_Q4_0, true>(p, map, smap, grid, y_dtype, st);
+    case KQ_TYPE_Q8_0: return launch_out<KQ_TYPE_Q8_0, false>(p, map, smap, grid, y_dtype, st);
+    case KQ_TYPE_Q2_K: return launch_out<KQ_TYPE_Q2_K, false>(p, map, smap, grid, y_dtype, st);
+    case KQ_TYPE_Q4_K: return corr ? launch_out<KQ_TYPE_Q4_K, true>(p, map, smap, grid, y_dtype, st)
+                                   : launch_out<KQ_TYPE_Q4_K, false>(p, map, smap, grid, y_dtype, st);
+    case KQ_TYPE_Q6_K: return launch_out<KQ_TYPE_Q6_K, false>(p, map, smap, grid, y_dtype, st);
+    case KQ_TYPE_IQ3_S: return launch_out<KQ_TYPE_IQ3_S, false>(p, map, smap, grid, y_dtype, st);
+  }
+  return KQ_EUNSUPPORTED;
+}
+
+}  // namespace kq

@@ -476,6 +476,7 @@ struct RowParams {
   int rows_per_stage, stages, stage_bytes;
   int a_stride, a_bytes, d_bytes, z_bytes;
   const int8_t* qs;
+  const int8_t* qsp;        // padded codes [m][kpad/64][80]: 64 codes + 16 bytes of padding (pair mode)
   const __half2* ds;        // [m][kpad/32] {d, raw block sum}
   const float* zr;          // [m][kpad/32 * zpb] token-major min-term table (zmode 2, 3) or nullptr
   int zmode;                // min term: 0 none, 1 raw block sum from ds, 2 zr[b], 3 zr[2b], zr[2b+1]
@@ -489,7 +490,17 @@ struct RowParams {
 constexpr int ROW_WARPS = 16;
 constexpr int ROW_THREADS = (ROW_WARPS + 1) * 32;
 
-template <int QT, int MT, typename OutT>
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {   // unsigned bytes x signed bytes
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
+// PAIR (Q4_K): a warp takes two rows at a time; lane = (row of the pair, super-block offset 0..3, quarter il 0..3)
+// and handles one 32-byte run of nibbles = the two 32-weight sub-blocks 2il (low nibbles) and 2il+1 (high
+// nibbles) of its super-block with 16-byte shared-memory loads.  The activation codes come from the padded
+// layout (80 bytes per 64 codes) so that the eight lanes of a load phase hit eight different bank groups.
+template <int QT, int MT, bool PAIR, typename OutT>
 __global__ void __launch_bounds__(ROW_THREADS, 1) gemv_rows_kernel(const RowParams p) {
   using F = Fmt<QT>;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -510,7 +521,7 @@ __global__ void __launch_bounds__(ROW_THREADS, 1) gemv_rows_kernel(const RowPara
   const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + MAX_STAGES), bar_act = smem_u32(bars + 2 * MAX_STAGES);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < S; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, R); }
+    for (int s = 0; s < S; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, PAIR ? R / 2 : R); }
     mbar_init(bar_act, 1);
     *s_abort = 0;
     *s_issued = 0;
@@ -527,10 +538,14 @@ __global__ void __launch_bounds__(ROW_THREADS, 1) gemv_rows_kernel(const RowPara
     if (lane == 0) {
       const int ntok = p.mcount < MT ? p.mcount : MT;
       const uint32_t dsb = (uint32_t)p.nb32tot * 4u, zb = (uint32_t)p.nb32tot * p.zpb * 4u;   // multiples of 64 bytes
-      uint32_t total = (uint32_t)ntok * ((uint32_t)p.klen + dsb + (p.zr != nullptr ? zb : 0u));
+      const uint32_t alen = PAIR ? (uint32_t)(p.klen / 64) * 80u : (uint32_t)p.klen;
+      uint32_t total = (uint32_t)ntok * (alen + dsb + (p.zr != nullptr ? zb : 0u));
       mbar_expect_tx(bar_act, total);
       for (int t = 0; t < ntok; ++t) {
-        bulk_g2s(smem_u32(sA + t * p.a_stride), p.qs + (size_t)(p.m0 + t) * p.kpad, (uint32_t)p.klen, bar_act);
+        if constexpr (PAIR)
+          bulk_g2s(smem_u32(sA + t * p.a_stride), p.qsp + (size_t)(p.m0 + t) * (p.kpad / 64) * 80, alen, bar_act);
+        else
+          bulk_g2s(smem_u32(sA + t * p.a_stride), p.qs + (size_t)(p.m0 + t) * p.kpad, alen, bar_act);
         bulk_g2s(smem_u32(sDS + (size_t)t * p.nb32tot), p.ds + (size_t)(p.m0 + t) * p.nb32tot, dsb, bar_act);
         if (p.zr != nullptr)
           bulk_g2s(smem_u32(sZ + (size_t)t * p.nb32tot * p.zpb), p.zr + (size_t)(p.m0 + t) * p.nb32tot * p.zpb, zb, bar_act);
@@ -564,6 +579,83 @@ __global__ void __launch_bounds__(ROW_THREADS, 1) gemv_rows_kernel(const RowPara
   OutT* y = reinterpret_cast<OutT*>(p.y);
   constexpr int NG = 32 / F::GROUP;
   const int zmode = p.zmode;
+  if constexpr (PAIR) {
+    static_assert(!PAIR || QT == KQ_TYPE_Q4_K, "pair mode is written for Q4_K");
+    const int npairs = (r1 - r0 + 1) / 2;
+    const int ri = lane >> 4, sbo = (lane >> 2) & 3, il = lane & 3;
+    const int nsb8 = p.nsb >> 3;
+    for (int j = warp; j < npairs; j += ROW_WARPS) {
+      const int i = 2 * j;
+      const int q = i / R, slot = q % S;
+      if (*s_issued <= q) {
+        const long long t0 = clock64();
+        while (*s_issued <= q) {
+          if (*s_abort || clock64() - t0 > WAIT_LIMIT) { *s_abort = 1; if (lane == 0) atomicExch(p.status, 4); return; }
+        }
+      }
+      if (!mbar_wait(bar_full + 8 * slot, (uint32_t)((q / S) & 1), s_abort)) { if (lane == 0) atomicExch(p.status, 3); return; }
+      const int row = r0 + i + ri;
+      const bool valid_row = row < r1;
+      const uint32_t off = (uint32_t)((uintptr_t)(p.W + (size_t)(r0 + q * R) * p.rowbytes) & 15);
+      const uint8_t* prow = ring + (size_t)slot * p.stage_bytes + off + (size_t)(i - q * R + ri) * p.rowbytes;
+      float acc[MT];
+#pragma unroll
+      for (int t = 0; t < MT; ++t) acc[t] = 0.f;
+      if (valid_row) {
+        for (int s = sbo; s < nsb8; s += 4) {
+          const uint8_t* bp = prow + (size_t)s * 144;
+          const uint4 hdr = *reinterpret_cast<const uint4*>(bp);
+          const uint32_t scw = il < 2 ? (hdr.y & 0x3F3F3F3Fu) : ((hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u));
+          const uint32_t mnw = il < 2 ? (hdr.z & 0x3F3F3F3Fu) : (((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u));
+          const int sh = 16 * (il & 1);
+          const float2 dm = __half22float2(*reinterpret_cast<const __half2*>(&hdr.x));
+          const float dl = dm.x * (float)((scw >> sh) & 0xFFu);
+          const float dh = dm.x * (float)((scw >> (sh + 8)) & 0xFFu) * 0.0625f;   // high nibbles are used as 16*q
+          const float ml = dm.y * (float)((mnw >> sh) & 0xFFu);
+          const float mh = dm.y * (float)((mnw >> (sh + 8)) & 0xFFu);
+          const uint4 w0 = *reinterpret_cast<const uint4*>(bp + 16 + 32 * il);
+          const uint4 w1 = *reinterpret_cast<const uint4*>(bp + 32 + 32 * il);
+          const uint32_t wq[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+          uint32_t lo[8], hi[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) { lo[k] = wq[k] & 0x0F0F0F0Fu; hi[k] = wq[k] & 0xF0F0F0F0u; }
+          const int b = s * 8 + 2 * il;
+#pragma unroll
+          for (int t = 0; t < MT; ++t) {
+            const uint4* ap = reinterpret_cast<const uint4*>(sA + (size_t)t * p.a_stride + (size_t)(s * 4 + il) * 80);
+            const uint4 a0 = ap[0], a1 = ap[1], a2 = ap[2], a3 = ap[3];
+            const uint32_t al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const uint32_t ah[8] = {a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
+            int Il = 0, Ih = 0;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) { Il = __dp4a((int)lo[k], (int)al[k], Il); Ih = dp4a_us(hi[k], ah[k], Ih); }
+            const uint2 dsw = *reinterpret_cast<const uint2*>(sDS + (size_t)t * p.nb32tot + b);
+            const float2 dsl = __half22float2(*reinterpret_cast<const __half2*>(&dsw.x));
+            const float2 dsh = __half22float2(*reinterpret_cast<const __half2*>(&dsw.y));
+            float zl = dsl.y, zh = dsh.y;
+            if (zmode != 1) {
+              const float2 z = *reinterpret_cast<const float2*>(sZ + (size_t)t * p.nb32tot + b);
+              zl = z.x; zh = z.y;
+            }
+            acc[t] += dl * (dsl.x * (float)Il) + dh * (dsh.x * (float)Ih) - (ml * zl + mh * zh);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_empty + 8 * slot);
+#pragma unroll
+      for (int t = 0; t < MT; ++t) {
+#pragma unroll
+        for (int mask = 8; mask > 0; mask >>= 1) acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], mask);
+      }
+      float mine = 0.f;
+#pragma unroll
+      for (int t = 0; t < MT; ++t) if ((lane & 15) == t) mine = acc[t];
+      if (valid_row && (lane & 15) < MT && (lane & 15) < p.mcount)
+        y[(size_t)(p.m0 + (lane & 15)) * p.stride_y + row] = from_f32<OutT>(mine);
+    }
+    return;
+  }
   for (int i = warp; r0 + i < r1; i += ROW_WARPS) {
     const int row = r0 + i;
     const int q = i / R, slot = q % S;
@@ -692,7 +784,7 @@ bool make_config(int type, int64_t n, int64_t k, int mtok, Config& c) {
 }
 
 // row-streaming kernel: whole rows per stage, the full K of `mt` tokens resident in shared memory
-bool make_row_config(int type, int64_t n, int64_t k, int mt, RowConfig& c) {
+bool make_row_config(int type, int64_t n, int64_t k, int mt, bool pair, RowConfig& c) {
   int blk, bytes;
   if (!type_geometry(type, &blk, &bytes)) return false;
   const int64_t rowbytes = k / blk * bytes;
@@ -700,11 +792,12 @@ bool make_row_config(int type, int64_t n, int64_t k, int mt, RowConfig& c) {
   int R = (int)(16384 / rowbytes);
   if (R < 1) R = 1;
   if (R > 16) R = 16;
+  if (pair) R = R < 2 ? 2 : (R & ~1);   // a warp's two rows never straddle stages
   c.rows_per_stage = R;
   c.stage_bytes = (int)((R * rowbytes + 32 + 127) / 128 * 128);
   const int64_t kpad = (k + 511) / 512 * 512;
   const bool zr = type == KQ_TYPE_Q2_K || type == KQ_TYPE_Q4_K;   // types whose min term may need the zr table
-  c.a_stride = (int)k + 32;
+  c.a_stride = pair ? (int)(k / 64) * 80 + 16 : (int)k + 32;
   c.a_bytes = (mt * c.a_stride + 127) / 128 * 128;
   c.d_bytes = (int)((mt * (kpad / 32) * 4 + 127) / 128 * 128);
   c.z_bytes = zr ? (int)((mt * (kpad / 32) * 4 * zpb + 127) / 128 * 128) : 0;
@@ -733,9 +826,9 @@ int launch_tc(const MmaParams& p, const Config& c, cudaStream_t st) {
   return KQ_OK;
 }
 
-template <int QT, int MT, typename OutT>
+template <int QT, int MT, bool PAIR, typename OutT>
 int launch_rows(const RowParams& p, const RowConfig& c, cudaStream_t st) {
-  auto kern = gemv_rows_kernel<QT, MT, OutT>;
+  auto kern = gemv_rows_kernel<QT, MT, PAIR, OutT>;
   static bool attr_set = false;
   if (!attr_set) {
     KQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT));
@@ -759,11 +852,21 @@ int launch_tc_nt(const MmaParams& p, const Config& c, int nt, cudaStream_t st) {
 
 template <int QT, typename OutT>
 int launch_rows_mt(const RowParams& p, const RowConfig& c, int mt, cudaStream_t st) {
+  if constexpr (QT == KQ_TYPE_Q4_K) {
+    if (p.qsp != nullptr) {
+      switch (mt) {
+        case 1: return launch_rows<QT, 1, true, OutT>(p, c, st);
+        case 2: return launch_rows<QT, 2, true, OutT>(p, c, st);
+        case 4: return launch_rows<QT, 4, true, OutT>(p, c, st);
+        default: return launch_rows<QT, 8, true, OutT>(p, c, st);
+      }
+    }
+  }
   switch (mt) {
-    case 1: return launch_rows<QT, 1, OutT>(p, c, st);
-    case 2: return launch_rows<QT, 2, OutT>(p, c, st);
-    case 4: return launch_rows<QT, 4, OutT>(p, c, st);
-    default: return launch_rows<QT, 8, OutT>(p, c, st);
+    case 1: return launch_rows<QT, 1, false, OutT>(p, c, st);
+    case 2: return launch_rows<QT, 2, false, OutT>(p, c, st);
+    case 4: return launch_rows<QT, 4, false, OutT>(p, c, st);
+    default: return launch_rows<QT, 8, false, OutT>(p, c, st);
   }
 }
 
@@ -786,7 +889,7 @@ int launch_typed(const MmaParams* pt, const Config* ct, const RowParams* pr, con
 bool gemv_mma_supported(const void* W, int type, int64_t n, int64_t k) {
   if ((uintptr_t)W % 16) return false;
   RowConfig c;
-  return make_row_config(type, n, k, 1, c);
+  return make_row_config(type, n, k, 1, false, c);
 }
 
 // impl: 0 = choose by m, 2 = tensor cores wherever the type has them, 3 = row-streaming dp4a
@@ -808,7 +911,7 @@ int launch_gemv_mma(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs&
     const bool tile_start = (m0 % 16) == 0;
     int rc, mcount;
     Config c;
-    if (has_tc && tile_start && impl != 3 && (impl == 2 || left >= options().tc_min_m) &&
+    if (has_tc && tile_start && impl != 3 && impl != 4 && (impl == 2 || left >= options().tc_min_m) &&
         make_config(type, n, k, left > 8 ? 16 : 8, c)) {
       mcount = (int)(left < 16 ? left : 16);
       const int nt = mcount > 8 ? 2 : 1;
@@ -827,14 +930,15 @@ int launch_gemv_mma(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs&
       const int cap = (int)(left < room ? left : room);
       int mt = cap >= 8 ? 8 : (cap >= 4 ? 4 : (cap >= 2 ? 2 : 1));
       RowConfig rcg;
-      while (mt > 1 && !make_row_config(type, n, k, mt, rcg)) mt >>= 1;   // fewer tokens per pass if K is long
-      if (!make_row_config(type, n, k, mt, rcg)) { set_error("row-streaming GEMV: no configuration for this shape"); return KQ_EUNSUPPORTED; }
+      const bool pair = type == KQ_TYPE_Q4_K && impl != 4 && (k % 256) == 0;
+      while (mt > 1 && !make_row_config(type, n, k, mt, pair, rcg)) mt >>= 1;   // fewer tokens per pass if K is long
+      if (!make_row_config(type, n, k, mt, pair, rcg)) { set_error("row-streaming GEMV: no configuration for this shape"); return KQ_EUNSUPPORTED; }
       mcount = mt;
       RowParams p;
       p.W = (const uint8_t*)W; p.rowbytes = k / blk * bytes; p.n = (int)n; p.nsb = (int)(k / 32);
       p.rows_per_stage = rcg.rows_per_stage; p.stages = rcg.stages; p.stage_bytes = rcg.stage_bytes;
       p.a_stride = rcg.a_stride; p.a_bytes = rcg.a_bytes; p.d_bytes = rcg.d_bytes; p.z_bytes = rcg.z_bytes;
-      p.qs = P.qs; p.ds = P.ds; p.zpb = zpb; p.kpad = (int)P.kpad; p.nb32tot = (int)(P.kpad / 32); p.klen = (int)k;
+      p.qs = P.qs; p.qsp = pair ? P.qsp : nullptr; p.ds = P.ds; p.zpb = zpb; p.kpad = (int)P.kpad; p.nb32tot = (int)(P.kpad / 32); p.klen = (int)k;
       p.zr = nullptr; p.zmode = 0;
       if (type == KQ_TYPE_Q4_0 || (type == KQ_TYPE_Q4_K && mmq)) p.zmode = 1;
       else if (type == KQ_TYPE_Q4_K) { p.zmode = 2; p.zr = P.z32r; }

@@ -46,6 +46,12 @@ __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const T* __restrict_
   const float d = __fdiv_rn(amax, 127.0f);
   const int8_t q = amax == 0.0f ? (int8_t)0 : (int8_t)roundf(__fdiv_rn(xi, d));
   if (P.qs) P.qs[row * kpad + col] = q;
+  if (P.xh) P.xh[row * kpad + col] = __float2half_rn(__half2float(__float2half_rn(d)) * (float)q);
+  if (P.qsp) {
+    int8_t* pp = P.qsp + (row * (kpad >> 6) + (col >> 6)) * 80;
+    pp[col & 63] = q;
+    if ((col & 63) < 16) pp[64 + (col & 63)] = 0;   // keep the padding defined
+  }
   if (wire36) wire36[(row * nb + b) * 36 + 4 + lane] = (uint8_t)q;
   const __half dh = __float2half_rn(d), sh = __float2half_rn(sum);
   if (P.dT != nullptr) {
@@ -69,6 +75,7 @@ __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const T* __restrict_
   if (lane == 0) {
     const __half2 v = __halves2half2(dh, sh);
     if (P.ds) P.ds[row * nb + b] = v;
+    if (P.xh) P.s8h[row * nb + b] = sh;
     if (wire36) *reinterpret_cast<__half2*>(wire36 + (row * nb + b) * 36) = v;
   }
 }
@@ -76,7 +83,7 @@ __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const T* __restrict_
 int launch_quantize(const void* x, int x_dtype, int64_t m, int64_t k, int64_t stride_x, const Q8Ptrs* Pp,
                     void* wire36, int64_t kpad, cudaStream_t st) {
   Q8Ptrs P;
-  if (Pp) P = *Pp; else { P = Q8Ptrs(); P.ds = nullptr; P.qs = nullptr; P.dT = P.z32 = P.zs8 = P.z16 = P.z32r = P.z16r = P.part = nullptr; P.cnt = P.status = nullptr; P.kpad = kpad; P.ncnt = 0; }
+  if (Pp) P = *Pp; else { P = Q8Ptrs(); P.ds = nullptr; P.qs = nullptr; P.qsp = nullptr; P.xh = nullptr; P.s8h = nullptr; P.dT = P.z32 = P.zs8 = P.z16 = P.z32r = P.z16r = P.part = nullptr; P.cnt = P.status = nullptr; P.kpad = kpad; P.ncnt = 0; }
   const int64_t mpad = Pp ? (m + 15) / 16 * 16 : m;
   const int64_t nblk = mpad * (kpad / 32);
   if (nblk == 0) return KQ_OK;

@@ -1,0 +1,91 @@
+"""GPU tests of the tcgen05 prefill GEMM (M >= 33 tokens) through the C ABI.
+
+The GEMM multiplies fp16-dequantized weights (bit-identical to ggml_dequantize) with fp16(d8*q8) activations and
+accumulates in fp32, so two checks apply: (1) against the dense product of exactly those fp16 operands it must agree
+to fp32 accumulation error - this pins tile layout, swizzle, descriptors and the K pipeline; (2) against the
+q8_1-semantics oracle (what the reference's MMQ kernels compute) it must stay inside the 1e-3 gate."""
+import numpy as np
+import pytest
+import torch
+
+from kaillm_b200 import capi
+from oracle import gguf_oracle as O
+from tests.gpu_util import act, dev, rel_l2, to_np, wire
+
+pytestmark = pytest.mark.gpu
+GATE = 1e-3
+
+
+def fp16_operand_product(w, qt, x, mmq):
+    """float64 product of the operands the GEMM feeds its tensor cores (incl. the raw-sum correction steps)."""
+    a = O.quantize_q8_1(x)
+    k = x.shape[1]
+    d = np.repeat(a["d"][:, : k // 32].astype(np.float32), 32, axis=1)
+    xh = (d * a["q"][:, :k].astype(np.float32)).astype(np.float16).astype(np.float64)
+    s8 = a["s"][:, : k // 32].astype(np.float64)
+    if qt == O.Q4_0:
+        u = O.unpack(w, qt)
+        wh = O.hmul(O.f2h(u["q"]), np.repeat(u["d"], 32, axis=1)).astype(np.float64)      # d*q without the -8
+        c = O.hmul(np.float16(-8.0), u["d"]).astype(np.float64)
+        return xh @ wh.T + s8 @ c.T
+    if qt == O.Q4_K and mmq:
+        u = O.unpack(w, qt)
+        d1 = O.hmul(np.repeat(u["d"], 8, axis=1), O.f2h(u["sc"]))                           # [n, k/32]
+        wh = O.hmul(np.repeat(d1, 32, axis=1), O.f2h(u["q"])).astype(np.float64)
+        c = -O.hmul(np.repeat(u["dmin"], 8, axis=1), O.f2h(u["mn"])).astype(np.float64)
+        return xh @ wh.T + s8 @ c.T
+    wh = O.dequantize(w, qt, "f16", half_fma=capi.get_option("half_fma")).astype(np.float64)
+    return xh @ wh.T
+
+
+@pytest.mark.parametrize("qt", O.QTYPES)
+@pytest.mark.parametrize("n,k,m", [(128, 256, 128), (256, 1024, 64), (200, 512, 33), (384, 2048, 300), (130, 768, 129)])
+def test_gemm_matches_fp16_operand_product_and_oracle(qt, n, k, m):
+    w, wt = wire(qt, n, k, seed=qt + n)
+    x, xt = act(m, k, seed=k + m, dt="bf16")
+    ws = capi.workspace_bytes(qt, m, n, k)
+    scratch = torch.empty(ws, dtype=torch.uint8, device=dev())
+    mmq = qt != 21
+    y = to_np(capi.mul_mat(wt, xt, qt, mmq=mmq, out_dtype=torch.float32, scratch=scratch))
+    assert capi.read_status(qt, m, n, k, scratch) == 0
+    assert rel_l2(y, fp16_operand_product(w, qt, x, mmq)) < 5e-6
+    assert rel_l2(y, O.mul_mat(w, qt, x, "mmq" if mmq else "mmvq")) < GATE
+
+
+def test_gemm_q4k_vec_flavour_folds_the_min_term():
+    qt, n, k, m = 12, 256, 1024, 96
+    w, wt = wire(qt, n, k, seed=2)
+    x, xt = act(m, k, seed=2, dt="bf16")
+    y = to_np(capi.mul_mat(wt, xt, qt, mmq=False, out_dtype=torch.float32))
+    assert rel_l2(y, fp16_operand_product(w, qt, x, False)) < 5e-6
+    assert rel_l2(y, O.mul_mat(w, qt, x, "mmvq")) < GATE
+
+
+@pytest.mark.parametrize("m", [256, 1024, 2048])
+def test_config4_q4k_prefill(m):
+    """BASELINE config 4: Q4_K N=17408 K=5120, bf16 activations; oracle on the first and last 64 rows."""
+    qt, n, k = 12, 17408, 5120
+    _, wt = wire(qt, n, k, seed=4)
+    x, xt = act(m, k, seed=m, dt="bf16")
+    w = wt.cpu().numpy()
+    y = capi.mul_mat(wt, xt, qt, mmq=True)
+    assert y.dtype == torch.bfloat16 and bool(torch.isfinite(y).all())
+    rows = np.r_[0:64, n - 64:n]
+    got = to_np(y)[:, rows]
+    want = O.mul_mat(w[rows], qt, x, "mmq")
+    assert rel_l2(got, O.round_to_dtype(want, "bf16")) < 3e-3      # includes the bf16 rounding of the outputs
+    y32 = to_np(capi.mul_mat(wt, xt, qt, mmq=True, out_dtype=torch.float32))[:, rows]
+    assert rel_l2(y32, want) < GATE
+
+
+def test_gemm_and_gemv_paths_agree():
+    qt, n, k, m = 14, 512, 2048, 64
+    _, wt = wire(qt, n, k, seed=9)
+    _, xt = act(m, k, seed=9, dt="f16")
+    y_gemm = capi.mul_mat(wt, xt, qt, mmq=True, out_dtype=torch.float32)
+    capi.set_option("gemm_min_m", 1 << 30)
+    try:
+        y_gemv = capi.mul_mat(wt, xt, qt, mmq=True, out_dtype=torch.float32)
+    finally:
+        capi.set_option("gemm_min_m", 33)
+    assert rel_l2(to_np(y_gemm), to_np(y_gemv)) < GATE
