@@ -71,7 +71,8 @@ int kq_quantize_q8_1(const void* x, int x_dtype, int64_t m, int64_t k, int64_t s
 
 /* y[m, n] = q8_1(x)[m, k] . W[n, k]^T with the arithmetic of the reference's MMVQ kernels.
  * y has row stride `stride_y` elements and dtype y_dtype (the reference uses x's dtype).
- * Any m >= 1 is accepted; the kernel variant is chosen inside by m.
+ * Any m >= 1 is accepted; the kernel is chosen inside by m: integer-dot GEMV kernels for m <= 80 (exact
+ * integer block dots), the tcgen05 fp16 GEMM above (outputs within rel-L2 1e-3 of the integer arithmetic).
  * Replaces ggml_mul_mat_vec_a8, vllm_gguf_plugin/csrc/gguf/gguf_kernel.cu:104-218
  * (kernels: csrc/gguf/mmvq.cuh:2-41, csrc/gguf/vecdotq.cuh). */
 int kq_mul_mat_vec_a8(const void* W, int type, int64_t n, int64_t k,
@@ -126,7 +127,10 @@ int kq_debug_group_dots(const void* W, int type, int64_t n, int64_t k,
 int kq_read_status(int type, int64_t m, int64_t n, int64_t k, const void* scratch, size_t scratch_bytes, int* status);
 
 /* Runtime knobs for tests and profiling (process-wide, not thread-safe against concurrent launches):
- *   "gemv_impl"   0 = choose by shape (default), 1 = force the dp4a kernel, 2 = force the tensor-core kernel
+ *   "gemv_impl"   0 = choose by shape (default), 1 = general dp4a kernel, 2 = streaming int8-mma kernel,
+ *                 3 = row-streaming dp4a kernel, 4 = the same without the Q4_K specialisation
+ *   "tc_min_m"    smallest m that the int8-mma kernel takes in mode 0 (default 8)
+ *   "gemm_min_m"  smallest m that goes to the tcgen05 GEMM (default 81: m <= 80 keeps exact integer dots)
  *   "half_fma"    1 = K-quant dequantize contracts fp16 mul+sub into one fma (default), 0 = two roundings
  * Returns KQ_EINVAL for an unknown name. */
 int kq_set_option(const char* name, int value);

@@ -11,18 +11,18 @@
 //   For those cases w^ is formed without the offset/min and extra K steps multiply the per-block coefficient
 //   c[row, b] (-8*d, or -dmin*m) with s8[tok, b] into the same accumulator.
 //
-//   CTA tile  128 weight rows (UMMA M, one TMEM lane per row) x BN = 128 tokens (UMMA N)
-//   warps 0-3 thread = weight row: reads its row's wire blocks straight from global/L2, dequantizes 64 weights at a
-//             time to packed fp16 registers and writes them to TMEM with tcgen05.st - the A operand never touches
-//             shared memory.  After the K loop the same threads read the accumulators back (tcgen05.ld) and
-//             store y (lanes = consecutive rows: coalesced).
-//   warp 4    one lane fetches the x^ tile [BN x 256] of each K step with four TMA tiled loads (128-byte swizzle)
-//   warp 5    one lane issues the MMAs: per K step (one 256-weight super-block) 16 x tcgen05.mma.kind::f16
-//             (128 x BN x 16), A from TMEM, B through a shared-memory descriptor; tcgen05.commit signals
-//             "buffers free" and, at the end, "accumulator complete".
-//   Two A buffers in TMEM (2 x 128 columns) and two B stages in shared memory (2 x 64 KB) overlap dequantization,
-//   loads and MMAs.  Every mbarrier wait is bounded; on give-up a status word is set, TMEM is released and the
-//   CTA returns.
+//   CTA tile  128 weight rows (UMMA M, one TMEM lane per row) x BN = 256 tokens (UMMA N); K step = 128
+//   warps 0-7 thread = (weight row, one of the step's two 64-weight atoms): reads its wire bytes straight from
+//             global/L2 (prefetched one step ahead), dequantizes 64 weights to packed fp16 registers and writes them
+//             to TMEM with tcgen05.st - the A operand never touches shared memory.  After the K loop the same
+//             threads read the accumulators back (tcgen05.ld) and store y (lanes = consecutive rows: coalesced).
+//   warp 8    one lane fetches the x^ tile [BN x 128] of each K step with two TMA tiled loads (128-byte swizzle)
+//   warp 9    one lane issues the MMAs: per K step 8 x tcgen05.mma.kind::f16 (128 x 256 x 16), A from TMEM, B
+//             through a shared-memory descriptor; tcgen05.commit signals "buffers free" and, at the end,
+//             "accumulator complete".
+//   A ring of 4 steps in TMEM (256 columns, beside the 256 accumulator columns) and a B ring of 3 steps in shared
+//   memory (192 KB) overlap dequantization, loads and MMAs.  Every mbarrier wait is bounded; on give-up a status
+//   word is set, TMEM is released and the CTA returns.
 #include <cuda.h>
 
 #include "kq_common.cuh"
@@ -31,14 +31,16 @@ namespace kq {
 namespace {
 
 constexpr int BM = 128;         // weight rows per CTA = UMMA M
-constexpr int BN = 128;         // tokens per CTA = UMMA N
-constexpr int KSTEP = 256;      // k per pipeline step
+constexpr int BN = 256;         // tokens per CTA = UMMA N
+constexpr int KSTEP = 128;      // k per pipeline step (two swizzle atoms)
 constexpr int ATOM = 64;        // k per 128-byte swizzle atom (fp16)
-constexpr int NBUF = 2;
-constexpr int GEMM_THREADS = 192;
+constexpr int NA = 4;           // A ring (TMEM): 4 x 64 columns
+constexpr int NB = 3;           // B ring (shared memory): 3 x 64 KB
+constexpr int DQ_WARPS = 8;     // dequantizing warps: warp w and w+4 share TMEM lanes 32*(w%4).., one atom each
+constexpr int GEMM_THREADS = (DQ_WARPS + 2) * 32;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t TMEM_D = 0;                 // accumulator: columns [0, BN)
-constexpr uint32_t TMEM_A = 256;               // A buffers: 2 x 128 columns (256 k of fp16 pairs each)
+constexpr uint32_t TMEM_A = 256;               // A ring
 constexpr int B_STAGE_BYTES = BN * KSTEP * 2;  // 64 KB
 constexpr long long GEMM_WAIT_LIMIT = 1ll << 28;
 
@@ -254,13 +256,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap smap) {
   using F = Fmt<QT>;
   extern __shared__ __align__(1024) uint8_t smem[];
-  uint8_t* sB = smem;                                            // NBUF x 64 KB, each atom [BN rows x 128 B] swizzled
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + NBUF * B_STAGE_BYTES);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
-  volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 17);
+  uint8_t* sB = smem;                                            // NB x 64 KB; each atom [BN rows x 128 B] swizzled
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + NB * B_STAGE_BYTES);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 24);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 25);
   uint32_t* s_grid = reinterpret_cast<uint32_t*>(bars + 32);     // IQ3_S codebook (2 KB)
-  const uint32_t bar_bfull = smem_u32(bars), bar_afull = smem_u32(bars + 2), bar_empty = smem_u32(bars + 4),
-                 bar_dfull = smem_u32(bars + 6);
+  const uint32_t bar_bfull = smem_u32(bars), bar_bempty = smem_u32(bars + 4), bar_afull = smem_u32(bars + 8),
+                 bar_aempty = smem_u32(bars + 12), bar_dfull = smem_u32(bars + 16);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int row_tile = blockIdx.x / p.ntok_tiles, tok_tile = blockIdx.x % p.ntok_tiles;
@@ -268,11 +270,8 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
   const int nsteps = nmain + (CORR ? p.ncorr : 0);
 
   if (tid == 0) {
-    for (int i = 0; i < NBUF; ++i) {
-      mbar_init(bar_bfull + 8 * i, 1);
-      mbar_init(bar_afull + 8 * i, 4);     // one arrival per producer warp
-      mbar_init(bar_empty + 8 * i, 1);     // tcgen05.commit
-    }
+    for (int i = 0; i < NB; ++i) { mbar_init(bar_bfull + 8 * i, 1); mbar_init(bar_bempty + 8 * i, 1); }
+    for (int i = 0; i < NA; ++i) { mbar_init(bar_afull + 8 * i, DQ_WARPS); mbar_init(bar_aempty + 8 * i, 1); }
     mbar_init(bar_dfull, 1);
     *s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -290,12 +289,12 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tbase = *tmem_slot;
 
-  if (warp == 4) {
+  if (warp == DQ_WARPS) {
     // -------------------------------------------------------------------------- activation loader (TMA)
     if (lane == 0) {
       for (int s = 0; s < nsteps; ++s) {
-        const int buf = s & 1;
-        if (s >= NBUF && !mbar_wait(bar_empty + 8 * buf, (uint32_t)(((s >> 1) - 1) & 1), s_abort)) break;
+        const int buf = s % NB, fill = s / NB;
+        if (fill > 0 && !mbar_wait(bar_bempty + 8 * buf, (uint32_t)((fill - 1) & 1), s_abort)) break;
         mbar_expect_tx(bar_bfull + 8 * buf, B_STAGE_BYTES);
 #pragma unroll
         for (int a = 0; a < KSTEP / ATOM; ++a) {
@@ -305,27 +304,27 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == DQ_WARPS + 1) {
     // -------------------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       // instruction descriptor: D = f32, A = B = f16, both K-major, N >> 3 at bit 17, M >> 4 at bit 24
       const uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
       bool ok = true;
       for (int s = 0; s < nsteps && ok; ++s) {
-        const int buf = s & 1;
-        const uint32_t par = (uint32_t)((s >> 1) & 1);
-        ok = mbar_wait(bar_bfull + 8 * buf, par, s_abort) && mbar_wait(bar_afull + 8 * buf, par, s_abort);
+        const int ab = s % NA, bb = s % NB;
+        ok = mbar_wait(bar_bfull + 8 * bb, (uint32_t)((s / NB) & 1), s_abort) &&
+             mbar_wait(bar_afull + 8 * ab, (uint32_t)((s / NA) & 1), s_abort);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
         for (int a = 0; a < KSTEP / ATOM; ++a) {
           // shared-memory descriptor: addr >> 4, LBO (unused with swizzle), SBO = 1024 B, version 1, 128-byte swizzle
-          const uint32_t baddr = smem_u32(sB + buf * B_STAGE_BYTES + a * (BN * 128));
+          const uint32_t baddr = smem_u32(sB + bb * B_STAGE_BYTES + a * (BN * 128));
           const uint64_t bdesc = (uint64_t)((baddr & 0x3FFFF) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) |
                                  (1ull << 46) | (2ull << 61);
 #pragma unroll
           for (int kk = 0; kk < ATOM / 16; ++kk) {
-            const uint32_t ta = tbase + TMEM_A + buf * 128 + a * 32 + kk * 8;
+            const uint32_t ta = tbase + TMEM_A + ab * 64 + a * 32 + kk * 8;
             const uint32_t accum = (s > 0 || a > 0 || kk > 0) ? 1u : 0u;
             asm volatile(
                 "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
@@ -333,43 +332,51 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
                 ::"r"(tbase + TMEM_D), "r"(ta), "l"(bdesc + (uint64_t)((kk * 32) >> 4)), "r"(idesc), "r"(accum) : "memory");
           }
         }
-        // completion of everything issued so far frees this step's A buffer and B stage
-        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_empty + 8 * buf) : "memory");
+        // completion of everything issued so far frees this step's A slot and B stage
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_aempty + 8 * ab) : "memory");
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_bempty + 8 * bb) : "memory");
       }
       if (ok) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_dfull) : "memory");
     }
   } else {
-    // -------------------------------------------------------------------------- dequantizers (thread = weight row)
-    int row = row_tile * BM + tid;
+    // -------------------------------------------------------------------------- dequantizers
+    const int rloc = (warp & 3) * 32 + lane;          // row inside the tile = TMEM lane
+    const int half = warp >> 2;                       // which of the step's two atoms
+    int row = row_tile * BM + rloc;
     const bool row_ok = row < p.n;
     if (!row_ok) row = p.n - 1;                       // clamp: loads stay in bounds, the store is skipped
     const uint8_t* wrow = p.W + (size_t)row * p.rowbytes;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    constexpr int ATOMS_PER_BLK = F::BLK >= 256 ? 4 : 1;   // 32-weight formats: dequant_atom indexes blocks itself
     bool ok = true;
     for (int s = 0; s < nsteps && ok; ++s) {
-      const int buf = s & 1;
-      if (s >= NBUF) ok = mbar_wait(bar_empty + 8 * buf, (uint32_t)(((s >> 1) - 1) & 1), s_abort);
+      const int ab = s % NA, fill = s / NA;
+      // dequantize before waiting for the slot: the wire bytes do not depend on the pipeline state
+      uint32_t v[32];
+      if (s < nmain) {
+        const int ga = s * (KSTEP / ATOM) + half;     // atom index along the row
+        const uint8_t* blk = F::BLK >= 256 ? wrow + (size_t)(ga / ATOMS_PER_BLK) * F::BYTES
+                                           : wrow + (size_t)ga * 2 * F::BYTES;
+        dequant_atom<QT, CORR>(blk, F::BLK >= 256 ? (ga % ATOMS_PER_BLK) : 0, s_grid, p.half_fma, v);
+      } else {
+        corr_atom<QT>(wrow, (s - nmain) * (KSTEP / ATOM) + half, p.nb32, v);
+      }
+      if (fill > 0) ok = mbar_wait(bar_aempty + 8 * ab, (uint32_t)((fill - 1) & 1), s_abort);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint8_t* blk = wrow + (size_t)s * (KSTEP / F::BLK) * F::BYTES;
-#pragma unroll 1
-      for (int a = 0; a < KSTEP / ATOM; ++a) {
-        uint32_t v[32];
-        if (s < nmain) dequant_atom<QT, CORR>(blk, a, s_grid, p.half_fma, v);
-        else corr_atom<QT>(wrow, (s - nmain) * (KSTEP / ATOM) + a, p.nb32, v);
-        tmem_st32(tbase + TMEM_A + lane_base + buf * 128 + a * 32, v);
-      }
+      tmem_st32(tbase + TMEM_A + lane_base + ab * 64 + half * 32, v);
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_afull + 8 * buf);
+      if (lane == 0) mbar_arrive(bar_afull + 8 * ab);
     }
-    // -------------------------------------------------------------------------- epilogue
+    // -------------------------------------------------------------------------- epilogue: warp w takes columns
+    // [128*half, 128*half+128) of its 32 lanes
     if (ok && mbar_wait(bar_dfull, 0, s_abort)) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       OutT* y = reinterpret_cast<OutT*>(p.y);
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32) {
         uint32_t r[32];
         tmem_ld32(tbase + TMEM_D + lane_base + c0, r);
 #pragma unroll
@@ -406,7 +413,7 @@ EncodeTiledFn encode_fn() {
 template <int QT, bool CORR, typename OutT>
 int launch(const GemmParams& p, const CUtensorMap& map, const CUtensorMap& smap, int grid, cudaStream_t st) {
   auto kern = gemm_tc_kernel<QT, CORR, OutT>;
-  const int smem = NBUF * B_STAGE_BYTES + 4096;
+  const int smem = NB * B_STAGE_BYTES + 4096;
   static bool attr_set = false;
   if (!attr_set) {
     KQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
