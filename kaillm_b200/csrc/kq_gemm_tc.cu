@@ -153,10 +153,11 @@ __device__ __forceinline__ void corr_atom(const uint8_t* __restrict__ wrow, int 
 // CORR: leave the offset (Q4_0) / min (Q4_K) out of w^; it is applied through corr_atom steps instead
 template <int QT, bool CORR>
 __device__ __forceinline__ void dequant_atom(const uint8_t* __restrict__ blk, int atom, const uint32_t* grid, int fma,
-                                             uint32_t (&out)[32]) {
+                                             const uint4 (&pre)[3], uint32_t (&out)[32]) {
   if constexpr (QT == KQ_TYPE_Q4_K) {
-    // atom a = sub-blocks 2a (low nibbles of qs[32a..32a+31]) and 2a+1 (high nibbles); 16-byte aligned block
-    const uint4 hdr = *reinterpret_cast<const uint4*>(blk);
+    // atom a = sub-blocks 2a (low nibbles of qs[32a..32a+31]) and 2a+1 (high nibbles); 16-byte aligned block.
+    // `pre` holds the block header and the atom's 32 nibble bytes, fetched one step ahead by the caller.
+    const uint4 hdr = pre[0];
     const __half2 dm = bits_h2(hdr.x);
     const uint32_t scw = atom < 2 ? (hdr.y & 0x3F3F3F3Fu) : ((hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u));
     const uint32_t mnw = atom < 2 ? (hdr.z & 0x3F3F3F3Fu) : (((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u));
@@ -168,8 +169,8 @@ __device__ __forceinline__ void dequant_atom(const uint8_t* __restrict__ blk, in
     const __half2 d1v = __half2half2(d1), d2v = __half2half2(d2);
     const __half2 nm1 = __half2half2(__hneg(m1)), nm2 = __half2half2(__hneg(m2));
     const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
-    const uint4 w0 = *reinterpret_cast<const uint4*>(blk + 16 + 32 * atom);
-    const uint4 w1 = *reinterpret_cast<const uint4*>(blk + 32 + 32 * atom);
+    const uint4 w0 = pre[1];
+    const uint4 w1 = pre[2];
     const uint32_t wq[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -349,6 +350,19 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     constexpr int ATOMS_PER_BLK = F::BLK >= 256 ? 4 : 1;   // 32-weight formats: dequant_atom indexes blocks itself
     bool ok = true;
+    uint4 pre[3] = {};
+    auto fetch = [&](int s) {   // Q4_K: the wire bytes of step s for this thread's atom (header + 32 nibble bytes)
+      if constexpr (QT == KQ_TYPE_Q4_K) {
+        if (s < nmain) {
+          const int ga = s * (KSTEP / ATOM) + half;
+          const uint8_t* blk = wrow + (size_t)(ga >> 2) * 144;
+          pre[0] = __ldg(reinterpret_cast<const uint4*>(blk));
+          pre[1] = __ldg(reinterpret_cast<const uint4*>(blk + 16 + 32 * (ga & 3)));
+          pre[2] = __ldg(reinterpret_cast<const uint4*>(blk + 32 + 32 * (ga & 3)));
+        }
+      }
+    };
+    fetch(0);
     for (int s = 0; s < nsteps && ok; ++s) {
       const int ab = s % NA, fill = s / NA;
       // dequantize before waiting for the slot: the wire bytes do not depend on the pipeline state
@@ -357,7 +371,9 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
         const int ga = s * (KSTEP / ATOM) + half;     // atom index along the row
         const uint8_t* blk = F::BLK >= 256 ? wrow + (size_t)(ga / ATOMS_PER_BLK) * F::BYTES
                                            : wrow + (size_t)ga * 2 * F::BYTES;
-        dequant_atom<QT, CORR>(blk, F::BLK >= 256 ? (ga % ATOMS_PER_BLK) : 0, s_grid, p.half_fma, v);
+        const uint4 cur[3] = {pre[0], pre[1], pre[2]};
+        fetch(s + 1);                                 // next step's bytes are in flight while this one is unpacked
+        dequant_atom<QT, CORR>(blk, F::BLK >= 256 ? (ga % ATOMS_PER_BLK) : 0, s_grid, p.half_fma, cur, v);
       } else {
         corr_atom<QT>(wrow, (s - nmain) * (KSTEP / ATOM) + half, p.nb32, v);
       }
