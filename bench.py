@@ -404,9 +404,15 @@ def main() -> None:
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches_step * args.steps,
             "roofline": roof, "cpu_baseline": cpu, "prefill_gemm": prefill,
         }
-        print(json.dumps(out))
+        print(json.dumps(out), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # leave without tearing the communicator down: destroy_process_group() after graph-captured collectives
+        # hung at exit on this stack; every rank is past its last collective here
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":

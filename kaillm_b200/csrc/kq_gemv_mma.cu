@@ -36,7 +36,10 @@ namespace {
 constexpr int TILE_ROWS = 16;
 // consumer warps: tensor-core mode 8 (a warp owns a tile); dp4a mode 16 (a warp owns one row of every tile)
 __host__ __device__ constexpr int consumer_warps(int mode) { return mode == 0 ? 8 : 16; }
-__host__ __device__ constexpr int cta_threads(int mode) { return (consumer_warps(mode) + 1) * 32; }
+// producer warps of the tensor-core kernel: the copy engine takes requests faster from several warps (4 lanes of
+// 4 warps: ~20 ns per request and SM; 16 lanes of one warp: ~40 ns), and a row segment is only 1-2 KB
+constexpr int NPROD = 4;
+__host__ __device__ constexpr int cta_threads(int mode) { return (consumer_warps(mode) + (mode == 0 ? NPROD : 1)) * 32; }
 constexpr uint32_t MAGIC_I = 0x4B400000u;  // bits of 12582912.0f: adding an int |v| < 2^22 gives the float 12582912+v
 constexpr float MAGIC_F = 12582912.0f;
 constexpr long long WAIT_LIMIT = 1ll << 27;   // ~70 ms at 1.9 GHz; a healthy wait lasts microseconds
@@ -294,7 +297,7 @@ __global__ void __launch_bounds__(cta_threads(MODE), 1) gemv_stream_kernel(const
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem + SMEM_HEADER - 8);
-  volatile int* s_issued = reinterpret_cast<volatile int*>(smem + SMEM_HEADER - 16);   // stages issued so far
+  volatile int* s_issued = reinterpret_cast<volatile int*>(smem + SMEM_HEADER - 32);   // stages issued, per producer warp
   uint32_t* s_grid = reinterpret_cast<uint32_t*>(smem + SMEM_HEADER);   // IQ3_S codebook (2 KB) when needed
   uint8_t* sA = smem + SMEM_HEADER + (QT == KQ_TYPE_IQ3_S ? 2048 : 0);
   float* sD = reinterpret_cast<float*>(sA + p.a_bytes);
@@ -312,10 +315,10 @@ __global__ void __launch_bounds__(cta_threads(MODE), 1) gemv_stream_kernel(const
   const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + MAX_STAGES), bar_act = smem_u32(bars + 2 * MAX_STAGES);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < S; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+    for (int s = 0; s < S; ++s) { mbar_init(bar_full + 8 * s, NPROD); mbar_init(bar_empty + 8 * s, 1); }
     mbar_init(bar_act, 1);
     *s_abort = 0;
-    *s_issued = 0;
+    for (int i = 0; i < NPROD; ++i) s_issued[i] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -324,25 +327,28 @@ __global__ void __launch_bounds__(cta_threads(MODE), 1) gemv_stream_kernel(const
   }
   __syncthreads();
 
-  if (warp == NW) {
-    // ------------------------------------------------------------------ producer
+  if (warp >= NW) {
+    // ------------------------------------------------------------------ producers: warp pw fetches rows 4pw..4pw+3
+    const int pw = warp - NW;
     const int k0 = blk0 * F::BLK, klen = (blk1 - blk0) * F::BLK;
     const int b32_0 = k0 >> 5, nb32 = klen >> 5;
     const int tt = p.m0 >> 4;
     constexpr int TOKCAP = 8 * NT;
     const int ntok = p.mcount < TOKCAP ? p.mcount : TOKCAP;
     const int mrow0 = p.m0;
-    if (lane == 0) {
-      uint32_t total = (uint32_t)ntok * klen + (uint32_t)nb32 * 64u;
-      if (p.zT != nullptr) total += (uint32_t)nb32 * p.zpb * 64u;
-      mbar_expect_tx(bar_act, total);
+    if (pw == 0) {
+      if (lane == 0) {
+        uint32_t total = (uint32_t)ntok * klen + (uint32_t)nb32 * 64u;
+        if (p.zT != nullptr) total += (uint32_t)nb32 * p.zpb * 64u;
+        mbar_expect_tx(bar_act, total);
+      }
+      __syncwarp();
+      if (lane < ntok)
+        bulk_g2s(smem_u32(sA + lane * p.a_stride), p.qs + (size_t)(mrow0 + lane) * p.kpad + k0, (uint32_t)klen, bar_act);
+      if (lane == 16) bulk_g2s(smem_u32(sD), p.dT + ((size_t)tt * p.nb32tot + b32_0) * 16, (uint32_t)nb32 * 64u, bar_act);
+      if (lane == 17 && p.zT != nullptr)
+        bulk_g2s(smem_u32(sZ), p.zT + ((size_t)tt * p.nb32tot + b32_0) * p.zpb * 16, (uint32_t)nb32 * p.zpb * 64u, bar_act);
     }
-    __syncwarp();
-    if (lane < ntok)
-      bulk_g2s(smem_u32(sA + lane * p.a_stride), p.qs + (size_t)(mrow0 + lane) * p.kpad + k0, (uint32_t)klen, bar_act);
-    if (lane == 16) bulk_g2s(smem_u32(sD), p.dT + ((size_t)tt * p.nb32tot + b32_0) * 16, (uint32_t)nb32 * 64u, bar_act);
-    if (lane == 17 && p.zT != nullptr)
-      bulk_g2s(smem_u32(sZ), p.zT + ((size_t)tt * p.nb32tot + b32_0) * p.zpb * 16, (uint32_t)nb32 * p.zpb * 64u, bar_act);
 
     int q = 0;
     bool ok = true;
@@ -356,8 +362,9 @@ __global__ void __launch_bounds__(cta_threads(MODE), 1) gemv_stream_kernel(const
         const int nb_c = (blk1 - blk_a) < p.cb ? (blk1 - blk_a) : p.cb;
         uint32_t bytes = 0;
         uintptr_t a0 = 0;
-        const int row = row0 + lane;
-        if (lane < TILE_ROWS && row < p.n) {
+        const int rloc = pw * (TILE_ROWS / NPROD) + lane;
+        const int row = row0 + rloc;
+        if (lane < TILE_ROWS / NPROD && row < p.n) {
           const uintptr_t ga = (uintptr_t)(p.W + (size_t)row * p.rowbytes + (size_t)blk_a * F::BYTES);
           a0 = ga & ~(uintptr_t)15;
           bytes = (uint32_t)(((ga + (size_t)nb_c * F::BYTES + 15) & ~(uintptr_t)15) - a0);
@@ -365,12 +372,14 @@ __global__ void __launch_bounds__(cta_threads(MODE), 1) gemv_stream_kernel(const
         uint32_t total = bytes;
 #pragma unroll
         for (int mask = 16; mask > 0; mask >>= 1) total += __shfl_xor_sync(0xffffffffu, total, mask);
-        if (lane == 0) mbar_expect_tx(bar_full + 8 * slot, total);
+        if (lane == 0) {   // every producer warp arrives once per stage, with the bytes of its own rows (possibly 0)
+          if (total) mbar_expect_tx(bar_full + 8 * slot, total); else mbar_arrive(bar_full + 8 * slot);
+        }
         __syncwarp();
         if (bytes)
-          bulk_g2s(smem_u32(ring + (size_t)slot * p.stage_bytes + (size_t)lane * p.slot_stride), (const void*)a0, bytes,
+          bulk_g2s(smem_u32(ring + (size_t)slot * p.stage_bytes + (size_t)rloc * p.slot_stride), (const void*)a0, bytes,
                    bar_full + 8 * slot);
-        if (lane == 0) { __threadfence_block(); *s_issued = q + 1; }   // after the expect_tx of this stage
+        if (lane == 0) { __threadfence_block(); s_issued[pw] = q + 1; }   // after the expect_tx of this stage
       }
     }
     // copies still in flight must land before the CTA may exit
@@ -399,9 +408,10 @@ __global__ void __launch_bounds__(cta_threads(MODE), 1) gemv_stream_kernel(const
       const size_t rbg = (size_t)(row0 + g) * p.rowbytes, rbh = (size_t)(row0 + g + 8) * p.rowbytes;
       for (int c = 0; c < nchunks; ++c) {
         const int q = idx * nchunks + c, slot = q % S;
-        if (*s_issued <= q) {   // not issued yet: the slot's barrier may still show an older generation
+        auto issued = [&]() { return s_issued[0] > q && s_issued[1] > q && s_issued[2] > q && s_issued[3] > q; };
+        if (!issued()) {   // not issued yet: the slot's barrier may still show an older generation
           const long long t0 = clock64();
-          while (*s_issued <= q) {
+          while (!issued()) {
             if (*s_abort || clock64() - t0 > WAIT_LIMIT) { *s_abort = 1; if (lane == 0) atomicExch(p.status, 4); return; }
           }
         }
@@ -749,13 +759,6 @@ bool make_config(int type, int64_t n, int64_t k, int mtok, Config& c) {
   const int ntiles = (int)((n + 15) / 16);
   const int sms = sm_count();
   const int zpb = z_per_block(type);
-  c.cb = 12288 / (16 * bytes);
-  if (c.cb < 1) c.cb = 1;
-  const int resid = type == KQ_TYPE_Q4_K ? 32 : 16;   // row-slot stride mod 128: spreads the 16 rows over the banks
-  int slot = ((c.cb * bytes + 16 + 15) / 16) * 16;
-  while (slot % 128 != resid) slot += 16;
-  c.slot_stride = slot;
-  c.stage_bytes = 16 * slot;
   const int header = SMEM_HEADER + (type == KQ_TYPE_IQ3_S ? 2048 : 0);
   double best = 1e30;
   bool found = false;
@@ -764,20 +767,31 @@ bool make_config(int type, int64_t n, int64_t k, int mtok, Config& c) {
     const int grid = sms / ks * ks;
     const int ngrp = grid / ks;
     const int klen = ((nblk + ks - 1) / ks) * blk;
+    // chunk = row segment of about 2 KB (>= ~1 KB keeps the copy engine at HBM speed), evenly dividing the split
+    const int bps = (nblk + ks - 1) / ks;
+    int cb_target = 2048 / bytes;
+    if (cb_target < 1) cb_target = 1;
+    const int nch = (bps + cb_target - 1) / cb_target;
+    const int cb = (bps + nch - 1) / nch;
+    const int resid = type == KQ_TYPE_Q4_K ? 32 : 16;   // row-slot stride mod 128: spreads the 16 rows over the banks
+    int slot = ((cb * bytes + 16 + 15) / 16) * 16;
+    while (slot % 128 != resid) slot += 16;
+    const int stage_bytes = 16 * slot;
     const int a_stride = klen + 32;
     const int a_bytes = (mtok * a_stride + 127) / 128 * 128;
     const int d_bytes = ((klen / 32) * 64 + 127) / 128 * 128;
     const int z_bytes = ((klen / 32) * 64 * zpb + 127) / 128 * 128;
     const int fixed = header + a_bytes + d_bytes + z_bytes;
-    int stages = (SMEM_LIMIT - fixed) / c.stage_bytes;
+    int stages = (SMEM_LIMIT - fixed) / stage_bytes;
     if (stages > MAX_STAGES) stages = MAX_STAGES;
-    if (stages < 4) continue;
+    if (stages < 3) continue;
     const int per = (ntiles + ngrp - 1) / ngrp;
     const double cost = (double)per / ks + 0.02 * (ks - 1);   // tiles per CTA x work per tile, small bias to fewer splits
     if (cost < best - 1e-9) {
       best = cost; found = true;
       c.ks = ks; c.grid = grid; c.a_stride = a_stride; c.a_bytes = a_bytes; c.d_bytes = d_bytes; c.z_bytes = z_bytes;
-      c.stages = stages; c.smem = fixed + stages * c.stage_bytes;
+      c.cb = cb; c.slot_stride = slot; c.stage_bytes = stage_bytes;
+      c.stages = stages; c.smem = fixed + stages * stage_bytes;
     }
   }
   return found;
