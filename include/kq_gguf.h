@@ -89,6 +89,25 @@ int kq_mul_mat_a8(const void* W, int type, int64_t n, int64_t k,
                   void* y, int y_dtype, int64_t stride_y,
                   void* scratch, size_t scratch_bytes, void* stream);
 
+/* kq_mul_mat_vec_a8 for hosts that cannot hand over scratch memory.
+ * Some embedders of this library own no device allocator at the point of the call: a runtime that has already
+ * handed all device memory to its own arena, a plug-in running inside another process's CUDA context under a
+ * no-allocation rule, a latency-critical path where cudaMalloc (a device-wide synchronising call) is forbidden.
+ * For them this entry point takes no scratch argument: the quantized activations, scale tables and split-K
+ * partials live in a device array built into the library image (about 14 MB, held by every GPU that loads the
+ * library until the process exits).  Inputs and outputs are still the caller's.  Same arithmetic and same kernels
+ * as kq_mul_mat_vec_a8.
+ *   Limits: m <= 16, n <= 32768, k <= 32768; anything larger returns KQ_ELIMIT with a message naming the limits.
+ *   The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *   current); make that first call outside of any stream capture.  No call allocates or frees device memory.
+ *   Every call on a device uses the same array and overwrites what the previous call left there (the counters
+ *   that must start at zero are cleared by the call itself), so two calls that may overlap on the GPU - different
+ *   streams, or different host threads - race; serialise them on one stream.
+ * This entry point has no counterpart in the reference. */
+int kq_mul_mat_vec_a8_static(const void* W, int type, int64_t n, int64_t k,
+                             const void* x, int x_dtype, int64_t m, int64_t stride_x,
+                             void* y, int y_dtype, int64_t stride_y, void* stream);
+
 /* The two halves of the mul_mat entry points, for layers that share one activation (q/k/v, gate/up):
  * kq_prepare_q8 quantizes x into `scratch`; kq_mul_mat_prepared multiplies any number of weight tensors
  * against the activations already held there (mmq != 0 selects the MMQ arithmetic).  n passed to

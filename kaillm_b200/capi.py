@@ -21,7 +21,7 @@ _DT = {torch.float32: KQ_F32, torch.float16: KQ_F16, torch.bfloat16: KQ_BF16}
 EXPORTS = (
     "kq_last_error", "kq_abi_version", "kq_block_geometry", "kq_workspace_bytes", "kq_quantize_q8_1",
     "kq_mul_mat_vec_a8", "kq_mul_mat_a8", "kq_dequantize", "kq_debug_group_dots", "kq_set_option",
-    "kq_get_option", "kq_prepare_q8", "kq_mul_mat_prepared", "kq_read_status",
+    "kq_get_option", "kq_prepare_q8", "kq_mul_mat_prepared", "kq_read_status", "kq_mul_mat_vec_a8_static",
 )
 
 
@@ -50,6 +50,7 @@ def _load() -> ctypes.CDLL:
     lib.kq_mul_mat_a8.argtypes = mm
     lib.kq_prepare_q8.argtypes = [i32, i64, i64, vp, i32, i64, i64, vp, sz, vp]
     lib.kq_mul_mat_prepared.argtypes = [vp, i32, i64, i64, i64, vp, i32, i64, i32, vp, sz, vp]
+    lib.kq_mul_mat_vec_a8_static.argtypes = [vp, i32, i64, i64, vp, i32, i64, i64, vp, i32, i64, vp]
     lib.kq_dequantize.argtypes = [vp, i32, i64, vp, i32, vp]
     lib.kq_read_status.argtypes = [i32, i64, i64, i64, vp, sz, ctypes.POINTER(i32)]
     lib.kq_debug_group_dots.argtypes = [vp, i32, i64, i64, vp, i32, i64, i64, vp, vp, vp, sz, vp]
@@ -147,6 +148,18 @@ def read_status(qtype: int, m: int, n: int, k: int, scratch: torch.Tensor) -> in
     with torch.cuda.device(scratch.device):
         _check(lib.kq_read_status(qtype, m, n, k, scratch.data_ptr(), scratch.numel(), ctypes.byref(v)))
     return v.value
+
+
+def mul_mat_vec_static(W: torch.Tensor, x: torch.Tensor, qtype: int, out: torch.Tensor) -> torch.Tensor:
+    """kq_mul_mat_vec_a8_static: the scratch-free entry point (library-owned device array; m<=16, n,k<=32768).
+
+    `out` must be preallocated by the caller, so the call itself allocates nothing on the device."""
+    m, k = x.shape
+    n = W.shape[0]
+    with torch.cuda.device(x.device):
+        _check(lib.kq_mul_mat_vec_a8_static(W.data_ptr(), qtype, n, k, x.data_ptr(), _DT[x.dtype], m, x.stride(0),
+                                            out.data_ptr(), _DT[out.dtype], out.stride(0), _stream(x.device)))
+    return out
 
 
 def dequantize(W: torch.Tensor, qtype: int, count: int, dtype=torch.float16) -> torch.Tensor:

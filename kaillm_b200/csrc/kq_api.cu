@@ -151,6 +151,49 @@ int kq_mul_mat_prepared(const void* W, int type, int64_t n, int64_t k, int64_t m
                  scratch_bytes, stream, true, false);
 }
 
+// ---------------------------------------------------------------------------------------------- no-allocation variant
+// Scratch for kq_mul_mat_vec_a8_static: a file-scope device array, one copy per GPU that loads the library.
+// Sized for the stated limits m <= 16, n <= 32768, k <= 32768 (layout of q8_layout at those maxima, rounded up).
+constexpr int64_t KQ_STATIC_MAX_M = 16, KQ_STATIC_MAX_N = 32768, KQ_STATIC_MAX_K = 32768;
+constexpr size_t KQ_STATIC_BYTES = 14u << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[KQ_STATIC_BYTES];
+
+// The array's name is only a host-side handle; kernels need its device address, looked up once per device.
+static void* static_scratch_ptr(int* rc) {
+  static void* ptrs[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) { *rc = cuda_fail(e, "cudaGetDevice"); return nullptr; }
+  if (dev < 0 || dev >= 64) { set_error("kq_mul_mat_vec_a8_static: device index %d out of range", dev); *rc = KQ_ELIMIT; return nullptr; }
+  if (!ptrs[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess) { *rc = cuda_fail(e, "cudaGetSymbolAddress(g_static_scratch)"); return nullptr; }
+    ptrs[dev] = p;
+  }
+  *rc = KQ_OK;
+  return ptrs[dev];
+}
+
+int kq_mul_mat_vec_a8_static(const void* W, int type, int64_t n, int64_t k, const void* x, int x_dtype, int64_t m,
+                             int64_t stride_x, void* y, int y_dtype, int64_t stride_y, void* stream) {
+  t_err[0] = 0;
+  if (m > KQ_STATIC_MAX_M || n > KQ_STATIC_MAX_N || k > KQ_STATIC_MAX_K) {
+    set_error("kq_mul_mat_vec_a8_static: size beyond the built-in scratch (limits: m <= %lld, n <= %lld, k <= %lld; got m=%lld n=%lld k=%lld)",
+              (long long)KQ_STATIC_MAX_M, (long long)KQ_STATIC_MAX_N, (long long)KQ_STATIC_MAX_K, (long long)m, (long long)n, (long long)k);
+    return KQ_ELIMIT;
+  }
+  if (m > 0 && n > 0 && k > 0 && q8_layout(m, n, k).total > KQ_STATIC_BYTES) {
+    set_error("kq_mul_mat_vec_a8_static: internal scratch layout exceeds the built-in array");
+    return KQ_ELIMIT;
+  }
+  int rc = KQ_OK;
+  void* scratch = static_scratch_ptr(&rc);
+  if (!scratch) return rc;
+  return mul_mat("kq_mul_mat_vec_a8_static", false, W, type, n, k, x, x_dtype, m, stride_x, y, y_dtype, stride_y, scratch,
+                 KQ_STATIC_BYTES, stream);
+}
+
 int kq_dequantize(const void* W, int type, int64_t count, void* out, int out_dtype, void* stream) {
   t_err[0] = 0;
   int b, s;
