@@ -148,7 +148,7 @@ int kq_read_status(int type, int64_t m, int64_t n, int64_t k, const void* scratc
 /* Runtime knobs for tests and profiling (process-wide, not thread-safe against concurrent launches):
  *   "gemv_impl"   0 = choose by shape (default), 1 = general dp4a kernel, 2 = streaming int8-mma kernel,
  *                 3 = row-streaming dp4a kernel, 4 = the same without the Q4_K specialisation
- *   "tc_min_m"    smallest m that the int8-mma kernel takes in mode 0 (default 9)
+ *   "tc_min_m"    smallest m that the int8-mma kernel takes in mode 0 (default 5)
  *   "gemm_min_m"  smallest m that goes to the tcgen05 GEMM (default 81: m <= 80 keeps exact integer dots)
  *   "half_fma"    1 = K-quant dequantize contracts fp16 mul+sub into one fma (default), 0 = two roundings
  * Returns KQ_EINVAL for an unknown name. */

@@ -22,7 +22,7 @@ int cuda_fail(cudaError_t e, const char* what) {
 }
 
 Options& options() {
-  static Options o = {0, 9, 81, 1, 0};
+  static Options o = {0, 5, 81, 1, 0};
   return o;
 }
 

@@ -590,7 +590,7 @@ __global__ void __launch_bounds__(ROW_THREADS, 1) gemv_rows_kernel(const RowPara
   constexpr int NG = 32 / F::GROUP;
   const int zmode = p.zmode;
   if constexpr (PAIR) {
-    static_assert(!PAIR || QT == KQ_TYPE_Q4_K, "pair mode is written for Q4_K");
+    static_assert(!PAIR || QT == KQ_TYPE_Q4_K || QT == KQ_TYPE_Q6_K, "pair mode is written for Q4_K and Q6_K");
     const int npairs = (r1 - r0 + 1) / 2;
     const int ri = lane >> 4, sbo = (lane >> 2) & 3, il = lane & 3;
     const int nsb8 = p.nsb >> 3;
@@ -612,6 +612,7 @@ __global__ void __launch_bounds__(ROW_THREADS, 1) gemv_rows_kernel(const RowPara
 #pragma unroll
       for (int t = 0; t < MT; ++t) acc[t] = 0.f;
       if (valid_row) {
+        if constexpr (QT == KQ_TYPE_Q4_K) {
         for (int s = sbo; s < nsb8; s += 4) {
           const uint8_t* bp = prow + (size_t)s * 144;
           const uint4 hdr = *reinterpret_cast<const uint4*>(bp);
@@ -649,6 +650,71 @@ __global__ void __launch_bounds__(ROW_THREADS, 1) gemv_rows_kernel(const RowPara
             }
             acc[t] += dl * (dsl.x * (float)Il) + dh * (dsh.x * (float)Ih) - (ml * zl + mh * zh);
           }
+        }
+        } else {
+        // Q6_K: lane = (row of the pair, super-block offset, part = (ip, ilh)); a part is 64 weights: for
+        // q4 = 0..3 the 16 weights 128ip + 32q4 + 16ilh .. of the super-block, i.e. 16 bytes of ql's first half
+        // (low nibbles -> q4=0, high -> q4=2), 16 bytes of its second half (q4=1, 3) and 16 bytes of qh.
+        // The 6-bit codes stay unsigned (u8 x s8 dp4a); the -32 offset is applied as -32 * d8 * sum(codes of the
+        // activation group), read from the token-major z16r table.
+        const int ip = il >> 1, ilh = il & 1;
+        for (int s = sbo; s < nsb8; s += 4) {
+          const uint8_t* bp = prow + (size_t)s * 210;
+          const uint8_t* pa = bp + 64 * ip + 16 * ilh;
+          // the three 16-byte runs sit 32 and 128-32ip-... bytes apart: same alignment phase; fetch aligned words
+          const uintptr_t a_al = (uintptr_t)pa & ~(uintptr_t)3;
+          const int shb = (int)((uintptr_t)pa & 3) * 8;         // 0 or 16 bits
+          const uint32_t* wa = reinterpret_cast<const uint32_t*>(a_al);
+          const uint32_t* wb = reinterpret_cast<const uint32_t*>(a_al + 32);
+          const uint32_t* wh = reinterpret_cast<const uint32_t*>(a_al + (128 + 32 * ip + 16 * ilh) - (64 * ip + 16 * ilh));
+          uint32_t A[4], B[4], H[4];
+          {
+            uint32_t ra[5], rb[5], rh[5];
+#pragma unroll
+            for (int w = 0; w < 5; ++w) { ra[w] = wa[w]; rb[w] = wb[w]; rh[w] = wh[w]; }
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+              A[w] = __funnelshift_r(ra[w], ra[w + 1], shb);
+              B[w] = __funnelshift_r(rb[w], rb[w + 1], shb);
+              H[w] = __funnelshift_r(rh[w], rh[w + 1], shb);
+            }
+          }
+          uint32_t q[4][4];   // [q4][word]
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            q[0][w] = (A[w] & 0x0F0F0F0Fu) | ((H[w] << 4) & 0x30303030u);
+            q[1][w] = (B[w] & 0x0F0F0F0Fu) | ((H[w] << 2) & 0x30303030u);
+            q[2][w] = ((A[w] >> 4) & 0x0F0F0F0Fu) | (H[w] & 0x30303030u);
+            q[3][w] = ((B[w] >> 4) & 0x0F0F0F0Fu) | ((H[w] >> 2) & 0x30303030u);
+          }
+          const float d = ld_h(bp + 208);
+          float wsc[4];
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) wsc[q4] = d * (float)(int8_t)bp[192 + 8 * ip + 2 * q4 + ilh];
+          const int b = s * 8 + 4 * ip;      // first of the part's four 32-blocks
+#pragma unroll
+          for (int t = 0; t < MT; ++t) {
+            const uint8_t* ap = sA + (size_t)t * p.a_stride + (size_t)(s * 4 + 2 * ip) * 80 + 16 * ilh;
+            const uint4 a0 = *reinterpret_cast<const uint4*>(ap);            // q4 = 0
+            const uint4 a1 = *reinterpret_cast<const uint4*>(ap + 32);       // q4 = 1
+            const uint4 a2 = *reinterpret_cast<const uint4*>(ap + 80);       // q4 = 2
+            const uint4 a3 = *reinterpret_cast<const uint4*>(ap + 112);      // q4 = 3
+            const uint32_t aw[4][4] = {{a0.x, a0.y, a0.z, a0.w}, {a1.x, a1.y, a1.z, a1.w}, {a2.x, a2.y, a2.z, a2.w}, {a3.x, a3.y, a3.z, a3.w}};
+            const uint4 dsw = *reinterpret_cast<const uint4*>(sDS + (size_t)t * p.nb32tot + b);
+            const uint32_t dsr[4] = {dsw.x, dsw.y, dsw.z, dsw.w};
+            const float* zp = sZ + ((size_t)t * p.nb32tot + b) * 2 + ilh;
+            float c = 0.f;
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              int I = 0;
+#pragma unroll
+              for (int w = 0; w < 4; ++w) I = dp4a_us(q[q4][w], aw[q4][w], I);
+              const float d8 = __low2float(*reinterpret_cast<const __half2*>(&dsr[q4]));
+              c += wsc[q4] * (d8 * (float)I - 32.0f * zp[2 * q4]);
+            }
+            acc[t] += c;
+          }
+        }
         }
       }
       __syncwarp();
@@ -810,11 +876,11 @@ bool make_row_config(int type, int64_t n, int64_t k, int mt, bool pair, RowConfi
   c.rows_per_stage = R;
   c.stage_bytes = (int)((R * rowbytes + 32 + 127) / 128 * 128);
   const int64_t kpad = (k + 511) / 512 * 512;
-  const bool zr = type == KQ_TYPE_Q2_K || type == KQ_TYPE_Q4_K;   // types whose min term may need the zr table
+  const bool zr = type == KQ_TYPE_Q2_K || type == KQ_TYPE_Q4_K || (pair && type == KQ_TYPE_Q6_K);
   c.a_stride = pair ? (int)(k / 64) * 80 + 16 : (int)k + 32;
   c.a_bytes = (mt * c.a_stride + 127) / 128 * 128;
   c.d_bytes = (int)((mt * (kpad / 32) * 4 + 127) / 128 * 128);
-  c.z_bytes = zr ? (int)((mt * (kpad / 32) * 4 * zpb + 127) / 128 * 128) : 0;
+  c.z_bytes = zr ? (int)((mt * (kpad / 32) * 4 * (type == KQ_TYPE_Q4_K ? 1 : 2) + 127) / 128 * 128) : 0;
   const int fixed = SMEM_HEADER + (type == KQ_TYPE_IQ3_S ? 2048 : 0) + c.a_bytes + c.d_bytes + c.z_bytes;
   if (fixed + 3 * (int64_t)c.stage_bytes > SMEM_LIMIT) return false;
   int stages = (SMEM_LIMIT - fixed) / c.stage_bytes;
@@ -866,7 +932,7 @@ int launch_tc_nt(const MmaParams& p, const Config& c, int nt, cudaStream_t st) {
 
 template <int QT, typename OutT>
 int launch_rows_mt(const RowParams& p, const RowConfig& c, int mt, cudaStream_t st) {
-  if constexpr (QT == KQ_TYPE_Q4_K) {
+  if constexpr (QT == KQ_TYPE_Q4_K || QT == KQ_TYPE_Q6_K) {
     if (p.qsp != nullptr) {
       switch (mt) {
         case 1: return launch_rows<QT, 1, true, OutT>(p, c, st);
@@ -944,7 +1010,8 @@ int launch_gemv_mma(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs&
       const int cap = (int)(left < room ? left : room);
       int mt = cap >= 8 ? 8 : (cap >= 4 ? 4 : (cap >= 2 ? 2 : 1));
       RowConfig rcg;
-      const bool pair = type == KQ_TYPE_Q4_K && impl != 4 && (k % 256) == 0;
+      // specialised consumers: Q4_K always; Q6_K only for 1-2 tokens (its per-token cost is higher than the general one's)
+      const bool pair = impl != 4 && (k % 256) == 0 && (type == KQ_TYPE_Q4_K || (type == KQ_TYPE_Q6_K && mt <= 2));
       while (mt > 1 && !make_row_config(type, n, k, mt, pair, rcg)) mt >>= 1;   // fewer tokens per pass if K is long
       if (!make_row_config(type, n, k, mt, pair, rcg)) { set_error("row-streaming GEMV: no configuration for this shape"); return KQ_EUNSUPPORTED; }
       mcount = mt;
@@ -957,6 +1024,7 @@ int launch_gemv_mma(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs&
       if (type == KQ_TYPE_Q4_0 || (type == KQ_TYPE_Q4_K && mmq)) p.zmode = 1;
       else if (type == KQ_TYPE_Q4_K) { p.zmode = 2; p.zr = P.z32r; }
       else if (type == KQ_TYPE_Q2_K) { p.zmode = 3; p.zr = P.z16r; }
+      else if (type == KQ_TYPE_Q6_K && pair) { p.zmode = 3; p.zr = P.z16r; p.zpb = 2; }   // -32 offset via group sums
       p.m0 = (int)m0; p.mcount = mcount; p.y = y; p.stride_y = stride_y; p.status = P.status;
       switch (type) {
         case KQ_TYPE_Q4_0: rc = launch_typed<KQ_TYPE_Q4_0>(nullptr, nullptr, &p, &rcg, mt, y_dtype, st); break;
