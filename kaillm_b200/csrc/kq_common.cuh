@@ -130,6 +130,9 @@ int launch_gemv_dp4a(const void* W, int type, int64_t n, int64_t k, const void* 
 bool gemv_mma_supported(const void* W, int type, int64_t n, int64_t k);
 int launch_gemv_mma(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m, void* y,
                     int y_dtype, int64_t stride_y, bool mmq, cudaStream_t st);
+bool gemv_tc5_supported(const void* W, int type, int64_t n, int64_t k);
+int launch_gemv_tc5(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m_total, int64_t m0, int mcount,
+                    void* y, int y_dtype, int64_t stride_y, bool mmq, cudaStream_t st);
 bool gemm_tc_supported(const void* W, int type, int64_t n, int64_t k);
 int launch_gemm_tc(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m, void* y, int y_dtype,
                    int64_t stride_y, bool mmq, cudaStream_t st);

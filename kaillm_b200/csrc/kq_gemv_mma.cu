@@ -991,6 +991,15 @@ int launch_gemv_mma(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs&
     const bool tile_start = (m0 % 16) == 0;
     int rc, mcount;
     Config c;
+    // impl 5 forces, impl 0 prefers the tcgen05 kernel where it applies
+    if (tile_start && (impl == 5 || (impl == 0 && left >= options().tc_min_m)) && gemv_tc5_supported(W, type, n, k)) {
+      mcount = (int)(left < 16 ? left : 16);
+      rc = launch_gemv_tc5(W, type, n, k, P, m, m0, mcount, y, y_dtype, stride_y, mmq, st);
+      if (rc) return rc;
+      m0 += mcount;
+      continue;
+    }
+    if (impl == 5) { set_error("tcgen05 GEMV: type/shape not covered"); return KQ_EUNSUPPORTED; }
     if (has_tc && tile_start && impl != 3 && impl != 4 && (impl == 2 || left >= options().tc_min_m) &&
         make_config(type, n, k, left > 8 ? 16 : 8, c)) {
       mcount = (int)(left < 16 ? left : 16);

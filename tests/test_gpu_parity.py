@@ -156,6 +156,32 @@ def test_streaming_dp4a_gemv_matches_oracle(qt, n, k, m):
     assert torch.equal(y, yb)
 
 
+@pytest.mark.parametrize("n,k,m", [(17408, 5120, 16), (9000, 5120, 5), (17408, 2048, 13), (300, 256, 7), (4000, 512, 33),
+                                   (128, 512, 1)])
+@pytest.mark.parametrize("mmq", [False, True])
+def test_tcgen05_gemv_q4k_matches_oracle(n, k, m, mmq):
+    """The tcgen05 kind::i8 decode kernel (stream-K over 128-row x 256-weight units), forced with gemv_impl=5."""
+    qt = 12
+    _, wt = wire(qt, n, k, seed=n + k)
+    x, xt = act(m, k, seed=m, dt="bf16")
+    w = wt.cpu().numpy()
+    scratch = torch.empty(capi.workspace_bytes(qt, m, n, k), dtype=torch.uint8, device=dev())
+    capi.set_option("gemv_impl", 5)
+    try:
+        y = capi.mul_mat(wt, xt, qt, mmq=mmq, out_dtype=torch.float32, scratch=scratch)
+        assert capi.read_status(qt, m, n, k, scratch) == 0
+        yb = capi.mul_mat(wt, xt, qt, mmq=mmq, out_dtype=torch.float32, scratch=scratch)   # counters self-reset
+        capi.set_option("gemv_impl", 1)
+        y1 = capi.mul_mat(wt, xt, qt, mmq=mmq, out_dtype=torch.float32)
+    finally:
+        capi.set_option("gemv_impl", 0)
+    rows = np.r_[0:min(n, 200), max(0, n - 200):n]
+    want = O.mul_mat(w[rows], qt, x, "mmq" if mmq else "mmvq")
+    assert rel_l2(to_np(y)[:, rows], want) < TIGHT
+    assert torch.equal(y, yb)
+    assert rel_l2(to_np(y), to_np(y1)) < TIGHT          # every row, against the general kernel
+
+
 def test_tensor_core_gemv_declines_unaligned_weights():
     qt, n, k = 14, 32, 512
     _, wt = wire(qt, n, k, seed=1)
