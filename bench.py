@@ -333,37 +333,83 @@ def main() -> None:
     e2e = None
     with torch.cuda.stream(stream):
         hx = {key: v.cpu().pin_memory() for key, v in xs.items()}
-        hy = {(m, n): torch.empty((m, n // world), dtype=torch.bfloat16).pin_memory() for m in MS for n in (K_HID, N_FF)}
         h2d = sum(hx[(m, k)].numel() * 2 for m in MS for _, _, _, k in mats)
-        d2h = sum(hy[(m, n)].numel() * 2 for m in MS for _, _, n, _ in mats)
-        dx = {key: torch.empty_like(v) for key, v in xs.items()}
+        d2h = sum(m * (n // world) * 2 for m in MS for _, _, n, _ in mats)
+        # one device input buffer and one pinned host result buffer per call: no reuse hazards inside a step
+        calls = [(m, W, qt, n, k) for m in MS for W, qt, n, k in mats]
+        dxs = [torch.empty_like(xs[(m, k)]) for m, _, _, _, k in calls]
+        hys = [torch.empty((m, n // world), dtype=torch.bfloat16).pin_memory() for m, _, _, n, _ in calls]
+        s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+
+        def e2e_enqueue(keep):
+            """H2D copies on one side stream, the op on the main stream, D2H reads on another side stream."""
+            s_in.wait_stream(stream)
+            s_out.wait_stream(stream)
+            for i, (m, W, qt, n, k) in enumerate(calls):
+                with torch.cuda.stream(s_in):
+                    dxs[i].copy_(hx[(m, k)], non_blocking=True)
+                    ev = torch.cuda.Event()
+                    ev.record(s_in)
+                stream.wait_event(ev)
+                y = linear.fused_mul_mat_gguf(dxs[i], W, qt)
+                if world > 1:
+                    dist.all_gather_into_tensor(yg[(m, n)], y)
+                ev2 = torch.cuda.Event()
+                ev2.record(stream)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev2)
+                    hys[i].copy_(y, non_blocking=True)
+                keep.append(y)   # outputs stay alive until the copies that read them are done
+            stream.wait_stream(s_in)
+            stream.wait_stream(s_out)
+
+        keep: list = []
+        e2e_enqueue(keep)
+        torch.cuda.synchronize()
+        eg = None
+        if not args.no_graph:
+            try:
+                keep_g: list = []
+                eg = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(eg, stream=stream):
+                    e2e_enqueue(keep_g)
+            except Exception as e:  # noqa: BLE001
+                print(f"[bench] e2e graph capture failed ({e!r}); running eagerly", file=sys.stderr)
+                eg = None
 
         def e2e_step():
-            for m in MS:
-                for W, qt, n, k in mats:
-                    dx[(m, k)].copy_(hx[(m, k)], non_blocking=True)
-                    y = linear.fused_mul_mat_gguf(dx[(m, k)], W, qt)
-                    if world > 1:
-                        dist.all_gather_into_tensor(yg[(m, n)], y)
-                    hy[(m, n)].copy_(y, non_blocking=True)
-            torch.cuda.current_stream().synchronize()
+            if eg is not None:
+                eg.replay()
+            else:
+                keep.clear()
+                e2e_enqueue(keep)
+            torch.cuda.current_stream().synchronize()   # the step's results are in host memory here
 
-        for _ in range(2):
+        for _ in range(3):
             e2e_step()
         barrier()
-        esteps = max(2, min(args.steps, 5))
+        esteps = max(2, min(args.steps, 10))
         e0.record(stream)
         for _ in range(esteps):
             e2e_step()
         e1.record(stream)
         barrier()
+        # every host result of the last step against a separate eager call of the same op on the device-resident input
+        bad = 0
+        for i, (m, W, qt, n, k) in enumerate(calls):
+            ref = linear.fused_mul_mat_gguf(xs[(m, k)], W, qt)
+            bad += int(not torch.equal(ref.cpu(), hys[i]))
+        if bad:
+            raise SystemExit(f"[bench] e2e results differ from the eager op on {bad} of {len(calls)} calls")
         t2 = torch.tensor([e0.elapsed_time(e1)], device=dev)
         if world > 1:
             dist.all_reduce(t2, op=dist.ReduceOp.MAX)
         ms_e2e = float(t2.item()) / esteps
         e2e = {"value": bytes_step / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
-               "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e,
-               "api": "kaillm_b200.linear.fused_mul_mat_gguf -> torch.ops._C_gguf.ggml_mul_mat_{vec_,}a8, eager"}
+               "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e, "results_checked": len(calls),
+               "api": "kaillm_b200.linear.fused_mul_mat_gguf -> torch.ops._C_gguf.ggml_mul_mat_{vec_,}a8; per call: "
+                      "H2D of x from pinned memory, the op, D2H of y into pinned memory (copies on side streams); "
+                      + ("whole step replayed as one CUDA graph" if eg is not None else "eager")}
 
     # ---- CPU baseline (oracle port of the reference's CPU path) on rank 0, bounded sample
     cpu = None

@@ -26,6 +26,7 @@ struct Options {
   int gemv_impl;       // 0 auto, 1 general dp4a kernel, 2 streaming tensor-core, 3 streaming dp4a
   int tc_min_m;        // auto mode: smallest token count that goes to the tensor-core consumers
   int gemm_min_m;      // smallest token count that goes to the tcgen05 GEMM
+  int pdl;             // 1: streaming kernels are launched with programmatic dependent launch
   int half_fma;        // 1: fp16 mul+sub contracted in K-quant dequantize
   long long launches;  // kernels launched by this library so far (host-side count)
 };
@@ -139,6 +140,26 @@ int launch_gemm_tc(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& 
 int launch_dequantize(const void* W, int type, int64_t count, void* out, int out_dtype, cudaStream_t st);
 
 #ifdef __CUDACC__
+// ------------------------------------------------------------------ programmatic dependent launch
+// A kernel launched with launch_pdl() may start while its predecessor in the stream is still running.  It must
+// call pdl_wait() before it touches anything the predecessor wrote (or writes anything the predecessor may
+// still read); what it does before that (barrier set-up, prefetch of the weights, which no kernel of this
+// library writes) overlaps the predecessor's tail.  pdl_trigger() lets the successor start as early as possible.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 // ------------------------------------------------------------------ device helpers
 __device__ __forceinline__ uint32_t ld_u16x2(const uint8_t* p) {
   // 32 bits from a 2-byte aligned address (wire blocks of 18/34/110/210 bytes are only 2-aligned)

@@ -61,6 +61,7 @@ struct MmaParams {
   int zpb;           // z entries per 32-block (1 or 2)
   int kpad, nb32tot;
   int m0, mcount;
+  int prefetch;      // ring stages each producer issues before it waits for the previous kernel
   void* y;
   int64_t stride_y;
   float* part;
@@ -309,6 +310,7 @@ __global__ void __launch_bounds__(cta_threads(MODE), 1) gemv_stream_kernel(const
   const int ks = blockIdx.x % p.ks;
   const int grp = blockIdx.x / p.ks, ngrp = gridDim.x / p.ks;
   const int rt0 = (int)((int64_t)grp * p.ntiles / ngrp), rt1 = (int)((int64_t)(grp + 1) * p.ntiles / ngrp);
+  pdl_trigger();
   if (rt0 >= rt1) return;
   const int blk0 = (int)((int64_t)ks * p.nblk / p.ks), blk1 = (int)((int64_t)(ks + 1) * p.nblk / p.ks);
   const int nchunks = (blk1 - blk0 + p.cb - 1) / p.cb;
@@ -336,7 +338,7 @@ __global__ void __launch_bounds__(cta_threads(MODE), 1) gemv_stream_kernel(const
     constexpr int TOKCAP = 8 * NT;
     const int ntok = p.mcount < TOKCAP ? p.mcount : TOKCAP;
     const int mrow0 = p.m0;
-    if (pw == 0) {
+    auto load_activations = [&]() {   // after pdl_wait(): the quantized activations come from the previous kernel
       if (lane == 0) {
         uint32_t total = (uint32_t)ntok * klen + (uint32_t)nb32 * 64u;
         if (p.zT != nullptr) total += (uint32_t)nb32 * p.zpb * 64u;
@@ -348,7 +350,8 @@ __global__ void __launch_bounds__(cta_threads(MODE), 1) gemv_stream_kernel(const
       if (lane == 16) bulk_g2s(smem_u32(sD), p.dT + ((size_t)tt * p.nb32tot + b32_0) * 16, (uint32_t)nb32 * 64u, bar_act);
       if (lane == 17 && p.zT != nullptr)
         bulk_g2s(smem_u32(sZ), p.zT + ((size_t)tt * p.nb32tot + b32_0) * p.zpb * 16, (uint32_t)nb32 * p.zpb * 64u, bar_act);
-    }
+    };
+    bool act_issued = false;
 
     int q = 0;
     bool ok = true;
@@ -356,6 +359,7 @@ __global__ void __launch_bounds__(cta_threads(MODE), 1) gemv_stream_kernel(const
       const int row0 = rt * TILE_ROWS;
       for (int c = 0; c < nchunks && ok; ++c, ++q) {
         const int slot = q % S;
+        if (q >= p.prefetch && pw == 0 && !act_issued) { pdl_wait(); load_activations(); act_issued = true; }
         if (q >= S) ok = mbar_wait(bar_empty + 8 * slot, (uint32_t)((q / S - 1) & 1), s_abort);
         if (!ok) break;
         const int blk_a = blk0 + c * p.cb;
@@ -382,6 +386,7 @@ __global__ void __launch_bounds__(cta_threads(MODE), 1) gemv_stream_kernel(const
         if (lane == 0) { __threadfence_block(); s_issued[pw] = q + 1; }   // after the expect_tx of this stage
       }
     }
+    if (pw == 0 && !act_issued) { pdl_wait(); load_activations(); act_issued = true; }
     // copies still in flight must land before the CTA may exit
     const int first = q > S ? q - S : 0;
     for (int qq = first; qq < q; ++qq) mbar_wait(bar_full + 8 * (qq % S), (uint32_t)((qq / S) & 1), s_abort);
@@ -492,6 +497,7 @@ struct RowParams {
   int zmode;                // min term: 0 none, 1 raw block sum from ds, 2 zr[b], 3 zr[2b], zr[2b+1]
   int zpb, kpad, nb32tot, klen;
   int m0, mcount;
+  int prefetch;             // ring stages issued before waiting for the previous kernel
   void* y;
   int64_t stride_y;
   int* status;
@@ -526,6 +532,7 @@ __global__ void __launch_bounds__(ROW_THREADS, 1) gemv_rows_kernel(const RowPara
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int S = p.stages, R = p.rows_per_stage;
   const int r0 = (int)((int64_t)blockIdx.x * p.n / gridDim.x), r1 = (int)((int64_t)(blockIdx.x + 1) * p.n / gridDim.x);
+  pdl_trigger();
   if (r0 >= r1) return;
   const int nstages = (r1 - r0 + R - 1) / R;
   const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + MAX_STAGES), bar_act = smem_u32(bars + 2 * MAX_STAGES);
@@ -546,6 +553,23 @@ __global__ void __launch_bounds__(ROW_THREADS, 1) gemv_rows_kernel(const RowPara
   if (warp == ROW_WARPS) {
     // ------------------------------------------------------------------ producer (one lane is enough)
     if (lane == 0) {
+      auto issue_stage = [&](int q) {
+        const int slot = q % S;
+        const int ra = r0 + q * R;
+        const int rb = (ra + R) < r1 ? (ra + R) : r1;
+        const uintptr_t ga = (uintptr_t)(p.W + (size_t)ra * p.rowbytes);
+        const uintptr_t ge = (uintptr_t)(p.W + (size_t)rb * p.rowbytes);
+        const uintptr_t a0 = ga & ~(uintptr_t)15;
+        const uint32_t bytes = (uint32_t)(((ge + 15) & ~(uintptr_t)15) - a0);
+        mbar_expect_tx(bar_full + 8 * slot, bytes);
+        bulk_g2s(smem_u32(ring + (size_t)slot * p.stage_bytes), (const void*)a0, bytes, bar_full + 8 * slot);
+        __threadfence_block();
+        *s_issued = q + 1;
+      };
+      // the weights do not depend on the previous kernel: fill the ring first, then wait for it
+      int q = 0;
+      for (; q < nstages && q < p.prefetch; ++q) issue_stage(q);
+      pdl_wait();
       const int ntok = p.mcount < MT ? p.mcount : MT;
       const uint32_t dsb = (uint32_t)p.nb32tot * 4u, zb = (uint32_t)p.nb32tot * p.zpb * 4u;   // multiples of 64 bytes
       const uint32_t alen = PAIR ? (uint32_t)(p.klen / 64) * 80u : (uint32_t)p.klen;
@@ -561,21 +585,10 @@ __global__ void __launch_bounds__(ROW_THREADS, 1) gemv_rows_kernel(const RowPara
           bulk_g2s(smem_u32(sZ + (size_t)t * p.nb32tot * p.zpb), p.zr + (size_t)(p.m0 + t) * p.nb32tot * p.zpb, zb, bar_act);
       }
       bool ok = true;
-      int q = 0;
       for (; q < nstages; ++q) {
-        const int slot = q % S;
-        if (q >= S) ok = mbar_wait(bar_empty + 8 * slot, (uint32_t)((q / S - 1) & 1), s_abort);
+        if (q >= S) ok = mbar_wait(bar_empty + 8 * (q % S), (uint32_t)((q / S - 1) & 1), s_abort);
         if (!ok) break;
-        const int ra = r0 + q * R;
-        const int rb = (ra + R) < r1 ? (ra + R) : r1;
-        const uintptr_t ga = (uintptr_t)(p.W + (size_t)ra * p.rowbytes);
-        const uintptr_t ge = (uintptr_t)(p.W + (size_t)rb * p.rowbytes);
-        const uintptr_t a0 = ga & ~(uintptr_t)15;
-        const uint32_t bytes = (uint32_t)(((ge + 15) & ~(uintptr_t)15) - a0);
-        mbar_expect_tx(bar_full + 8 * slot, bytes);
-        bulk_g2s(smem_u32(ring + (size_t)slot * p.stage_bytes), (const void*)a0, bytes, bar_full + 8 * slot);
-        __threadfence_block();
-        *s_issued = q + 1;
+        issue_stage(q);
       }
       const int first = q > S ? q - S : 0;
       for (int qq = first; qq < q; ++qq) mbar_wait(bar_full + 8 * (qq % S), (uint32_t)((qq / S) & 1), s_abort);
@@ -900,7 +913,7 @@ int launch_tc(const MmaParams& p, const Config& c, cudaStream_t st) {
     KQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT));
     attr_set = true;
   }
-  kern<<<c.grid, cta_threads(0), c.smem, st>>>(p);
+  KQ_CUDA_TRY(launch_pdl(kern, dim3(c.grid), dim3(cta_threads(0)), (size_t)c.smem, st, options().pdl != 0, p));
   options().launches += 1;
   KQ_CUDA_TRY(cudaGetLastError());
   return KQ_OK;
@@ -914,7 +927,7 @@ int launch_rows(const RowParams& p, const RowConfig& c, cudaStream_t st) {
     KQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT));
     attr_set = true;
   }
-  kern<<<c.grid, ROW_THREADS, c.smem, st>>>(p);
+  KQ_CUDA_TRY(launch_pdl(kern, dim3(c.grid), dim3(ROW_THREADS), (size_t)c.smem, st, options().pdl != 0, p));
   options().launches += 1;
   KQ_CUDA_TRY(cudaGetLastError());
   return KQ_OK;
@@ -991,8 +1004,8 @@ int launch_gemv_mma(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs&
     const bool tile_start = (m0 % 16) == 0;
     int rc, mcount;
     Config c;
-    // impl 5 forces, impl 0 prefers the tcgen05 kernel where it applies
-    if (tile_start && (impl == 5 || (impl == 0 && left >= options().tc_min_m)) && gemv_tc5_supported(W, type, n, k)) {
+    // the tcgen05 kernel runs on request only (impl 5): its 144-byte weight rows keep the copy engine request-bound
+    if (tile_start && impl == 5 && gemv_tc5_supported(W, type, n, k)) {
       mcount = (int)(left < 16 ? left : 16);
       rc = launch_gemv_tc5(W, type, n, k, P, m, m0, mcount, y, y_dtype, stride_y, mmq, st);
       if (rc) return rc;
@@ -1010,6 +1023,7 @@ int launch_gemv_mma(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs&
       p.stage_bytes = c.stage_bytes; p.a_stride = c.a_stride; p.a_bytes = c.a_bytes; p.d_bytes = c.d_bytes;
       p.z_bytes = c.z_bytes; p.qs = P.qs; p.dT = P.dT; p.kpad = (int)P.kpad; p.nb32tot = (int)(P.kpad / 32);
       p.zT = zT; p.zpb = zpb;
+      p.prefetch = options().pdl < c.stages ? options().pdl : c.stages;
       p.m0 = (int)m0; p.mcount = mcount; p.y = y; p.stride_y = stride_y; p.part = P.part; p.cnt = P.cnt; p.status = P.status;
       rc = type == KQ_TYPE_Q4_K ? launch_typed<KQ_TYPE_Q4_K>(&p, &c, nullptr, nullptr, nt, y_dtype, st)
                                 : launch_typed<KQ_TYPE_Q6_K>(&p, &c, nullptr, nullptr, nt, y_dtype, st);
@@ -1034,6 +1048,7 @@ int launch_gemv_mma(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs&
       else if (type == KQ_TYPE_Q4_K) { p.zmode = 2; p.zr = P.z32r; }
       else if (type == KQ_TYPE_Q2_K) { p.zmode = 3; p.zr = P.z16r; }
       else if (type == KQ_TYPE_Q6_K && pair) { p.zmode = 3; p.zr = P.z16r; p.zpb = 2; }   // -32 offset via group sums
+      p.prefetch = options().pdl < rcg.stages ? options().pdl : rcg.stages;
       p.m0 = (int)m0; p.mcount = mcount; p.y = y; p.stride_y = stride_y; p.status = P.status;
       switch (type) {
         case KQ_TYPE_Q4_0: rc = launch_typed<KQ_TYPE_Q4_0>(nullptr, nullptr, &p, &rcg, mt, y_dtype, st); break;

@@ -16,6 +16,8 @@ template <typename T>
 __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const T* __restrict__ x, int64_t stride_x, int k,
                                                             int kpad, int64_t m, int64_t mpad, Q8Ptrs P,
                                                             uint8_t* __restrict__ wire36) {
+  pdl_trigger();   // a GEMV launched behind this kernel may set up and prefetch its weights meanwhile
+  pdl_wait();      // the scratch this kernel rewrites may still be read by the launch before it
   const int lane = threadIdx.x & 31;
   const int nb = kpad >> 5;
   const int64_t gthread = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -90,23 +92,26 @@ int launch_quantize(const void* x, int x_dtype, int64_t m, int64_t k, int64_t st
   int64_t gridl = (nblk + 7) / 8;
   if (gridl * 256 < P.ncnt) gridl = (P.ncnt + 255) / 256;
   const unsigned grid = (unsigned)gridl;
+  const bool pdl = options().pdl != 0;
+  cudaError_t lrc = cudaSuccess;
   switch (x_dtype) {
     case KQ_F32:
-      quantize_q8_1_kernel<float><<<grid, 256, 0, st>>>((const float*)x, stride_x, (int)k, (int)kpad, m, mpad, P,
-                                                       (uint8_t*)wire36);
+      lrc = launch_pdl(quantize_q8_1_kernel<float>, dim3(grid), dim3(256), 0, st, pdl, (const float*)x, stride_x, (int)k,
+                       (int)kpad, m, mpad, P, (uint8_t*)wire36);
       break;
     case KQ_F16:
-      quantize_q8_1_kernel<__half><<<grid, 256, 0, st>>>((const __half*)x, stride_x, (int)k, (int)kpad, m, mpad, P,
-                                                        (uint8_t*)wire36);
+      lrc = launch_pdl(quantize_q8_1_kernel<__half>, dim3(grid), dim3(256), 0, st, pdl, (const __half*)x, stride_x, (int)k,
+                       (int)kpad, m, mpad, P, (uint8_t*)wire36);
       break;
     case KQ_BF16:
-      quantize_q8_1_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, stride_x, (int)k, (int)kpad,
-                                                               m, mpad, P, (uint8_t*)wire36);
+      lrc = launch_pdl(quantize_q8_1_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, pdl, (const __nv_bfloat16*)x, stride_x, (int)k,
+                       (int)kpad, m, mpad, P, (uint8_t*)wire36);
       break;
     default:
       set_error("unsupported activation dtype %d", x_dtype);
       return KQ_EUNSUPPORTED;
   }
+  KQ_CUDA_TRY(lrc);
   options().launches += 1;
   KQ_CUDA_TRY(cudaGetLastError());
   return KQ_OK;
