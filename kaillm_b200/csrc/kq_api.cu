@@ -22,7 +22,7 @@ int cuda_fail(cudaError_t e, const char* what) {
 }
 
 Options& options() {
-  static Options o = {0, 5, 81, 2, 1, 0};
+  static Options o = {0, 5, 81, 2, 1, 0, 0, 0};
   return o;
 }
 
@@ -237,6 +237,8 @@ int kq_set_option(const char* name, int value) {
   if (name && !strcmp(name, "half_fma")) { options().half_fma = value; return KQ_OK; }
   if (name && !strcmp(name, "tc_min_m")) { options().tc_min_m = value; return KQ_OK; }
   if (name && !strcmp(name, "gemm_min_m")) { options().gemm_min_m = value; return KQ_OK; }
+  if (name && !strcmp(name, "tile_debug")) { options().tile_debug = value; return KQ_OK; }
+  if (name && !strcmp(name, "tile_segments")) { options().tile_segments = value != 0; return KQ_OK; }
   if (name && !strcmp(name, "pdl")) { options().pdl = value < 0 ? 0 : value; return KQ_OK; }
   set_error("kq_set_option: unknown option");
   return KQ_EINVAL;
@@ -247,6 +249,7 @@ int kq_get_option(const char* name, int* value) {
   if (name && value && !strcmp(name, "half_fma")) { *value = options().half_fma; return KQ_OK; }
   if (name && value && !strcmp(name, "tc_min_m")) { *value = options().tc_min_m; return KQ_OK; }
   if (name && value && !strcmp(name, "gemm_min_m")) { *value = options().gemm_min_m; return KQ_OK; }
+  if (name && value && !strcmp(name, "tile_segments")) { *value = options().tile_segments; return KQ_OK; }
   if (name && value && !strcmp(name, "pdl")) { *value = options().pdl; return KQ_OK; }
   if (name && value && !strcmp(name, "launch_count")) { *value = (int)(options().launches & 0x7fffffff); return KQ_OK; }
   set_error("kq_get_option: unknown option");

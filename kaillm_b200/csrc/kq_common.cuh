@@ -23,12 +23,16 @@ int cuda_fail(cudaError_t e, const char* what);
   } while (0)
 
 struct Options {
-  int gemv_impl;       // 0 auto, 1 general dp4a kernel, 2 streaming tensor-core, 3 streaming dp4a
+  int gemv_impl;       // 0 auto, 1 general dp4a, 2 tile-per-warp mma, 3 row-streaming dp4a, 4 same without the
+                       // specialised consumers, 5 tcgen05 (Q4_K), 6 shared-stage mma (token-major tiles)
   int tc_min_m;        // auto mode: smallest token count that goes to the tensor-core consumers
   int gemm_min_m;      // smallest token count that goes to the tcgen05 GEMM
-  int pdl;             // 1: streaming kernels are launched with programmatic dependent launch
+  int pdl;             // 0: plain launches; p > 0: programmatic dependent launch, p ring stages prefetched before
+                       // the kernel waits for its predecessor
   int half_fma;        // 1: fp16 mul+sub contracted in K-quant dequantize
   long long launches;  // kernels launched by this library so far (host-side count)
+  int tile_segments;   // 1: the tile GEMV fetches row segments even when its K slice is the whole row
+  int tile_debug;      // timing experiments (results are wrong): 1 no arithmetic, 2 no weight copies
 };
 Options& options();
 
@@ -131,6 +135,9 @@ int launch_gemv_dp4a(const void* W, int type, int64_t n, int64_t k, const void* 
 bool gemv_mma_supported(const void* W, int type, int64_t n, int64_t k);
 int launch_gemv_mma(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m, void* y,
                     int y_dtype, int64_t stride_y, bool mmq, cudaStream_t st);
+bool gemv_tile_supported(const void* W, int type, int64_t n, int64_t k, int mtok);
+int launch_gemv_tile(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m0, int mcount, void* y,
+                     int y_dtype, int64_t stride_y, bool mmq, cudaStream_t st);
 bool gemv_tc5_supported(const void* W, int type, int64_t n, int64_t k);
 int launch_gemv_tc5(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m_total, int64_t m0, int mcount,
                     void* y, int y_dtype, int64_t stride_y, bool mmq, cudaStream_t st);

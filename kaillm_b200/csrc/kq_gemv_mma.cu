@@ -1013,6 +1013,16 @@ int launch_gemv_mma(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs&
       continue;
     }
     if (impl == 5) { set_error("tcgen05 GEMV: type/shape not covered"); return KQ_EUNSUPPORTED; }
+    // 5..16 tokens of Q4_K / Q6_K: all warps share a stage of 8 rows, tokens on the mma's M side
+    if (has_tc && tile_start && (impl == 6 || (impl == 0 && left >= options().tc_min_m)) &&
+        gemv_tile_supported(W, type, n, k, (int)(left < 16 ? left : 16))) {
+      mcount = (int)(left < 16 ? left : 16);
+      rc = launch_gemv_tile(W, type, n, k, P, m0, mcount, y, y_dtype, stride_y, mmq, st);
+      if (rc) return rc;
+      m0 += mcount;
+      continue;
+    }
+    if (impl == 6) { set_error("tile GEMV: type/shape not covered"); return KQ_EUNSUPPORTED; }
     if (has_tc && tile_start && impl != 3 && impl != 4 && (impl == 2 || left >= options().tc_min_m) &&
         make_config(type, n, k, left > 8 ? 16 : 8, c)) {
       mcount = (int)(left < 16 ? left : 16);

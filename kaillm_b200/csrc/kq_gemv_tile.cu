@@ -1,0 +1,630 @@
+// Decode GEMV for 5..16 tokens per pass (Q4_K, Q6_K): int8 mma.sync with the TOKENS on the 16-wide M side.
+//
+//   grid      one CTA per SM, in `ks` groups; group s works on K slice s of every weight row it owns
+//   stage     8 consecutive weight rows x the CTA's K slice.  With ks == 1 that is one contiguous piece of the
+//             wire tensor and ONE bulk copy; otherwise eight row segments of a few KB each
+//   CTA       16 consumer warps + 1 reducer warp + 1 producer warp
+//   consumer  ALL sixteen warps work on every stage: the stage's super-blocks are dealt round-robin over the
+//             warps (unit = stage x super-block, unit u belongs to warp u % 16, so the load evens out over a few
+//             stages).  Per 32-weight sub-block one m16n8k32 mma gives the 16 tokens x 8 rows integer dots
+//             (m16n8k16 per 16-weight group for Q6_K); the block scales are applied in fp32 on the way into
+//             the warp's 16 x 8 partial tile.  The Q4_K min term is itself a small GEMM over the eight
+//             sub-blocks of a super-block (mins 0..63, exact in tf32) x (d8 * block sum, split hi + lo), done
+//             with two tf32 mmas per super-block.
+//   reducer   adds the sixteen partial tiles of a stage in warp order (deterministic) and stores the outputs;
+//             with ks > 1 it publishes fp32 partials and the last split to arrive adds them in split order
+//   rings     stage ring: full (copy bytes) / empty (16 consumer arrivals);  partial-tile ring of two buffers:
+//             red_full (16 arrivals) / red_empty (reducer), so a consumer runs at most two stages ahead
+//
+// Every consumer visits every stage, so a parity wait is never more than one phase behind.  All waits are
+// bounded (about 2^27 clocks): the waiter raises a CTA-wide abort flag and a status word, every warp leaves
+// its loop and the producer waits, again bounded, for the copies it has in flight.
+//
+// Combine: vllm_gguf_plugin/csrc/gguf/vecdotq.cuh:328-379 (Q4_K), 447-491 (Q6_K).
+#include "kq_common.cuh"
+
+namespace kq {
+
+namespace {
+
+constexpr int TL_ROWS = 8;
+constexpr int TL_CW = 16;                         // consumer warps
+constexpr int TL_THREADS = (TL_CW + 2) * 32;      // + reducer + producer
+constexpr int TL_HEADER = 1024;
+constexpr int TL_MAX_STAGES = 16;
+constexpr int TL_SMEM_LIMIT = 232448;
+constexpr uint32_t TL_MAGIC_I = 0x4B400000u;      // bits of 12582912.0f
+constexpr float TL_MAGIC_F = 12582912.0f;
+constexpr long long TL_WAIT_LIMIT = 1ll << 27;
+
+struct TileParams {
+  const uint8_t* W;
+  int64_t rowbytes;
+  int n, nblk, ks, ntiles;
+  int stages, row_stride, stage_bytes, contig;
+  int a_stride, a_bytes, d_bytes, z_bytes;
+  const int8_t* qs;
+  const float* dT;
+  const float* zT;
+  int kpad, nb32tot;
+  int m0, mcount, prefetch;
+  int debug;   // timing experiments only: 1 = consumers skip the arithmetic, 2 = the producer skips the weight copies
+  void* y;
+  int64_t stride_y;
+  float* part;
+  int* cnt;
+  int* status;
+};
+
+struct TileConfig {
+  int ks, grid, stages, row_stride, stage_bytes, contig, a_stride, a_bytes, d_bytes, z_bytes, smem;
+};
+
+__device__ __forceinline__ uint32_t s_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void bar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void bar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool bar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(20000u)   // the thread may stay suspended this many ns before the test returns false
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (bar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (int it = 1;; ++it) {
+    if (bar_try(bar, parity)) return true;
+    __nanosleep(32);   // a waiting warp stays out of the issue slots of the working ones
+    if ((it & 15) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > TL_WAIT_LIMIT) { *abort_flag = 1; return false; }
+    }
+  }
+}
+__device__ __forceinline__ void copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+// tokens (A, 16 x 32 s8) x weights (B, 32 x 8 s8) -> s32
+__device__ __forceinline__ void mma_i8_k32(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                           uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+__device__ __forceinline__ void mma_i8_k16(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+               : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+               : "r"(a0), "r"(a1), "r"(b0), "r"(0));
+}
+// d += A (16 x 8 tf32) x B (8 x 8 tf32)
+__device__ __forceinline__ void mma_tf32_k8(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                            uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ float magic_f(int v) { return __int_as_float(v + (int)TL_MAGIC_I) - TL_MAGIC_F; }
+__device__ __forceinline__ uint32_t byte_of(uint32_t w, int i) { return __byte_perm(w, 0u, 0x4440u | (uint32_t)i); }
+__device__ __forceinline__ int sbyte_of(uint32_t w, int i) {   // sign-extended byte i in one permute
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(w), "r"(0u), "r"((uint32_t)i | ((8u | (uint32_t)i) * 0x1110u)));
+  return (int)r;
+}
+
+// shared-memory loads by 32-bit shared address: keeps every access an LDS with an immediate offset
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ float2 ldsf2(uint32_t a) {
+  float2 v;
+  asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ float ldsf(uint32_t a) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+  return v;
+}
+// 32 bits at a 2-byte aligned address.  AL = 0: the address is 4-byte aligned; 1: it is 2 mod 4; 2: either, decided
+// per lane without a branch (the callers sit between warp-wide mma instructions and must not diverge)
+template <int AL>
+__device__ __forceinline__ uint32_t lds32_h(uint32_t a) {
+  if constexpr (AL == 0) return lds32(a);
+  else if constexpr (AL == 1) return __funnelshift_r(lds32(a - 2), lds32(a + 2), 16);
+  else {
+    const uint32_t b = a & ~3u;
+    return __funnelshift_r(lds32(b), lds32(b + 4), (a & 2u) << 3);
+  }
+}
+
+struct TileView {       // shared addresses of the CTA's activation slice
+  uint32_t sA;          // [tokens][a_stride] codes
+  uint32_t a_stride;
+  uint32_t sD;          // [32-block][16 tokens] fp32 d8
+  uint32_t sZ;          // [32-block][16 tokens] fp32 min-term factor (Q4_K)
+};
+
+// Lane (g, t) of a consumer warp: B-operand column g = token g (and g + 8 in the second half), A-operand row g =
+// weight row g of the stage; it ends up with the outputs of row g for tokens 2t, 2t+1 (and 8+2t, 8+2t+1).
+//
+// ---------------------------------------------------------------------------------------------- Q4_K unit
+// One super-block (pg: its first byte in row g).  The 16 A rows of an m16n8k32 mma are the 8 weight rows twice:
+// rows 0-7 carry the low nibbles of 32 bytes (sub-block 2il), rows 8-15 the high nibbles (sub-block 2il+1), so
+// the unpacked words drop into the A fragment as they are.  One mma against the activations of sub-block 2il
+// (its rows 8-15 are ignored) and one against those of 2il+1 (rows 0-7 ignored).  Inside a 32-block the k
+// index is permuted (fragment k = 4t+i <-> position 8t+i, 16+4t+i <-> 8t+4+i) on both operands, so a lane
+// reads its two activation registers with one 64-bit load.  b0: first 32-block of the super-block in the slice.
+template <int NH>
+__device__ __forceinline__ void unit_q4k(uint32_t pg, int b0, const TileView& A, int g, int t, float (&acc)[4]) {
+  const uint4 h = lds128(pg);   // {d, dmin}, scales[12]
+  const uint32_t sc[2] = {h.y & 0x3F3F3F3Fu, (h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u)};
+  const uint32_t mn[2] = {h.z & 0x3F3F3F3Fu, ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u)};
+  float u[4] = {0.f, 0.f, 0.f, 0.f};
+  const uint32_t tok = A.sA + (uint32_t)g * A.a_stride + (uint32_t)b0 * 32u + 8u * (uint32_t)t;
+  const uint32_t dsc = A.sD + ((uint32_t)b0 * 16u + 2u * (uint32_t)t) * 4u;
+#pragma unroll
+  for (int il = 0; il < 4; ++il) {
+    const uint2 w = lds64(pg + 16 + 32 * il + 8 * t);
+    const uint32_t a0 = w.x & 0x0F0F0F0Fu, a1 = (w.x >> 4) & 0x0F0F0F0Fu;
+    const uint32_t a2 = w.y & 0x0F0F0F0Fu, a3 = (w.y >> 4) & 0x0F0F0F0Fu;
+    const int sl = (int)byte_of(sc[il >> 1], (2 * il) & 3), sh = (int)byte_of(sc[il >> 1], (2 * il + 1) & 3);
+#pragma unroll
+    for (int hf = 0; hf < NH; ++hf) {
+      const uint2 xl = lds64(tok + hf * 8 * A.a_stride + (2 * il) * 32);
+      const uint2 xh = lds64(tok + hf * 8 * A.a_stride + (2 * il + 1) * 32);
+      int Dl[4], Dh[4];
+      mma_i8_k32(Dl, a0, a1, a2, a3, xl.x, xl.y);
+      mma_i8_k32(Dh, a0, a1, a2, a3, xh.x, xh.y);
+      const float2 dl = ldsf2(dsc + ((2 * il) * 16 + 8 * hf) * 4);
+      const float2 dh = ldsf2(dsc + ((2 * il + 1) * 16 + 8 * hf) * 4);
+      u[2 * hf] = fmaf(magic_f(Dl[0] * sl), dl.x, u[2 * hf]);   // |dot * sc| <= 32*15*127*63 < 2^22
+      u[2 * hf + 1] = fmaf(magic_f(Dl[1] * sl), dl.y, u[2 * hf + 1]);
+      u[2 * hf] = fmaf(magic_f(Dh[2] * sh), dh.x, u[2 * hf]);
+      u[2 * hf + 1] = fmaf(magic_f(Dh[3] * sh), dh.y, u[2 * hf + 1]);
+    }
+  }
+  // min term: [rows x 8 sub-blocks] (mins 0..63, exact in tf32) x [8 sub-blocks x tokens] (d8 * block sum, hi + lo)
+  const uint32_t m0 = __float_as_uint((float)byte_of(mn[0], t)), m1 = __float_as_uint((float)byte_of(mn[1], t));
+  const float2 dd = __half22float2(*reinterpret_cast<const __half2*>(&h.x));   // {d, dmin} of row g
+#pragma unroll
+  for (int hf = 0; hf < NH; ++hf) {
+    const float z0 = ldsf(A.sZ + (((uint32_t)b0 + t) * 16u + 8u * hf + g) * 4u);
+    const float z1 = ldsf(A.sZ + (((uint32_t)b0 + t + 4) * 16u + 8u * hf + g) * 4u);
+    const uint32_t h0 = __float_as_uint(z0) & 0xFFFFE000u, h1 = __float_as_uint(z1) & 0xFFFFE000u;
+    float dm[4] = {0.f, 0.f, 0.f, 0.f};
+    mma_tf32_k8(dm, m0, 0u, m1, 0u, h0, h1);
+    mma_tf32_k8(dm, m0, 0u, m1, 0u, __float_as_uint(z0 - __uint_as_float(h0)), __float_as_uint(z1 - __uint_as_float(h1)));
+    acc[2 * hf] += dd.x * u[2 * hf] - dd.y * dm[0];
+    acc[2 * hf + 1] += dd.x * u[2 * hf + 1] - dd.y * dm[1];
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- Q6_K unit
+// 16-weight scale groups: A rows 0-7 carry group s=0 of a 32-block, rows 8-15 group s=1 (m16n8k16); one mma
+// against the activations of each half-block.  Group (ip, q4, s) holds weights 128ip + 32q4 + 16s + 4t.. of the
+// super-block: low nibbles from ql[64ip + 32(q4&1) + 16s + 4t] >> 4(q4>>1), two high bits from
+// qh[32ip + 16s + 4t] >> 2q4.  The two groups share the activation scale, so their scaled dots are added as
+// integers before the conversion (|sum| < 2^24).
+__device__ __forceinline__ uint32_t unpack6_tl(uint32_t qlw, uint32_t qhw, int q4) {
+  const uint32_t lo = q4 >> 1 ? qlw >> 4 : qlw;
+  const uint32_t hi = q4 == 0 ? qhw << 4 : (q4 == 1 ? qhw << 2 : (q4 == 2 ? qhw : qhw >> 2));
+  return sub32_bytes((lo & 0x0F0F0F0Fu) | (hi & 0x30303030u));
+}
+
+template <int NH, int AL>
+__device__ __forceinline__ void unit_q6k(uint32_t pg, int b0, const TileView& A, int g, int t, float (&acc)[4]) {
+  uint32_t sc[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) sc[i] = lds32_h<AL>(pg + 192 + 4 * i);
+  float u[4] = {0.f, 0.f, 0.f, 0.f};
+  const uint32_t tok = A.sA + (uint32_t)g * A.a_stride + (uint32_t)b0 * 32u + 4u * (uint32_t)t;
+  const uint32_t dsc = A.sD + ((uint32_t)b0 * 16u + 2u * (uint32_t)t) * 4u;
+#pragma unroll
+  for (int ip = 0; ip < 2; ++ip) {
+    uint32_t ql[2][2], qh[2];   // [s][q4 & 1]
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      ql[s][0] = lds32_h<AL>(pg + 64 * ip + 16 * s + 4 * t);
+      ql[s][1] = lds32_h<AL>(pg + 64 * ip + 32 + 16 * s + 4 * t);
+      qh[s] = lds32_h<AL>(pg + 128 + 32 * ip + 16 * s + 4 * t);
+    }
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4) {
+      const int b = 4 * ip + q4, gi = 8 * ip + 2 * q4;
+      const uint32_t a0 = unpack6_tl(ql[0][q4 & 1], qh[0], q4), a1 = unpack6_tl(ql[1][q4 & 1], qh[1], q4);
+      const int s0 = sbyte_of(sc[gi >> 2], gi & 3), s1 = sbyte_of(sc[gi >> 2], (gi & 3) + 1);
+#pragma unroll
+      for (int hf = 0; hf < NH; ++hf) {
+        const uint32_t x0 = lds32(tok + hf * 8 * A.a_stride + b * 32);
+        const uint32_t x1 = lds32(tok + hf * 8 * A.a_stride + b * 32 + 16);
+        int D0[4], D1[4];
+        mma_i8_k16(D0, a0, a1, x0);
+        mma_i8_k16(D1, a0, a1, x1);
+        const float2 d8 = ldsf2(dsc + (b * 16 + 8 * hf) * 4);
+        u[2 * hf] = fmaf((float)(D0[0] * s0 + D1[2] * s1), d8.x, u[2 * hf]);
+        u[2 * hf + 1] = fmaf((float)(D0[1] * s0 + D1[3] * s1), d8.y, u[2 * hf + 1]);
+      }
+    }
+  }
+  unsigned short dw;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(dw) : "r"(pg + 208));
+  const float d = __half2float(__ushort_as_half(dw));
+#pragma unroll
+  for (int i = 0; i < 2 * NH; ++i) acc[i] = fmaf(d, u[i], acc[i]);
+}
+
+// ---------------------------------------------------------------------------------------------- kernel
+// NH = 1: up to 8 tokens per pass, NH = 2: up to 16
+template <int QT, int NH, typename OutT>
+__global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TileParams p) {
+  using F = Fmt<QT>;
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(smem + TL_HEADER - 8);
+  uint8_t* sA = smem + TL_HEADER;
+  float* sD = reinterpret_cast<float*>(sA + p.a_bytes);
+  float* sZ = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sD) + p.d_bytes);
+  float4* sRed = reinterpret_cast<float4*>(reinterpret_cast<uint8_t*>(sZ) + p.z_bytes);   // [2][16 warps][32 lanes]
+  uint8_t* ring = reinterpret_cast<uint8_t*>(sRed) + 2 * TL_CW * 512;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int S = p.stages;
+  const int ks = blockIdx.x % p.ks;
+  const int grp = blockIdx.x / p.ks, ngrp = gridDim.x / p.ks;
+  const int rt0 = (int)((int64_t)grp * p.ntiles / ngrp), rt1 = (int)((int64_t)(grp + 1) * p.ntiles / ngrp);
+  pdl_trigger();
+  if (rt0 >= rt1) return;
+  const int nst = rt1 - rt0;
+  const int blk0 = (int)((int64_t)ks * p.nblk / p.ks), blk1 = (int)((int64_t)(ks + 1) * p.nblk / p.ks);
+  const int nsb = blk1 - blk0;
+  const uint32_t bar_full = s_u32(bars), bar_empty = s_u32(bars + TL_MAX_STAGES), bar_act = s_u32(bars + 2 * TL_MAX_STAGES);
+  const uint32_t bar_rfull = s_u32(bars + 2 * TL_MAX_STAGES + 1), bar_rempty = s_u32(bars + 2 * TL_MAX_STAGES + 3);
+  const uint32_t bar_fin = s_u32(bars + 2 * TL_MAX_STAGES + 5);   // split-K: the reducer has published this CTA's tiles
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) { bar_init(bar_full + 8 * s, 1); bar_init(bar_empty + 8 * s, TL_CW); }
+    bar_init(bar_act, 1);
+    for (int b = 0; b < 2; ++b) { bar_init(bar_rfull + 8 * b, TL_CW); bar_init(bar_rempty + 8 * b, 1); }
+    bar_init(bar_fin, 1);
+    *s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+
+  if (warp == TL_CW + 1) {
+    // ------------------------------------------------------------------ producer
+    const int k0 = blk0 * F::BLK, klen = nsb * F::BLK;
+    const int b32_0 = k0 >> 5, nb32 = klen >> 5;
+    const int tt = p.m0 >> 4;
+    const int ntok = p.mcount < 8 * NH ? p.mcount : 8 * NH;
+    const size_t seg0 = (size_t)blk0 * F::BYTES;
+    const uint32_t seglen = (uint32_t)nsb * F::BYTES;
+    const int contig = p.contig, skip_copies = p.debug == 2;
+    int slot = 0;          // ring position of the next stage to issue
+    uint32_t eph = 1;      // parity that shows the slot's previous contents consumed (passes at once on the first lap)
+    auto issue_stage = [&](int q) {
+      const int row0 = (rt0 + q) * TL_ROWS;
+      const uint32_t dst = s_u32(ring + (size_t)slot * p.stage_bytes);
+      const uint32_t bar = bar_full + 8 * slot;
+      if (skip_copies) {
+        if (lane == 0) bar_arrive(bar);
+      } else if (contig) {
+        if (lane == 0) {
+          const int rows = (p.n - row0) < TL_ROWS ? (p.n - row0) : TL_ROWS;
+          const uintptr_t ga = (uintptr_t)(p.W + (size_t)row0 * p.rowbytes);
+          const uintptr_t a0 = ga & ~(uintptr_t)15;
+          const uint32_t bytes = (uint32_t)(((ga + (size_t)rows * p.rowbytes + 15) & ~(uintptr_t)15) - a0);
+          bar_expect_tx(bar, bytes);
+          copy_g2s(dst, (const void*)a0, bytes, bar);
+        }
+      } else {
+        uint32_t bytes = 0;
+        uintptr_t a0 = 0;
+        const int row = row0 + lane;
+        if (lane < TL_ROWS && row < p.n) {
+          const uintptr_t ga = (uintptr_t)(p.W + (size_t)row * p.rowbytes + seg0);
+          a0 = ga & ~(uintptr_t)15;
+          bytes = (uint32_t)(((ga + seglen + 15) & ~(uintptr_t)15) - a0);
+        }
+        uint32_t total = bytes;
+#pragma unroll
+        for (int mask = 4; mask > 0; mask >>= 1) total += __shfl_xor_sync(0xffffffffu, total, mask);
+        if (lane == 0) bar_expect_tx(bar, total);   // row0 < n, so total > 0
+        __syncwarp();
+        if (bytes) copy_g2s(dst + (uint32_t)lane * p.row_stride, (const void*)a0, bytes, bar);
+      }
+      if (++slot == S) { slot = 0; eph ^= 1; }
+    };
+    int q = 0;
+    for (; q < nst && q < p.prefetch; ++q) issue_stage(q);   // the weights do not depend on the previous kernel
+    pdl_wait();
+    {
+      if (lane == 0) {
+        uint32_t total = (uint32_t)ntok * klen + (uint32_t)nb32 * 64u;
+        if (p.zT != nullptr) total += (uint32_t)nb32 * 64u;
+        bar_expect_tx(bar_act, total);
+      }
+      __syncwarp();
+      if (lane < ntok)
+        copy_g2s(s_u32(sA + lane * p.a_stride), p.qs + (size_t)(p.m0 + lane) * p.kpad + k0, (uint32_t)klen, bar_act);
+      if (lane == 16) copy_g2s(s_u32(sD), p.dT + ((size_t)tt * p.nb32tot + b32_0) * 16, (uint32_t)nb32 * 64u, bar_act);
+      if (lane == 17 && p.zT != nullptr)
+        copy_g2s(s_u32(sZ), p.zT + ((size_t)tt * p.nb32tot + b32_0) * 16, (uint32_t)nb32 * 64u, bar_act);
+    }
+    bool ok = true;
+    for (; q < nst; ++q) {
+      if (q >= S) ok = bar_wait(bar_empty + 8 * slot, eph, s_abort);
+      if (!ok) break;
+      issue_stage(q);
+    }
+    // copies still in flight must land before the CTA may exit: the last min(q, S) stages issued
+    {
+      const int pending = q < S ? q : S;
+      int sl = slot;
+      uint32_t fph = eph ^ 1u;   // parity of the fill most recently issued into slots below `slot`
+      for (int i = 0; i < pending; ++i) {
+        if (--sl < 0) { sl = S - 1; fph ^= 1u; }
+        bar_wait(bar_full + 8 * sl, q <= S ? 0u : fph, s_abort);
+      }
+    }
+    bar_wait(bar_act, 0, s_abort);
+    if (!ok && lane == 0) atomicExch(p.status, 1);
+    return;
+  }
+
+  if (warp == TL_CW) {
+    // ------------------------------------------------------------------ reducer
+    OutT* y = reinterpret_cast<OutT*>(p.y);
+    const int g = lane >> 2, t = lane & 3;
+    const int nks = p.ks;
+    for (int q = 0; q < nst; ++q) {
+      const int buf = q & 1;
+      if (!bar_wait(bar_rfull + 8 * buf, (uint32_t)((q >> 1) & 1), s_abort)) { if (lane == 0) atomicExch(p.status, 5); return; }
+      float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int w = 0; w < TL_CW; ++w) {
+        const float4 v = sRed[(buf * TL_CW + w) * 32 + lane];
+        sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+      }
+      __syncwarp();
+      if (lane == 0) bar_arrive(bar_rempty + 8 * buf);
+      const int row0 = (rt0 + q) * TL_ROWS;
+      const float vals[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+      for (int i = 0; i < 2 * NH; ++i) {
+        const int row = row0 + g, tl = 2 * t + (i & 1) + 8 * (i >> 1);
+        if (row < p.n && tl < p.mcount) {
+          if (nks == 1) y[(size_t)(p.m0 + tl) * p.stride_y + row] = from_f32<OutT>(vals[i]);
+          else __stcg(p.part + ((size_t)ks * 16 + tl) * p.n + row, vals[i]);   // published after the loop
+        }
+      }
+    }
+    if (nks > 1) {
+      // one fence and one round of counter updates for all tiles of this CTA.  The split that arrives last at a
+      // tile's counter finishes the tile; the list of those tiles goes to the consumer warps (idle by now),
+      // which finish them in parallel.  The partial tiles' buffers are free: every consumer is past its last stage.
+      uint8_t* s_last = reinterpret_cast<uint8_t*>(sRed);
+      __threadfence();
+      __syncwarp();
+      for (int idx = lane; idx < nst; idx += 32) s_last[idx] = atomicAdd(p.cnt + rt0 + idx, 1) == nks - 1;
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) bar_arrive(bar_fin);
+    }
+    return;
+  }
+
+  // -------------------------------------------------------------------- consumers
+  if (!bar_wait(bar_act, 0, s_abort)) { if (lane == 0) atomicExch(p.status, 2); return; }
+  const TileView A{s_u32(sA), (uint32_t)p.a_stride, s_u32(sD), s_u32(sZ)};
+  const int g = lane >> 2, t = lane & 3;
+  const int contig = p.contig;
+  const uint32_t row_stride = contig ? (uint32_t)p.rowbytes : (uint32_t)p.row_stride;
+  const uint32_t stage_bytes = (uint32_t)p.stage_bytes, ring_a = s_u32(ring);
+  const int skip_math = p.debug == 1;
+  const bool rows_same_parity = (p.rowbytes & 3) == 0 && (row_stride & 3u) == 0;   // all rows of a stage equally aligned mod 4
+  // row r of a stage starts at r * row_stride + the low four bits of its global address
+  const uint32_t off_base = (uint32_t)(((uintptr_t)p.W + (size_t)blk0 * F::BYTES) & 15);
+  const uint32_t row_step = (uint32_t)(p.rowbytes & 15);
+  int first = warp;   // first super-block of the current stage that belongs to this warp
+  int slot = 0;
+  uint32_t fph = 0;
+  for (int q = 0; q < nst; ++q) {
+    const int buf = q & 1;
+    if (!bar_wait(bar_full + 8 * slot, fph, s_abort)) { if (lane == 0) atomicExch(p.status, 3); return; }
+    const uint32_t row0 = (uint32_t)(rt0 + q) * TL_ROWS;
+    const uint32_t lowbits = contig ? (off_base + row0 * row_step) & 15u : (off_base + (row0 + g) * row_step) & 15u;
+    const uint32_t rg = ring_a + (uint32_t)slot * stage_bytes + (uint32_t)g * row_stride + lowbits;   // row g of the stage
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    int sbi = first;
+    if (skip_math) {
+      while (sbi < nsb) sbi += TL_CW;
+    } else {
+      for (; sbi < nsb; sbi += TL_CW) {
+        const uint32_t pg = rg + (uint32_t)sbi * F::BYTES;
+        if constexpr (QT == KQ_TYPE_Q4_K) unit_q4k<NH>(pg, sbi * 8, A, g, t, acc);
+        if constexpr (QT == KQ_TYPE_Q6_K) {
+          // every branch here is taken by all 32 lanes alike (the units contain warp-wide mma instructions)
+          if (!rows_same_parity) unit_q6k<NH, 2>(pg, sbi * 8, A, g, t, acc);
+          else if (pg & 2) unit_q6k<NH, 1>(pg, sbi * 8, A, g, t, acc);
+          else unit_q6k<NH, 0>(pg, sbi * 8, A, g, t, acc);
+        }
+      }
+    }
+    first = sbi - nsb;   // (q * nsb + sbi) % 16 == warp carries over to the next stage
+    __syncwarp();
+    if (lane == 0) bar_arrive(bar_empty + 8 * slot);
+    if (++slot == S) { slot = 0; fph ^= 1u; }
+    if (q >= 2 && !bar_wait(bar_rempty + 8 * buf, (uint32_t)(((q >> 1) - 1) & 1), s_abort)) {
+      if (lane == 0) atomicExch(p.status, 4);
+      return;
+    }
+    sRed[(buf * TL_CW + warp) * 32 + lane] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    __syncwarp();
+    if (lane == 0) bar_arrive(bar_rfull + 8 * buf);
+  }
+  if (p.ks > 1) {
+    // split-K finish: add the splits' partials in split order (deterministic) for the tiles this CTA completed
+    if (!bar_wait(bar_fin, 0, s_abort)) { if (lane == 0) atomicExch(p.status, 6); return; }
+    const uint8_t* s_last = reinterpret_cast<const uint8_t*>(sRed);
+    OutT* y = reinterpret_cast<OutT*>(p.y);
+    const int nks = p.ks;
+    for (int idx = warp; idx < nst; idx += TL_CW) {
+      if (!s_last[idx]) continue;
+      const int rt = rt0 + idx, row0 = rt * TL_ROWS;
+#pragma unroll
+      for (int i = 0; i < 2 * NH; ++i) {
+        const int row = row0 + g, tl = 2 * t + (i & 1) + 8 * (i >> 1);
+        if (row < p.n && tl < p.mcount) {
+          float v[4];
+#pragma unroll
+          for (int sp = 0; sp < 4; ++sp) v[sp] = sp < nks ? __ldcg(p.part + ((size_t)sp * 16 + tl) * p.n + row) : 0.f;
+          float tot = v[0];
+#pragma unroll
+          for (int sp = 1; sp < 4; ++sp) if (sp < nks) tot += v[sp];
+          y[(size_t)(p.m0 + tl) * p.stride_y + row] = from_f32<OutT>(tot);
+        }
+      }
+      if (lane == 0) p.cnt[rt] = 0;   // ready for the next launch on this scratch
+    }
+  }
+}
+
+int tl_sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  }
+  return n;
+}
+
+// smallest K split whose activation slice leaves room for a ring of >= 4 stages
+bool make_tile_config(int type, int64_t n, int64_t k, int mtok, TileConfig& c) {
+  if (type != KQ_TYPE_Q4_K && type != KQ_TYPE_Q6_K) return false;
+  int blk, bytes;
+  if (!type_geometry(type, &blk, &bytes)) return false;
+  if (k % blk) return false;
+  const int nblk = (int)(k / blk);
+  const int64_t rowbytes = (int64_t)nblk * bytes;
+  const int sms = tl_sm_count();
+  const int seg_mode = options().tile_segments;   // 1: row segments even when the slice is the whole row
+  for (int ks = 1; ks <= 4; ks *= 2) {
+    if (nblk < ks) break;
+    const int grid = sms / ks * ks;
+    const int nsb = (nblk + ks - 1) / ks;
+    const int klen = nsb * blk;
+    const int contig = (ks == 1 && !seg_mode) ? 1 : 0;
+    const int resid = type == KQ_TYPE_Q4_K ? 32 : 16;   // row stride mod 128: spreads the 8 rows over the banks
+    int row_stride = (int)rowbytes;
+    int stage_bytes;
+    if (contig) {
+      stage_bytes = (int)((TL_ROWS * rowbytes + 16 + 127) / 128 * 128);
+    } else {
+      row_stride = ((nsb * bytes + 16 + 15) / 16) * 16;
+      while (row_stride % 128 != resid) row_stride += 16;
+      stage_bytes = (TL_ROWS * row_stride + 127) / 128 * 128;
+    }
+    const int a_stride = klen + resid;
+    const int a_bytes = (mtok * a_stride + 127) / 128 * 128;
+    const int d_bytes = ((klen / 32) * 64 + 127) / 128 * 128;
+    const int z_bytes = type == KQ_TYPE_Q4_K ? d_bytes : 0;
+    const int fixed = TL_HEADER + a_bytes + d_bytes + z_bytes + 2 * TL_CW * 512;
+    int stages = (TL_SMEM_LIMIT - fixed) / stage_bytes;
+    if (stages > TL_MAX_STAGES) stages = TL_MAX_STAGES;
+    if (stages < 3) continue;
+    if (ks > 1 && (int64_t)(n + TL_ROWS - 1) / TL_ROWS / (grid / ks) + 1 > 2 * TL_CW * 512) continue;   // finish list
+    if (stages < 4 && ks < 4 && nblk >= 2 * ks) continue;   // a deeper ring with a finer split is better
+    c.ks = ks; c.grid = grid; c.stages = stages; c.row_stride = row_stride; c.stage_bytes = stage_bytes; c.contig = contig;
+    c.a_stride = a_stride; c.a_bytes = a_bytes; c.d_bytes = d_bytes; c.z_bytes = z_bytes;
+    c.smem = fixed + stages * stage_bytes;
+    return true;
+  }
+  return false;
+}
+
+template <int QT, int NH, typename OutT>
+int launch_tile(const TileParams& p, const TileConfig& c, cudaStream_t st) {
+  auto kern = gemv_tile_kernel<QT, NH, OutT>;
+  static bool configured = false;
+  if (!configured) {
+    KQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TL_SMEM_LIMIT));
+    configured = true;
+  }
+  KQ_CUDA_TRY(launch_pdl(kern, dim3(c.grid), dim3(TL_THREADS), (size_t)c.smem, st, options().pdl != 0, p));
+  options().launches += 1;
+  KQ_CUDA_TRY(cudaGetLastError());
+  return KQ_OK;
+}
+
+template <int QT>
+int launch_tile_typed(const TileParams& p, const TileConfig& c, int nh, int y_dtype, cudaStream_t st) {
+  switch (y_dtype) {
+    case KQ_F32: return nh == 2 ? launch_tile<QT, 2, float>(p, c, st) : launch_tile<QT, 1, float>(p, c, st);
+    case KQ_F16: return nh == 2 ? launch_tile<QT, 2, __half>(p, c, st) : launch_tile<QT, 1, __half>(p, c, st);
+    case KQ_BF16: return nh == 2 ? launch_tile<QT, 2, __nv_bfloat16>(p, c, st) : launch_tile<QT, 1, __nv_bfloat16>(p, c, st);
+  }
+  set_error("unsupported output dtype %d", y_dtype);
+  return KQ_EUNSUPPORTED;
+}
+
+}  // namespace
+
+bool gemv_tile_supported(const void* W, int type, int64_t n, int64_t k, int mtok) {
+  if ((uintptr_t)W % 2) return false;
+  TileConfig c;
+  return make_tile_config(type, n, k, mtok > 8 ? 16 : 8, c);
+}
+
+// one pass of up to 16 tokens starting at m0 (a multiple of 16)
+int launch_gemv_tile(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m0, int mcount, void* y,
+                     int y_dtype, int64_t stride_y, bool mmq, cudaStream_t st) {
+  const int nh = mcount > 8 ? 2 : 1;
+  TileConfig c;
+  if (!make_tile_config(type, n, k, 8 * nh, c)) { set_error("tile GEMV: shape not covered"); return KQ_EUNSUPPORTED; }
+  int blk, bytes;
+  type_geometry(type, &blk, &bytes);
+  TileParams p;
+  p.W = (const uint8_t*)W; p.rowbytes = k / blk * bytes; p.n = (int)n; p.nblk = (int)(k / blk); p.ks = c.ks;
+  p.ntiles = (int)((n + TL_ROWS - 1) / TL_ROWS); p.stages = c.stages; p.row_stride = c.row_stride;
+  p.stage_bytes = c.stage_bytes; p.contig = c.contig; p.a_stride = c.a_stride; p.a_bytes = c.a_bytes;
+  p.d_bytes = c.d_bytes; p.z_bytes = c.z_bytes; p.qs = P.qs; p.dT = P.dT;
+  p.zT = type == KQ_TYPE_Q4_K ? (mmq ? P.zs8 : P.z32) : nullptr;
+  p.kpad = (int)P.kpad; p.nb32tot = (int)(P.kpad / 32); p.m0 = (int)m0; p.mcount = mcount;
+  p.prefetch = options().pdl < c.stages ? options().pdl : c.stages;
+  p.debug = options().tile_debug;
+  p.y = y; p.stride_y = stride_y; p.part = P.part; p.cnt = P.cnt; p.status = P.status;
+  return type == KQ_TYPE_Q4_K ? launch_tile_typed<KQ_TYPE_Q4_K>(p, c, nh, y_dtype, st)
+                              : launch_tile_typed<KQ_TYPE_Q6_K>(p, c, nh, y_dtype, st);
+}
+
+}  // namespace kq

@@ -182,6 +182,38 @@ def test_tcgen05_gemv_q4k_matches_oracle(n, k, m, mmq):
     assert rel_l2(to_np(y), to_np(y1)) < TIGHT          # every row, against the general kernel
 
 
+@pytest.mark.parametrize("qt", [12, 14])
+@pytest.mark.parametrize("n,k,m", [(8, 256, 5), (17, 512, 8), (100, 1024, 9), (2368, 2048, 12), (4736, 5120, 16),
+                                   (333, 4352, 16), (70, 17408, 5), (1190, 17408, 16), (48, 768, 33), (3000, 14336, 13)])
+@pytest.mark.parametrize("mmq", [False, True])
+@pytest.mark.parametrize("segments", [0, 1])
+def test_shared_stage_mma_gemv_matches_oracle_and_dp4a(qt, n, k, m, mmq, segments):
+    """gemv_impl=6: sixteen warps share each stage of 8 rows, tokens on the mma's M side, K split when the
+    activation slice would not fit; with tile_segments=1 the rows are fetched as separate segments."""
+    if segments and m not in (8, 16):
+        pytest.skip("segment mode is covered at two token counts")
+    _, wt = wire(qt, n, k, seed=n + k)
+    x, xt = act(m, k, seed=m, dt="bf16")
+    w = wt.cpu().numpy()
+    scratch = torch.empty(capi.workspace_bytes(qt, m, n, k), dtype=torch.uint8, device=dev())
+    capi.set_option("gemv_impl", 6)
+    capi.set_option("tile_segments", segments)
+    try:
+        y = capi.mul_mat(wt, xt, qt, mmq=mmq, out_dtype=torch.float32, scratch=scratch)
+        assert capi.read_status(qt, m, n, k, scratch) == 0
+        yb = capi.mul_mat(wt, xt, qt, mmq=mmq, out_dtype=torch.float32, scratch=scratch)   # counters self-reset
+        capi.set_option("gemv_impl", 1)
+        y1 = capi.mul_mat(wt, xt, qt, mmq=mmq, out_dtype=torch.float32)
+    finally:
+        capi.set_option("gemv_impl", 0)
+        capi.set_option("tile_segments", 0)
+    rows = np.r_[0:min(n, 150), max(0, n - 150):n]
+    want = O.mul_mat(w[rows], qt, x, "mmq" if mmq else "mmvq")
+    assert rel_l2(to_np(y)[:, rows], want) < TIGHT
+    assert torch.equal(y, yb)
+    assert rel_l2(to_np(y), to_np(y1)) < TIGHT          # every row, against the general kernel
+
+
 def test_tensor_core_gemv_declines_unaligned_weights():
     qt, n, k = 14, 32, 512
     _, wt = wire(qt, n, k, seed=1)
