@@ -22,7 +22,7 @@ int cuda_fail(cudaError_t e, const char* what) {
 }
 
 Options& options() {
-  static Options o = {0, 5, 81, 2, 1, 0, 0, 0};
+  static Options o = {0, 3, 81, 2, 1, 0, 0};
   return o;
 }
 
@@ -237,7 +237,6 @@ int kq_set_option(const char* name, int value) {
   if (name && !strcmp(name, "half_fma")) { options().half_fma = value; return KQ_OK; }
   if (name && !strcmp(name, "tc_min_m")) { options().tc_min_m = value; return KQ_OK; }
   if (name && !strcmp(name, "gemm_min_m")) { options().gemm_min_m = value; return KQ_OK; }
-  if (name && !strcmp(name, "tile_debug")) { options().tile_debug = value; return KQ_OK; }
   if (name && !strcmp(name, "tile_segments")) { options().tile_segments = value != 0; return KQ_OK; }
   if (name && !strcmp(name, "pdl")) { options().pdl = value < 0 ? 0 : value; return KQ_OK; }
   set_error("kq_set_option: unknown option");

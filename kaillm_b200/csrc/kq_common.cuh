@@ -32,7 +32,6 @@ struct Options {
   int half_fma;        // 1: fp16 mul+sub contracted in K-quant dequantize
   long long launches;  // kernels launched by this library so far (host-side count)
   int tile_segments;   // 1: the tile GEMV fetches row segments even when its K slice is the whole row
-  int tile_debug;      // timing experiments (results are wrong): 1 no arithmetic, 2 no weight copies
 };
 Options& options();
 

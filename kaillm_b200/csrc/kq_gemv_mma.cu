@@ -1013,7 +1013,7 @@ int launch_gemv_mma(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs&
       continue;
     }
     if (impl == 5) { set_error("tcgen05 GEMV: type/shape not covered"); return KQ_EUNSUPPORTED; }
-    // 5..16 tokens of Q4_K / Q6_K: all warps share a stage of 8 rows, tokens on the mma's M side
+    // 3..16 tokens of Q4_K / Q6_K: the shared-stage mma kernel (all warps of a CTA on every stage of 8 rows)
     if (has_tc && tile_start && (impl == 6 || (impl == 0 && left >= options().tc_min_m)) &&
         gemv_tile_supported(W, type, n, k, (int)(left < 16 ? left : 16))) {
       mcount = (int)(left < 16 ? left : 16);

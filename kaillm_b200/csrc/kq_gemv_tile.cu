@@ -1,24 +1,33 @@
-// Decode GEMV for 5..16 tokens per pass (Q4_K, Q6_K): int8 mma.sync with the TOKENS on the 16-wide M side.
+// Decode GEMV for 3..16 tokens per pass (Q4_K, Q6_K): int8 mma.sync, every warp of the CTA on every stage.
 //
-//   grid      one CTA per SM, in `ks` groups; group s works on K slice s of every weight row it owns
+//   grid      one CTA per SM, in `ks` groups; group s works on K slice s of every weight row it owns (ks is the
+//             smallest of 1, 2, 4 whose activation slice leaves room for a ring of >= 4 stages)
 //   stage     8 consecutive weight rows x the CTA's K slice.  With ks == 1 that is one contiguous piece of the
 //             wire tensor and ONE bulk copy; otherwise eight row segments of a few KB each
 //   CTA       16 consumer warps + 1 reducer warp + 1 producer warp
-//   consumer  ALL sixteen warps work on every stage: the stage's super-blocks are dealt round-robin over the
-//             warps (unit = stage x super-block, unit u belongs to warp u % 16, so the load evens out over a few
-//             stages).  Per 32-weight sub-block one m16n8k32 mma gives the 16 tokens x 8 rows integer dots
-//             (m16n8k16 per 16-weight group for Q6_K); the block scales are applied in fp32 on the way into
-//             the warp's 16 x 8 partial tile.  The Q4_K min term is itself a small GEMM over the eight
-//             sub-blocks of a super-block (mins 0..63, exact in tf32) x (d8 * block sum, split hi + lo), done
-//             with two tf32 mmas per super-block.
-//   reducer   adds the sixteen partial tiles of a stage in warp order (deterministic) and stores the outputs;
-//             with ks > 1 it publishes fp32 partials and the last split to arrive adds them in split order
+//   consumer  the stage's super-blocks are dealt round-robin over the sixteen warps (unit = stage x super-block,
+//             unit u belongs to warp u % 16, so the load evens out over a few stages).  Lane (g, t) unpacks the
+//             weights of row g and reads the activations of token g (and g + 8 for 9..16 tokens); it ends up
+//             with the outputs of row g for tokens 2t, 2t+1, so the block scales it needs are those of its own row.
+//             Q4_K: the 16 A rows of an m16n8k32 mma are the 8 weight rows twice - low nibbles (sub-block 2i) in
+//             rows 0-7, high nibbles (sub-block 2i+1) in rows 8-15 - so the unpacked words are the A fragment
+//             as they stand; one mma against the activations of each of the two sub-blocks, half of each result
+//             unused.  Q6_K: the same with the two 16-weight scale groups of a 32-block and m16n8k16.
+//             The scales are applied in fp32 on the way into the warp's 8 x 16 partial tile.  The Q4_K min term
+//             is a small GEMM over the eight sub-blocks of a super-block (mins 0..63, exact in tf32) x
+//             (d8 * block sum, split hi + lo): two tf32 mmas per super-block and token half.
+//   reducer   adds the sixteen partial tiles of a stage in warp order (deterministic) and stores the outputs.
+//             With ks > 1 it stores fp32 partials instead; after its last stage it raises the tiles' counters
+//             (one fence, one round of atomics), and the consumer warps, idle by then, finish in parallel the
+//             tiles at which this CTA arrived last, adding the splits in split order.
 //   rings     stage ring: full (copy bytes) / empty (16 consumer arrivals);  partial-tile ring of two buffers:
 //             red_full (16 arrivals) / red_empty (reducer), so a consumer runs at most two stages ahead
 //
 // Every consumer visits every stage, so a parity wait is never more than one phase behind.  All waits are
-// bounded (about 2^27 clocks): the waiter raises a CTA-wide abort flag and a status word, every warp leaves
-// its loop and the producer waits, again bounded, for the copies it has in flight.
+// bounded (about 2^27 clocks) and sleep between polls: the waiter raises a CTA-wide abort flag and a status
+// word, every warp leaves its loop and the producer waits, again bounded, for the copies it has in flight.
+// No branch around an mma depends on the lane: the alignment cases of Q6_K are either the same for all 32
+// lanes or handled without a branch.
 //
 // Combine: vllm_gguf_plugin/csrc/gguf/vecdotq.cuh:328-379 (Q4_K), 447-491 (Q6_K).
 #include "kq_common.cuh"
@@ -31,6 +40,8 @@ constexpr int TL_ROWS = 8;
 constexpr int TL_CW = 16;                         // consumer warps
 constexpr int TL_THREADS = (TL_CW + 2) * 32;      // + reducer + producer
 constexpr int TL_HEADER = 1024;
+constexpr int TL_NRED = 2;                        // partial-tile buffers (a power of two)
+constexpr int TL_SLEEP_C = 64, TL_SLEEP_R = 200, TL_SLEEP_P = 400;   // ns between polls: consumers, reducer, producer
 constexpr int TL_MAX_STAGES = 16;
 constexpr int TL_SMEM_LIMIT = 232448;
 constexpr uint32_t TL_MAGIC_I = 0x4B400000u;      // bits of 12582912.0f
@@ -48,7 +59,6 @@ struct TileParams {
   const float* zT;
   int kpad, nb32tot;
   int m0, mcount, prefetch;
-  int debug;   // timing experiments only: 1 = consumers skip the arithmetic, 2 = the producer skips the weight copies
   void* y;
   int64_t stride_y;
   float* part;
@@ -79,13 +89,15 @@ __device__ __forceinline__ bool bar_try(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// bounded wait; SLEEP_NS between polls keeps a waiting warp out of the issue slots of the working ones
+template <int SLEEP_NS = 64>
 __device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (bar_try(bar, parity)) return true;
   const long long t0 = clock64();
   for (int it = 1;; ++it) {
+    __nanosleep(SLEEP_NS);
     if (bar_try(bar, parity)) return true;
-    __nanosleep(32);   // a waiting warp stays out of the issue slots of the working ones
-    if ((it & 15) == 0) {
+    if ((it & 63) == 0) {
       if (*abort_flag) return false;
       if (clock64() - t0 > TL_WAIT_LIMIT) { *abort_flag = 1; return false; }
     }
@@ -100,20 +112,20 @@ __device__ __forceinline__ void copy_g2s(uint32_t dst, const void* src, uint32_t
 // tokens (A, 16 x 32 s8) x weights (B, 32 x 8 s8) -> s32
 __device__ __forceinline__ void mma_i8_k32(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                            uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
       : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 __device__ __forceinline__ void mma_i8_k16(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+  asm("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
                : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
                : "r"(a0), "r"(a1), "r"(b0), "r"(0));
 }
 // d += A (16 x 8 tf32) x B (8 x 8 tf32)
 __device__ __forceinline__ void mma_tf32_k8(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                             uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -127,32 +139,14 @@ __device__ __forceinline__ int sbyte_of(uint32_t w, int i) {   // sign-extended 
   return (int)r;
 }
 
-// shared-memory loads by 32-bit shared address: keeps every access an LDS with an immediate offset
-__device__ __forceinline__ uint32_t lds32(uint32_t a) {
-  uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ uint2 lds64(uint32_t a) {
-  uint2 v;
-  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ uint4 lds128(uint32_t a) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ float2 ldsf2(uint32_t a) {
-  float2 v;
-  asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a));
-  return v;
-}
-__device__ __forceinline__ float ldsf(uint32_t a) {
-  float v;
-  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
-  return v;
-}
+// shared-memory loads by byte offset into the CTA's dynamic shared memory: ordinary loads (the compiler may
+// schedule them around the arithmetic, but never across an mbarrier wait, which clobbers memory)
+extern __shared__ __align__(128) uint8_t tl_smem[];
+__device__ __forceinline__ uint32_t lds32(uint32_t a) { return *reinterpret_cast<const uint32_t*>(tl_smem + a); }
+__device__ __forceinline__ uint2 lds64(uint32_t a) { return *reinterpret_cast<const uint2*>(tl_smem + a); }
+__device__ __forceinline__ uint4 lds128(uint32_t a) { return *reinterpret_cast<const uint4*>(tl_smem + a); }
+__device__ __forceinline__ float2 ldsf2(uint32_t a) { return *reinterpret_cast<const float2*>(tl_smem + a); }
+__device__ __forceinline__ float ldsf(uint32_t a) { return *reinterpret_cast<const float*>(tl_smem + a); }
 // 32 bits at a 2-byte aligned address.  AL = 0: the address is 4-byte aligned; 1: it is 2 mod 4; 2: either, decided
 // per lane without a branch (the callers sit between warp-wide mma instructions and must not diverge)
 template <int AL>
@@ -165,7 +159,7 @@ __device__ __forceinline__ uint32_t lds32_h(uint32_t a) {
   }
 }
 
-struct TileView {       // shared addresses of the CTA's activation slice
+struct TileView {       // byte offsets (into the dynamic shared memory) of the CTA's activation slice
   uint32_t sA;          // [tokens][a_stride] codes
   uint32_t a_stride;
   uint32_t sD;          // [32-block][16 tokens] fp32 d8
@@ -274,9 +268,7 @@ __device__ __forceinline__ void unit_q6k(uint32_t pg, int b0, const TileView& A,
       }
     }
   }
-  unsigned short dw;
-  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(dw) : "r"(pg + 208));
-  const float d = __half2float(__ushort_as_half(dw));
+  const float d = __half2float(*reinterpret_cast<const __half*>(tl_smem + pg + 208));
 #pragma unroll
   for (int i = 0; i < 2 * NH; ++i) acc[i] = fmaf(d, u[i], acc[i]);
 }
@@ -286,14 +278,14 @@ __device__ __forceinline__ void unit_q6k(uint32_t pg, int b0, const TileView& A,
 template <int QT, int NH, typename OutT>
 __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TileParams p) {
   using F = Fmt<QT>;
-  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* const smem = tl_smem;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem + TL_HEADER - 8);
   uint8_t* sA = smem + TL_HEADER;
   float* sD = reinterpret_cast<float*>(sA + p.a_bytes);
   float* sZ = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sD) + p.d_bytes);
   float4* sRed = reinterpret_cast<float4*>(reinterpret_cast<uint8_t*>(sZ) + p.z_bytes);   // [2][16 warps][32 lanes]
-  uint8_t* ring = reinterpret_cast<uint8_t*>(sRed) + 2 * TL_CW * 512;
+  uint8_t* ring = reinterpret_cast<uint8_t*>(sRed) + TL_NRED * TL_CW * 512;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int S = p.stages;
@@ -306,13 +298,13 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
   const int blk0 = (int)((int64_t)ks * p.nblk / p.ks), blk1 = (int)((int64_t)(ks + 1) * p.nblk / p.ks);
   const int nsb = blk1 - blk0;
   const uint32_t bar_full = s_u32(bars), bar_empty = s_u32(bars + TL_MAX_STAGES), bar_act = s_u32(bars + 2 * TL_MAX_STAGES);
-  const uint32_t bar_rfull = s_u32(bars + 2 * TL_MAX_STAGES + 1), bar_rempty = s_u32(bars + 2 * TL_MAX_STAGES + 3);
-  const uint32_t bar_fin = s_u32(bars + 2 * TL_MAX_STAGES + 5);   // split-K: the reducer has published this CTA's tiles
+  const uint32_t bar_rfull = s_u32(bars + 2 * TL_MAX_STAGES + 1), bar_rempty = s_u32(bars + 2 * TL_MAX_STAGES + 1 + TL_NRED);
+  const uint32_t bar_fin = s_u32(bars + 2 * TL_MAX_STAGES + 1 + 2 * TL_NRED);   // split-K: the reducer has published this CTA's tiles
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) { bar_init(bar_full + 8 * s, 1); bar_init(bar_empty + 8 * s, TL_CW); }
     bar_init(bar_act, 1);
-    for (int b = 0; b < 2; ++b) { bar_init(bar_rfull + 8 * b, TL_CW); bar_init(bar_rempty + 8 * b, 1); }
+    for (int b = 0; b < TL_NRED; ++b) { bar_init(bar_rfull + 8 * b, TL_CW); bar_init(bar_rempty + 8 * b, 1); }
     bar_init(bar_fin, 1);
     *s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -328,16 +320,14 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
     const int ntok = p.mcount < 8 * NH ? p.mcount : 8 * NH;
     const size_t seg0 = (size_t)blk0 * F::BYTES;
     const uint32_t seglen = (uint32_t)nsb * F::BYTES;
-    const int contig = p.contig, skip_copies = p.debug == 2;
+    const int contig = p.contig;
     int slot = 0;          // ring position of the next stage to issue
     uint32_t eph = 1;      // parity that shows the slot's previous contents consumed (passes at once on the first lap)
     auto issue_stage = [&](int q) {
       const int row0 = (rt0 + q) * TL_ROWS;
       const uint32_t dst = s_u32(ring + (size_t)slot * p.stage_bytes);
       const uint32_t bar = bar_full + 8 * slot;
-      if (skip_copies) {
-        if (lane == 0) bar_arrive(bar);
-      } else if (contig) {
+      if (contig) {
         if (lane == 0) {
           const int rows = (p.n - row0) < TL_ROWS ? (p.n - row0) : TL_ROWS;
           const uintptr_t ga = (uintptr_t)(p.W + (size_t)row0 * p.rowbytes);
@@ -382,7 +372,7 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
     }
     bool ok = true;
     for (; q < nst; ++q) {
-      if (q >= S) ok = bar_wait(bar_empty + 8 * slot, eph, s_abort);
+      if (q >= S) ok = bar_wait<TL_SLEEP_P>(bar_empty + 8 * slot, eph, s_abort);
       if (!ok) break;
       issue_stage(q);
     }
@@ -407,8 +397,8 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
     const int g = lane >> 2, t = lane & 3;
     const int nks = p.ks;
     for (int q = 0; q < nst; ++q) {
-      const int buf = q & 1;
-      if (!bar_wait(bar_rfull + 8 * buf, (uint32_t)((q >> 1) & 1), s_abort)) { if (lane == 0) atomicExch(p.status, 5); return; }
+      const int buf = q & (TL_NRED - 1);
+      if (!bar_wait<TL_SLEEP_R>(bar_rfull + 8 * buf, (uint32_t)((q / TL_NRED) & 1), s_abort)) { if (lane == 0) atomicExch(p.status, 5); return; }
       float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
       for (int w = 0; w < TL_CW; ++w) {
@@ -445,12 +435,12 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
 
   // -------------------------------------------------------------------- consumers
   if (!bar_wait(bar_act, 0, s_abort)) { if (lane == 0) atomicExch(p.status, 2); return; }
-  const TileView A{s_u32(sA), (uint32_t)p.a_stride, s_u32(sD), s_u32(sZ)};
+  const TileView A{(uint32_t)(sA - smem), (uint32_t)p.a_stride, (uint32_t)(reinterpret_cast<uint8_t*>(sD) - smem),
+                   (uint32_t)(reinterpret_cast<uint8_t*>(sZ) - smem)};
   const int g = lane >> 2, t = lane & 3;
   const int contig = p.contig;
   const uint32_t row_stride = contig ? (uint32_t)p.rowbytes : (uint32_t)p.row_stride;
-  const uint32_t stage_bytes = (uint32_t)p.stage_bytes, ring_a = s_u32(ring);
-  const int skip_math = p.debug == 1;
+  const uint32_t stage_bytes = (uint32_t)p.stage_bytes, ring_a = (uint32_t)(ring - smem);
   const bool rows_same_parity = (p.rowbytes & 3) == 0 && (row_stride & 3u) == 0;   // all rows of a stage equally aligned mod 4
   // row r of a stage starts at r * row_stride + the low four bits of its global address
   const uint32_t off_base = (uint32_t)(((uintptr_t)p.W + (size_t)blk0 * F::BYTES) & 15);
@@ -459,32 +449,28 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
   int slot = 0;
   uint32_t fph = 0;
   for (int q = 0; q < nst; ++q) {
-    const int buf = q & 1;
-    if (!bar_wait(bar_full + 8 * slot, fph, s_abort)) { if (lane == 0) atomicExch(p.status, 3); return; }
+    const int buf = q & (TL_NRED - 1);
+    if (!bar_wait<TL_SLEEP_C>(bar_full + 8 * slot, fph, s_abort)) { if (lane == 0) atomicExch(p.status, 3); return; }
     const uint32_t row0 = (uint32_t)(rt0 + q) * TL_ROWS;
     const uint32_t lowbits = contig ? (off_base + row0 * row_step) & 15u : (off_base + (row0 + g) * row_step) & 15u;
     const uint32_t rg = ring_a + (uint32_t)slot * stage_bytes + (uint32_t)g * row_stride + lowbits;   // row g of the stage
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     int sbi = first;
-    if (skip_math) {
-      while (sbi < nsb) sbi += TL_CW;
-    } else {
-      for (; sbi < nsb; sbi += TL_CW) {
-        const uint32_t pg = rg + (uint32_t)sbi * F::BYTES;
-        if constexpr (QT == KQ_TYPE_Q4_K) unit_q4k<NH>(pg, sbi * 8, A, g, t, acc);
-        if constexpr (QT == KQ_TYPE_Q6_K) {
-          // every branch here is taken by all 32 lanes alike (the units contain warp-wide mma instructions)
-          if (!rows_same_parity) unit_q6k<NH, 2>(pg, sbi * 8, A, g, t, acc);
-          else if (pg & 2) unit_q6k<NH, 1>(pg, sbi * 8, A, g, t, acc);
-          else unit_q6k<NH, 0>(pg, sbi * 8, A, g, t, acc);
-        }
+    for (; sbi < nsb; sbi += TL_CW) {
+      const uint32_t pg = rg + (uint32_t)sbi * F::BYTES;
+      if constexpr (QT == KQ_TYPE_Q4_K) unit_q4k<NH>(pg, sbi * 8, A, g, t, acc);
+      if constexpr (QT == KQ_TYPE_Q6_K) {
+        // every branch here is taken by all 32 lanes alike (the units contain warp-wide mma instructions)
+        if (!rows_same_parity) unit_q6k<NH, 2>(pg, sbi * 8, A, g, t, acc);
+        else if (pg & 2) unit_q6k<NH, 1>(pg, sbi * 8, A, g, t, acc);
+        else unit_q6k<NH, 0>(pg, sbi * 8, A, g, t, acc);
       }
     }
     first = sbi - nsb;   // (q * nsb + sbi) % 16 == warp carries over to the next stage
     __syncwarp();
     if (lane == 0) bar_arrive(bar_empty + 8 * slot);
     if (++slot == S) { slot = 0; fph ^= 1u; }
-    if (q >= 2 && !bar_wait(bar_rempty + 8 * buf, (uint32_t)(((q >> 1) - 1) & 1), s_abort)) {
+    if (q >= TL_NRED && !bar_wait<TL_SLEEP_C>(bar_rempty + 8 * buf, (uint32_t)(((q / TL_NRED) - 1) & 1), s_abort)) {
       if (lane == 0) atomicExch(p.status, 4);
       return;
     }
@@ -558,11 +544,11 @@ bool make_tile_config(int type, int64_t n, int64_t k, int mtok, TileConfig& c) {
     const int a_bytes = (mtok * a_stride + 127) / 128 * 128;
     const int d_bytes = ((klen / 32) * 64 + 127) / 128 * 128;
     const int z_bytes = type == KQ_TYPE_Q4_K ? d_bytes : 0;
-    const int fixed = TL_HEADER + a_bytes + d_bytes + z_bytes + 2 * TL_CW * 512;
+    const int fixed = TL_HEADER + a_bytes + d_bytes + z_bytes + TL_NRED * TL_CW * 512;
     int stages = (TL_SMEM_LIMIT - fixed) / stage_bytes;
     if (stages > TL_MAX_STAGES) stages = TL_MAX_STAGES;
     if (stages < 3) continue;
-    if (ks > 1 && (int64_t)(n + TL_ROWS - 1) / TL_ROWS / (grid / ks) + 1 > 2 * TL_CW * 512) continue;   // finish list
+    if (ks > 1 && (int64_t)(n + TL_ROWS - 1) / TL_ROWS / (grid / ks) + 1 > TL_NRED * TL_CW * 512) continue;   // finish list
     if (stages < 4 && ks < 4 && nblk >= 2 * ks) continue;   // a deeper ring with a finer split is better
     c.ks = ks; c.grid = grid; c.stages = stages; c.row_stride = row_stride; c.stage_bytes = stage_bytes; c.contig = contig;
     c.a_stride = a_stride; c.a_bytes = a_bytes; c.d_bytes = d_bytes; c.z_bytes = z_bytes;
@@ -621,7 +607,6 @@ int launch_gemv_tile(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs
   p.zT = type == KQ_TYPE_Q4_K ? (mmq ? P.zs8 : P.z32) : nullptr;
   p.kpad = (int)P.kpad; p.nb32tot = (int)(P.kpad / 32); p.m0 = (int)m0; p.mcount = mcount;
   p.prefetch = options().pdl < c.stages ? options().pdl : c.stages;
-  p.debug = options().tile_debug;
   p.y = y; p.stride_y = stride_y; p.part = P.part; p.cnt = P.cnt; p.status = P.status;
   return type == KQ_TYPE_Q4_K ? launch_tile_typed<KQ_TYPE_Q4_K>(p, c, nh, y_dtype, st)
                               : launch_tile_typed<KQ_TYPE_Q6_K>(p, c, nh, y_dtype, st);
