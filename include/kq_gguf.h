@@ -146,9 +146,15 @@ int kq_debug_group_dots(const void* W, int type, int64_t n, int64_t k,
 int kq_read_status(int type, int64_t m, int64_t n, int64_t k, const void* scratch, size_t scratch_bytes, int* status);
 
 /* Runtime knobs for tests and profiling (process-wide, not thread-safe against concurrent launches):
- *   "gemv_impl"   0 = choose by shape (default), 1 = general dp4a kernel, 2 = streaming int8-mma kernel,
- *                 3 = row-streaming dp4a kernel, 4 = the same without the Q4_K specialisation
- *   "tc_min_m"    smallest m that the int8-mma kernel takes in mode 0 (default 5)
+ *   "gemv_impl"   0 = choose by shape (default), 1 = general dp4a kernel, 2 = tile-per-warp int8-mma kernel,
+ *                 3 = row-streaming dp4a kernel, 4 = the same without the specialised Q4_K / Q6_K consumers,
+ *                 5 = tcgen05 kind::i8 kernel (Q4_K), 6 = shared-stage int8-mma kernel (Q4_K, Q6_K);
+ *                 a forced kernel that does not cover the type or shape returns KQ_EUNSUPPORTED
+ *   "tc_min_m"    smallest m that the shared-stage int8-mma kernel takes in mode 0 (default 3)
+ *   "pdl"         0 = plain launches; p > 0 (default 2) = the quantizer and the streaming kernels are launched
+ *                 with programmatic stream serialization and prefetch p ring stages of weights before they
+ *                 wait for the previous kernel of the stream
+ *   "tile_segments" 1 = the shared-stage kernel fetches row segments even when a stage is contiguous (default 0)
  *   "gemm_min_m"  smallest m that goes to the tcgen05 GEMM (default 81: m <= 80 keeps exact integer dots)
  *   "half_fma"    1 = K-quant dequantize contracts fp16 mul+sub into one fma (default), 0 = two roundings
  * Returns KQ_EINVAL for an unknown name. */
