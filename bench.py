@@ -41,6 +41,11 @@ K_HID, N_FF = 5120, 17408
 MS = (1, 2, 8, 16)
 
 
+# DRAM bytes per Q4_K 17408x5120 GEMV launch measured by ncu (dram__bytes_read.sum + dram__bytes_write.sum):
+# 50.16 MB for the row-streaming kernel (1-2 tokens), 50.24 MB for the shared-stage kernel (8-16 tokens)
+DRAM_TRAFFIC_Q4K = 50.2e6
+
+
 def algorithmic_bytes(qt: int, n: int, k: int, m: int, esize: int = 2) -> int:
     blk, nb = {12: (256, 144), 14: (256, 210)}[qt]
     return n * (k // blk) * nb + m * k * esize + m * n * esize
@@ -294,10 +299,12 @@ def main() -> None:
         alg = sum(algorithmic_bytes(Q4_K, N_FF // world, K_HID, m) for m in MS) / len(MS)
         peak, how = measured_peaks()
         ach = alg / (us * 1e-6) / 1e9
-        roof = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+        roof = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": DRAM_TRAFFIC_Q4K / world,
                 "kernel": "Q4_K decode GEMV (gate/up 17408x5120), mean over M=1,2,8,16", "us_per_launch": us,
                 "algorithmic_bytes_per_launch": alg, "peak_source": f"of {how} (MEASURED_PEAKS.json hbm_gbs)",
-                "note": "region = 4 q8_1 quantize launches + %d GEMV launches, divided by the GEMV launches" % n_launch}
+                "note": "region = 4 q8_1 quantize launches + %d GEMV launches, divided by the GEMV launches; traffic = "
+                        "dram__bytes_read+write per launch from the ncu captures summarised under profiles/ "
+                        "(50.16 MB row-streaming kernel, 50.24 MB shared-stage kernel; full matrix, scaled by 1/ranks)" % n_launch}
 
     # ---- prefill GEMM (tcgen05): Q4_K N=17408 K=5120 at M=2048, TFLOP/s against the measured bf16 tensor peak
     prefill = None
