@@ -216,12 +216,46 @@ def main() -> None:
     bytes_step = sum(algorithmic_bytes(qt, n, k, m) for m in MS for _, qt, n, k in mats)
     calls_step = len(MS) * len(mats)
 
+    # N > 1: every output slice is all-gathered.  The gather is the library's own peer-store kernel over NVLink
+    # (kq_p2p_allgather on torch symmetric memory; NCCL all_gather_into_tensor if symmetric memory cannot be set up).
+    # The gather of call i runs on a second stream and overlaps the GEMV of call i+1 (the calls of this workload are
+    # independent); every call has its own slice and gather buffer, and a step ends only when all gathers have
+    # completed (the side stream is joined into the main one).
+    comm = torch.cuda.Stream(device=dev) if world > 1 else None
+    p2p = None
+    gather_how = None
+    if world > 1:
+        from kaillm_b200 import sharded
+        ysl = [torch.empty((m, n // world), dtype=torch.bfloat16, device=dev) for m in MS for _, _, n, _ in mats]
+        try:
+            p2p = sharded.P2PGather(max_bytes=max(MS) * (N_FF // world) * 2, nbuf=len(ysl), device=dev)
+            gather_how = "kq_p2p_allgather (peer stores over NVLink)"
+        except Exception as e:  # noqa: BLE001 - keep the NCCL path
+            print(f"[bench] symmetric memory unavailable ({e!r}); using NCCL all_gather_into_tensor", file=sys.stderr)
+            ygl = [torch.empty((world, m, n // world), dtype=torch.bfloat16, device=dev) for m in MS for _, _, n, _ in mats]
+            gather_how = "NCCL all_gather_into_tensor"
+
     def step():
+        cur = torch.cuda.current_stream()
+        if world > 1:
+            comm.wait_stream(cur)
+        i = 0
         for m in MS:
             for W, qt, n, k in mats:
-                y = capi.mul_mat(W, xs[(m, k)], qt, mmq=use_mmq(m, n), out=ys[(m, n)], scratch=scratch, n=n // world)
+                out = ysl[i] if world > 1 else ys[(m, n)]
+                y = capi.mul_mat(W, xs[(m, k)], qt, mmq=use_mmq(m, n), out=out, scratch=scratch, n=n // world)
                 if world > 1:
-                    dist.all_gather_into_tensor(yg[(m, n)], y)
+                    ev = torch.cuda.Event()
+                    ev.record(cur)
+                    with torch.cuda.stream(comm):
+                        comm.wait_event(ev)
+                        if p2p is not None:
+                            p2p.gather_raw(y, i)
+                        else:
+                            dist.all_gather_into_tensor(ygl[i], y)
+                i += 1
+        if world > 1:
+            cur.wait_stream(comm)
 
     def barrier():
         if world > 1:
@@ -360,7 +394,10 @@ def main() -> None:
                 stream.wait_event(ev)
                 y = linear.fused_mul_mat_gguf(dxs[i], W, qt)
                 if world > 1:
-                    dist.all_gather_into_tensor(yg[(m, n)], y)
+                    if p2p is not None:
+                        p2p.gather_raw(y, i)
+                    else:
+                        dist.all_gather_into_tensor(yg[(m, n)], y)
                 ev2 = torch.cuda.Event()
                 ev2.record(stream)
                 with torch.cuda.stream(s_out):
@@ -442,6 +479,8 @@ def main() -> None:
                "sample": f"one whole MLP block at M={m} (Q4_K gate+up {r4}x{K_HID}, Q6_K down {r6}x{N_FF}): "
                          "numpy dequantize with gguf-reader arithmetic + torch.matmul fp32"}
 
+    if p2p is not None:
+        p2p.check()
     if rank == 0:
         out = {
             "metric": "quantized GEMV HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
@@ -452,7 +491,9 @@ def main() -> None:
                        "calls_per_step": calls_step, "bytes_per_step": bytes_step,
                        "l2": "stack of %.2f GB per rank >> 126 MB L2, no flush needed" % (sum(w.numel() for w, *_ in mats) / 1e9),
                        "launch": "cuda graph replay" if graph is not None else "eager",
-                       "parallelism": f"row-sharded x{world} + all-gather" if world > 1 else "single GPU"},
+                       "parallelism": (f"row-sharded x{world} + all-gather of every output by {gather_how} (gathers on a "
+                                       "second stream, overlapping the next call's GEMV; joined at the end of each step)")
+                       if world > 1 else "single GPU"},
             "frac_of_measured_hbm": value / measured_peaks()[0], "frac_of_nominal_8tbs": value / 8000.0,
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches_step * args.steps,
             "roofline": roof, "cpu_baseline": cpu, "prefill_gemm": prefill,

@@ -139,6 +139,26 @@ int kq_debug_group_dots(const void* W, int type, int64_t n, int64_t k,
                         int32_t* dots, int32_t* sums,
                         void* scratch, size_t scratch_bytes, void* stream);
 
+/* All-gather of the ranks' [M, N/world] output slices by peer stores over NVLink (one kernel, no library
+ * collective).  It takes the place of the all-gather that follows a row(N)-sharded linear layer
+ * (vLLM's tensor_model_parallel_all_gather behind the column-parallel GGUF layers whose weights
+ * quantization/params.py:230-247 shards); the reference itself has no such kernel.
+ *   src          this rank's slice (bytes long)
+ *   peer_dst     HOST array of `world` device pointers: every rank's gather buffer (world * bytes each), mapped into
+ *                this process (e.g. torch symmetric memory); entry `rank` is the local buffer.  The slice lands at
+ *                offset rank * bytes of every buffer, so each buffer ends up as [world][M][N/world].
+ *   peer_flags   HOST array of `world` device pointers: every rank's flag array, uint32 [slots][8], zero before the
+ *                first call
+ *   epoch, done  LOCAL device arrays, uint32 [slots], zero before the first call (call counter / CTA counter)
+ *   slot         which flag slot this call uses; calls that may be in flight at the same time need different slots
+ *   status       LOCAL device int: set non-zero if the bounded wait for a peer's flag ran out (kernel returns early)
+ * Every rank must make the same sequence of calls per slot.  When the kernel has completed, the local gather buffer
+ * holds all ranks' slices.  Alternate two gather buffers per stream if the gathered data is read by later kernels
+ * (a peer may write the next call's slice as soon as this rank has published its own next call).
+ * world <= 8.  Only plain loads and stores touch peer memory. */
+int kq_p2p_allgather(const void* src, size_t bytes, void* const* peer_dst, uint32_t* const* peer_flags,
+                     uint32_t* epoch, uint32_t* done, int slot, int rank, int world, int* status, void* stream);
+
 /* Diagnostics: copies the device-side status word of a scratch buffer to the host (SYNCHRONISES with the
  * device; not for the serving path).  0 = every kernel that used the scratch finished normally; non-zero = a
  * bounded wait inside a kernel gave up and the kernel returned early (its outputs are then undefined).

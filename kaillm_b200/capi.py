@@ -22,6 +22,7 @@ EXPORTS = (
     "kq_last_error", "kq_abi_version", "kq_block_geometry", "kq_workspace_bytes", "kq_quantize_q8_1",
     "kq_mul_mat_vec_a8", "kq_mul_mat_a8", "kq_dequantize", "kq_debug_group_dots", "kq_set_option",
     "kq_get_option", "kq_prepare_q8", "kq_mul_mat_prepared", "kq_read_status", "kq_mul_mat_vec_a8_static",
+    "kq_p2p_allgather",
 )
 
 
@@ -54,6 +55,7 @@ def _load() -> ctypes.CDLL:
     lib.kq_dequantize.argtypes = [vp, i32, i64, vp, i32, vp]
     lib.kq_read_status.argtypes = [i32, i64, i64, i64, vp, sz, ctypes.POINTER(i32)]
     lib.kq_debug_group_dots.argtypes = [vp, i32, i64, i64, vp, i32, i64, i64, vp, vp, vp, sz, vp]
+    lib.kq_p2p_allgather.argtypes = [vp, sz, ctypes.POINTER(vp), ctypes.POINTER(vp), vp, vp, i32, i32, i32, vp, vp]
     lib.kq_set_option.argtypes = [ctypes.c_char_p, i32]
     lib.kq_get_option.argtypes = [ctypes.c_char_p, ctypes.POINTER(i32)]
     return lib
@@ -160,6 +162,19 @@ def mul_mat_vec_static(W: torch.Tensor, x: torch.Tensor, qtype: int, out: torch.
         _check(lib.kq_mul_mat_vec_a8_static(W.data_ptr(), qtype, n, k, x.data_ptr(), _DT[x.dtype], m, x.stride(0),
                                             out.data_ptr(), _DT[out.dtype], out.stride(0), _stream(x.device)))
     return out
+
+
+def p2p_allgather(src: torch.Tensor, peer_dst: list[int], peer_flags: list[int], epoch: torch.Tensor,
+                  done: torch.Tensor, slot: int, rank: int, status: torch.Tensor) -> None:
+    """kq_p2p_allgather: push `src` (contiguous) into slot `rank` of every rank's gather buffer and wait for the peers.
+
+    peer_dst / peer_flags are device addresses (ints) valid in this process, one per rank."""
+    world = len(peer_dst)
+    dst = (ctypes.c_void_p * world)(*peer_dst)
+    flg = (ctypes.c_void_p * world)(*peer_flags)
+    with torch.cuda.device(src.device):
+        _check(lib.kq_p2p_allgather(src.data_ptr(), src.numel() * src.element_size(), dst, flg, epoch.data_ptr(),
+                                    done.data_ptr(), slot, rank, world, status.data_ptr(), _stream(src.device)))
 
 
 def dequantize(W: torch.Tensor, qtype: int, count: int, dtype=torch.float16) -> torch.Tensor:

@@ -232,6 +232,15 @@ int kq_read_status(int type, int64_t m, int64_t n, int64_t k, const void* scratc
   return KQ_OK;
 }
 
+int kq_p2p_allgather(const void* src, size_t bytes, void* const* peer_dst, uint32_t* const* peer_flags,
+                     uint32_t* epoch, uint32_t* done, int slot, int rank, int world, int* status, void* stream) {
+  if (!src || !peer_dst || !peer_flags || !epoch || !done || !status) {
+    set_error("kq_p2p_allgather: null pointer argument");
+    return KQ_EINVAL;
+  }
+  return launch_p2p_allgather(src, bytes, peer_dst, peer_flags, epoch, done, slot, rank, world, status, (cudaStream_t)stream);
+}
+
 int kq_set_option(const char* name, int value) {
   if (name && !strcmp(name, "gemv_impl")) { options().gemv_impl = value; return KQ_OK; }
   if (name && !strcmp(name, "half_fma")) { options().half_fma = value; return KQ_OK; }

@@ -140,6 +140,8 @@ int launch_gemv_tile(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs
 bool gemv_tc5_supported(const void* W, int type, int64_t n, int64_t k);
 int launch_gemv_tc5(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m_total, int64_t m0, int mcount,
                     void* y, int y_dtype, int64_t stride_y, bool mmq, cudaStream_t st);
+int launch_p2p_allgather(const void* src, size_t bytes, void* const* peer_dst, uint32_t* const* peer_flags,
+                         uint32_t* epoch, uint32_t* done, int slot, int rank, int world, int* status, cudaStream_t st);
 bool gemm_tc_supported(const void* W, int type, int64_t n, int64_t k);
 int launch_gemm_tc(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m, void* y, int y_dtype,
                    int64_t stride_y, bool mmq, cudaStream_t st);

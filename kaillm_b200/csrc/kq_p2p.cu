@@ -1,0 +1,117 @@
+// All-gather of the ranks' output slices over NVLink by plain peer stores: every rank pushes its [M, N/G] slice into
+// slot `rank` of every rank's gather buffer (the ranks' buffers are mapped into each other's address space by the
+// caller, e.g. through torch symmetric memory), then raises a flag on every rank and waits until the flags of all
+// ranks have reached the same call count.  One small kernel per call, no library collective:
+//
+//   copy     all CTAs: 16-byte loads of the local slice, one 16-byte store per destination rank (the local rank's
+//            own buffer included); byte tail for sizes that are not a multiple of 16
+//   publish  each CTA fences at system scope and counts itself done; the last CTA advances the call's epoch
+//            (a device counter per flag slot, so a captured graph can be replayed) and stores it into
+//            flag[slot][rank] of every rank (release, system scope)
+//   wait     the last CTA's first `world` threads wait (acquire, system scope; sleeping between polls) until
+//            flag[slot][r] >= epoch for every r, so when the kernel has completed the local gather buffer is whole
+//
+// The wait is bounded (about 2^28 clocks): on time-out the kernel writes a status word and returns; the caller
+// reads it with its next synchronisation.  Only plain loads/stores touch peer memory (no TMA, no multicast).
+// Buffer reuse: a rank may overwrite slot `rank` of a peer's buffer as soon as that peer has published the
+// NEXT call on the same stream; a caller that alternates two buffers per stream is race-free.
+#include "kq_common.cuh"
+
+namespace kq {
+
+namespace {
+
+constexpr int P2P_MAX_RANKS = 8;
+constexpr long long P2P_WAIT_LIMIT = 1ll << 28;
+
+struct P2PParams {
+  const uint8_t* src;
+  size_t bytes;
+  uint8_t* dst[P2P_MAX_RANKS];        // each rank's gather buffer (world * bytes)
+  uint32_t* flags[P2P_MAX_RANKS];     // each rank's flag array [slots][P2P_MAX_RANKS]
+  uint32_t* epoch;                    // local: calls made so far per slot
+  uint32_t* done;                     // local: CTAs finished per slot (returns to zero)
+  int* status;
+  int slot, rank, world;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(256) p2p_allgather_kernel(const P2PParams p) {
+  const size_t nvec = p.bytes / 16;
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nthr = (size_t)gridDim.x * blockDim.x;
+  const size_t off0 = (size_t)p.rank * p.bytes;
+  const bool aligned = (((uintptr_t)p.src | off0 | p.bytes) & 15) == 0;
+  if (aligned) {
+    for (size_t i = tid; i < nvec; i += nthr) {
+      const uint4 v = *reinterpret_cast<const uint4*>(p.src + i * 16);
+      for (int r = 0; r < p.world; ++r) *reinterpret_cast<uint4*>(p.dst[r] + off0 + i * 16) = v;
+    }
+  } else {
+    for (size_t i = tid; i < p.bytes; i += nthr) {
+      const uint8_t v = p.src[i];
+      for (int r = 0; r < p.world; ++r) p.dst[r][off0 + i] = v;
+    }
+  }
+  __syncthreads();
+  __shared__ int s_last;
+  if (threadIdx.x == 0) {
+    __threadfence_system();   // this CTA's stores (ordered before by the barrier) are visible system-wide
+    s_last = atomicAdd(p.done + p.slot, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __shared__ uint32_t s_epoch;
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    p.done[p.slot] = 0;
+    const uint32_t e = p.epoch[p.slot] + 1;
+    p.epoch[p.slot] = e;
+    s_epoch = e;
+    for (int r = 0; r < p.world; ++r) st_release_sys(p.flags[r] + p.slot * P2P_MAX_RANKS + p.rank, e);
+  }
+  __syncthreads();
+  if ((int)threadIdx.x < p.world) {
+    const uint32_t e = s_epoch;
+    const uint32_t* f = p.flags[p.rank] + p.slot * P2P_MAX_RANKS + threadIdx.x;
+    const long long t0 = clock64();
+    while ((int32_t)(ld_acquire_sys(f) - e) < 0) {
+      __nanosleep(100);
+      if (clock64() - t0 > P2P_WAIT_LIMIT) { atomicExch(p.status, 1 + (int)threadIdx.x); break; }
+    }
+  }
+}
+
+}  // namespace
+
+int launch_p2p_allgather(const void* src, size_t bytes, void* const* peer_dst, uint32_t* const* peer_flags,
+                         uint32_t* epoch, uint32_t* done, int slot, int rank, int world, int* status, cudaStream_t st) {
+  if (world < 1 || world > P2P_MAX_RANKS || rank < 0 || rank >= world || slot < 0) {
+    set_error("kq_p2p_allgather: world %d (max %d), rank %d, slot %d", world, P2P_MAX_RANKS, rank, slot);
+    return KQ_EINVAL;
+  }
+  if (bytes == 0) return KQ_OK;
+  P2PParams p;
+  p.src = (const uint8_t*)src; p.bytes = bytes; p.epoch = epoch; p.done = done; p.status = status;
+  p.slot = slot; p.rank = rank; p.world = world;
+  for (int r = 0; r < P2P_MAX_RANKS; ++r) {
+    p.dst[r] = r < world ? (uint8_t*)peer_dst[r] : nullptr;
+    p.flags[r] = r < world ? peer_flags[r] : nullptr;
+  }
+  size_t blocks = (bytes / 16 + 255) / 256;
+  if (blocks < 1) blocks = 1;
+  if (blocks > 32) blocks = 32;
+  p2p_allgather_kernel<<<(unsigned)blocks, 256, 0, st>>>(p);
+  options().launches += 1;
+  KQ_CUDA_TRY(cudaGetLastError());
+  return KQ_OK;
+}
+
+}  // namespace kq
