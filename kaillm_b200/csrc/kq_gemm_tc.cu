@@ -30,18 +30,21 @@
 namespace kq {
 namespace {
 
-constexpr int BM = 128;         // weight rows per CTA = UMMA M
-constexpr int BN = 256;         // tokens per CTA = UMMA N
+constexpr int BM = 128;         // UMMA M: weight rows per accumulator (one TMEM lane per row)
+constexpr int RT = 2;           // accumulators (row tiles) per CTA: the CTA covers RT * BM = 256 weight rows
+constexpr int BN = 128;         // tokens per CTA = UMMA N
 constexpr int KSTEP = 128;      // k per pipeline step (two swizzle atoms)
 constexpr int ATOM = 64;        // k per 128-byte swizzle atom (fp16)
-constexpr int NA = 4;           // A ring (TMEM): 4 x 64 columns
-constexpr int NB = 3;           // B ring (shared memory): 3 x 64 KB
-constexpr int DQ_WARPS = 8;     // dequantizing warps: warp w and w+4 share TMEM lanes 32*(w%4).., one atom each
+constexpr int NA = 2;           // A ring (TMEM): 2 slots x (RT x 64) columns
+constexpr int NB = 5;           // B ring (shared memory): 5 x 32 KB
+constexpr int DQ_WARPS = 16;    // dequantizing warps: warp w -> TMEM lanes 32*(w%4).., atom (w>>2)&1 of the step, row tile w>>3
 constexpr int GEMM_THREADS = (DQ_WARPS + 2) * 32;
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t TMEM_D = 0;                 // accumulator: columns [0, BN)
-constexpr uint32_t TMEM_A = 256;               // A ring
-constexpr int B_STAGE_BYTES = BN * KSTEP * 2;  // 64 KB
+constexpr uint32_t TMEM_D = 0;                 // accumulators: row tile t in columns [t * BN, (t + 1) * BN)
+constexpr uint32_t TMEM_A = 256;               // A ring: slot ab, row tile t, atom a at 256 + ab * 128 + t * 64 + a * 32
+constexpr int A_SLOT_COLS = RT * 64;
+constexpr int B_STAGE_BYTES = BN * KSTEP * 2;  // 32 KB
+constexpr int W_STAGE_BYTES = RT * BM * 144;   // Q4_K: one super-block column of the CTA's 256 rows
 constexpr long long GEMM_WAIT_LIMIT = 1ll << 28;
 
 __constant__ uint16_t c_iq3s_codes_g[512] = {
@@ -141,12 +144,29 @@ __device__ __forceinline__ __half corr_coef(const uint8_t* __restrict__ wrow, in
 
 template <int QT>
 __device__ __forceinline__ void corr_atom(const uint8_t* __restrict__ wrow, int atom, int nb32, uint32_t (&out)[32]) {
-#pragma unroll 4
-  for (int i = 0; i < 32; ++i) {
-    const int b = atom * 64 + 2 * i;
-    const __half c0 = b < nb32 ? corr_coef<QT>(wrow, b) : __float2half_rn(0.f);
-    const __half c1 = b + 1 < nb32 ? corr_coef<QT>(wrow, b + 1) : __float2half_rn(0.f);
-    out[i] = h2_bits(__halves2half2(c0, c1));
+  if constexpr (QT == KQ_TYPE_Q4_K) {
+    // 64 coefficients = 8 super-blocks x 8 sub-block mins; one 16-byte header load per super-block
+#pragma unroll
+    for (int sb = 0; sb < 8; ++sb) {
+      const int b0 = atom * 64 + sb * 8;
+      uint4 h = make_uint4(0u, 0u, 0u, 0u);
+      if (b0 < nb32) h = __ldg(reinterpret_cast<const uint4*>(wrow + (size_t)(b0 >> 3) * 144));
+      const __half ndmin = __hneg(__high2half(bits_h2(h.x)));
+      const uint32_t mn[2] = {h.z & 0x3F3F3F3Fu, ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u)};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int m0 = (int)((mn[j >> 1] >> (16 * (j & 1))) & 0xFFu), m1 = (int)((mn[j >> 1] >> (16 * (j & 1) + 8)) & 0xFFu);
+        out[4 * sb + j] = h2_bits(__halves2half2(__hmul_rn(ndmin, __int2half_rn(m0)), __hmul_rn(ndmin, __int2half_rn(m1))));
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const int b = atom * 64 + 2 * i;
+      const __half c0 = b < nb32 ? corr_coef<QT>(wrow, b) : __float2half_rn(0.f);
+      const __half c1 = b + 1 < nb32 ? corr_coef<QT>(wrow, b + 1) : __float2half_rn(0.f);
+      out[i] = h2_bits(__halves2half2(c0, c1));
+    }
   }
 }
 
@@ -259,11 +279,13 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sB = smem;                                            // NB x 64 KB; each atom [BN rows x 128 B] swizzled
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + NB * B_STAGE_BYTES);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 24);
-  volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 25);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 26);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 27);
   uint32_t* s_grid = reinterpret_cast<uint32_t*>(bars + 32);     // IQ3_S codebook (2 KB)
-  const uint32_t bar_bfull = smem_u32(bars), bar_bempty = smem_u32(bars + 4), bar_afull = smem_u32(bars + 8),
-                 bar_aempty = smem_u32(bars + 12), bar_dfull = smem_u32(bars + 16);
+  uint8_t* sW = smem + NB * B_STAGE_BYTES + 4096;                // Q4_K: one super-block column of the tile, 256 rows x 144 B
+  const uint32_t bar_bfull = smem_u32(bars), bar_bempty = smem_u32(bars + 8), bar_afull = smem_u32(bars + 16),
+                 bar_aempty = smem_u32(bars + 20), bar_dfull = smem_u32(bars + 24);
+  static_assert(NB <= 8 && NA <= 4, "barrier layout");
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int row_tile = blockIdx.x / p.ntok_tiles, tok_tile = blockIdx.x % p.ntok_tiles;
@@ -325,12 +347,15 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
                                  (1ull << 46) | (2ull << 61);
 #pragma unroll
           for (int kk = 0; kk < ATOM / 16; ++kk) {
-            const uint32_t ta = tbase + TMEM_A + ab * 64 + a * 32 + kk * 8;
             const uint32_t accum = (s > 0 || a > 0 || kk > 0) ? 1u : 0u;
-            asm volatile(
-                "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-                ::"r"(tbase + TMEM_D), "r"(ta), "l"(bdesc + (uint64_t)((kk * 32) >> 4)), "r"(idesc), "r"(accum) : "memory");
+#pragma unroll
+            for (int t = 0; t < RT; ++t) {   // both row tiles against the same B tile
+              const uint32_t ta = tbase + TMEM_A + ab * A_SLOT_COLS + t * 64 + a * 32 + kk * 8;
+              asm volatile(
+                  "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                  "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                  ::"r"(tbase + TMEM_D + t * BN), "r"(ta), "l"(bdesc + (uint64_t)((kk * 32) >> 4)), "r"(idesc), "r"(accum) : "memory");
+            }
           }
         }
         // completion of everything issued so far frees this step's A slot and B stage
@@ -341,60 +366,100 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
     }
   } else {
     // -------------------------------------------------------------------------- dequantizers
-    const int rloc = (warp & 3) * 32 + lane;          // row inside the tile = TMEM lane
-    const int half = warp >> 2;                       // which of the step's two atoms
-    int row = row_tile * BM + rloc;
+    const int rloc = (warp & 3) * 32 + lane;          // row inside a row tile = TMEM lane
+    const int half = (warp >> 2) & 1;                 // which of the step's two atoms
+    const int t = warp >> 3;                          // which of the CTA's row tiles
+    int row = (row_tile * RT + t) * BM + rloc;
     const bool row_ok = row < p.n;
     if (!row_ok) row = p.n - 1;                       // clamp: loads stay in bounds, the store is skipped
     const uint8_t* wrow = p.W + (size_t)row * p.rowbytes;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     constexpr int ATOMS_PER_BLK = F::BLK >= 256 ? 4 : 1;   // 32-weight formats: dequant_atom indexes blocks itself
     bool ok = true;
-    uint4 pre[3] = {};
-    auto fetch = [&](int s) {   // Q4_K: the wire bytes of step s for this thread's atom (header + 32 nibble bytes)
+    const uint4 pre[3] = {};
+    // Q4_K: the wire bytes of a super-block column of the CTA's rows (256 rows x 144 B) are staged through shared
+    // memory by all dequantizing threads with 16-byte asynchronous copies (consecutive threads take consecutive
+    // 16-byte pieces of a row, so the global reads coalesce), then every thread pulls its row's header and the two
+    // 32-byte nibble runs of its two atoms into registers and the buffer is free for the next column while the two
+    // K steps are unpacked.  The named barrier is reached by every dequantizing thread on every iteration, also
+    // after a wait has given up (`ok` only guards the work), so it cannot be left waiting.
+    uint4 hdr4 = {}, qa[2][2] = {};
+    constexpr int DQ_THREADS = DQ_WARPS * 32;
+    constexpr int NCHUNK = (RT * BM * 9 + DQ_THREADS - 1) / DQ_THREADS;   // 16-byte pieces per thread and column
+    const int dq_tid = warp * 32 + lane;
+    const uint8_t* csrc[NCHUNK];
+    uint32_t cdst[NCHUNK];
+    if constexpr (QT == KQ_TYPE_Q4_K) {
+#pragma unroll
+      for (int i = 0; i < NCHUNK; ++i) {
+        const int c = dq_tid + i * DQ_THREADS;
+        const int r = c / 9, part = c - 9 * r;
+        int grow = row_tile * RT * BM + r;
+        if (grow >= p.n) grow = p.n - 1;
+        csrc[i] = c < RT * BM * 9 ? p.W + (size_t)grow * p.rowbytes + part * 16 : nullptr;
+        cdst[i] = smem_u32(sW + r * 144 + part * 16);
+      }
+    }
+    auto stage_block = [&](int sblk) {                          // issue the copies of super-block column sblk
       if constexpr (QT == KQ_TYPE_Q4_K) {
-        if (s < nmain) {
-          const int ga = s * (KSTEP / ATOM) + half;
-          const uint8_t* blk = wrow + (size_t)(ga >> 2) * 144;
-          pre[0] = __ldg(reinterpret_cast<const uint4*>(blk));
-          pre[1] = __ldg(reinterpret_cast<const uint4*>(blk + 16 + 32 * (ga & 3)));
-          pre[2] = __ldg(reinterpret_cast<const uint4*>(blk + 32 + 32 * (ga & 3)));
-        }
+#pragma unroll
+        for (int i = 0; i < NCHUNK; ++i)
+          if (csrc[i]) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(cdst[i]), "l"(csrc[i] + (size_t)sblk * 144) : "memory");
+        asm volatile("cp.async.commit_group;" ::: "memory");
       }
     };
-    fetch(0);
-    for (int s = 0; s < nsteps && ok; ++s) {
+    auto dq_barrier = [&]() { asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS) : "memory"); };
+    if constexpr (QT == KQ_TYPE_Q4_K) stage_block(0);
+    for (int s = 0; s < nsteps; ++s) {
       const int ab = s % NA, fill = s / NA;
       // dequantize before waiting for the slot: the wire bytes do not depend on the pipeline state
       uint32_t v[32];
       if (s < nmain) {
         const int ga = s * (KSTEP / ATOM) + half;     // atom index along the row
-        const uint8_t* blk = F::BLK >= 256 ? wrow + (size_t)(ga / ATOMS_PER_BLK) * F::BYTES
-                                           : wrow + (size_t)ga * 2 * F::BYTES;
-        const uint4 cur[3] = {pre[0], pre[1], pre[2]};
-        fetch(s + 1);                                 // next step's bytes are in flight while this one is unpacked
-        dequant_atom<QT, CORR>(blk, F::BLK >= 256 ? (ga % ATOMS_PER_BLK) : 0, s_grid, p.half_fma, cur, v);
+        if constexpr (QT == KQ_TYPE_Q4_K) {
+          if ((s & 1) == 0) {                         // a new super-block column: steps s and s+1
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            dq_barrier();                             // the whole column has landed
+            const uint8_t* mine = sW + (t * BM + rloc) * 144;
+            hdr4 = *reinterpret_cast<const uint4*>(mine);
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {             // atoms `half` (this step) and `half + 2` (next step)
+              qa[e][0] = *reinterpret_cast<const uint4*>(mine + 16 + 32 * (half + 2 * e));
+              qa[e][1] = *reinterpret_cast<const uint4*>(mine + 32 + 32 * (half + 2 * e));
+            }
+            dq_barrier();                             // everyone has its bytes: the buffer may be refilled
+            if (s + 2 < nmain) stage_block((s >> 1) + 1);
+          }
+          const bool odd = (s & 1) != 0;
+          const uint4 cur[3] = {hdr4, odd ? qa[1][0] : qa[0][0], odd ? qa[1][1] : qa[0][1]};
+          dequant_atom<QT, CORR>(nullptr, ga & 3, s_grid, p.half_fma, cur, v);
+        } else {
+          const uint8_t* blk = F::BLK >= 256 ? wrow + (size_t)(ga / ATOMS_PER_BLK) * F::BYTES
+                                             : wrow + (size_t)ga * 2 * F::BYTES;
+          dequant_atom<QT, CORR>(blk, F::BLK >= 256 ? (ga % ATOMS_PER_BLK) : 0, s_grid, p.half_fma, pre, v);
+        }
       } else {
         corr_atom<QT>(wrow, (s - nmain) * (KSTEP / ATOM) + half, p.nb32, v);
       }
-      if (fill > 0) ok = mbar_wait(bar_aempty + 8 * ab, (uint32_t)((fill - 1) & 1), s_abort);
-      if (!ok) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      tmem_st32(tbase + TMEM_A + lane_base + ab * 64 + half * 32, v);
-      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_afull + 8 * ab);
+      if (ok && fill > 0) ok = mbar_wait(bar_aempty + 8 * ab, (uint32_t)((fill - 1) & 1), s_abort);
+      if (ok) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        tmem_st32(tbase + TMEM_A + lane_base + ab * A_SLOT_COLS + t * 64 + half * 32, v);
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_afull + 8 * ab);
+      }
     }
     // -------------------------------------------------------------------------- epilogue: warp w takes columns
-    // [128*half, 128*half+128) of its 32 lanes
+    // [64*half, 64*half+64) of its 32 lanes in its row tile's accumulator
     if (ok && mbar_wait(bar_dfull, 0, s_abort)) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       OutT* y = reinterpret_cast<OutT*>(p.y);
 #pragma unroll 1
       for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32) {
         uint32_t r[32];
-        tmem_ld32(tbase + TMEM_D + lane_base + c0, r);
+        tmem_ld32(tbase + TMEM_D + lane_base + t * BN + c0, r);
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int tok = tok_tile * BN + c0 + j;
@@ -429,7 +494,7 @@ EncodeTiledFn encode_fn() {
 template <int QT, bool CORR, typename OutT>
 int launch(const GemmParams& p, const CUtensorMap& map, const CUtensorMap& smap, int grid, cudaStream_t st) {
   auto kern = gemm_tc_kernel<QT, CORR, OutT>;
-  const int smem = NB * B_STAGE_BYTES + 4096;
+  const int smem = NB * B_STAGE_BYTES + 4096 + (QT == KQ_TYPE_Q4_K ? W_STAGE_BYTES : 0);
   static bool attr_set = false;
   if (!attr_set) {
     KQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -492,7 +557,7 @@ int launch_gemm_tc(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& 
   p.W = (const uint8_t*)W; p.rowbytes = k / blk * bytes; p.n = (int)n; p.k = (int)k; p.m = (int)m;
   p.ntok_tiles = (int)((m + BN - 1) / BN);
   p.y = y; p.stride_y = stride_y; p.status = P.status; p.half_fma = options().half_fma;
-  const int grid = (int)((n + BM - 1) / BM) * p.ntok_tiles;
+  const int grid = (int)((n + RT * BM - 1) / (RT * BM)) * p.ntok_tiles;
   switch (type) {
     case KQ_TYPE_Q4_0: return launch_out<KQ_TYPE_Q4_0, true>(p, map, smap, grid, y_dtype, st);
     case KQ_TYPE_Q8_0: return launch_out<KQ_TYPE_Q8_0, false>(p, map, smap, grid, y_dtype, st);
