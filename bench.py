@@ -368,7 +368,24 @@ def main() -> None:
             prefill = {"workload": "Q4_K N=17408 K=5120, bf16 activations M=2048 (quantize + tcgen05 GEMM)", "ms": msg,
                        "tflops": tf, "peak_tflops": peak_tf, "frac": tf / peak_tf,
                        "peak_source": "of measured (bf16_tflops burst)" if pk else "of fallback", "launches_per_call": gl}
-            del xp, yp, sp
+            del yp, sp
+            # LM head of the same configuration: Q6_K N=248320 K=5120 (1.04 GB of wire bytes)
+            n_lm = 248320
+            Wl = synth.wire_torch(Q6_K, n_lm, K_HID, 777, dev)
+            yl = torch.empty((mp, n_lm), dtype=torch.bfloat16, device=dev)
+            sl = torch.empty(capi.workspace_bytes(Q6_K, mp, n_lm, K_HID), dtype=torch.uint8, device=dev)
+            for _ in range(2):
+                capi.mul_mat(Wl, xp, Q6_K, mmq=True, out=yl, scratch=sl)
+            torch.cuda.synchronize()
+            e0.record(stream)
+            for _ in range(3):
+                capi.mul_mat(Wl, xp, Q6_K, mmq=True, out=yl, scratch=sl)
+            e1.record(stream)
+            torch.cuda.synchronize()
+            msl = e0.elapsed_time(e1) / 3
+            tfl = 2.0 * mp * n_lm * K_HID / (msl * 1e-3) / 1e12
+            prefill["lm_head_q6k"] = {"workload": "Q6_K N=248320 K=5120, M=2048", "ms": msl, "tflops": tfl, "frac": tfl / peak_tf}
+            del xp, Wl, yl, sl
 
     # ---- end to end through the op API with host buffers
     e2e = None

@@ -82,7 +82,11 @@ static int mul_mat(const char* fn, bool mmq, const void* W, int type, int64_t n,
   const bool gemm = impl == 0 && m >= options().gemm_min_m && gemm_tc_supported(W, type, n, k);
   if (!gemm && need_x) P.xh = nullptr;   // the fp16 copy of the activations is only written for the GEMM
   if (x) {
-    rc = launch_quantize(x, x_dtype, m, k, stride_x, &P, nullptr, p.L.kpad, st);
+    Q8Ptrs Pq = P;
+    if (gemm) {   // the GEMM reads only the fp16 activations and raw block sums: skip the GEMV-side tables
+      Pq.qs = nullptr; Pq.qsp = nullptr; Pq.ds = nullptr; Pq.dT = nullptr;
+    }
+    rc = launch_quantize(x, x_dtype, m, k, stride_x, &Pq, nullptr, p.L.kpad, st);
     if (rc) return rc;
   }
   if (gemm) return launch_gemm_tc(W, type, n, k, P, m, y, y_dtype, stride_y, mmq, st);

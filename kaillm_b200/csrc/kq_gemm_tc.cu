@@ -45,6 +45,8 @@ constexpr uint32_t TMEM_A = 256;               // A ring: slot ab, row tile t, a
 constexpr int A_SLOT_COLS = RT * 64;
 constexpr int B_STAGE_BYTES = BN * KSTEP * 2;  // 32 KB
 constexpr int W_STAGE_BYTES = RT * BM * 144;   // Q4_K: one super-block column of the CTA's 256 rows
+constexpr int W6_ROW = 232;                    // Q6_K: bytes per staged row (216-byte aligned window of a 210-byte block, padded)
+constexpr int W6_STAGE_BYTES = RT * BM * W6_ROW;
 constexpr long long GEMM_WAIT_LIMIT = 1ll << 28;
 
 __constant__ uint16_t c_iq3s_codes_g[512] = {
@@ -62,6 +64,7 @@ struct GemmParams {
   int64_t stride_y;
   int* status;
   int half_fma;
+  int stage6;         // Q6_K: rows and W are 8-byte aligned, the block columns go through shared memory
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -271,6 +274,34 @@ __device__ __forceinline__ void dequant_atom(const uint8_t* __restrict__ blk, in
   }
 }
 
+// Q6_K atom from registers: ql = the 64 low-nibble bytes of the atom's half super-block (16 words), qh = its 32
+// high-bit bytes (8 words), scw = its four int8 scales, p = which nibble / which pair of 2-bit fields (atom & 1).
+// Same fp16 operation order as ggml_dequantize: half(sc * q) in one rounding, then * d.
+__device__ __forceinline__ void dequant_q6k_regs(const uint32_t (&ql)[16], const uint32_t (&qh)[8], uint32_t scw, __half d,
+                                                 int p, uint32_t (&out)[32]) {
+  const __half2 k1056 = __half2half2(__ushort_as_half(0x6420));   // 1024 + 32
+  const __half2 d2 = __half2half2(d);
+  __half2 sc2[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) sc2[i] = __half2half2(__int2half_rn((int)(int8_t)(scw >> (8 * i))));
+#pragma unroll
+  for (int run = 0; run < 2; ++run) {        // q4 = 2p + run: weights 32*run .. 32*run+31 of the atom
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      const uint32_t qlw = ql[8 * run + w] >> (4 * p);
+      const uint32_t qhw = qh[w];
+      const int sh = 4 * p + 2 * run;            // the 2-bit field of this run, moved to bits 4-5
+      const uint32_t hi = sh <= 4 ? qhw << (4 - sh) : qhw >> (sh - 4);
+      const uint32_t code = (qlw & 0x0F0F0F0Fu) | (hi & 0x30303030u);
+      const __half2 q01 = __hsub2(bits_h2(__byte_perm(code, 0x64646464u, 0x4140)), k1056);
+      const __half2 q23 = __hsub2(bits_h2(__byte_perm(code, 0x64646464u, 0x4342)), k1056);
+      const __half2 s2 = sc2[2 * run + (w >> 2)];
+      out[16 * run + 2 * w] = h2_bits(__hmul2_rn(d2, __hmul2_rn(q01, s2)));
+      out[16 * run + 2 * w + 1] = h2_bits(__hmul2_rn(d2, __hmul2_rn(q23, s2)));
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ kernel
 template <int QT, bool CORR, typename OutT>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -282,7 +313,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 26);
   volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 27);
   uint32_t* s_grid = reinterpret_cast<uint32_t*>(bars + 32);     // IQ3_S codebook (2 KB)
-  uint8_t* sW = smem + NB * B_STAGE_BYTES + 4096;                // Q4_K: one super-block column of the tile, 256 rows x 144 B
+  uint8_t* sW = smem + NB * B_STAGE_BYTES + 4096;                // staged super-block column of the CTA's 256 rows (Q4_K 144 B, Q6_K 232 B per row)
   const uint32_t bar_bfull = smem_u32(bars), bar_bempty = smem_u32(bars + 8), bar_afull = smem_u32(bars + 16),
                  bar_aempty = smem_u32(bars + 20), bar_dfull = smem_u32(bars + 24);
   static_assert(NB <= 8 && NA <= 4, "barrier layout");
@@ -384,20 +415,27 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
     // K steps are unpacked.  The named barrier is reached by every dequantizing thread on every iteration, also
     // after a wait has given up (`ok` only guards the work), so it cannot be left waiting.
     uint4 hdr4 = {}, qa[2][2] = {};
+    uint32_t q6l[2][16] = {}, q6h[2][8] = {}, q6s[2] = {};   // Q6_K: the thread's two atoms of the current column
+    __half q6d = __float2half_rn(0.f);
+    const bool st6 = QT == KQ_TYPE_Q6_K && p.stage6 != 0;
     constexpr int DQ_THREADS = DQ_WARPS * 32;
-    constexpr int NCHUNK = (RT * BM * 9 + DQ_THREADS - 1) / DQ_THREADS;   // 16-byte pieces per thread and column
+    // pieces per row and column: Q4_K 9 x 16 B (the block), Q6_K 27 x 8 B (the 8-byte aligned window around the block)
+    constexpr int PIECES = QT == KQ_TYPE_Q6_K ? 27 : 9;
+    constexpr int PIECE_B = QT == KQ_TYPE_Q6_K ? 8 : 16;
+    constexpr int SROW = QT == KQ_TYPE_Q6_K ? W6_ROW : 144;
+    constexpr int NCHUNK = (QT == KQ_TYPE_Q4_K || QT == KQ_TYPE_Q6_K) ? (RT * BM * PIECES + DQ_THREADS - 1) / DQ_THREADS : 1;
     const int dq_tid = warp * 32 + lane;
     const uint8_t* csrc[NCHUNK];
     uint32_t cdst[NCHUNK];
-    if constexpr (QT == KQ_TYPE_Q4_K) {
+    if (QT == KQ_TYPE_Q4_K || st6) {
 #pragma unroll
       for (int i = 0; i < NCHUNK; ++i) {
         const int c = dq_tid + i * DQ_THREADS;
-        const int r = c / 9, part = c - 9 * r;
+        const int r = c / PIECES, part = c - PIECES * r;
         int grow = row_tile * RT * BM + r;
         if (grow >= p.n) grow = p.n - 1;
-        csrc[i] = c < RT * BM * 9 ? p.W + (size_t)grow * p.rowbytes + part * 16 : nullptr;
-        cdst[i] = smem_u32(sW + r * 144 + part * 16);
+        csrc[i] = c < RT * BM * PIECES ? p.W + (size_t)grow * p.rowbytes + part * PIECE_B : nullptr;
+        cdst[i] = smem_u32(sW + r * SROW + part * PIECE_B);
       }
     }
     auto stage_block = [&](int sblk) {                          // issue the copies of super-block column sblk
@@ -407,9 +445,16 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
           if (csrc[i]) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(cdst[i]), "l"(csrc[i] + (size_t)sblk * 144) : "memory");
         asm volatile("cp.async.commit_group;" ::: "memory");
       }
+      if constexpr (QT == KQ_TYPE_Q6_K) {
+        const size_t col = ((size_t)sblk * 210) & ~(size_t)7;   // rows and W are 8-byte aligned: the same for every row
+#pragma unroll
+        for (int i = 0; i < NCHUNK; ++i)
+          if (csrc[i]) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(cdst[i]), "l"(csrc[i] + col) : "memory");
+        asm volatile("cp.async.commit_group;" ::: "memory");
+      }
     };
     auto dq_barrier = [&]() { asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS) : "memory"); };
-    if constexpr (QT == KQ_TYPE_Q4_K) stage_block(0);
+    if (QT == KQ_TYPE_Q4_K || st6) stage_block(0);
     for (int s = 0; s < nsteps; ++s) {
       const int ab = s % NA, fill = s / NA;
       // dequantize before waiting for the slot: the wire bytes do not depend on the pipeline state
@@ -433,6 +478,33 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
           const bool odd = (s & 1) != 0;
           const uint4 cur[3] = {hdr4, odd ? qa[1][0] : qa[0][0], odd ? qa[1][1] : qa[0][1]};
           dequant_atom<QT, CORR>(nullptr, ga & 3, s_grid, p.half_fma, cur, v);
+        } else if (st6) {
+          if constexpr (QT == KQ_TYPE_Q6_K) {
+            if ((s & 1) == 0) {                       // a new super-block column: atoms `half` (now) and `half + 2` (next step)
+              asm volatile("cp.async.wait_group 0;" ::: "memory");
+              dq_barrier();
+              const uint32_t off = (uint32_t)(((size_t)(s >> 1) * 210) & 7);   // where the block starts inside its window
+              const uint8_t* mine = sW + (t * BM + rloc) * W6_ROW + off;
+              const uint32_t fsh = ((uint32_t)(uintptr_t)mine & 2u) << 3;      // 0 or 16: the same for all rows
+              auto words = [&](const uint8_t* ptr, uint32_t* dst, int n) {     // n 32-bit words from a 2-byte aligned address
+                const uint32_t* q = reinterpret_cast<const uint32_t*>((uintptr_t)ptr & ~(uintptr_t)3);
+                uint32_t lo = q[0];
+#pragma unroll
+                for (int i = 0; i < n; ++i) { const uint32_t hi = q[i + 1]; dst[i] = __funnelshift_r(lo, hi, fsh); lo = hi; }
+              };
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                words(mine + 64 * e, q6l[e], 16);
+                words(mine + 128 + 32 * e, q6h[e], 8);
+                words(mine + 192 + 8 * e + 4 * half, &q6s[e], 1);
+              }
+              q6d = *reinterpret_cast<const __half*>(mine + 208);
+              dq_barrier();
+              if (s + 2 < nmain) stage_block((s >> 1) + 1);
+            }
+            if (s & 1) dequant_q6k_regs(q6l[1], q6h[1], q6s[1], q6d, half, v);
+            else dequant_q6k_regs(q6l[0], q6h[0], q6s[0], q6d, half, v);
+          }
         } else {
           const uint8_t* blk = F::BLK >= 256 ? wrow + (size_t)(ga / ATOMS_PER_BLK) * F::BYTES
                                              : wrow + (size_t)ga * 2 * F::BYTES;
@@ -494,7 +566,7 @@ EncodeTiledFn encode_fn() {
 template <int QT, bool CORR, typename OutT>
 int launch(const GemmParams& p, const CUtensorMap& map, const CUtensorMap& smap, int grid, cudaStream_t st) {
   auto kern = gemm_tc_kernel<QT, CORR, OutT>;
-  const int smem = NB * B_STAGE_BYTES + 4096 + (QT == KQ_TYPE_Q4_K ? W_STAGE_BYTES : 0);
+  const int smem = NB * B_STAGE_BYTES + 4096 + (QT == KQ_TYPE_Q4_K ? W_STAGE_BYTES : (QT == KQ_TYPE_Q6_K ? W6_STAGE_BYTES : 0));
   static bool attr_set = false;
   if (!attr_set) {
     KQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -557,6 +629,7 @@ int launch_gemm_tc(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& 
   p.W = (const uint8_t*)W; p.rowbytes = k / blk * bytes; p.n = (int)n; p.k = (int)k; p.m = (int)m;
   p.ntok_tiles = (int)((m + BN - 1) / BN);
   p.y = y; p.stride_y = stride_y; p.status = P.status; p.half_fma = options().half_fma;
+  p.stage6 = type == KQ_TYPE_Q6_K && ((uintptr_t)W % 8) == 0 && (p.rowbytes % 8) == 0;
   const int grid = (int)((n + RT * BM - 1) / (RT * BM)) * p.ntok_tiles;
   switch (type) {
     case KQ_TYPE_Q4_0: return launch_out<KQ_TYPE_Q4_0, true>(p, map, smap, grid, y_dtype, st);
