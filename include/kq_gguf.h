@@ -175,6 +175,9 @@ int kq_read_status(int type, int64_t m, int64_t n, int64_t k, const void* scratc
  *                 with programmatic stream serialization and prefetch p ring stages of weights before they
  *                 wait for the previous kernel of the stream
  *   "tile_segments" 1 = the shared-stage kernel fetches row segments even when a stage is contiguous (default 0)
+ *   "fuse_q8"     1 (default) = calls of 1-2 tokens on large matrices skip the quantizer launch: the row-streaming
+ *                 kernel quantizes the activations itself, bit-identically, while its first weight stages are in
+ *                 flight; 2 = wherever that kernel runs (tests); 0 = always launch the quantizer
  *   "gemm_min_m"  smallest m that goes to the tcgen05 GEMM (default 81: m <= 80 keeps exact integer dots)
  *   "half_fma"    1 = K-quant dequantize contracts fp16 mul+sub into one fma (default), 0 = two roundings
  * Returns KQ_EINVAL for an unknown name. */

@@ -22,7 +22,7 @@ int cuda_fail(cudaError_t e, const char* what) {
 }
 
 Options& options() {
-  static Options o = {0, 3, 81, 2, 1, 0, 0};
+  static Options o = {0, 3, 81, 2, 1, 0, 0, 1};
   return o;
 }
 
@@ -81,6 +81,14 @@ static int mul_mat(const char* fn, bool mmq, const void* W, int type, int64_t n,
   const int impl = options().gemv_impl;
   const bool gemm = impl == 0 && m >= options().gemm_min_m && gemm_tc_supported(W, type, n, k);
   if (!gemm && need_x) P.xh = nullptr;   // the fp16 copy of the activations is only written for the GEMM
+  // 1-2 tokens on the row-streaming kernel: its consumer warps quantize x themselves while the first weights arrive
+  // (measured: it pays when all (token, 32-block) pairs fit one pass of the 512 consumer lanes and the matrix is big
+  // enough for the ~2 us of quantization to hide behind the pipeline fill: 16.9 -> 15.4 us on Q4_K 17408x5120 at one
+  // token; a second pass, or a matrix of a few MB, makes it slower than the separate launch)
+  const bool fuse_fits = options().fuse_q8 == 2 || (m * (k / 32) <= 512 && n * p.rowbytes >= (32ll << 20));   // 2: wherever it can run (tests)
+  const bool fuse = x && !gemm && options().fuse_q8 && m <= 2 && fuse_fits &&
+                    impl != 1 && gemv_rows_only(type, m) && gemv_mma_supported(W, type, n, k);
+  if (fuse) return launch_gemv_mma(W, type, n, k, P, m, y, y_dtype, stride_y, mmq, st, x, x_dtype, stride_x);
   if (x) {
     Q8Ptrs Pq = P;
     if (gemm) {   // the GEMM reads only the fp16 activations and raw block sums: skip the GEMV-side tables
@@ -251,6 +259,7 @@ int kq_set_option(const char* name, int value) {
   if (name && !strcmp(name, "tc_min_m")) { options().tc_min_m = value; return KQ_OK; }
   if (name && !strcmp(name, "gemm_min_m")) { options().gemm_min_m = value; return KQ_OK; }
   if (name && !strcmp(name, "tile_segments")) { options().tile_segments = value != 0; return KQ_OK; }
+  if (name && !strcmp(name, "fuse_q8")) { options().fuse_q8 = value < 0 ? 0 : (value > 2 ? 2 : value); return KQ_OK; }
   if (name && !strcmp(name, "pdl")) { options().pdl = value < 0 ? 0 : value; return KQ_OK; }
   set_error("kq_set_option: unknown option");
   return KQ_EINVAL;
@@ -262,6 +271,7 @@ int kq_get_option(const char* name, int* value) {
   if (name && value && !strcmp(name, "tc_min_m")) { *value = options().tc_min_m; return KQ_OK; }
   if (name && value && !strcmp(name, "gemm_min_m")) { *value = options().gemm_min_m; return KQ_OK; }
   if (name && value && !strcmp(name, "tile_segments")) { *value = options().tile_segments; return KQ_OK; }
+  if (name && value && !strcmp(name, "fuse_q8")) { *value = options().fuse_q8; return KQ_OK; }
   if (name && value && !strcmp(name, "pdl")) { *value = options().pdl; return KQ_OK; }
   if (name && value && !strcmp(name, "launch_count")) { *value = (int)(options().launches & 0x7fffffff); return KQ_OK; }
   set_error("kq_get_option: unknown option");

@@ -32,6 +32,7 @@ struct Options {
   int half_fma;        // 1: fp16 mul+sub contracted in K-quant dequantize
   long long launches;  // kernels launched by this library so far (host-side count)
   int tile_segments;   // 1: the tile GEMV fetches row segments even when its K slice is the whole row
+  int fuse_q8;         // 1: calls of 1-2 tokens quantize the activations inside the row-streaming kernel (no quantizer launch)
 };
 Options& options();
 
@@ -132,8 +133,10 @@ int launch_gemv_dp4a(const void* W, int type, int64_t n, int64_t k, const void* 
 // tensor-core GEMV; returns KQ_EUNSUPPORTED (without setting an error) when the shape/alignment is not
 // covered, so the caller can fall back to the dp4a kernel
 bool gemv_mma_supported(const void* W, int type, int64_t n, int64_t k);
+bool gemv_rows_only(int type, int64_t m);
 int launch_gemv_mma(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m, void* y,
-                    int y_dtype, int64_t stride_y, bool mmq, cudaStream_t st);
+                    int y_dtype, int64_t stride_y, bool mmq, cudaStream_t st, const void* fuse_x = nullptr,
+                    int x_dtype = 0, int64_t stride_x = 0);
 bool gemv_tile_supported(const void* W, int type, int64_t n, int64_t k, int mtok);
 int launch_gemv_tile(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m0, int mcount, void* y,
                      int y_dtype, int64_t stride_y, bool mmq, cudaStream_t st);

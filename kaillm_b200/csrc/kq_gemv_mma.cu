@@ -498,6 +498,9 @@ struct RowParams {
   int zpb, kpad, nb32tot, klen;
   int m0, mcount;
   int prefetch;             // ring stages issued before waiting for the previous kernel
+  const void* x;            // non-null: raw activations; the consumer warps quantize them into shared memory themselves
+  int x_dtype;
+  int64_t stride_x;
   void* y;
   int64_t stride_y;
   int* status;
@@ -510,6 +513,99 @@ __device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {   // uns
   int d;
   asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
   return d;
+}
+
+// q8_1 quantization of the CTA's activations straight into shared memory (1-2 tokens), one LANE per 32-block.
+// Bit-identical to quantize_q8_1_kernel, which gives a block to a warp: |x| max and the integer code sums do not
+// depend on the order; the fp32 block sum is formed by the same tree as that kernel's xor butterfly (pairs 16 apart,
+// then 8, 4, 2, 1: fp addition is commutative, so every lane of the butterfly holds this tree's value); d = amax/127
+// and roundf(x/d) are the same IEEE operations.  Written in the layouts the consumers read; runs while the first
+// weight stages are in flight.
+template <bool PAIR>
+__device__ __forceinline__ void quantize_rows_smem(const RowParams& p, uint8_t* sA, __half2* sDS, float* sZ, int warp,
+                                                   int lane, int ntok) {
+  const int nb = p.klen >> 5;
+  const int esize = p.x_dtype == KQ_F32 ? 4 : 2;
+  for (int idx = warp * 32 + lane; idx < ntok * nb; idx += ROW_WARPS * 32) {   // (token, block) pairs over all 512 lanes
+    const int t = idx / nb, b = idx - t * nb;
+    const uint8_t* xrow = reinterpret_cast<const uint8_t*>(p.x) + (size_t)(p.m0 + t) * p.stride_x * esize;
+    {
+      float v[32];
+      const uint8_t* src = xrow + (size_t)b * 32 * esize;
+      if (p.x_dtype == KQ_F32) {
+        if (((uintptr_t)src & 15) == 0) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float4 f = reinterpret_cast<const float4*>(src)[i];
+            v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = reinterpret_cast<const float*>(src)[i];
+        }
+      } else {
+        uint32_t w[16];
+        if (((uintptr_t)src & 15) == 0) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint4 u = reinterpret_cast<const uint4*>(src)[i];
+            w[4 * i] = u.x; w[4 * i + 1] = u.y; w[4 * i + 2] = u.z; w[4 * i + 3] = u.w;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            w[i] = (uint32_t)reinterpret_cast<const uint16_t*>(src)[2 * i] | ((uint32_t)reinterpret_cast<const uint16_t*>(src)[2 * i + 1] << 16);
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          if (p.x_dtype == KQ_BF16) {
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+          } else {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+            v[2 * i] = f.x; v[2 * i + 1] = f.y;
+          }
+        }
+      }
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
+      const float d = __fdiv_rn(amax, 127.0f);
+      uint32_t codes[8];
+      int s16 = 0, s16b = 0;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const int q = amax == 0.0f ? 0 : (int)(int8_t)roundf(__fdiv_rn(v[i], d));
+        if (i < 16) s16 += q; else s16b += q;
+        if ((i & 3) == 0) codes[i >> 2] = 0;
+        codes[i >> 2] |= (uint32_t)(q & 0xFF) << (8 * (i & 3));
+      }
+      // block sum: the butterfly's tree
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+        for (int i = 0; i < off; ++i) v[i] = v[i] + v[i + off];
+      const float sum = v[0];
+      uint8_t* dst;
+      if constexpr (PAIR) {
+        uint8_t* grp = sA + (size_t)t * p.a_stride + (b >> 1) * 80;
+        dst = grp + (b & 1) * 32;
+        if ((b & 1) == 0) *reinterpret_cast<uint4*>(grp + 64) = make_uint4(0u, 0u, 0u, 0u);   // keep the padding defined
+      } else {
+        dst = sA + (size_t)t * p.a_stride + b * 32;
+      }
+      reinterpret_cast<uint4*>(dst)[0] = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+      reinterpret_cast<uint4*>(dst)[1] = make_uint4(codes[4], codes[5], codes[6], codes[7]);
+      const __half dh = __float2half_rn(d), sh = __float2half_rn(sum);
+      sDS[(size_t)t * p.nb32tot + b] = __halves2half2(dh, sh);
+      const float df = __half2float(dh);
+      if (p.zmode == 2) sZ[(size_t)t * p.nb32tot + b] = df * (float)(s16 + s16b);
+      if (p.zmode == 3) {
+        sZ[((size_t)t * p.nb32tot + b) * 2] = df * (float)s16;
+        sZ[((size_t)t * p.nb32tot + b) * 2 + 1] = df * (float)s16b;
+      }
+    }
+  }
 }
 
 // PAIR (Q4_K): a warp takes two rows at a time; lane = (row of the pair, super-block offset 0..3, quarter il 0..3)
@@ -533,6 +629,7 @@ __global__ void __launch_bounds__(ROW_THREADS, 1) gemv_rows_kernel(const RowPara
   const int S = p.stages, R = p.rows_per_stage;
   const int r0 = (int)((int64_t)blockIdx.x * p.n / gridDim.x), r1 = (int)((int64_t)(blockIdx.x + 1) * p.n / gridDim.x);
   pdl_trigger();
+  if (p.x != nullptr && blockIdx.x == 0 && threadIdx.x == 0 && p.m0 == 0) *p.status = 0;   // no quantizer launch clears it
   if (r0 >= r1) return;
   const int nstages = (r1 - r0 + R - 1) / R;
   const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + MAX_STAGES), bar_act = smem_u32(bars + 2 * MAX_STAGES);
@@ -570,11 +667,11 @@ __global__ void __launch_bounds__(ROW_THREADS, 1) gemv_rows_kernel(const RowPara
       int q = 0;
       for (; q < nstages && q < p.prefetch; ++q) issue_stage(q);
       pdl_wait();
-      const int ntok = p.mcount < MT ? p.mcount : MT;
+      const int ntok = p.x != nullptr ? 0 : (p.mcount < MT ? p.mcount : MT);   // fused: the consumers quantize x themselves
       const uint32_t dsb = (uint32_t)p.nb32tot * 4u, zb = (uint32_t)p.nb32tot * p.zpb * 4u;   // multiples of 64 bytes
       const uint32_t alen = PAIR ? (uint32_t)(p.klen / 64) * 80u : (uint32_t)p.klen;
       uint32_t total = (uint32_t)ntok * (alen + dsb + (p.zr != nullptr ? zb : 0u));
-      mbar_expect_tx(bar_act, total);
+      if (ntok > 0) mbar_expect_tx(bar_act, total);
       for (int t = 0; t < ntok; ++t) {
         if constexpr (PAIR)
           bulk_g2s(smem_u32(sA + t * p.a_stride), p.qsp + (size_t)(p.m0 + t) * (p.kpad / 64) * 80, alen, bar_act);
@@ -598,7 +695,14 @@ __global__ void __launch_bounds__(ROW_THREADS, 1) gemv_rows_kernel(const RowPara
   }
 
   // -------------------------------------------------------------------- consumers
-  if (!mbar_wait(bar_act, 0, s_abort)) { if (lane == 0) atomicExch(p.status, 2); return; }
+  if (p.x != nullptr) {
+    pdl_wait();                                   // x may come from the kernel before this one
+    quantize_rows_smem<PAIR>(p, sA, sDS, sZ, warp, lane, p.mcount < MT ? p.mcount : MT);
+    asm volatile("bar.sync 2, %0;" ::"n"(ROW_WARPS * 32) : "memory");   // all sixteen consumer warps, nobody has left yet
+  } else if (!mbar_wait(bar_act, 0, s_abort)) {
+    if (lane == 0) atomicExch(p.status, 2);
+    return;
+  }
   OutT* y = reinterpret_cast<OutT*>(p.y);
   constexpr int NG = 32 / F::GROUP;
   const int zmode = p.zmode;
@@ -986,8 +1090,18 @@ bool gemv_mma_supported(const void* W, int type, int64_t n, int64_t k) {
 }
 
 // impl: 0 = choose by m, 2 = tensor cores wherever the type has them, 3 = row-streaming dp4a
+// True when every token of an m-token call goes to the row-streaming kernel (which can quantize raw activations itself).
+bool gemv_rows_only(int type, int64_t m) {
+  const int impl = options().gemv_impl;
+  if (impl == 3 || impl == 4) return true;
+  if (impl != 0) return false;
+  const bool has_tc = (type == KQ_TYPE_Q4_K || type == KQ_TYPE_Q6_K);
+  return !has_tc || m < options().tc_min_m;
+}
+
+// fuse_x != nullptr (only with gemv_rows_only): the activations have NOT been quantized into P; the kernel reads them raw
 int launch_gemv_mma(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m, void* y, int y_dtype,
-                    int64_t stride_y, bool mmq, cudaStream_t st) {
+                    int64_t stride_y, bool mmq, cudaStream_t st, const void* fuse_x, int x_dtype, int64_t stride_x) {
   int blk, bytes;
   type_geometry(type, &blk, &bytes);
   const int impl = options().gemv_impl;
@@ -1060,6 +1174,7 @@ int launch_gemv_mma(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs&
       else if (type == KQ_TYPE_Q6_K && pair) { p.zmode = 3; p.zr = P.z16r; p.zpb = 2; }   // -32 offset via group sums
       p.prefetch = options().pdl < rcg.stages ? options().pdl : rcg.stages;
       p.m0 = (int)m0; p.mcount = mcount; p.y = y; p.stride_y = stride_y; p.status = P.status;
+      p.x = fuse_x; p.x_dtype = x_dtype; p.stride_x = stride_x;
       switch (type) {
         case KQ_TYPE_Q4_0: rc = launch_typed<KQ_TYPE_Q4_0>(nullptr, nullptr, &p, &rcg, mt, y_dtype, st); break;
         case KQ_TYPE_Q8_0: rc = launch_typed<KQ_TYPE_Q8_0>(nullptr, nullptr, &p, &rcg, mt, y_dtype, st); break;

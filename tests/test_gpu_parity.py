@@ -214,6 +214,32 @@ def test_shared_stage_mma_gemv_matches_oracle_and_dp4a(qt, n, k, m, mmq, segment
     assert rel_l2(to_np(y), to_np(y1)) < TIGHT          # every row, against the general kernel
 
 
+@pytest.mark.parametrize("qt", QT)
+@pytest.mark.parametrize("n,k,m", [(64, 512, 1), (333, 2048, 2), (1200, 5120, 1), (100, 17408, 2), (17, 256, 1)])
+@pytest.mark.parametrize("dt", ["bf16", "f16", "f32"])
+def test_in_kernel_quantization_equals_quantizer_launch(qt, n, k, m, dt):
+    """1-2 tokens: the row-streaming kernel can quantize the activations itself (fuse_q8); the result must be
+    bit-identical to the two-launch path (quantizer kernel + GEMV) and match the oracle."""
+    w, wt = wire(qt, n, k, seed=n + k + qt)
+    x, xt = act(m, k, seed=m + 7, dt=dt)
+    scratch = torch.empty(capi.workspace_bytes(qt, m, n, k), dtype=torch.uint8, device=dev())
+    capi.set_option("fuse_q8", 2)          # also on matrices too small for the default heuristic
+    try:
+        l0 = capi.get_option("launch_count")
+        y1 = capi.mul_mat(wt, xt, qt, out_dtype=torch.float32, scratch=scratch)
+        fused_launches = capi.get_option("launch_count") - l0
+        assert capi.read_status(qt, m, n, k, scratch) == 0
+        capi.set_option("fuse_q8", 0)
+        l0 = capi.get_option("launch_count")
+        y0 = capi.mul_mat(wt, xt, qt, out_dtype=torch.float32, scratch=scratch)
+        plain_launches = capi.get_option("launch_count") - l0
+    finally:
+        capi.set_option("fuse_q8", 1)
+    assert torch.equal(y1, y0)
+    assert plain_launches == fused_launches + 1
+    assert rel_l2(to_np(y1), O.mul_mat(w, qt, x, "mmvq")) < TIGHT
+
+
 def test_tensor_core_gemv_declines_unaligned_weights():
     qt, n, k = 14, 32, 512
     _, wt = wire(qt, n, k, seed=1)
