@@ -82,10 +82,89 @@ __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const T* __restrict_
   }
 }
 
+// GEMM-only flavour (large M): one LANE per (token, 32-block).  Writes only what the tcgen05 GEMM reads: the fp16
+// activations d*q and the fp16 raw block sums.  Same values as quantize_q8_1_kernel: amax and the codes do not depend on
+// the order, and the fp32 block sum is formed by the tree of that kernel's xor butterfly (pairs 16 apart, then 8, 4, 2, 1).
+template <typename T>
+__global__ void __launch_bounds__(256) quantize_xh_kernel(const T* __restrict__ x, int64_t stride_x, int k, int kpad,
+                                                          int64_t m, Q8Ptrs P) {
+  pdl_trigger();
+  pdl_wait();
+  const int64_t gthread = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (P.cnt != nullptr && gthread < P.ncnt) P.cnt[gthread] = 0;
+  if (P.status != nullptr && gthread == 0) P.status[0] = 0;
+  const int nbk = k >> 5, nb = kpad >> 5;
+  if (gthread >= m * nbk) return;
+  const int64_t row = gthread / nbk;
+  const int b = (int)(gthread - row * nbk);
+  const T* src = x + row * stride_x + (int64_t)b * 32;
+  float v[32];
+  if constexpr (sizeof(T) == 2) {
+    uint32_t w[16];
+    if (((uintptr_t)src & 15) == 0) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint4 u = reinterpret_cast<const uint4*>(src)[i];
+        w[4 * i] = u.x; w[4 * i + 1] = u.y; w[4 * i + 2] = u.z; w[4 * i + 3] = u.w;
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const T lo = *reinterpret_cast<const T*>(reinterpret_cast<const uint16_t*>(&w[i]));
+        const T hi = *reinterpret_cast<const T*>(reinterpret_cast<const uint16_t*>(&w[i]) + 1);
+        v[2 * i] = to_f32<T>(lo); v[2 * i + 1] = to_f32<T>(hi);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = to_f32<T>(src[i]);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = to_f32<T>(src[i]);
+  }
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  const float d = __fdiv_rn(amax, 127.0f);
+  const float dh = __half2float(__float2half_rn(d));
+  uint32_t out[16];
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) {
+    const float q0 = amax == 0.0f ? 0.f : (float)(int8_t)roundf(__fdiv_rn(v[i], d));
+    const float q1 = amax == 0.0f ? 0.f : (float)(int8_t)roundf(__fdiv_rn(v[i + 1], d));
+    const __half2 h = __halves2half2(__float2half_rn(dh * q0), __float2half_rn(dh * q1));
+    out[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+    for (int i = 0; i < off; ++i) v[i] = v[i] + v[i + off];
+  uint4* dst = reinterpret_cast<uint4*>(P.xh + row * kpad + (int64_t)b * 32);   // kpad is a multiple of 512: 16-byte aligned
+#pragma unroll
+  for (int i = 0; i < 4; ++i) dst[i] = make_uint4(out[4 * i], out[4 * i + 1], out[4 * i + 2], out[4 * i + 3]);
+  P.s8h[row * nb + b] = __float2half_rn(v[0]);
+}
+
 int launch_quantize(const void* x, int x_dtype, int64_t m, int64_t k, int64_t stride_x, const Q8Ptrs* Pp,
                     void* wire36, int64_t kpad, cudaStream_t st) {
   Q8Ptrs P;
   if (Pp) P = *Pp; else { P = Q8Ptrs(); P.ds = nullptr; P.qs = nullptr; P.qsp = nullptr; P.xh = nullptr; P.s8h = nullptr; P.dT = P.z32 = P.zs8 = P.z16 = P.z32r = P.z16r = P.part = nullptr; P.cnt = P.status = nullptr; P.kpad = kpad; P.ncnt = 0; }
+  const bool pdl_on = options().pdl != 0;
+  if (P.xh && P.s8h && !P.qs && !P.qsp && !P.ds && !P.dT && !wire36 && (k % 32) == 0 && m > 0) {
+    // only the GEMM's operands are wanted (large M): lane-per-block kernel
+    int64_t gl = (m * (k / 32) + 255) / 256;
+    if (gl * 256 < P.ncnt) gl = (P.ncnt + 255) / 256;
+    cudaError_t rc2;
+    switch (x_dtype) {
+      case KQ_F32: rc2 = launch_pdl(quantize_xh_kernel<float>, dim3((unsigned)gl), dim3(256), 0, st, pdl_on, (const float*)x, stride_x, (int)k, (int)kpad, m, P); break;
+      case KQ_F16: rc2 = launch_pdl(quantize_xh_kernel<__half>, dim3((unsigned)gl), dim3(256), 0, st, pdl_on, (const __half*)x, stride_x, (int)k, (int)kpad, m, P); break;
+      case KQ_BF16: rc2 = launch_pdl(quantize_xh_kernel<__nv_bfloat16>, dim3((unsigned)gl), dim3(256), 0, st, pdl_on, (const __nv_bfloat16*)x, stride_x, (int)k, (int)kpad, m, P); break;
+      default: set_error("unsupported activation dtype %d", x_dtype); return KQ_EUNSUPPORTED;
+    }
+    KQ_CUDA_TRY(rc2);
+    options().launches += 1;
+    KQ_CUDA_TRY(cudaGetLastError());
+    return KQ_OK;
+  }
   const int64_t mpad = Pp ? (m + 15) / 16 * 16 : m;
   const int64_t nblk = mpad * (kpad / 32);
   if (nblk == 0) return KQ_OK;

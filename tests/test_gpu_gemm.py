@@ -90,3 +90,18 @@ def test_gemm_and_gemv_paths_agree():
     finally:
         capi.set_option("gemm_min_m", old)
     assert rel_l2(to_np(y_gemm), to_np(y_gemv)) < GATE
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f16", "f32"])
+@pytest.mark.parametrize("qt,n,k,m", [(12, 256, 1024, 200), (14, 384, 2048, 96), (2, 128, 512, 130)])
+def test_gemm_only_quantizer_equals_full_quantizer(qt, n, k, m, dt):
+    """kq_mul_mat_a8 at large M quantizes with the lane-per-block kernel that writes only the GEMM's operands;
+    kq_prepare_q8 + kq_mul_mat_prepared goes through the warp-per-block kernel that writes everything.  Same bits."""
+    _, wt = wire(qt, n, k, seed=n + qt)
+    _, xt = act(m, k, seed=m + 1, dt=dt)
+    scratch = torch.empty(capi.workspace_bytes(qt, m, n, k), dtype=torch.uint8, device=dev())
+    y1 = capi.mul_mat(wt, xt, qt, mmq=True, out_dtype=torch.float32, scratch=scratch)
+    y0 = torch.empty_like(y1)
+    capi.prepare_q8(xt, qt, n, scratch)
+    capi.mul_mat_prepared(wt, qt, m, k, y0, scratch, mmq=True)
+    assert torch.equal(y1, y0)
