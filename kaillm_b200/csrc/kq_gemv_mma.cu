@@ -1095,8 +1095,8 @@ bool gemv_rows_only(int type, int64_t m) {
   const int impl = options().gemv_impl;
   if (impl == 3 || impl == 4) return true;
   if (impl != 0) return false;
-  const bool has_tc = (type == KQ_TYPE_Q4_K || type == KQ_TYPE_Q6_K);
-  return !has_tc || m < options().tc_min_m;
+  const bool has_tile = (type == KQ_TYPE_Q4_K || type == KQ_TYPE_Q6_K || type == KQ_TYPE_Q8_0);
+  return !has_tile || m < options().tc_min_m;
 }
 
 // fuse_x != nullptr (only with gemv_rows_only): the activations have NOT been quantized into P; the kernel reads them raw
@@ -1128,7 +1128,7 @@ int launch_gemv_mma(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs&
     }
     if (impl == 5) { set_error("tcgen05 GEMV: type/shape not covered"); return KQ_EUNSUPPORTED; }
     // 3..16 tokens of Q4_K / Q6_K: the shared-stage mma kernel (all warps of a CTA on every stage of 8 rows)
-    if (has_tc && tile_start && (impl == 6 || (impl == 0 && left >= options().tc_min_m)) &&
+    if (tile_start && (impl == 6 || (impl == 0 && left >= options().tc_min_m)) &&
         gemv_tile_supported(W, type, n, k, (int)(left < 16 ? left : 16))) {
       mcount = (int)(left < 16 ? left : 16);
       rc = launch_gemv_tile(W, type, n, k, P, m0, mcount, y, y_dtype, stride_y, mmq, st);

@@ -1,4 +1,4 @@
-// Decode GEMV for 3..16 tokens per pass (Q4_K, Q6_K): int8 mma.sync, every warp of the CTA on every stage.
+// Decode GEMV for 3..16 tokens per pass (Q4_K, Q6_K, Q8_0): int8 mma.sync, every warp of the CTA on every stage.
 //
 //   grid      one CTA per SM, in `ks` groups; group s works on K slice s of every weight row it owns (ks is the
 //             smallest of 1, 2, 4 whose activation slice leaves room for a ring of >= 4 stages)
@@ -273,7 +273,42 @@ __device__ __forceinline__ void unit_q6k(uint32_t pg, int b0, const TileView& A,
   for (int i = 0; i < 2 * NH; ++i) acc[i] = fmaf(d, u[i], acc[i]);
 }
 
+// ---------------------------------------------------------------------------------------------- Q8_0 unit
+// Eight consecutive 34-byte blocks (256 weights, 272 bytes; pg is 16-byte aligned).  The weights are int8 already:
+// A rows 0-7 carry block 2i, rows 8-15 block 2i+1, one mma against the activations of each.  Inside a block the
+// codes start at byte 2, so an even block's words straddle aligned words (funnel shift) and an odd block's are aligned.
+template <int NH>
+__device__ __forceinline__ void unit_q80(uint32_t pg, int b0, const TileView& A, int g, int t, float (&acc)[4]) {
+  const uint32_t tok = A.sA + (uint32_t)g * A.a_stride + (uint32_t)b0 * 32u + 8u * (uint32_t)t;
+  const uint32_t dsc = A.sD + ((uint32_t)b0 * 16u + 2u * (uint32_t)t) * 4u;
+#pragma unroll
+  for (int pr = 0; pr < 4; ++pr) {
+    const uint32_t pe = pg + 68 * pr, po = pe + 34;        // even / odd block of the pair
+    const uint32_t x0 = lds32(pe + 8 * t), x1 = lds32(pe + 8 * t + 4), x2 = lds32(pe + 8 * t + 8);
+    const uint32_t a0 = __funnelshift_r(x0, x1, 16), a2 = __funnelshift_r(x1, x2, 16);
+    const uint32_t a1 = lds32(po + 2 + 8 * t), a3 = lds32(po + 6 + 8 * t);
+    const float de = __half2float(*reinterpret_cast<const __half*>(tl_smem + pe));
+    const float d_odd = __half2float(*reinterpret_cast<const __half*>(tl_smem + po));
+#pragma unroll
+    for (int hf = 0; hf < NH; ++hf) {
+      const uint2 xl = lds64(tok + hf * 8 * A.a_stride + (2 * pr) * 32);
+      const uint2 xh = lds64(tok + hf * 8 * A.a_stride + (2 * pr + 1) * 32);
+      int Dl[4], Dh[4];
+      mma_i8_k32(Dl, a0, a1, a2, a3, xl.x, xl.y);
+      mma_i8_k32(Dh, a0, a1, a2, a3, xh.x, xh.y);
+      const float2 dl = ldsf2(dsc + ((2 * pr) * 16 + 8 * hf) * 4);
+      const float2 dh = ldsf2(dsc + ((2 * pr + 1) * 16 + 8 * hf) * 4);
+      acc[2 * hf] = fmaf((float)Dl[0], de * dl.x, acc[2 * hf]);
+      acc[2 * hf + 1] = fmaf((float)Dl[1], de * dl.y, acc[2 * hf + 1]);
+      acc[2 * hf] = fmaf((float)Dh[2], d_odd * dh.x, acc[2 * hf]);
+      acc[2 * hf + 1] = fmaf((float)Dh[3], d_odd * dh.y, acc[2 * hf + 1]);
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------- kernel
+// The kernel's unit of K is 256 weights: a super-block of the K-quants, eight blocks of Q8_0.
+template <int QT> struct TileUnit { static constexpr int BYTES = Fmt<QT>::BYTES * (256 / Fmt<QT>::BLK); };
 // NH = 1: up to 8 tokens per pass, NH = 2: up to 16
 template <int QT, int NH, typename OutT>
 __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TileParams p) {
@@ -314,12 +349,12 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
 
   if (warp == TL_CW + 1) {
     // ------------------------------------------------------------------ producer
-    const int k0 = blk0 * F::BLK, klen = nsb * F::BLK;
+    const int k0 = blk0 * 256, klen = nsb * 256;
     const int b32_0 = k0 >> 5, nb32 = klen >> 5;
     const int tt = p.m0 >> 4;
     const int ntok = p.mcount < 8 * NH ? p.mcount : 8 * NH;
-    const size_t seg0 = (size_t)blk0 * F::BYTES;
-    const uint32_t seglen = (uint32_t)nsb * F::BYTES;
+    const size_t seg0 = (size_t)blk0 * TileUnit<QT>::BYTES;
+    const uint32_t seglen = (uint32_t)nsb * TileUnit<QT>::BYTES;
     const int contig = p.contig;
     int slot = 0;          // ring position of the next stage to issue
     uint32_t eph = 1;      // parity that shows the slot's previous contents consumed (passes at once on the first lap)
@@ -443,7 +478,7 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
   const uint32_t stage_bytes = (uint32_t)p.stage_bytes, ring_a = (uint32_t)(ring - smem);
   const bool rows_same_parity = (p.rowbytes & 3) == 0 && (row_stride & 3u) == 0;   // all rows of a stage equally aligned mod 4
   // row r of a stage starts at r * row_stride + the low four bits of its global address
-  const uint32_t off_base = (uint32_t)(((uintptr_t)p.W + (size_t)blk0 * F::BYTES) & 15);
+  const uint32_t off_base = (uint32_t)(((uintptr_t)p.W + (size_t)blk0 * TileUnit<QT>::BYTES) & 15);
   const uint32_t row_step = (uint32_t)(p.rowbytes & 15);
   int first = warp;   // first super-block of the current stage that belongs to this warp
   int slot = 0;
@@ -457,8 +492,9 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     int sbi = first;
     for (; sbi < nsb; sbi += TL_CW) {
-      const uint32_t pg = rg + (uint32_t)sbi * F::BYTES;
+      const uint32_t pg = rg + (uint32_t)sbi * TileUnit<QT>::BYTES;
       if constexpr (QT == KQ_TYPE_Q4_K) unit_q4k<NH>(pg, sbi * 8, A, g, t, acc);
+      if constexpr (QT == KQ_TYPE_Q8_0) unit_q80<NH>(pg, sbi * 8, A, g, t, acc);
       if constexpr (QT == KQ_TYPE_Q6_K) {
         // every branch here is taken by all 32 lanes alike (the units contain warp-wide mma instructions)
         if (!rows_same_parity) unit_q6k<NH, 2>(pg, sbi * 8, A, g, t, acc);
@@ -516,10 +552,12 @@ int tl_sm_count() {
 
 // smallest K split whose activation slice leaves room for a ring of >= 4 stages
 bool make_tile_config(int type, int64_t n, int64_t k, int mtok, TileConfig& c) {
-  if (type != KQ_TYPE_Q4_K && type != KQ_TYPE_Q6_K) return false;
+  if (type != KQ_TYPE_Q4_K && type != KQ_TYPE_Q6_K && type != KQ_TYPE_Q8_0) return false;
   int blk, bytes;
   if (!type_geometry(type, &blk, &bytes)) return false;
-  if (k % blk) return false;
+  if (k % 256) return false;
+  bytes *= 256 / blk;   // the kernel's unit of K is 256 weights
+  blk = 256;
   const int nblk = (int)(k / blk);
   const int64_t rowbytes = (int64_t)nblk * bytes;
   const int sms = tl_sm_count();
@@ -530,7 +568,7 @@ bool make_tile_config(int type, int64_t n, int64_t k, int mtok, TileConfig& c) {
     const int nsb = (nblk + ks - 1) / ks;
     const int klen = nsb * blk;
     const int contig = (ks == 1 && !seg_mode) ? 1 : 0;
-    const int resid = type == KQ_TYPE_Q4_K ? 32 : 16;   // row stride mod 128: spreads the 8 rows over the banks
+    const int resid = type == KQ_TYPE_Q6_K ? 16 : 32;   // row stride mod 128: spreads the 8 rows over the banks
     int row_stride = (int)rowbytes;
     int stage_bytes;
     if (contig) {
@@ -600,7 +638,7 @@ int launch_gemv_tile(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs
   int blk, bytes;
   type_geometry(type, &blk, &bytes);
   TileParams p;
-  p.W = (const uint8_t*)W; p.rowbytes = k / blk * bytes; p.n = (int)n; p.nblk = (int)(k / blk); p.ks = c.ks;
+  p.W = (const uint8_t*)W; p.rowbytes = k / blk * bytes; p.n = (int)n; p.nblk = (int)(k / 256); p.ks = c.ks;   // units of 256 weights
   p.ntiles = (int)((n + TL_ROWS - 1) / TL_ROWS); p.stages = c.stages; p.row_stride = c.row_stride;
   p.stage_bytes = c.stage_bytes; p.contig = c.contig; p.a_stride = c.a_stride; p.a_bytes = c.a_bytes;
   p.d_bytes = c.d_bytes; p.z_bytes = c.z_bytes; p.qs = P.qs; p.dT = P.dT;
@@ -608,8 +646,11 @@ int launch_gemv_tile(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs
   p.kpad = (int)P.kpad; p.nb32tot = (int)(P.kpad / 32); p.m0 = (int)m0; p.mcount = mcount;
   p.prefetch = options().pdl < c.stages ? options().pdl : c.stages;
   p.y = y; p.stride_y = stride_y; p.part = P.part; p.cnt = P.cnt; p.status = P.status;
-  return type == KQ_TYPE_Q4_K ? launch_tile_typed<KQ_TYPE_Q4_K>(p, c, nh, y_dtype, st)
-                              : launch_tile_typed<KQ_TYPE_Q6_K>(p, c, nh, y_dtype, st);
+  switch (type) {
+    case KQ_TYPE_Q4_K: return launch_tile_typed<KQ_TYPE_Q4_K>(p, c, nh, y_dtype, st);
+    case KQ_TYPE_Q6_K: return launch_tile_typed<KQ_TYPE_Q6_K>(p, c, nh, y_dtype, st);
+    default: return launch_tile_typed<KQ_TYPE_Q8_0>(p, c, nh, y_dtype, st);
+  }
 }
 
 }  // namespace kq
