@@ -44,7 +44,7 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   return v;
 }
 
-__global__ void __launch_bounds__(256) p2p_allgather_kernel(const P2PParams p) {
+__global__ void __launch_bounds__(1024) p2p_allgather_kernel(const P2PParams p) {
   const size_t nvec = p.bytes / 16;
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nthr = (size_t)gridDim.x * blockDim.x;
   const size_t off0 = (size_t)p.rank * p.bytes;
@@ -61,22 +61,26 @@ __global__ void __launch_bounds__(256) p2p_allgather_kernel(const P2PParams p) {
     }
   }
   __syncthreads();
-  __shared__ int s_last;
-  if (threadIdx.x == 0) {
-    __threadfence_system();   // this CTA's stores (ordered before by the barrier) are visible system-wide
-    s_last = atomicAdd(p.done + p.slot, 1u) == gridDim.x - 1;
+  if (gridDim.x > 1) {
+    __shared__ int s_last;
+    if (threadIdx.x == 0) {
+      __threadfence_system();   // this CTA's stores (ordered before by the barrier) are visible system-wide
+      s_last = atomicAdd(p.done + p.slot, 1u) == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (!s_last) return;
   }
-  __syncthreads();
-  if (!s_last) return;
   __shared__ uint32_t s_epoch;
   if (threadIdx.x == 0) {
-    __threadfence_system();
-    p.done[p.slot] = 0;
+    __threadfence_system();   // every CTA's stores (ordered before by the barrier / the counter) are visible system-wide
+    if (gridDim.x > 1) p.done[p.slot] = 0;
     const uint32_t e = p.epoch[p.slot] + 1;
     p.epoch[p.slot] = e;
     s_epoch = e;
-    for (int r = 0; r < p.world; ++r) st_release_sys(p.flags[r] + p.slot * P2P_MAX_RANKS + p.rank, e);
   }
+  __syncthreads();
+  if ((int)threadIdx.x < p.world)   // one lane per destination: the flag stores travel in parallel
+    st_release_sys(p.flags[threadIdx.x] + p.slot * P2P_MAX_RANKS + p.rank, s_epoch);
   __syncthreads();
   if ((int)threadIdx.x < p.world) {
     const uint32_t e = s_epoch;
@@ -105,10 +109,16 @@ int launch_p2p_allgather(const void* src, size_t bytes, void* const* peer_dst, u
     p.dst[r] = r < world ? (uint8_t*)peer_dst[r] : nullptr;
     p.flags[r] = r < world ? peer_flags[r] : nullptr;
   }
-  size_t blocks = (bytes / 16 + 255) / 256;
-  if (blocks < 1) blocks = 1;
-  if (blocks > 32) blocks = 32;
-  p2p_allgather_kernel<<<(unsigned)blocks, 256, 0, st>>>(p);
+  // decode-sized slices (<= 256 KB) go through ONE CTA of 1024 threads: one system-scope fence and no CTA counter on
+  // the way to the flags; larger ones use up to 32 CTAs
+  size_t blocks = 1;
+  unsigned threads = 1024;
+  if (bytes > (256u << 10)) {
+    threads = 256;
+    blocks = (bytes / 16 + 255) / 256;
+    if (blocks > 32) blocks = 32;
+  }
+  p2p_allgather_kernel<<<(unsigned)blocks, threads, 0, st>>>(p);
   options().launches += 1;
   KQ_CUDA_TRY(cudaGetLastError());
   return KQ_OK;
