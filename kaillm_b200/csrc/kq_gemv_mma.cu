@@ -1095,7 +1095,7 @@ bool gemv_rows_only(int type, int64_t m) {
   const int impl = options().gemv_impl;
   if (impl == 3 || impl == 4) return true;
   if (impl != 0) return false;
-  const bool has_tile = (type == KQ_TYPE_Q4_K || type == KQ_TYPE_Q6_K || type == KQ_TYPE_Q8_0);
+  const bool has_tile = type != KQ_TYPE_Q2_K;
   return !has_tile || m < options().tc_min_m;
 }
 
@@ -1128,7 +1128,9 @@ int launch_gemv_mma(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs&
     }
     if (impl == 5) { set_error("tcgen05 GEMV: type/shape not covered"); return KQ_EUNSUPPORTED; }
     // 3..16 tokens of Q4_K / Q6_K: the shared-stage mma kernel (all warps of a CTA on every stage of 8 rows)
-    if (tile_start && (impl == 6 || (impl == 0 && left >= options().tc_min_m)) &&
+    // (Q4_0's 18-byte blocks decode slowly there: the row-streaming kernel is faster up to 8 tokens)
+    const int tile_min = type == KQ_TYPE_Q4_0 ? 9 : options().tc_min_m;
+    if (tile_start && (impl == 6 || (impl == 0 && left >= tile_min)) &&
         gemv_tile_supported(W, type, n, k, (int)(left < 16 ? left : 16))) {
       mcount = (int)(left < 16 ? left : 16);
       rc = launch_gemv_tile(W, type, n, k, P, m0, mcount, y, y_dtype, stride_y, mmq, st);

@@ -1,4 +1,4 @@
-// Decode GEMV for 3..16 tokens per pass (Q4_K, Q6_K, Q8_0): int8 mma.sync, every warp of the CTA on every stage.
+// Decode GEMV for 3..16 tokens per pass (Q4_K, Q6_K, Q8_0, Q4_0, IQ3_S): int8 mma.sync, every warp of the CTA on every stage.
 //
 //   grid      one CTA per SM, in `ks` groups; group s works on K slice s of every weight row it owns (ks is the
 //             smallest of 1, 2, 4 whose activation slice leaves room for a ring of >= 4 stages)
@@ -47,6 +47,11 @@ constexpr int TL_SMEM_LIMIT = 232448;
 constexpr uint32_t TL_MAGIC_I = 0x4B400000u;      // bits of 12582912.0f
 constexpr float TL_MAGIC_F = 12582912.0f;
 constexpr long long TL_WAIT_LIMIT = 1ll << 27;
+
+__constant__ uint16_t c_iq3s_codes_t[512] = {
+#include "kq_iq3s_codes.inc"
+};
+constexpr int TL_GRID_BYTES = 2048;               // IQ3_S: the expanded 512-entry codebook in shared memory
 
 struct TileParams {
   const uint8_t* W;
@@ -306,6 +311,72 @@ __device__ __forceinline__ void unit_q80(uint32_t pg, int b0, const TileView& A,
   }
 }
 
+// ---------------------------------------------------------------------------------------------- Q4_0 / IQ3_S units
+// 32-weight sub-blocks with one scale each: sub-blocks 2i and 2i+1 of the unit share an mma (A rows 0-7 / 8-15), as
+// for Q8_0.  A lane decodes only the eight weights it feeds (k = 8t..8t+7 of the sub-block, natural order).
+// Contribution of a sub-block: wa * d8 * dot - wb * z (Q4_0: wa = d, wb = 8d, z = the fp16 raw block sum, as
+// vecdotq.cuh:46-66; IQ3_S: wa = d*(0.5+s)*0.5, no second term, vecdotq.cuh IQ3_S path).
+template <int QT>
+__device__ __forceinline__ void decode_part(const uint8_t* u, int j, int t, const uint32_t* grid, uint32_t& w0, uint32_t& w1,
+                                            float& wa, float& wb) {
+  if constexpr (QT == KQ_TYPE_Q4_0) {
+    const uint8_t* b = u + 18 * j;
+    const float d = ld_h(b);
+    const uint32_t q0 = ld_u16x2(b + 2 + 8 * (t & 1)), q1 = ld_u16x2(b + 6 + 8 * (t & 1));
+    const int sh = (t >> 1) * 4;                       // lanes 2, 3 take the high nibbles (weights 16..31)
+    w0 = (q0 >> sh) & 0x0F0F0F0Fu;
+    w1 = (q1 >> sh) & 0x0F0F0F0Fu;
+    wa = d; wb = 8.0f * d;
+  } else {   // IQ3_S
+    const float d = ld_h(u);
+    const uint8_t* qs = u + 2 + 8 * j;
+    const uint32_t qh = u[66 + j];
+    const uint32_t i1 = qs[2 * t] | ((qh << (8 - 2 * t)) & 256u);
+    const uint32_t i2 = qs[2 * t + 1] | ((qh << (7 - 2 * t)) & 256u);
+    const uint32_t sg = u[74 + 4 * j + t];
+    w0 = negate_bytes(grid[i1], nibble_to_bytemask(sg & 15u));
+    w1 = negate_bytes(grid[i2], nibble_to_bytemask(sg >> 4));
+    const uint32_t s4 = (u[106 + (j >> 1)] >> (4 * (j & 1))) & 15u;
+    wa = d * (0.5f + (float)s4) * 0.5f; wb = 0.f;
+  }
+}
+
+template <int QT, int NH>
+__device__ __forceinline__ void unit_g32(uint32_t pg, int b0, const TileView& A, const uint32_t* grid, int g, int t,
+                                         float (&acc)[4]) {
+  const uint8_t* u = tl_smem + pg;
+  const uint32_t tok = A.sA + (uint32_t)g * A.a_stride + (uint32_t)b0 * 32u + 8u * (uint32_t)t;
+  const uint32_t dsc = A.sD + ((uint32_t)b0 * 16u + 2u * (uint32_t)t) * 4u;
+  const uint32_t zsc = A.sZ + ((uint32_t)b0 * 16u + 2u * (uint32_t)t) * 4u;
+#pragma unroll
+  for (int pr = 0; pr < 4; ++pr) {
+    uint32_t a0, a1, a2, a3;
+    float wa0, wb0, wa1, wb1;
+    decode_part<QT>(u, 2 * pr, t, grid, a0, a2, wa0, wb0);
+    decode_part<QT>(u, 2 * pr + 1, t, grid, a1, a3, wa1, wb1);
+#pragma unroll
+    for (int hf = 0; hf < NH; ++hf) {
+      const uint2 xl = lds64(tok + hf * 8 * A.a_stride + (2 * pr) * 32);
+      const uint2 xh = lds64(tok + hf * 8 * A.a_stride + (2 * pr + 1) * 32);
+      int Dl[4], Dh[4];
+      mma_i8_k32(Dl, a0, a1, a2, a3, xl.x, xl.y);
+      mma_i8_k32(Dh, a0, a1, a2, a3, xh.x, xh.y);
+      const float2 dl = ldsf2(dsc + ((2 * pr) * 16 + 8 * hf) * 4);
+      const float2 dh = ldsf2(dsc + ((2 * pr + 1) * 16 + 8 * hf) * 4);
+      acc[2 * hf] = fmaf((float)Dl[0], wa0 * dl.x, acc[2 * hf]);
+      acc[2 * hf + 1] = fmaf((float)Dl[1], wa0 * dl.y, acc[2 * hf + 1]);
+      acc[2 * hf] = fmaf((float)Dh[2], wa1 * dh.x, acc[2 * hf]);
+      acc[2 * hf + 1] = fmaf((float)Dh[3], wa1 * dh.y, acc[2 * hf + 1]);
+      if constexpr (QT == KQ_TYPE_Q4_0) {
+        const float2 zl = ldsf2(zsc + ((2 * pr) * 16 + 8 * hf) * 4);
+        const float2 zh = ldsf2(zsc + ((2 * pr + 1) * 16 + 8 * hf) * 4);
+        acc[2 * hf] -= wb0 * zl.x + wb1 * zh.x;
+        acc[2 * hf + 1] -= wb0 * zl.y + wb1 * zh.y;
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------- kernel
 // The kernel's unit of K is 256 weights: a super-block of the K-quants, eight blocks of Q8_0.
 template <int QT> struct TileUnit { static constexpr int BYTES = Fmt<QT>::BYTES * (256 / Fmt<QT>::BLK); };
@@ -316,7 +387,8 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
   uint8_t* const smem = tl_smem;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem + TL_HEADER - 8);
-  uint8_t* sA = smem + TL_HEADER;
+  uint32_t* s_grid = reinterpret_cast<uint32_t*>(smem + TL_HEADER);   // IQ3_S only
+  uint8_t* sA = smem + TL_HEADER + (QT == KQ_TYPE_IQ3_S ? TL_GRID_BYTES : 0);
   float* sD = reinterpret_cast<float*>(sA + p.a_bytes);
   float* sZ = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sD) + p.d_bytes);
   float4* sRed = reinterpret_cast<float4*>(reinterpret_cast<uint8_t*>(sZ) + p.z_bytes);   // [2][16 warps][32 lanes]
@@ -344,6 +416,9 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
     *s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if constexpr (QT == KQ_TYPE_IQ3_S) {
+    for (int i = threadIdx.x; i < 512; i += TL_THREADS) s_grid[i] = iq3s_expand(c_iq3s_codes_t[i], KQ_IQ3S_TOP);
   }
   __syncthreads();
 
@@ -495,6 +570,7 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
       const uint32_t pg = rg + (uint32_t)sbi * TileUnit<QT>::BYTES;
       if constexpr (QT == KQ_TYPE_Q4_K) unit_q4k<NH>(pg, sbi * 8, A, g, t, acc);
       if constexpr (QT == KQ_TYPE_Q8_0) unit_q80<NH>(pg, sbi * 8, A, g, t, acc);
+      if constexpr (QT == KQ_TYPE_Q4_0 || QT == KQ_TYPE_IQ3_S) unit_g32<QT, NH>(pg, sbi * 8, A, s_grid, g, t, acc);
       if constexpr (QT == KQ_TYPE_Q6_K) {
         // every branch here is taken by all 32 lanes alike (the units contain warp-wide mma instructions)
         if (!rows_same_parity) unit_q6k<NH, 2>(pg, sbi * 8, A, g, t, acc);
@@ -552,7 +628,8 @@ int tl_sm_count() {
 
 // smallest K split whose activation slice leaves room for a ring of >= 4 stages
 bool make_tile_config(int type, int64_t n, int64_t k, int mtok, TileConfig& c) {
-  if (type != KQ_TYPE_Q4_K && type != KQ_TYPE_Q6_K && type != KQ_TYPE_Q8_0) return false;
+  if (type != KQ_TYPE_Q4_K && type != KQ_TYPE_Q6_K && type != KQ_TYPE_Q8_0 && type != KQ_TYPE_Q4_0 && type != KQ_TYPE_IQ3_S)
+    return false;
   int blk, bytes;
   if (!type_geometry(type, &blk, &bytes)) return false;
   if (k % 256) return false;
@@ -581,8 +658,8 @@ bool make_tile_config(int type, int64_t n, int64_t k, int mtok, TileConfig& c) {
     const int a_stride = klen + resid;
     const int a_bytes = (mtok * a_stride + 127) / 128 * 128;
     const int d_bytes = ((klen / 32) * 64 + 127) / 128 * 128;
-    const int z_bytes = type == KQ_TYPE_Q4_K ? d_bytes : 0;
-    const int fixed = TL_HEADER + a_bytes + d_bytes + z_bytes + TL_NRED * TL_CW * 512;
+    const int z_bytes = (type == KQ_TYPE_Q4_K || type == KQ_TYPE_Q4_0) ? d_bytes : 0;
+    const int fixed = TL_HEADER + (type == KQ_TYPE_IQ3_S ? TL_GRID_BYTES : 0) + a_bytes + d_bytes + z_bytes + TL_NRED * TL_CW * 512;
     int stages = (TL_SMEM_LIMIT - fixed) / stage_bytes;
     if (stages > TL_MAX_STAGES) stages = TL_MAX_STAGES;
     if (stages < 3) continue;
@@ -642,13 +719,15 @@ int launch_gemv_tile(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs
   p.ntiles = (int)((n + TL_ROWS - 1) / TL_ROWS); p.stages = c.stages; p.row_stride = c.row_stride;
   p.stage_bytes = c.stage_bytes; p.contig = c.contig; p.a_stride = c.a_stride; p.a_bytes = c.a_bytes;
   p.d_bytes = c.d_bytes; p.z_bytes = c.z_bytes; p.qs = P.qs; p.dT = P.dT;
-  p.zT = type == KQ_TYPE_Q4_K ? (mmq ? P.zs8 : P.z32) : nullptr;
+  p.zT = type == KQ_TYPE_Q4_K ? (mmq ? P.zs8 : P.z32) : (type == KQ_TYPE_Q4_0 ? P.zs8 : nullptr);
   p.kpad = (int)P.kpad; p.nb32tot = (int)(P.kpad / 32); p.m0 = (int)m0; p.mcount = mcount;
   p.prefetch = options().pdl < c.stages ? options().pdl : c.stages;
   p.y = y; p.stride_y = stride_y; p.part = P.part; p.cnt = P.cnt; p.status = P.status;
   switch (type) {
     case KQ_TYPE_Q4_K: return launch_tile_typed<KQ_TYPE_Q4_K>(p, c, nh, y_dtype, st);
     case KQ_TYPE_Q6_K: return launch_tile_typed<KQ_TYPE_Q6_K>(p, c, nh, y_dtype, st);
+    case KQ_TYPE_Q4_0: return launch_tile_typed<KQ_TYPE_Q4_0>(p, c, nh, y_dtype, st);
+    case KQ_TYPE_IQ3_S: return launch_tile_typed<KQ_TYPE_IQ3_S>(p, c, nh, y_dtype, st);
     default: return launch_tile_typed<KQ_TYPE_Q8_0>(p, c, nh, y_dtype, st);
   }
 }

@@ -182,7 +182,7 @@ def test_tcgen05_gemv_q4k_matches_oracle(n, k, m, mmq):
     assert rel_l2(to_np(y), to_np(y1)) < TIGHT          # every row, against the general kernel
 
 
-@pytest.mark.parametrize("qt", [12, 14, 8])
+@pytest.mark.parametrize("qt", [12, 14, 8, 2, 21])
 @pytest.mark.parametrize("n,k,m", [(8, 256, 5), (17, 512, 8), (100, 1024, 9), (2368, 2048, 12), (4736, 5120, 16),
                                    (333, 4352, 16), (70, 17408, 5), (1190, 17408, 16), (48, 768, 33), (3000, 14336, 13)])
 @pytest.mark.parametrize("mmq", [False, True])
@@ -192,6 +192,8 @@ def test_shared_stage_mma_gemv_matches_oracle_and_dp4a(qt, n, k, m, mmq, segment
     activation slice would not fit; with tile_segments=1 the rows are fetched as separate segments."""
     if segments and m not in (8, 16):
         pytest.skip("segment mode is covered at two token counts")
+    if qt == 21 and mmq:
+        pytest.skip("IQ3_S has no MMQ flavour")
     _, wt = wire(qt, n, k, seed=n + k)
     x, xt = act(m, k, seed=m, dt="bf16")
     w = wt.cpu().numpy()
