@@ -1095,8 +1095,7 @@ bool gemv_rows_only(int type, int64_t m) {
   const int impl = options().gemv_impl;
   if (impl == 3 || impl == 4) return true;
   if (impl != 0) return false;
-  const bool has_tile = type != KQ_TYPE_Q2_K;
-  return !has_tile || m < options().tc_min_m;
+  return m < options().tc_min_m;
 }
 
 // fuse_x != nullptr (only with gemv_rows_only): the activations have NOT been quantized into P; the kernel reads them raw

@@ -1,4 +1,4 @@
-// Decode GEMV for 3..16 tokens per pass (Q4_K, Q6_K, Q8_0, Q4_0, IQ3_S): int8 mma.sync, every warp of the CTA on every stage.
+// Decode GEMV for 3..16 tokens per pass (all six formats): int8 mma.sync, every warp of the CTA on every stage.
 //
 //   grid      one CTA per SM, in `ks` groups; group s works on K slice s of every weight row it owns (ks is the
 //             smallest of 1, 2, 4 whose activation slice leaves room for a ring of >= 4 stages)
@@ -62,6 +62,7 @@ struct TileParams {
   const int8_t* qs;
   const float* dT;
   const float* zT;
+  int zpb;            // z entries per 32-block in zT (2 for Q2_K: one per 16-weight group)
   int kpad, nb32tot;
   int m0, mcount, prefetch;
   void* y;
@@ -377,6 +378,42 @@ __device__ __forceinline__ void unit_g32(uint32_t pg, int b0, const TileView& A,
   }
 }
 
+// ---------------------------------------------------------------------------------------------- Q2_K unit
+// 16-weight groups with their own 4-bit scale and min.  Per 32-weight sub-block ONE m16n8k32 mma: lanes t = 0, 1
+// hold weights 0..15 (group 0) and feed A rows 0-7, lanes t = 2, 3 hold weights 16..31 (group 1) and feed rows
+// 8-15; the other half of each lane's fragment is zero, so rows 0-7 of the result are the group-0 dots and rows
+// 8-15 the group-1 dots.  y += d*sc*d8*dot - dmin*m*(d8 * group sum of the activation codes), vecdotq.cuh Q2_K path.
+template <int NH>
+__device__ __forceinline__ void unit_q2k(uint32_t pg, int b0, const TileView& A, int g, int t, float (&acc)[4]) {
+  const uint8_t* u = tl_smem + pg;
+  const float2 dd = __half22float2(*reinterpret_cast<const __half2*>(u + 80));   // {d, dmin}
+  const uint32_t tok = A.sA + (uint32_t)g * A.a_stride + (uint32_t)b0 * 32u + 8u * (uint32_t)t;
+  const uint32_t dsc = A.sD + ((uint32_t)b0 * 16u + 2u * (uint32_t)t) * 4u;
+  const uint32_t zsc = A.sZ + ((uint32_t)b0 * 32u + 2u * (uint32_t)t) * 4u;       // [2 per block][16 tokens]
+  const bool lo_half = t < 2;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int n = j >> 2, jj = j & 3;
+    const uint32_t w0 = (ld_u32(u + 16 + 32 * n + 8 * t) >> (2 * jj)) & 0x03030303u;
+    const uint32_t w1 = (ld_u32(u + 16 + 32 * n + 8 * t + 4) >> (2 * jj)) & 0x03030303u;
+    const uint32_t a0 = lo_half ? w0 : 0u, a2 = lo_half ? w1 : 0u, a1 = lo_half ? 0u : w0, a3 = lo_half ? 0u : w1;
+    const uint32_t s0 = u[2 * j], s1 = u[2 * j + 1];
+    const float wa0 = dd.x * (float)(s0 & 15u), wb0 = dd.y * (float)(s0 >> 4);
+    const float wa1 = dd.x * (float)(s1 & 15u), wb1 = dd.y * (float)(s1 >> 4);
+#pragma unroll
+    for (int hf = 0; hf < NH; ++hf) {
+      const uint2 x = lds64(tok + hf * 8 * A.a_stride + j * 32);
+      int D[4];
+      mma_i8_k32(D, a0, a1, a2, a3, x.x, x.y);
+      const float2 d8 = ldsf2(dsc + (j * 16 + 8 * hf) * 4);
+      const float2 z0 = ldsf2(zsc + ((2 * j) * 16 + 8 * hf) * 4);
+      const float2 z1 = ldsf2(zsc + ((2 * j + 1) * 16 + 8 * hf) * 4);
+      acc[2 * hf] += d8.x * (wa0 * (float)D[0] + wa1 * (float)D[2]) - (wb0 * z0.x + wb1 * z1.x);
+      acc[2 * hf + 1] += d8.y * (wa0 * (float)D[1] + wa1 * (float)D[3]) - (wb0 * z0.y + wb1 * z1.y);
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------- kernel
 // The kernel's unit of K is 256 weights: a super-block of the K-quants, eight blocks of Q8_0.
 template <int QT> struct TileUnit { static constexpr int BYTES = Fmt<QT>::BYTES * (256 / Fmt<QT>::BLK); };
@@ -470,7 +507,7 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
     {
       if (lane == 0) {
         uint32_t total = (uint32_t)ntok * klen + (uint32_t)nb32 * 64u;
-        if (p.zT != nullptr) total += (uint32_t)nb32 * 64u;
+        if (p.zT != nullptr) total += (uint32_t)nb32 * p.zpb * 64u;
         bar_expect_tx(bar_act, total);
       }
       __syncwarp();
@@ -478,7 +515,7 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
         copy_g2s(s_u32(sA + lane * p.a_stride), p.qs + (size_t)(p.m0 + lane) * p.kpad + k0, (uint32_t)klen, bar_act);
       if (lane == 16) copy_g2s(s_u32(sD), p.dT + ((size_t)tt * p.nb32tot + b32_0) * 16, (uint32_t)nb32 * 64u, bar_act);
       if (lane == 17 && p.zT != nullptr)
-        copy_g2s(s_u32(sZ), p.zT + ((size_t)tt * p.nb32tot + b32_0) * 16, (uint32_t)nb32 * 64u, bar_act);
+        copy_g2s(s_u32(sZ), p.zT + ((size_t)tt * p.nb32tot + b32_0) * p.zpb * 16, (uint32_t)nb32 * p.zpb * 64u, bar_act);
     }
     bool ok = true;
     for (; q < nst; ++q) {
@@ -571,6 +608,7 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
       if constexpr (QT == KQ_TYPE_Q4_K) unit_q4k<NH>(pg, sbi * 8, A, g, t, acc);
       if constexpr (QT == KQ_TYPE_Q8_0) unit_q80<NH>(pg, sbi * 8, A, g, t, acc);
       if constexpr (QT == KQ_TYPE_Q4_0 || QT == KQ_TYPE_IQ3_S) unit_g32<QT, NH>(pg, sbi * 8, A, s_grid, g, t, acc);
+      if constexpr (QT == KQ_TYPE_Q2_K) unit_q2k<NH>(pg, sbi * 8, A, g, t, acc);
       if constexpr (QT == KQ_TYPE_Q6_K) {
         // every branch here is taken by all 32 lanes alike (the units contain warp-wide mma instructions)
         if (!rows_same_parity) unit_q6k<NH, 2>(pg, sbi * 8, A, g, t, acc);
@@ -628,8 +666,6 @@ int tl_sm_count() {
 
 // smallest K split whose activation slice leaves room for a ring of >= 4 stages
 bool make_tile_config(int type, int64_t n, int64_t k, int mtok, TileConfig& c) {
-  if (type != KQ_TYPE_Q4_K && type != KQ_TYPE_Q6_K && type != KQ_TYPE_Q8_0 && type != KQ_TYPE_Q4_0 && type != KQ_TYPE_IQ3_S)
-    return false;
   int blk, bytes;
   if (!type_geometry(type, &blk, &bytes)) return false;
   if (k % 256) return false;
@@ -658,7 +694,7 @@ bool make_tile_config(int type, int64_t n, int64_t k, int mtok, TileConfig& c) {
     const int a_stride = klen + resid;
     const int a_bytes = (mtok * a_stride + 127) / 128 * 128;
     const int d_bytes = ((klen / 32) * 64 + 127) / 128 * 128;
-    const int z_bytes = (type == KQ_TYPE_Q4_K || type == KQ_TYPE_Q4_0) ? d_bytes : 0;
+    const int z_bytes = (type == KQ_TYPE_Q4_K || type == KQ_TYPE_Q4_0) ? d_bytes : (type == KQ_TYPE_Q2_K ? 2 * d_bytes : 0);
     const int fixed = TL_HEADER + (type == KQ_TYPE_IQ3_S ? TL_GRID_BYTES : 0) + a_bytes + d_bytes + z_bytes + TL_NRED * TL_CW * 512;
     int stages = (TL_SMEM_LIMIT - fixed) / stage_bytes;
     if (stages > TL_MAX_STAGES) stages = TL_MAX_STAGES;
@@ -719,7 +755,8 @@ int launch_gemv_tile(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs
   p.ntiles = (int)((n + TL_ROWS - 1) / TL_ROWS); p.stages = c.stages; p.row_stride = c.row_stride;
   p.stage_bytes = c.stage_bytes; p.contig = c.contig; p.a_stride = c.a_stride; p.a_bytes = c.a_bytes;
   p.d_bytes = c.d_bytes; p.z_bytes = c.z_bytes; p.qs = P.qs; p.dT = P.dT;
-  p.zT = type == KQ_TYPE_Q4_K ? (mmq ? P.zs8 : P.z32) : (type == KQ_TYPE_Q4_0 ? P.zs8 : nullptr);
+  p.zT = type == KQ_TYPE_Q4_K ? (mmq ? P.zs8 : P.z32) : (type == KQ_TYPE_Q4_0 ? P.zs8 : (type == KQ_TYPE_Q2_K ? P.z16 : nullptr));
+  p.zpb = type == KQ_TYPE_Q2_K ? 2 : 1;
   p.kpad = (int)P.kpad; p.nb32tot = (int)(P.kpad / 32); p.m0 = (int)m0; p.mcount = mcount;
   p.prefetch = options().pdl < c.stages ? options().pdl : c.stages;
   p.y = y; p.stride_y = stride_y; p.part = P.part; p.cnt = P.cnt; p.status = P.status;
@@ -728,6 +765,7 @@ int launch_gemv_tile(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs
     case KQ_TYPE_Q6_K: return launch_tile_typed<KQ_TYPE_Q6_K>(p, c, nh, y_dtype, st);
     case KQ_TYPE_Q4_0: return launch_tile_typed<KQ_TYPE_Q4_0>(p, c, nh, y_dtype, st);
     case KQ_TYPE_IQ3_S: return launch_tile_typed<KQ_TYPE_IQ3_S>(p, c, nh, y_dtype, st);
+    case KQ_TYPE_Q2_K: return launch_tile_typed<KQ_TYPE_Q2_K>(p, c, nh, y_dtype, st);
     default: return launch_tile_typed<KQ_TYPE_Q8_0>(p, c, nh, y_dtype, st);
   }
 }

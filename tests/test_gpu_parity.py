@@ -182,7 +182,7 @@ def test_tcgen05_gemv_q4k_matches_oracle(n, k, m, mmq):
     assert rel_l2(to_np(y), to_np(y1)) < TIGHT          # every row, against the general kernel
 
 
-@pytest.mark.parametrize("qt", [12, 14, 8, 2, 21])
+@pytest.mark.parametrize("qt", [12, 14, 8, 2, 21, 10])
 @pytest.mark.parametrize("n,k,m", [(8, 256, 5), (17, 512, 8), (100, 1024, 9), (2368, 2048, 12), (4736, 5120, 16),
                                    (333, 4352, 16), (70, 17408, 5), (1190, 17408, 16), (48, 768, 33), (3000, 14336, 13)])
 @pytest.mark.parametrize("mmq", [False, True])
