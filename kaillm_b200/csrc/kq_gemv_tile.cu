@@ -233,10 +233,12 @@ __device__ __forceinline__ void unit_q4k(uint32_t pg, int b0, const TileView& A,
 // super-block: low nibbles from ql[64ip + 32(q4&1) + 16s + 4t] >> 4(q4>>1), two high bits from
 // qh[32ip + 16s + 4t] >> 2q4.  The two groups share the activation scale, so their scaled dots are added as
 // integers before the conversion (|sum| < 2^24).
+// Four 6-bit codes -> four int8 values 4*(code - 32): the code sits in bits 2..7 of its byte with its top bit flipped,
+// which is the two's-complement byte of 4*(code - 32) (range -128..124).  The factor 4 is taken out again through d.
 __device__ __forceinline__ uint32_t unpack6_tl(uint32_t qlw, uint32_t qhw, int q4) {
-  const uint32_t lo = q4 >> 1 ? qlw >> 4 : qlw;
-  const uint32_t hi = q4 == 0 ? qhw << 4 : (q4 == 1 ? qhw << 2 : (q4 == 2 ? qhw : qhw >> 2));
-  return sub32_bytes((lo & 0x0F0F0F0Fu) | (hi & 0x30303030u));
+  const uint32_t lo = q4 >> 1 ? qlw >> 2 : qlw << 2;                                          // nibble -> bits 2..5
+  const uint32_t hi = q4 == 0 ? qhw << 6 : (q4 == 1 ? qhw << 4 : (q4 == 2 ? qhw << 2 : qhw));  // 2 bits -> bits 6, 7
+  return (lo & 0x3C3C3C3Cu) | ((hi & 0xC0C0C0C0u) ^ 0x80808080u);
 }
 
 template <int NH, int AL>
@@ -274,7 +276,7 @@ __device__ __forceinline__ void unit_q6k(uint32_t pg, int b0, const TileView& A,
       }
     }
   }
-  const float d = __half2float(*reinterpret_cast<const __half*>(tl_smem + pg + 208));
+  const float d = 0.25f * __half2float(*reinterpret_cast<const __half*>(tl_smem + pg + 208));   // the weights carry a factor 4
 #pragma unroll
   for (int i = 0; i < 2 * NH; ++i) acc[i] = fmaf(d, u[i], acc[i]);
 }
