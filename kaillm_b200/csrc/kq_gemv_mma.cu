@@ -1,6 +1,8 @@
-// Decode GEMV, tensor-core flavour (M = 1..16 per pass): a persistent, warp-specialised kernel that streams the
-// wire bytes through shared memory with bulk asynchronous copies and forms the integer block dots with
-// int8 mma.sync.
+// Decode GEMV: the dispatch over the streaming kernels (launch_gemv_mma, bottom of the file) and two of them:
+//   gemv_rows_kernel    1-2 tokens (and every count for shapes the shared-stage kernel does not take): whole rows per
+//                       stage, dp4a consumers, optional in-kernel q8_1 quantization; described above its definition
+//   gemv_stream_kernel  the first int8 mma.sync kernel (a warp owns a 16-row tile), kept behind gemv_impl=2 for
+//                       comparison; described here.  The default for 3..80 tokens is kq_gemv_tile.cu.
 //
 //   grid      one CTA per SM (148), split into `ks` groups; group s works on the K range of split s
 //   CTA       8 consumer warps + 1 producer warp
