@@ -37,6 +37,19 @@ def test_mul_mat_a8_matches_reference_kernels(ref_ops, qt, n, k, m):
     assert rel_l2(ref, O.mul_mat(w, qt, x, "mmq")) < TIGHT
 
 
+@pytest.mark.parametrize("qt", [2, 8, 10, 12, 14])
+@pytest.mark.parametrize("n,k,m", [(256, 1024, 200), (300, 2048, 130)])
+def test_prefill_gemm_matches_reference_kernels(ref_ops, qt, n, k, m):
+    """More than 80 tokens: this library switches to the tcgen05 GEMM with fp16 operands; the reference stays on its
+    integer MMQ kernels.  The gate is the path's 1e-3."""
+    w, wt = wire(qt, n, k, seed=qt + 5)
+    x, xt = act(m, k, seed=m + 5, dt="f32")          # fp32 in, fp32 out: no output rounding in the comparison
+    ref = to_np(ref_ops.ggml_mul_mat_a8(wt, xt, qt, n))
+    mine = to_np(torch.ops._C_gguf.ggml_mul_mat_a8(wt, xt, qt, n))
+    assert mine.shape == ref.shape == (m, n)
+    assert rel_l2(mine, ref) < GATE
+
+
 @pytest.mark.parametrize("qt", QT)
 @pytest.mark.parametrize("dt", ["f16", "bf16"])
 def test_low_precision_io_matches_reference(ref_ops, qt, dt):
