@@ -399,28 +399,41 @@ def main() -> None:
         hys = [torch.empty((m, n // world), dtype=torch.bfloat16).pin_memory() for m, _, _, n, _ in calls]
         s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
 
+        GROUP = 12   # calls per synchronisation point between the streams (4 MLP blocks)
+
         def e2e_enqueue(keep):
-            """H2D copies on one side stream, the op on the main stream, D2H reads on another side stream."""
+            """H2D copies on one side stream, the op on the main stream, D2H reads on another side stream.  The streams
+            meet once per GROUP calls, not per call, so that consecutive kernels of the main stream stay adjacent
+            (programmatic dependent launch needs a kernel as the direct predecessor)."""
             s_in.wait_stream(stream)
             s_out.wait_stream(stream)
-            for i, (m, W, qt, n, k) in enumerate(calls):
-                with torch.cuda.stream(s_in):
+            evs = []
+            with torch.cuda.stream(s_in):            # every input copy of the step, an event after each group
+                for i, (m, W, qt, n, k) in enumerate(calls):
                     dxs[i].copy_(hx[(m, k)], non_blocking=True)
-                    ev = torch.cuda.Event()
-                    ev.record(s_in)
-                stream.wait_event(ev)
-                y = linear.fused_mul_mat_gguf(dxs[i], W, qt)
-                if world > 1:
-                    if p2p is not None:
-                        p2p.gather_raw(y, i)
-                    else:
-                        dist.all_gather_into_tensor(yg[(m, n)], y)
+                    if (i + 1) % GROUP == 0 or i + 1 == len(calls):
+                        ev = torch.cuda.Event()
+                        ev.record(s_in)
+                        evs.append(ev)
+            for g0 in range(0, len(calls), GROUP):
+                stream.wait_event(evs[g0 // GROUP])
+                ys_g = []
+                for i in range(g0, min(g0 + GROUP, len(calls))):
+                    m, W, qt, n, k = calls[i]
+                    y = linear.fused_mul_mat_gguf(dxs[i], W, qt)
+                    if world > 1:
+                        if p2p is not None:
+                            p2p.gather_raw(y, i)
+                        else:
+                            dist.all_gather_into_tensor(yg[(m, n)], y)
+                    ys_g.append((i, y))
+                    keep.append(y)   # outputs stay alive until the copies that read them are done
                 ev2 = torch.cuda.Event()
                 ev2.record(stream)
                 with torch.cuda.stream(s_out):
                     s_out.wait_event(ev2)
-                    hys[i].copy_(y, non_blocking=True)
-                keep.append(y)   # outputs stay alive until the copies that read them are done
+                    for i, y in ys_g:
+                        hys[i].copy_(y, non_blocking=True)
             stream.wait_stream(s_in)
             stream.wait_stream(s_out)
 
@@ -469,7 +482,8 @@ def main() -> None:
         e2e = {"value": bytes_step / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e, "results_checked": len(calls),
                "api": "kaillm_b200.linear.fused_mul_mat_gguf -> torch.ops._C_gguf.ggml_mul_mat_{vec_,}a8; per call: "
-                      "H2D of x from pinned memory, the op, D2H of y into pinned memory (copies on side streams); "
+                      "H2D of x from pinned memory, the op, D2H of y into pinned memory (copies on side streams that meet the "
+                      "compute stream every 12 calls); "
                       + ("whole step replayed as one CUDA graph" if eg is not None else "eager")}
 
     # ---- CPU baseline (oracle port of the reference's CPU path) on rank 0, bounded sample
