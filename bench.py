@@ -218,21 +218,30 @@ def main() -> None:
 
     # N > 1: every output slice is all-gathered.  The gather is the library's own peer-store kernel over NVLink
     # (kq_p2p_allgather on torch symmetric memory; NCCL all_gather_into_tensor if symmetric memory cannot be set up).
-    # The gather of call i runs on a second stream and overlaps the GEMV of call i+1 (the calls of this workload are
-    # independent); every call has its own slice and gather buffer, and a step ends only when all gathers have
-    # completed (the side stream is joined into the main one).
+    # The three GEMVs of an MLP block write their [M, N/world] slices side by side into one buffer and ONE gather per
+    # block carries all three to every rank.  The gathers run on a second stream and overlap the next block's GEMVs
+    # (the blocks of this workload are independent); every block has its own slice and gather buffers, and a step
+    # ends only when all gathers have completed (the side stream is joined into the main one).
     comm = torch.cuda.Stream(device=dev) if world > 1 else None
     p2p = None
     gather_how = None
     if world > 1:
         from kaillm_b200 import sharded
-        ysl = [torch.empty((m, n // world), dtype=torch.bfloat16, device=dev) for m in MS for _, _, n, _ in mats]
+        blk_elems = {m: sum(m * (n // world) for _, _, n, _ in mats[:3]) for m in MS}
+        nblocks = len(mats) // 3
+        yblk = [torch.empty((1, blk_elems[m]), dtype=torch.bfloat16, device=dev) for m in MS for _ in range(nblocks)]
+        ysl = []                                   # per call: a [M, N/world] view into its block's buffer
+        for bi, m in enumerate(m for m in MS for _ in range(nblocks)):
+            off = 0
+            for _, _, n, _ in mats[:3]:
+                ysl.append(yblk[bi][0, off:off + m * (n // world)].view(m, n // world))
+                off += m * (n // world)
         try:
-            p2p = sharded.P2PGather(max_bytes=max(MS) * (N_FF // world) * 2, nbuf=len(ysl), device=dev)
+            p2p = sharded.P2PGather(max_bytes=blk_elems[max(MS)] * 2, nbuf=len(ysl), device=dev)
             gather_how = "kq_p2p_allgather (peer stores over NVLink)"
         except Exception as e:  # noqa: BLE001 - keep the NCCL path
             print(f"[bench] symmetric memory unavailable ({e!r}); using NCCL all_gather_into_tensor", file=sys.stderr)
-            ygl = [torch.empty((world, m, n // world), dtype=torch.bfloat16, device=dev) for m in MS for _, _, n, _ in mats]
+            ygl = [torch.empty((world, 1, b.numel()), dtype=torch.bfloat16, device=dev) for b in yblk]
             gather_how = "NCCL all_gather_into_tensor"
 
     def step():
@@ -243,17 +252,18 @@ def main() -> None:
         for m in MS:
             for W, qt, n, k in mats:
                 out = ysl[i] if world > 1 else ys[(m, n)]
-                y = capi.mul_mat(W, xs[(m, k)], qt, mmq=use_mmq(m, n), out=out, scratch=scratch, n=n // world)
-                if world > 1:
+                capi.mul_mat(W, xs[(m, k)], qt, mmq=use_mmq(m, n), out=out, scratch=scratch, n=n // world)
+                i += 1
+                if world > 1 and i % 3 == 0:         # the block's three slices are written: one gather for all of them
+                    bi = i // 3 - 1
                     ev = torch.cuda.Event()
                     ev.record(cur)
                     with torch.cuda.stream(comm):
                         comm.wait_event(ev)
                         if p2p is not None:
-                            p2p.gather_raw(y, i)
+                            p2p.gather_raw(yblk[bi], bi)
                         else:
-                            dist.all_gather_into_tensor(ygl[i], y)
-                i += 1
+                            dist.all_gather_into_tensor(ygl[bi], yblk[bi])
         if world > 1:
             cur.wait_stream(comm)
 
@@ -522,8 +532,9 @@ def main() -> None:
                        "calls_per_step": calls_step, "bytes_per_step": bytes_step,
                        "l2": "stack of %.2f GB per rank >> 126 MB L2, no flush needed" % (sum(w.numel() for w, *_ in mats) / 1e9),
                        "launch": "cuda graph replay" if graph is not None else "eager",
-                       "parallelism": (f"row-sharded x{world} + all-gather of every output by {gather_how} (gathers on a "
-                                       "second stream, overlapping the next call's GEMV; joined at the end of each step)")
+                       "parallelism": (f"row-sharded x{world} + all-gather of every output by {gather_how} (one gather per MLP block carries "
+                                       "its three output slices; the gathers run on a second stream and overlap the next block; joined "
+                                       "at the end of each step)")
                        if world > 1 else "single GPU"},
             "frac_of_measured_hbm": value / measured_peaks()[0], "frac_of_nominal_8tbs": value / 8000.0,
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches_step * args.steps,
