@@ -12,7 +12,7 @@
 //             Q4_K: the 16 A rows of an m16n8k32 mma are the 8 weight rows twice - low nibbles (sub-block 2i) in
 //             rows 0-7, high nibbles (sub-block 2i+1) in rows 8-15 - so the unpacked words are the A fragment
 //             as they stand; one mma against the activations of each of the two sub-blocks, half of each result
-//             unused.  Q6_K: the same with the two 16-weight scale groups of a 32-block and m16n8k16.
+//             unused.  Q6_K: the two 16-weight scale groups of a 32-block sit in the two row halves of one mma.
 //             The scales are applied in fp32 on the way into the warp's 8 x 16 partial tile.  The Q4_K min term
 //             is a small GEMM over the eight sub-blocks of a super-block (mins 0..63, exact in tf32) x
 //             (d8 * block sum, split hi + lo): two tf32 mmas per super-block and token half.
@@ -228,8 +228,8 @@ __device__ __forceinline__ void unit_q4k(uint32_t pg, int b0, const TileView& A,
 }
 
 // ---------------------------------------------------------------------------------------------- Q6_K unit
-// 16-weight scale groups: A rows 0-7 carry group s=0 of a 32-block, rows 8-15 group s=1 (m16n8k16); one mma
-// against the activations of each half-block.  Group (ip, q4, s) holds weights 128ip + 32q4 + 16s + 4t.. of the
+// 16-weight scale groups: A rows 0-7 carry group s=0 of a 32-block in the first 16 k slots, rows 8-15 group s=1 in the
+// last 16 (zeros elsewhere), so one m16n8k32 against the block's activations yields both groups' dots.  Group (ip, q4, s) holds weights 128ip + 32q4 + 16s + 4t.. of the
 // super-block: low nibbles from ql[64ip + 32(q4&1) + 16s + 4t] >> 4(q4>>1), two high bits from
 // qh[32ip + 16s + 4t] >> 2q4.  The two groups share the activation scale, so their scaled dots are added as
 // integers before the conversion (|sum| < 2^24).
@@ -267,12 +267,12 @@ __device__ __forceinline__ void unit_q6k(uint32_t pg, int b0, const TileView& A,
       for (int hf = 0; hf < NH; ++hf) {
         const uint32_t x0 = lds32(tok + hf * 8 * A.a_stride + b * 32);
         const uint32_t x1 = lds32(tok + hf * 8 * A.a_stride + b * 32 + 16);
-        int D0[4], D1[4];
-        mma_i8_k16(D0, a0, a1, x0);
-        mma_i8_k16(D1, a0, a1, x1);
+        // one m16n8k32: rows 0-7 = group 0 in the first 16 k slots (zeros in the rest), rows 8-15 = group 1 in the last 16
+        int D[4];
+        mma_i8_k32(D, a0, 0u, 0u, a1, x0, x1);
         const float2 d8 = ldsf2(dsc + (b * 16 + 8 * hf) * 4);
-        u[2 * hf] = fmaf((float)(D0[0] * s0 + D1[2] * s1), d8.x, u[2 * hf]);
-        u[2 * hf + 1] = fmaf((float)(D0[1] * s0 + D1[3] * s1), d8.y, u[2 * hf + 1]);
+        u[2 * hf] = fmaf((float)(D[0] * s0 + D[2] * s1), d8.x, u[2 * hf]);
+        u[2 * hf + 1] = fmaf((float)(D[1] * s0 + D[3] * s1), d8.y, u[2 * hf + 1]);
       }
     }
   }
