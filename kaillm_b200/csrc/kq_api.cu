@@ -87,7 +87,7 @@ static int mul_mat(const char* fn, bool mmq, const void* W, int type, int64_t n,
   // token; a second pass, or a matrix of a few MB, makes it slower than the separate launch)
   const bool fuse_fits = options().fuse_q8 == 2 || (m * (k / 32) <= 512 && n * p.rowbytes >= (32ll << 20));   // 2: wherever it can run (tests)
   const bool fuse = x && !gemm && options().fuse_q8 && m <= 2 && fuse_fits &&
-                    impl != 1 && gemv_rows_only(type, m) && gemv_mma_supported(W, type, n, k);
+                    impl != 1 && gemv_rows_only(type, n, k, m) && gemv_mma_supported(W, type, n, k);
   if (fuse) return launch_gemv_mma(W, type, n, k, P, m, y, y_dtype, stride_y, mmq, st, x, x_dtype, stride_x);
   if (x) {
     Q8Ptrs Pq = P;

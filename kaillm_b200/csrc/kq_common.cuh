@@ -133,11 +133,12 @@ int launch_gemv_dp4a(const void* W, int type, int64_t n, int64_t k, const void* 
 // tensor-core GEMV; returns KQ_EUNSUPPORTED (without setting an error) when the shape/alignment is not
 // covered, so the caller can fall back to the dp4a kernel
 bool gemv_mma_supported(const void* W, int type, int64_t n, int64_t k);
-bool gemv_rows_only(int type, int64_t m);
+bool gemv_rows_only(int type, int64_t n, int64_t k, int64_t m);
 int launch_gemv_mma(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m, void* y,
                     int y_dtype, int64_t stride_y, bool mmq, cudaStream_t st, const void* fuse_x = nullptr,
                     int x_dtype = 0, int64_t stride_x = 0);
 bool gemv_tile_supported(const void* W, int type, int64_t n, int64_t k, int mtok);
+int gemv_tile_splits(int type, int64_t n, int64_t k, int mtok);
 int launch_gemv_tile(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m0, int mcount, void* y,
                      int y_dtype, int64_t stride_y, bool mmq, cudaStream_t st);
 bool gemv_tc5_supported(const void* W, int type, int64_t n, int64_t k);

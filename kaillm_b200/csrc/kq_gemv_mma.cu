@@ -1092,12 +1092,23 @@ bool gemv_mma_supported(const void* W, int type, int64_t n, int64_t k) {
 }
 
 // impl: 0 = choose by m, 2 = tensor cores wherever the type has them, 3 = row-streaming dp4a
+// Smallest token count that goes to the shared-stage mma kernel in auto mode.  Q4_0's 18-byte blocks decode slowly
+// there (row-streaming kernel up to 8 tokens).  Q6_K's row-streaming consumer tops out near 3 TB/s, the mma kernel
+// near 4.2 TB/s, so whenever it needs no K split (K up to about 8K) the mma kernel takes 1-2 tokens as well: 27.2 ->
+// 21.0 us on 17408x5120, 352 -> 246 us on a 248320x5120 LM head; with a K split (5120x17408) the row kernel stays ahead.
+static int tile_min_tokens(int type, int64_t n, int64_t k) {
+  if (type == KQ_TYPE_Q4_0) return 9;
+  if (type == KQ_TYPE_Q6_K && gemv_tile_splits(type, n, k, 8) == 1) return 1;
+  if (type == KQ_TYPE_IQ3_S) return 2;   // its generic row decoder pays per token: 29.4 -> 27.0 us at 2 tokens
+  return options().tc_min_m;
+}
+
 // True when every token of an m-token call goes to the row-streaming kernel (which can quantize raw activations itself).
-bool gemv_rows_only(int type, int64_t m) {
+bool gemv_rows_only(int type, int64_t n, int64_t k, int64_t m) {
   const int impl = options().gemv_impl;
   if (impl == 3 || impl == 4) return true;
   if (impl != 0) return false;
-  return m < options().tc_min_m;
+  return m < tile_min_tokens(type, n, k);
 }
 
 // fuse_x != nullptr (only with gemv_rows_only): the activations have NOT been quantized into P; the kernel reads them raw
@@ -1129,8 +1140,7 @@ int launch_gemv_mma(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs&
     }
     if (impl == 5) { set_error("tcgen05 GEMV: type/shape not covered"); return KQ_EUNSUPPORTED; }
     // 3..16 tokens of Q4_K / Q6_K: the shared-stage mma kernel (all warps of a CTA on every stage of 8 rows)
-    // (Q4_0's 18-byte blocks decode slowly there: the row-streaming kernel is faster up to 8 tokens)
-    const int tile_min = type == KQ_TYPE_Q4_0 ? 9 : options().tc_min_m;
+    const int tile_min = tile_min_tokens(type, n, k);
     if (tile_start && (impl == 6 || (impl == 0 && left >= tile_min)) &&
         gemv_tile_supported(W, type, n, k, (int)(left < 16 ? left : 16))) {
       mcount = (int)(left < 16 ? left : 16);

@@ -744,6 +744,12 @@ bool gemv_tile_supported(const void* W, int type, int64_t n, int64_t k, int mtok
   return make_tile_config(type, n, k, mtok > 8 ? 16 : 8, c);
 }
 
+// K splits the shared-stage kernel would use for this shape (0 = shape not covered)
+int gemv_tile_splits(int type, int64_t n, int64_t k, int mtok) {
+  TileConfig c;
+  return make_tile_config(type, n, k, mtok > 8 ? 16 : 8, c) ? c.ks : 0;
+}
+
 // one pass of up to 16 tokens starting at m0 (a multiple of 16)
 int launch_gemv_tile(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m0, int mcount, void* y,
                      int y_dtype, int64_t stride_y, bool mmq, cudaStream_t st) {

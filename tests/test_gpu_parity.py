@@ -226,6 +226,7 @@ def test_in_kernel_quantization_equals_quantizer_launch(qt, n, k, m, dt):
     x, xt = act(m, k, seed=m + 7, dt=dt)
     scratch = torch.empty(capi.workspace_bytes(qt, m, n, k), dtype=torch.uint8, device=dev())
     capi.set_option("fuse_q8", 2)          # also on matrices too small for the default heuristic
+    capi.set_option("gemv_impl", 3)        # the row-streaming kernel for every format (auto mode sends some to the mma kernel)
     try:
         l0 = capi.get_option("launch_count")
         y1 = capi.mul_mat(wt, xt, qt, out_dtype=torch.float32, scratch=scratch)
@@ -237,6 +238,7 @@ def test_in_kernel_quantization_equals_quantizer_launch(qt, n, k, m, dt):
         plain_launches = capi.get_option("launch_count") - l0
     finally:
         capi.set_option("fuse_q8", 1)
+        capi.set_option("gemv_impl", 0)
     assert torch.equal(y1, y0)
     assert plain_launches == fused_launches + 1
     assert rel_l2(to_np(y1), O.mul_mat(w, qt, x, "mmvq")) < TIGHT
