@@ -111,7 +111,8 @@ int kq_mul_mat_vec_a8_static(const void* W, int type, int64_t n, int64_t k,
 /* The two halves of the mul_mat entry points, for layers that share one activation (q/k/v, gate/up):
  * kq_prepare_q8 quantizes x into `scratch`; kq_mul_mat_prepared multiplies any number of weight tensors
  * against the activations already held there (mmq != 0 selects the MMQ arithmetic).  n passed to
- * kq_prepare_q8 must be >= every n used with that scratch (it sizes the split-K area).
+ * kq_prepare_q8 must be >= every n used with that scratch (it sizes the split-K area; everything the preparation
+ * writes sits at offsets that do not depend on n, so weight tensors of different n share one preparation).
  * Replace the quantize_row_q8_1_cuda call and the kernel launch inside ggml_mul_mat_vec_a8 /
  * ggml_mul_mat_a8, vllm_gguf_plugin/csrc/gguf/gguf_kernel.cu:116-118 and 119-215, 232-287; the
  * reference's production path shares the preparation the same way
@@ -151,7 +152,10 @@ int kq_debug_group_dots(const void* W, int type, int64_t n, int64_t k,
  *                first call
  *   epoch, done  LOCAL device arrays, uint32 [slots], zero before the first call (call counter / CTA counter)
  *   slot         which flag slot this call uses; calls that may be in flight at the same time need different slots
- *   status       LOCAL device int: set non-zero if the bounded wait for a peer's flag ran out (kernel returns early)
+ *   status       LOCAL device int: set non-zero if the bounded wait for a peer's flag ran out (about two seconds; the
+ *                kernel then returns early and the local gather buffer is incomplete - treat its contents as undefined)
+ * src, the slice size and every peer_dst entry should be 16-byte aligned (16-byte stores); if any of them is not,
+ * the copy falls back to single bytes.  Null entries and misaligned flag arrays are KQ_EINVAL.
  * Every rank must make the same sequence of calls per slot.  When the kernel has completed, the local gather buffer
  * holds all ranks' slices.  Alternate two gather buffers per stream if the gathered data is read by later kernels
  * (a peer may write the next call's slice as soon as this rank has published its own next call).
@@ -165,10 +169,22 @@ int kq_p2p_allgather(const void* src, size_t bytes, void* const* peer_dst, uint3
  * The sizes must be the ones the scratch was used with.  No counterpart in the reference. */
 int kq_read_status(int type, int64_t m, int64_t n, int64_t k, const void* scratch, size_t scratch_bytes, int* status);
 
+/* The same for the array built into the library that kq_mul_mat_vec_a8_static uses on the current device
+ * (SYNCHRONISES; 0 = the kernels of every call so far finished normally).  No counterpart in the reference. */
+int kq_read_status_static(int* status);
+
+/* Test hook, host arithmetic only (no GPU work): the byte ranges the streaming kernels read when they stage weight
+ * bytes of a tensor of n rows of rowbytes bytes at address `base` (16-byte aligned) in shared memory.  seg_len == 0:
+ * whole rows [row_a, row_b); seg_len > 0: bytes [seg_off, seg_off + seg_len) of row row_a.  Returns the 16-byte
+ * aligned bulk-copy range [bulk_start, bulk_start + bulk_bytes) and the number of bytes after it that are fetched by
+ * plain loads.  The kernels call the same function; a test can assert that nothing past base + n * rowbytes is
+ * read.  No counterpart in the reference. */
+int kq_debug_copy_window(uint64_t base, int64_t n, int64_t rowbytes, int64_t row_a, int64_t row_b, int64_t seg_off,
+                         int64_t seg_len, uint64_t* bulk_start, uint64_t* bulk_bytes, uint64_t* tail_bytes);
+
 /* Runtime knobs for tests and profiling (process-wide, not thread-safe against concurrent launches):
- *   "gemv_impl"   0 = choose by shape (default), 1 = general dp4a kernel, 2 = tile-per-warp int8-mma kernel,
- *                 3 = row-streaming dp4a kernel, 4 = the same without the specialised Q4_K / Q6_K consumers,
- *                 5 = tcgen05 kind::i8 kernel (Q4_K), 6 = shared-stage int8-mma kernel (Q4_K, Q6_K);
+ *   "gemv_impl"   0 = choose by shape (default), 1 = general dp4a kernel, 3 = row-streaming dp4a kernel,
+ *                 4 = the same without the specialised Q4_K / Q6_K consumers, 6 = shared-stage int8-mma kernel;
  *                 a forced kernel that does not cover the type or shape returns KQ_EUNSUPPORTED
  *   "tc_min_m"    smallest m that the shared-stage int8-mma kernel takes in mode 0 (default 3)
  *   "pdl"         0 = plain launches; p > 0 (default 2) = the quantizer and the streaming kernels are launched

@@ -22,7 +22,7 @@ EXPORTS = (
     "kq_last_error", "kq_abi_version", "kq_block_geometry", "kq_workspace_bytes", "kq_quantize_q8_1",
     "kq_mul_mat_vec_a8", "kq_mul_mat_a8", "kq_dequantize", "kq_debug_group_dots", "kq_set_option",
     "kq_get_option", "kq_prepare_q8", "kq_mul_mat_prepared", "kq_read_status", "kq_mul_mat_vec_a8_static",
-    "kq_p2p_allgather",
+    "kq_p2p_allgather", "kq_read_status_static", "kq_debug_copy_window",
 )
 
 
@@ -56,6 +56,9 @@ def _load() -> ctypes.CDLL:
     lib.kq_read_status.argtypes = [i32, i64, i64, i64, vp, sz, ctypes.POINTER(i32)]
     lib.kq_debug_group_dots.argtypes = [vp, i32, i64, i64, vp, i32, i64, i64, vp, vp, vp, sz, vp]
     lib.kq_p2p_allgather.argtypes = [vp, sz, ctypes.POINTER(vp), ctypes.POINTER(vp), vp, vp, i32, i32, i32, vp, vp]
+    lib.kq_read_status_static.argtypes = [ctypes.POINTER(i32)]
+    u64p = ctypes.POINTER(ctypes.c_uint64)
+    lib.kq_debug_copy_window.argtypes = [ctypes.c_uint64, i64, i64, i64, i64, i64, i64, u64p, u64p, u64p]
     lib.kq_set_option.argtypes = [ctypes.c_char_p, i32]
     lib.kq_get_option.argtypes = [ctypes.c_char_p, ctypes.POINTER(i32)]
     return lib
@@ -150,6 +153,21 @@ def read_status(qtype: int, m: int, n: int, k: int, scratch: torch.Tensor) -> in
     with torch.cuda.device(scratch.device):
         _check(lib.kq_read_status(qtype, m, n, k, scratch.data_ptr(), scratch.numel(), ctypes.byref(v)))
     return v.value
+
+
+def read_status_static() -> int:
+    """Status word of the library-owned scratch array of the current device (synchronises)."""
+    v = ctypes.c_int()
+    _check(lib.kq_read_status_static(ctypes.byref(v)))
+    return v.value
+
+
+def copy_window(base: int, n: int, rowbytes: int, row_a: int, row_b: int, seg_off: int = 0, seg_len: int = 0):
+    """(bulk_start, bulk_bytes, tail_bytes) the streaming kernels would read for these rows (host arithmetic only)."""
+    a, b, c = ctypes.c_uint64(), ctypes.c_uint64(), ctypes.c_uint64()
+    _check(lib.kq_debug_copy_window(base, n, rowbytes, row_a, row_b, seg_off, seg_len, ctypes.byref(a), ctypes.byref(b),
+                                    ctypes.byref(c)))
+    return a.value, b.value, c.value
 
 
 def mul_mat_vec_static(W: torch.Tensor, x: torch.Tensor, qtype: int, out: torch.Tensor) -> torch.Tensor:

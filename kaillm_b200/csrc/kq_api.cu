@@ -26,6 +26,16 @@ Options& options() {
   return o;
 }
 
+int sm_count() {
+  static int counts[64] = {0};
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = -1;
+  if (dev >= 0 && counts[dev] > 0) return counts[dev];
+  if (dev < 0 || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  if (dev >= 0) counts[dev] = n;
+  return n;
+}
+
 static bool dtype_ok(int dt) { return dt == KQ_F32 || dt == KQ_F16 || dt == KQ_BF16; }
 static size_t dtype_size(int dt) { return dt == KQ_F32 ? 4 : 2; }
 
@@ -206,6 +216,17 @@ int kq_mul_mat_vec_a8_static(const void* W, int type, int64_t n, int64_t k, cons
                  KQ_STATIC_BYTES, stream);
 }
 
+int kq_read_status_static(int* status) {
+  t_err[0] = 0;
+  if (!status) { set_error("kq_read_status_static: null pointer"); return KQ_EINVAL; }
+  int rc = KQ_OK;
+  const uint8_t* scratch = (const uint8_t*)static_scratch_ptr(&rc);
+  if (!scratch) return rc;
+  // the status word sits at a fixed offset of the layout, whatever sizes the array was last used with
+  KQ_CUDA_TRY(cudaMemcpy(status, scratch + q8_layout(1, 1, 32).off_status, sizeof(int), cudaMemcpyDeviceToHost));
+  return KQ_OK;
+}
+
 int kq_dequantize(const void* W, int type, int64_t count, void* out, int out_dtype, void* stream) {
   t_err[0] = 0;
   int b, s;
@@ -251,6 +272,28 @@ int kq_p2p_allgather(const void* src, size_t bytes, void* const* peer_dst, uint3
     return KQ_EINVAL;
   }
   return launch_p2p_allgather(src, bytes, peer_dst, peer_flags, epoch, done, slot, rank, world, status, (cudaStream_t)stream);
+}
+
+int kq_debug_copy_window(uint64_t base, int64_t n, int64_t rowbytes, int64_t row_a, int64_t row_b, int64_t seg_off,
+                         int64_t seg_len, uint64_t* bulk_start, uint64_t* bulk_bytes, uint64_t* tail_bytes) {
+  t_err[0] = 0;
+  if (n <= 0 || rowbytes <= 0 || row_a < 0 || row_b <= row_a || row_b > n || seg_off < 0 || !bulk_start || !bulk_bytes || !tail_bytes) {
+    set_error("kq_debug_copy_window: bad argument");
+    return KQ_EINVAL;
+  }
+  const uintptr_t wend = (uintptr_t)base + (uintptr_t)(n * rowbytes);
+  uintptr_t ga, ge;
+  if (seg_len > 0) {   // one row segment (row_b is ignored)
+    if (seg_off + seg_len > rowbytes) { set_error("kq_debug_copy_window: segment outside the row"); return KQ_EINVAL; }
+    ga = (uintptr_t)base + (uintptr_t)(row_a * rowbytes + seg_off);
+    ge = ga + (uintptr_t)seg_len;
+  } else {             // whole rows [row_a, row_b)
+    ga = (uintptr_t)base + (uintptr_t)(row_a * rowbytes);
+    ge = (uintptr_t)base + (uintptr_t)(row_b * rowbytes);
+  }
+  const CopyWindow w = copy_window(ga, ge, wend);
+  *bulk_start = (uint64_t)w.a0; *bulk_bytes = w.bulk; *tail_bytes = w.tail;
+  return KQ_OK;
 }
 
 int kq_set_option(const char* name, int value) {

@@ -22,9 +22,22 @@ int cuda_fail(cudaError_t e, const char* what);
     if (_e != cudaSuccess) return ::kq::cuda_fail(_e, #expr); \
   } while (0)
 
+// One-time set-up that belongs to a (function, device) pair, e.g. cudaFuncSetAttribute: a flag per device ordinal.
+// Setting an attribute twice is harmless, so two threads racing on the first call need no lock.
+struct DeviceOnce {
+  bool set[64] = {};
+  int dev = -1;
+  bool first_time() {
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { dev = -1; return true; }
+    return !set[dev];
+  }
+  void done() { if (dev >= 0) set[dev] = true; }
+};
+int sm_count();   // multiprocessors of the CURRENT device (cached per device ordinal)
+
 struct Options {
-  int gemv_impl;       // 0 auto, 1 general dp4a, 2 tile-per-warp mma, 3 row-streaming dp4a, 4 same without the
-                       // specialised consumers, 5 tcgen05 (Q4_K), 6 shared-stage mma (token-major tiles)
+  int gemv_impl;       // 0 auto, 1 general dp4a, 3 row-streaming dp4a, 4 same without the specialised consumers,
+                       // 6 shared-stage mma (token-major tiles)
   int tc_min_m;        // auto mode: smallest token count that goes to the tensor-core consumers
   int gemm_min_m;      // smallest token count that goes to the tcgen05 GEMM
   int pdl;             // 0: plain launches; p > 0: programmatic dependent launch, p ring stages prefetched before
@@ -75,9 +88,12 @@ inline int type_group(int type) { return (type == KQ_TYPE_Q2_K || type == KQ_TYP
 //   z32r  float [m][kpad/32]        same values as z32, token-major (row-streaming kernel)
 //   z16r  float [m][kpad/16]        same values as z16, token-major
 //   part  float [4][16][n]          split-K partial sums of one 16-token pass
-//   cnt   int   [n]                 split-K arrival counters, per row or per 16-row tile (zeroed by the
-//                                   quantizer, reset by the kernel that used them)
+//   cnt   int   [KQ_CNT_SLOTS]      split-K arrival counters, one per 8-row tile (the quantizer zeroes the first
+//                                   ceil(n/8) of them, the kernel that used them resets them)
 //   status int  [64]                device-side error word (bounded waits that gave up)
+// Only `part` (which needs no initialisation) and the total depend on n, and `part` comes last: a scratch prepared
+// for n_max rows is laid out identically for every weight tensor of n <= n_max rows that shares it.
+constexpr int KQ_CNT_SLOTS = 65536;   // 8-row tiles a split-K launch may have (n <= 524288); larger n runs unsplit
 struct Q8Layout {
   int64_t kpad, mt;
   size_t off_ds, off_qs, off_qsp, off_xh, off_s8h, off_dT, off_z32, off_zs8, off_z16, off_z32r, off_z16r, off_part, off_cnt, off_status, total;
@@ -89,6 +105,8 @@ inline Q8Layout q8_layout(int64_t m, int64_t n, int64_t k) {
   L.mt = (m + 15) / 16;
   const size_t nb = (size_t)L.kpad / 32;
   size_t p = 0;
+  L.off_status = p; p = align_up(p + 256, 256);
+  L.off_cnt = p;    p = align_up(p + (size_t)KQ_CNT_SLOTS * 4, 256);
   L.off_ds = p;     p = align_up(p + (size_t)m * nb * 4, 256);
   L.off_qs = p;     p = align_up(p + (size_t)m * L.kpad, 256);
   L.off_qsp = p;    p = align_up(p + (size_t)m * (L.kpad / 64) * 80, 256);
@@ -101,8 +119,6 @@ inline Q8Layout q8_layout(int64_t m, int64_t n, int64_t k) {
   L.off_z32r = p;   p = align_up(p + (size_t)m * nb * 4, 256);
   L.off_z16r = p;   p = align_up(p + (size_t)m * nb * 8, 256);
   L.off_part = p;   p = align_up(p + (size_t)4 * 16 * n * 4, 256);
-  L.off_cnt = p;    p = align_up(p + (size_t)n * 4, 256);
-  L.off_status = p; p = align_up(p + 256, 256);
   L.total = p;
   return L;
 }
@@ -119,8 +135,32 @@ inline Q8Ptrs q8_ptrs(void* scratch, const Q8Layout& L, int64_t n) {
   P.z16 = (float*)(s + L.off_z16); P.z32r = (float*)(s + L.off_z32r); P.z16r = (float*)(s + L.off_z16r);
   P.part = (float*)(s + L.off_part);
   P.cnt = (int*)(s + L.off_cnt); P.status = (int*)(s + L.off_status);
-  P.kpad = L.kpad; P.ncnt = (int)n;
+  P.kpad = L.kpad;
+  const int64_t tiles = (n + 7) / 8;
+  P.ncnt = (int)(tiles < KQ_CNT_SLOTS ? tiles : KQ_CNT_SLOTS);
   return P;
+}
+
+// Bulk-copy window of the weight bytes [ga, ge) of a tensor that ends at wend.  cp.async.bulk moves 16-byte units
+// between 16-byte aligned addresses, so the window starts at ga rounded down (the caller guarantees a 16-byte aligned
+// tensor base, so that never reaches below the tensor) and ends at ge rounded up - unless that would pass the end of
+// the tensor: then the bulk part stops at the last 16-byte boundary and the remaining `tail` bytes (< 16, an even
+// number) are fetched with plain 2-byte loads.  Nothing outside [base, wend) is ever read.
+struct CopyWindow {
+  uintptr_t a0;    // start of the bulk copy (16-byte aligned)
+  uint32_t lead;   // ga - a0: where the wanted bytes start inside the staged window
+  uint32_t bulk;   // bytes of the bulk copy (a multiple of 16, may be 0)
+  uint32_t tail;   // bytes after the bulk part to fetch with plain loads: [a0 + bulk, ge)
+};
+__host__ __device__ inline CopyWindow copy_window(uintptr_t ga, uintptr_t ge, uintptr_t wend) {
+  CopyWindow w;
+  w.a0 = ga & ~(uintptr_t)15;
+  w.lead = (uint32_t)(ga - w.a0);
+  uintptr_t e = (ge + 15) & ~(uintptr_t)15;
+  w.tail = 0;
+  if (e > wend) { e = ge & ~(uintptr_t)15; if (e < w.a0) e = w.a0; w.tail = (uint32_t)(ge - e); }
+  w.bulk = (uint32_t)(e - w.a0);
+  return w;
 }
 
 // kernels (defined in the .cu files)
@@ -141,9 +181,6 @@ bool gemv_tile_supported(const void* W, int type, int64_t n, int64_t k, int mtok
 int gemv_tile_splits(int type, int64_t n, int64_t k, int mtok);
 int launch_gemv_tile(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m0, int mcount, void* y,
                      int y_dtype, int64_t stride_y, bool mmq, cudaStream_t st);
-bool gemv_tc5_supported(const void* W, int type, int64_t n, int64_t k);
-int launch_gemv_tc5(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m_total, int64_t m0, int mcount,
-                    void* y, int y_dtype, int64_t stride_y, bool mmq, cudaStream_t st);
 int launch_p2p_allgather(const void* src, size_t bytes, void* const* peer_dst, uint32_t* const* peer_flags,
                          uint32_t* epoch, uint32_t* done, int slot, int rank, int world, int* status, cudaStream_t st);
 bool gemm_tc_supported(const void* W, int type, int64_t n, int64_t k);

@@ -447,9 +447,16 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
       }
       if constexpr (QT == KQ_TYPE_Q6_K) {
         const size_t col = ((size_t)sblk * 210) & ~(size_t)7;   // rows and W are 8-byte aligned: the same for every row
+        // the aligned window of the last block of the last row may reach up to 6 bytes past the tensor: such a piece
+        // reads only the bytes that exist (the rest of its 8 bytes is zero-filled)
+        const uint8_t* wend = p.W + (size_t)p.n * p.rowbytes;
 #pragma unroll
         for (int i = 0; i < NCHUNK; ++i)
-          if (csrc[i]) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(cdst[i]), "l"(csrc[i] + col) : "memory");
+          if (csrc[i]) {
+            const uint8_t* src = csrc[i] + col;
+            const uint32_t have = src + 8 <= wend ? 8u : (src < wend ? (uint32_t)(wend - src) : 0u);
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(cdst[i]), "l"(src), "r"(have) : "memory");
+          }
         asm volatile("cp.async.commit_group;" ::: "memory");
       }
     };
@@ -567,10 +574,10 @@ template <int QT, bool CORR, typename OutT>
 int launch(const GemmParams& p, const CUtensorMap& map, const CUtensorMap& smap, int grid, cudaStream_t st) {
   auto kern = gemm_tc_kernel<QT, CORR, OutT>;
   const int smem = NB * B_STAGE_BYTES + 4096 + (QT == KQ_TYPE_Q4_K ? W_STAGE_BYTES : (QT == KQ_TYPE_Q6_K ? W6_STAGE_BYTES : 0));
-  static bool attr_set = false;
-  if (!attr_set) {
+  static DeviceOnce attr_set;   // the attribute belongs to the (function, device) pair
+  if (attr_set.first_time()) {
     KQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    attr_set = true;
+    attr_set.done();
   }
   kern<<<grid, GEMM_THREADS, smem, st>>>(p, map, smap);
   options().launches += 1;

@@ -472,34 +472,45 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
     const int contig = p.contig;
     int slot = 0;          // ring position of the next stage to issue
     uint32_t eph = 1;      // parity that shows the slot's previous contents consumed (passes at once on the first lap)
+    const uintptr_t wend = (uintptr_t)(p.W + (size_t)p.n * p.rowbytes);
+    // the last bytes of the tensor, when it ends inside a 16-byte unit, come by plain 2-byte loads (see copy_window)
+    auto fetch_tail = [&](uint8_t* dst_generic, const CopyWindow& cw, uintptr_t ge) {
+      const uint16_t* src = reinterpret_cast<const uint16_t*>(ge - cw.tail);
+      uint16_t* d16 = reinterpret_cast<uint16_t*>(dst_generic + cw.bulk);
+      for (uint32_t i = 0; i < cw.tail / 2; ++i) d16[i] = src[i];
+      __threadfence_block();
+    };
     auto issue_stage = [&](int q) {
       const int row0 = (rt0 + q) * TL_ROWS;
-      const uint32_t dst = s_u32(ring + (size_t)slot * p.stage_bytes);
+      uint8_t* dstg = ring + (size_t)slot * p.stage_bytes;
+      const uint32_t dst = s_u32(dstg);
       const uint32_t bar = bar_full + 8 * slot;
       if (contig) {
         if (lane == 0) {
           const int rows = (p.n - row0) < TL_ROWS ? (p.n - row0) : TL_ROWS;
           const uintptr_t ga = (uintptr_t)(p.W + (size_t)row0 * p.rowbytes);
-          const uintptr_t a0 = ga & ~(uintptr_t)15;
-          const uint32_t bytes = (uint32_t)(((ga + (size_t)rows * p.rowbytes + 15) & ~(uintptr_t)15) - a0);
-          bar_expect_tx(bar, bytes);
-          copy_g2s(dst, (const void*)a0, bytes, bar);
+          const uintptr_t ge = ga + (size_t)rows * p.rowbytes;
+          const CopyWindow cw = copy_window(ga, ge, wend);
+          if (cw.tail) fetch_tail(dstg, cw, ge);
+          bar_expect_tx(bar, cw.bulk);
+          if (cw.bulk) copy_g2s(dst, (const void*)cw.a0, cw.bulk, bar);
         }
       } else {
-        uint32_t bytes = 0;
-        uintptr_t a0 = 0;
+        CopyWindow cw;
+        cw.a0 = 0; cw.lead = 0; cw.bulk = 0; cw.tail = 0;
         const int row = row0 + lane;
         if (lane < TL_ROWS && row < p.n) {
           const uintptr_t ga = (uintptr_t)(p.W + (size_t)row * p.rowbytes + seg0);
-          a0 = ga & ~(uintptr_t)15;
-          bytes = (uint32_t)(((ga + seglen + 15) & ~(uintptr_t)15) - a0);
+          cw = copy_window(ga, ga + seglen, wend);
+          if (cw.tail) fetch_tail(dstg + (size_t)lane * p.row_stride, cw, ga + seglen);
         }
-        uint32_t total = bytes;
+        uint32_t total = cw.bulk;
 #pragma unroll
         for (int mask = 4; mask > 0; mask >>= 1) total += __shfl_xor_sync(0xffffffffu, total, mask);
-        if (lane == 0) bar_expect_tx(bar, total);   // row0 < n, so total > 0
+        __syncwarp();                               // the tail stores above are ordered before the arrive
+        if (lane == 0) bar_expect_tx(bar, total);
         __syncwarp();
-        if (bytes) copy_g2s(dst + (uint32_t)lane * p.row_stride, (const void*)a0, bytes, bar);
+        if (cw.bulk) copy_g2s(dst + (uint32_t)lane * p.row_stride, (const void*)cw.a0, cw.bulk, bar);
       }
       if (++slot == S) { slot = 0; eph ^= 1; }
     };
@@ -657,15 +668,6 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
   }
 }
 
-int tl_sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-  }
-  return n;
-}
-
 // smallest K split whose activation slice leaves room for a ring of >= 4 stages
 bool make_tile_config(int type, int64_t n, int64_t k, int mtok, TileConfig& c) {
   int blk, bytes;
@@ -675,7 +677,7 @@ bool make_tile_config(int type, int64_t n, int64_t k, int mtok, TileConfig& c) {
   blk = 256;
   const int nblk = (int)(k / blk);
   const int64_t rowbytes = (int64_t)nblk * bytes;
-  const int sms = tl_sm_count();
+  const int sms = sm_count();
   const int seg_mode = options().tile_segments;   // 1: row segments even when the slice is the whole row
   for (int ks = 1; ks <= 4; ks *= 2) {
     if (nblk < ks) break;
@@ -702,6 +704,7 @@ bool make_tile_config(int type, int64_t n, int64_t k, int mtok, TileConfig& c) {
     if (stages > TL_MAX_STAGES) stages = TL_MAX_STAGES;
     if (stages < 3) continue;
     if (ks > 1 && (int64_t)(n + TL_ROWS - 1) / TL_ROWS / (grid / ks) + 1 > TL_NRED * TL_CW * 512) continue;   // finish list
+    if (ks > 1 && (n + TL_ROWS - 1) / TL_ROWS > KQ_CNT_SLOTS) continue;   // one arrival counter per 8-row tile
     if (stages < 4 && ks < 4 && nblk >= 2 * ks) continue;   // a deeper ring with a finer split is better
     c.ks = ks; c.grid = grid; c.stages = stages; c.row_stride = row_stride; c.stage_bytes = stage_bytes; c.contig = contig;
     c.a_stride = a_stride; c.a_bytes = a_bytes; c.d_bytes = d_bytes; c.z_bytes = z_bytes;
@@ -714,10 +717,10 @@ bool make_tile_config(int type, int64_t n, int64_t k, int mtok, TileConfig& c) {
 template <int QT, int NH, typename OutT>
 int launch_tile(const TileParams& p, const TileConfig& c, cudaStream_t st) {
   auto kern = gemv_tile_kernel<QT, NH, OutT>;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;   // the attribute belongs to the (function, device) pair
+  if (configured.first_time()) {
     KQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TL_SMEM_LIMIT));
-    configured = true;
+    configured.done();
   }
   KQ_CUDA_TRY(launch_pdl(kern, dim3(c.grid), dim3(TL_THREADS), (size_t)c.smem, st, options().pdl != 0, p));
   options().launches += 1;

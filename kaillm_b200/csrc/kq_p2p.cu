@@ -11,8 +11,9 @@
 //   wait     the last CTA's first `world` threads wait (acquire, system scope; sleeping between polls) until
 //            flag[slot][r] >= epoch for every r, so when the kernel has completed the local gather buffer is whole
 //
-// The wait is bounded (about 2^28 clocks): on time-out the kernel writes a status word and returns; the caller
-// reads it with its next synchronisation.  Only plain loads/stores touch peer memory (no TMA, no multicast).
+// The wait is bounded (2^32 clocks, a good two seconds - ranks of one job may be skewed by hundreds of milliseconds
+// at their first call): on time-out the kernel writes a status word and returns with the gather buffer incomplete;
+// the caller reads the word with its next synchronisation.  Only plain loads/stores touch peer memory (no TMA, no multicast).
 // Buffer reuse: a rank may overwrite slot `rank` of a peer's buffer as soon as that peer has published the
 // NEXT call on the same stream; a caller that alternates two buffers per stream is race-free.
 #include "kq_common.cuh"
@@ -22,7 +23,7 @@ namespace kq {
 namespace {
 
 constexpr int P2P_MAX_RANKS = 8;
-constexpr long long P2P_WAIT_LIMIT = 1ll << 28;
+constexpr long long P2P_WAIT_LIMIT = 1ll << 32;
 
 struct P2PParams {
   const uint8_t* src;
@@ -33,6 +34,7 @@ struct P2PParams {
   uint32_t* done;                     // local: CTAs finished per slot (returns to zero)
   int* status;
   int slot, rank, world;
+  int vec16;                          // host-checked: src, every destination and the slice size are 16-byte aligned
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
@@ -48,8 +50,7 @@ __global__ void __launch_bounds__(1024) p2p_allgather_kernel(const P2PParams p) 
   const size_t nvec = p.bytes / 16;
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nthr = (size_t)gridDim.x * blockDim.x;
   const size_t off0 = (size_t)p.rank * p.bytes;
-  const bool aligned = (((uintptr_t)p.src | off0 | p.bytes) & 15) == 0;
-  if (aligned) {
+  if (p.vec16) {
     for (size_t i = tid; i < nvec; i += nthr) {
       const uint4 v = *reinterpret_cast<const uint4*>(p.src + i * 16);
       for (int r = 0; r < p.world; ++r) *reinterpret_cast<uint4*>(p.dst[r] + off0 + i * 16) = v;
@@ -105,10 +106,17 @@ int launch_p2p_allgather(const void* src, size_t bytes, void* const* peer_dst, u
   P2PParams p;
   p.src = (const uint8_t*)src; p.bytes = bytes; p.epoch = epoch; p.done = done; p.status = status;
   p.slot = slot; p.rank = rank; p.world = world;
+  uintptr_t bits = (uintptr_t)src | (uintptr_t)bytes;   // rank * bytes is then aligned as well
   for (int r = 0; r < P2P_MAX_RANKS; ++r) {
     p.dst[r] = r < world ? (uint8_t*)peer_dst[r] : nullptr;
     p.flags[r] = r < world ? peer_flags[r] : nullptr;
+    if (r < world) {
+      if (!peer_dst[r] || !peer_flags[r]) { set_error("kq_p2p_allgather: null buffer or flag pointer for rank %d", r); return KQ_EINVAL; }
+      if ((uintptr_t)peer_flags[r] % 4) { set_error("kq_p2p_allgather: flag array of rank %d is not 4-byte aligned", r); return KQ_EINVAL; }
+      bits |= (uintptr_t)peer_dst[r];
+    }
   }
+  p.vec16 = (bits & 15) == 0;   // otherwise every byte travels on its own (correct for any alignment, slow)
   // decode-sized slices (<= 256 KB) go through ONE CTA of 1024 threads: one system-scope fence and no CTA counter on
   // the way to the flags; larger ones use up to 32 CTAs
   size_t blocks = 1;

@@ -21,7 +21,17 @@ import sys
 import sysconfig
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_CSRC = os.environ.get("KQ_REFERENCE_CSRC", "/root/reference/runtime-source/vllm_gguf_plugin/csrc")
+
+
+def reference_root() -> str:
+    """The kaiLLM source tree: $KQ_REFERENCE_ROOT, else a `reference` directory beside this repository."""
+    env = os.environ.get("KQ_REFERENCE_ROOT")
+    if env:
+        return env
+    return os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+REF_CSRC = os.environ.get("KQ_REFERENCE_CSRC") or os.path.join(reference_root(), "runtime-source", "vllm_gguf_plugin", "csrc")
 OUT_DIR = os.path.join(HERE, "_ref")
 OUT = os.path.join(OUT_DIR, "_C_gguf_ref.so")
 NVCC = os.environ.get("KQ_NVCC", "/usr/local/cuda/bin/nvcc")

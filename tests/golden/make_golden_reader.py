@@ -1,7 +1,8 @@
 """Generate tests/golden/reader_dequant.npz from the reference's own gguf-reader.
 
 Run in a container that has the reference tree (it cannot travel to the GPU box):
-    python tests/golden/make_golden_reader.py [/root/reference]
+    python tests/golden/make_golden_reader.py [<path of the kaiLLM tree>]
+(default: $KQ_REFERENCE_ROOT, else a `reference` directory beside this repository)
 For each supported GGML type a small seeded wire tensor (kaillm_b200.synth.wire_numpy) is dequantized
 with `gguf.quants.dequantize` (gguf-reader/gguf/quants.py:68) imported from the reference tree; inputs
 and outputs are stored so the oracle can be checked against the reference's arithmetic anywhere.
@@ -13,7 +14,7 @@ import sys
 import numpy as np
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+ref = sys.argv[1] if len(sys.argv) > 1 else (os.environ.get("KQ_REFERENCE_ROOT") or os.path.join(os.path.dirname(ROOT), "reference"))
 sys.path.insert(0, os.path.join(ref, "runtime-source", "gguf-reader"))
 import gguf  # noqa: E402
 from gguf import quants  # noqa: E402

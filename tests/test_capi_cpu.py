@@ -119,3 +119,37 @@ def test_torch_extension_registers_reference_schemas():
     for name, schema in want.items():
         assert str(getattr(torch.ops._C_gguf, name).default._schema) == schema
     assert hasattr(torch.ops._C_gguf, "ggml_moe_a8") and hasattr(torch.ops._C_gguf, "ggml_moe_a8_vec")
+
+
+@pytest.mark.parametrize("rowbytes", [18 * 3, 34 * 5, 210 * 20, 110 * 8, 144 * 20, 84 * 7, 210])
+@pytest.mark.parametrize("n", [1, 2, 7, 8, 9, 33])
+def test_streaming_kernels_never_read_past_the_tensor(rowbytes, n):
+    """Host arithmetic of the bulk-copy windows (the kernels call the same function): for tensors whose byte size is
+    not a multiple of 16 no bulk range or plain-load tail may end beyond base + n * rowbytes, the bulk range stays
+    16-byte aligned, and bulk + tail together cover the wanted bytes."""
+    base = 0x7F0000001000
+    end = base + n * rowbytes
+    cases = []
+    for rows in (1, 2, 8, 16):
+        for a in range(0, n, rows):
+            cases.append((a, min(a + rows, n), 0, 0))
+    seg = max(2, (rowbytes // 4) // 2 * 2)
+    for r in range(n):
+        for off in range(0, rowbytes, seg):
+            cases.append((r, r + 1, off, min(seg, rowbytes - off)))
+    for a, b, off, ln in cases:
+        start, bulk, tail = capi.copy_window(base, n, rowbytes, a, b, off, ln)
+        ga = base + a * rowbytes + off
+        ge = ga + ln if ln else base + b * rowbytes
+        assert start % 16 == 0 and bulk % 16 == 0 and tail < 16 and tail % 2 == 0
+        assert base <= start <= ga
+        assert start + bulk + tail >= ge and start + bulk <= end and start + bulk + tail <= end
+        if tail:
+            assert start + bulk + tail == ge
+
+
+def test_copy_window_rejects_bad_arguments():
+    with pytest.raises(capi.KqError):
+        capi.copy_window(4096, 4, 144, 3, 5)
+    with pytest.raises(capi.KqError):
+        capi.copy_window(4096, 4, 144, 0, 1, 100, 80)

@@ -63,7 +63,7 @@ def test_gemm_q4k_vec_flavour_folds_the_min_term():
 
 @pytest.mark.parametrize("m", [256, 1024, 2048])
 def test_config4_q4k_prefill(m):
-    """BASELINE config 4: Q4_K N=17408 K=5120, bf16 activations; oracle on the first and last 64 rows."""
+    """Prefill benchmark shape: Q4_K N=17408 K=5120, bf16 activations; oracle on the first and last 64 rows."""
     qt, n, k = 12, 17408, 5120
     _, wt = wire(qt, n, k, seed=4)
     x, xt = act(m, k, seed=m, dt="bf16")
@@ -105,3 +105,24 @@ def test_gemm_only_quantizer_equals_full_quantizer(qt, n, k, m, dt):
     capi.prepare_q8(xt, qt, n, scratch)
     capi.mul_mat_prepared(wt, qt, m, k, y0, scratch, mmq=True)
     assert torch.equal(y1, y0)
+
+
+@pytest.mark.parametrize("qt,k,n_max,n_small", [(14, 17408, 1024, 296), (12, 17408, 1024, 136), (14, 17408, 4096, 40)])
+@pytest.mark.parametrize("m", [8, 16])
+def test_one_preparation_serves_weight_tensors_of_different_n(qt, k, n_max, n_small, m):
+    """q/k/v-style sharing: kq_prepare_q8 sized for the widest tensor, then split-K launches on a narrower and on the
+    widest one, in both orders, on a scratch that held 0xFF everywhere before the preparation."""
+    _, w_big = wire(qt, n_max, k, seed=1)
+    _, w_small = wire(qt, n_small, k, seed=2)
+    x, xt = act(m, k, seed=3, dt="bf16")
+    ws = capi.workspace_bytes(qt, m, n_max, k)
+    for order in ((w_small, w_big), (w_big, w_small), (w_small, w_small)):
+        scratch = torch.full((ws,), 0xFF, dtype=torch.uint8, device=dev())
+        capi.prepare_q8(xt, qt, n_max, scratch)
+        for wt in order:
+            n = wt.shape[0]
+            y = torch.full((m, n), float("nan"), dtype=torch.float32, device=dev())
+            capi.mul_mat_prepared(wt, qt, m, k, y, scratch)
+            assert capi.read_status(qt, m, n_max, k, scratch) == 0
+            want = O.mul_mat(wt.cpu().numpy(), qt, x, "mmvq")
+            assert rel_l2(to_np(y), want) < 2e-5

@@ -112,31 +112,7 @@ def test_mul_mat_low_precision_output(qt, dt):
     assert (got == want).mean() > 0.98                     # only rounding-boundary cases may differ
 
 
-# ------------------------------------------------------------------ tensor-core GEMV specifically
-@pytest.mark.parametrize("qt", [12, 14])
-@pytest.mark.parametrize("n,k,m", [(16, 256, 1), (17, 512, 3), (100, 1024, 8), (2368, 2048, 9), (4736, 5120, 16),
-                                   (333, 4352, 16), (64, 17408, 5), (48, 768, 33)])
-@pytest.mark.parametrize("mmq", [False, True])
-def test_tensor_core_gemv_matches_oracle_and_dp4a(qt, n, k, m, mmq):
-    w, wt = wire(qt, n, k, seed=n + k)
-    x, xt = act(m, k, seed=m, dt="bf16")
-    ws = capi.workspace_bytes(qt, m, n, k)
-    scratch = torch.empty(ws, dtype=torch.uint8, device=dev())
-    capi.set_option("gemv_impl", 2)
-    try:
-        y2 = capi.mul_mat(wt, xt, qt, mmq=mmq, out_dtype=torch.float32, scratch=scratch)
-        assert capi.read_status(qt, m, n, k, scratch) == 0
-        y2b = capi.mul_mat(wt, xt, qt, mmq=mmq, out_dtype=torch.float32, scratch=scratch)   # counters self-reset
-        capi.set_option("gemv_impl", 1)
-        y1 = capi.mul_mat(wt, xt, qt, mmq=mmq, out_dtype=torch.float32)
-    finally:
-        capi.set_option("gemv_impl", 0)
-    want = O.mul_mat(w, qt, x, "mmq" if mmq else "mmvq")
-    assert rel_l2(to_np(y2), want) < TIGHT
-    assert torch.equal(y2, y2b)
-    assert rel_l2(to_np(y2), to_np(y1)) < TIGHT
-
-
+# ------------------------------------------------------------------ the streaming kernels specifically
 @pytest.mark.parametrize("qt", QT)
 @pytest.mark.parametrize("n,k,m", [(16, 512, 1), (17, 1024, 2), (100, 2048, 3), (2368, 2048, 5), (1200, 5120, 9),
                                    (333, 4352, 17), (64, 17408, 4), (48, 768, 33), (5, 256, 80)])
@@ -154,32 +130,6 @@ def test_streaming_dp4a_gemv_matches_oracle(qt, n, k, m):
         capi.set_option("gemv_impl", 0)
     assert rel_l2(to_np(y), O.mul_mat(w, qt, x, "mmvq")) < TIGHT
     assert torch.equal(y, yb)
-
-
-@pytest.mark.parametrize("n,k,m", [(17408, 5120, 16), (9000, 5120, 5), (17408, 2048, 13), (300, 256, 7), (4000, 512, 33),
-                                   (128, 512, 1)])
-@pytest.mark.parametrize("mmq", [False, True])
-def test_tcgen05_gemv_q4k_matches_oracle(n, k, m, mmq):
-    """The tcgen05 kind::i8 decode kernel (stream-K over 128-row x 256-weight units), forced with gemv_impl=5."""
-    qt = 12
-    _, wt = wire(qt, n, k, seed=n + k)
-    x, xt = act(m, k, seed=m, dt="bf16")
-    w = wt.cpu().numpy()
-    scratch = torch.empty(capi.workspace_bytes(qt, m, n, k), dtype=torch.uint8, device=dev())
-    capi.set_option("gemv_impl", 5)
-    try:
-        y = capi.mul_mat(wt, xt, qt, mmq=mmq, out_dtype=torch.float32, scratch=scratch)
-        assert capi.read_status(qt, m, n, k, scratch) == 0
-        yb = capi.mul_mat(wt, xt, qt, mmq=mmq, out_dtype=torch.float32, scratch=scratch)   # counters self-reset
-        capi.set_option("gemv_impl", 1)
-        y1 = capi.mul_mat(wt, xt, qt, mmq=mmq, out_dtype=torch.float32)
-    finally:
-        capi.set_option("gemv_impl", 0)
-    rows = np.r_[0:min(n, 200), max(0, n - 200):n]
-    want = O.mul_mat(w[rows], qt, x, "mmq" if mmq else "mmvq")
-    assert rel_l2(to_np(y)[:, rows], want) < TIGHT
-    assert torch.equal(y, yb)
-    assert rel_l2(to_np(y), to_np(y1)) < TIGHT          # every row, against the general kernel
 
 
 @pytest.mark.parametrize("qt", [12, 14, 8, 2, 21, 10])
@@ -244,7 +194,7 @@ def test_in_kernel_quantization_equals_quantizer_launch(qt, n, k, m, dt):
     assert rel_l2(to_np(y1), O.mul_mat(w, qt, x, "mmvq")) < TIGHT
 
 
-def test_tensor_core_gemv_declines_unaligned_weights():
+def test_streaming_gemv_declines_unaligned_weights():
     qt, n, k = 14, 32, 512
     _, wt = wire(qt, n, k, seed=1)
     _, xt = act(2, k, seed=1, dt="bf16")
@@ -254,7 +204,7 @@ def test_tensor_core_gemv_declines_unaligned_weights():
     ref = capi.mul_mat(wt, xt, qt, out_dtype=torch.float32)
     got = capi.mul_mat(wv, xt, qt, out_dtype=torch.float32)     # auto: falls back to the general kernel
     assert rel_l2(to_np(got), to_np(ref)) < TIGHT
-    capi.set_option("gemv_impl", 2)
+    capi.set_option("gemv_impl", 6)
     try:
         with pytest.raises(capi.KqError) as e:
             capi.mul_mat(wv, xt, qt, out_dtype=torch.float32)
@@ -263,7 +213,7 @@ def test_tensor_core_gemv_declines_unaligned_weights():
         capi.set_option("gemv_impl", 0)
 
 
-# ------------------------------------------------------------------ BASELINE.json configurations
+# ------------------------------------------------------------------ the benchmark configurations at full size
 def test_config1_q4_0_single_linear():
     """Q4_0 N=8192 K=2048, fp32 activation [1,2048], seed 0."""
     w, wt = wire(2, 8192, 2048, seed=0)
