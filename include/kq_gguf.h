@@ -173,14 +173,16 @@ int kq_read_status(int type, int64_t m, int64_t n, int64_t k, const void* scratc
  * (SYNCHRONISES; 0 = the kernels of every call so far finished normally).  No counterpart in the reference. */
 int kq_read_status_static(int* status);
 
-/* Test hook, host arithmetic only (no GPU work): the byte ranges the streaming kernels read when they stage weight
- * bytes of a tensor of n rows of rowbytes bytes at address `base` (16-byte aligned) in shared memory.  seg_len == 0:
- * whole rows [row_a, row_b); seg_len > 0: bytes [seg_off, seg_off + seg_len) of row row_a.  Returns the 16-byte
- * aligned bulk-copy range [bulk_start, bulk_start + bulk_bytes) and the number of bytes after it that are fetched by
- * plain loads.  The kernels call the same function; a test can assert that nothing past base + n * rowbytes is
- * read.  No counterpart in the reference. */
+/* Test hook, host arithmetic only (no GPU work): what the streaming kernels read of a tensor of n rows of rowbytes
+ * bytes at address `base` (16-byte aligned).  They stage weight bytes in shared memory with bulk copies of 16-byte
+ * units, so they are given only the first `streamed_rows` rows - the largest count whose byte size is a multiple of 16
+ * (all n for every even n); the few rows that may remain go to the general kernel, which reads with plain loads.
+ * seg_len == 0: whole rows [row_a, row_b); seg_len > 0: bytes [seg_off, seg_off + seg_len) of row row_a.  Returns the
+ * bulk-copy range [bulk_start, bulk_start + bulk_bytes) for rows inside the streamed part (0, 0 otherwise).  The
+ * kernels and the dispatch call the same functions; a test can assert that nothing outside
+ * [base, base + n * rowbytes) is read.  No counterpart in the reference. */
 int kq_debug_copy_window(uint64_t base, int64_t n, int64_t rowbytes, int64_t row_a, int64_t row_b, int64_t seg_off,
-                         int64_t seg_len, uint64_t* bulk_start, uint64_t* bulk_bytes, uint64_t* tail_bytes);
+                         int64_t seg_len, int64_t* streamed_rows, uint64_t* bulk_start, uint64_t* bulk_bytes);
 
 /* Runtime knobs for tests and profiling (process-wide, not thread-safe against concurrent launches):
  *   "gemv_impl"   0 = choose by shape (default), 1 = general dp4a kernel, 3 = row-streaming dp4a kernel,

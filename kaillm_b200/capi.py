@@ -58,7 +58,7 @@ def _load() -> ctypes.CDLL:
     lib.kq_p2p_allgather.argtypes = [vp, sz, ctypes.POINTER(vp), ctypes.POINTER(vp), vp, vp, i32, i32, i32, vp, vp]
     lib.kq_read_status_static.argtypes = [ctypes.POINTER(i32)]
     u64p = ctypes.POINTER(ctypes.c_uint64)
-    lib.kq_debug_copy_window.argtypes = [ctypes.c_uint64, i64, i64, i64, i64, i64, i64, u64p, u64p, u64p]
+    lib.kq_debug_copy_window.argtypes = [ctypes.c_uint64, i64, i64, i64, i64, i64, i64, ctypes.POINTER(i64), u64p, u64p]
     lib.kq_set_option.argtypes = [ctypes.c_char_p, i32]
     lib.kq_get_option.argtypes = [ctypes.c_char_p, ctypes.POINTER(i32)]
     return lib
@@ -163,11 +163,11 @@ def read_status_static() -> int:
 
 
 def copy_window(base: int, n: int, rowbytes: int, row_a: int, row_b: int, seg_off: int = 0, seg_len: int = 0):
-    """(bulk_start, bulk_bytes, tail_bytes) the streaming kernels would read for these rows (host arithmetic only)."""
-    a, b, c = ctypes.c_uint64(), ctypes.c_uint64(), ctypes.c_uint64()
-    _check(lib.kq_debug_copy_window(base, n, rowbytes, row_a, row_b, seg_off, seg_len, ctypes.byref(a), ctypes.byref(b),
-                                    ctypes.byref(c)))
-    return a.value, b.value, c.value
+    """(streamed_rows, bulk_start, bulk_bytes) of the streaming kernels for these rows (host arithmetic only)."""
+    ns, a, b = ctypes.c_int64(), ctypes.c_uint64(), ctypes.c_uint64()
+    _check(lib.kq_debug_copy_window(base, n, rowbytes, row_a, row_b, seg_off, seg_len, ctypes.byref(ns), ctypes.byref(a),
+                                    ctypes.byref(b)))
+    return ns.value, a.value, b.value
 
 
 def mul_mat_vec_static(W: torch.Tensor, x: torch.Tensor, qtype: int, out: torch.Tensor) -> torch.Tensor:

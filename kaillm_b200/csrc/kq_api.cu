@@ -96,7 +96,7 @@ static int mul_mat(const char* fn, bool mmq, const void* W, int type, int64_t n,
   // enough for the ~2 us of quantization to hide behind the pipeline fill: 16.9 -> 15.4 us on Q4_K 17408x5120 at one
   // token; a second pass, or a matrix of a few MB, makes it slower than the separate launch)
   const bool fuse_fits = options().fuse_q8 == 2 || (m * (k / 32) <= 512 && n * p.rowbytes >= (32ll << 20));   // 2: wherever it can run (tests)
-  const bool fuse = x && !gemm && options().fuse_q8 && m <= 2 && fuse_fits &&
+  const bool fuse = x && !gemm && options().fuse_q8 && m <= 2 && fuse_fits && stream_rows(n, p.rowbytes) == n &&
                     impl != 1 && gemv_rows_only(type, n, k, m) && gemv_mma_supported(W, type, n, k);
   if (fuse) return launch_gemv_mma(W, type, n, k, P, m, y, y_dtype, stride_y, mmq, st, x, x_dtype, stride_x);
   if (x) {
@@ -108,8 +108,22 @@ static int mul_mat(const char* fn, bool mmq, const void* W, int type, int64_t n,
     if (rc) return rc;
   }
   if (gemm) return launch_gemm_tc(W, type, n, k, P, m, y, y_dtype, stride_y, mmq, st);
-  if (impl != 1 && gemv_mma_supported(W, type, n, k))
-    return launch_gemv_mma(W, type, n, k, P, m, y, y_dtype, stride_y, mmq, st);
+  if (impl != 1 && gemv_mma_supported(W, type, n, k)) {
+    // the streaming kernels take the rows whose total size is a multiple of 16 bytes (all of them for every even n);
+    // up to 7 rows at the end of an odd-sized tensor go to the general kernel, so nothing is read past the tensor
+    const int64_t ns = stream_rows(n, p.rowbytes);
+    if (ns > 0) {
+      rc = launch_gemv_mma(W, type, ns, k, P, m, y, y_dtype, stride_y, mmq, st);
+      if (rc) return rc;
+    }
+    if (ns == n) return KQ_OK;
+    if (impl < 2)
+      return launch_gemv_dp4a((const uint8_t*)W + ns * p.rowbytes, type, n - ns, k, P.ds, P.qs, p.L.kpad, m,
+                              (uint8_t*)y + ns * dtype_size(y_dtype), y_dtype, stride_y, mmq, nullptr, nullptr, st);
+    if (ns == 0) { set_error("%s: the streaming GEMV does not cover this shape/alignment", fn); return KQ_EUNSUPPORTED; }
+    return launch_gemv_dp4a((const uint8_t*)W + ns * p.rowbytes, type, n - ns, k, P.ds, P.qs, p.L.kpad, m,
+                            (uint8_t*)y + ns * dtype_size(y_dtype), y_dtype, stride_y, mmq, nullptr, nullptr, st);
+  }
   if (impl >= 2) { set_error("%s: the streaming GEMV does not cover this shape/alignment", fn); return KQ_EUNSUPPORTED; }
   return launch_gemv_dp4a(W, type, n, k, P.ds, P.qs, p.L.kpad, m, y, y_dtype, stride_y, mmq, nullptr, nullptr, st);
 }
@@ -275,24 +289,27 @@ int kq_p2p_allgather(const void* src, size_t bytes, void* const* peer_dst, uint3
 }
 
 int kq_debug_copy_window(uint64_t base, int64_t n, int64_t rowbytes, int64_t row_a, int64_t row_b, int64_t seg_off,
-                         int64_t seg_len, uint64_t* bulk_start, uint64_t* bulk_bytes, uint64_t* tail_bytes) {
+                         int64_t seg_len, int64_t* streamed_rows, uint64_t* bulk_start, uint64_t* bulk_bytes) {
   t_err[0] = 0;
-  if (n <= 0 || rowbytes <= 0 || row_a < 0 || row_b <= row_a || row_b > n || seg_off < 0 || !bulk_start || !bulk_bytes || !tail_bytes) {
+  if (n <= 0 || rowbytes <= 0 || (rowbytes & 1) || (base & 15) || !streamed_rows || !bulk_start || !bulk_bytes) {
     set_error("kq_debug_copy_window: bad argument");
     return KQ_EINVAL;
   }
-  const uintptr_t wend = (uintptr_t)base + (uintptr_t)(n * rowbytes);
+  const int64_t ns = stream_rows(n, rowbytes);
+  *streamed_rows = ns;
+  *bulk_start = 0; *bulk_bytes = 0;
+  if (row_a < 0 || row_b <= row_a || row_b > ns) return KQ_OK;   // rows outside the streamed part: no window
   uintptr_t ga, ge;
   if (seg_len > 0) {   // one row segment (row_b is ignored)
-    if (seg_off + seg_len > rowbytes) { set_error("kq_debug_copy_window: segment outside the row"); return KQ_EINVAL; }
+    if (seg_off < 0 || seg_off + seg_len > rowbytes) { set_error("kq_debug_copy_window: segment outside the row"); return KQ_EINVAL; }
     ga = (uintptr_t)base + (uintptr_t)(row_a * rowbytes + seg_off);
     ge = ga + (uintptr_t)seg_len;
   } else {             // whole rows [row_a, row_b)
     ga = (uintptr_t)base + (uintptr_t)(row_a * rowbytes);
     ge = (uintptr_t)base + (uintptr_t)(row_b * rowbytes);
   }
-  const CopyWindow w = copy_window(ga, ge, wend);
-  *bulk_start = (uint64_t)w.a0; *bulk_bytes = w.bulk; *tail_bytes = w.tail;
+  const CopyWindow w = copy_window(ga, ge);
+  *bulk_start = (uint64_t)w.a0; *bulk_bytes = w.bulk;
   return KQ_OK;
 }
 

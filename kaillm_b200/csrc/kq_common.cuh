@@ -141,26 +141,29 @@ inline Q8Ptrs q8_ptrs(void* scratch, const Q8Layout& L, int64_t n) {
   return P;
 }
 
-// Bulk-copy window of the weight bytes [ga, ge) of a tensor that ends at wend.  cp.async.bulk moves 16-byte units
-// between 16-byte aligned addresses, so the window starts at ga rounded down (the caller guarantees a 16-byte aligned
-// tensor base, so that never reaches below the tensor) and ends at ge rounded up - unless that would pass the end of
-// the tensor: then the bulk part stops at the last 16-byte boundary and the remaining `tail` bytes (< 16, an even
-// number) are fetched with plain 2-byte loads.  Nothing outside [base, wend) is ever read.
+// Bulk-copy window of the weight bytes [ga, ge): cp.async.bulk moves 16-byte units between 16-byte aligned addresses,
+// so the staged window starts at ga rounded down and ends at ge rounded up.  The streaming kernels are only ever given
+// a 16-byte aligned tensor base and a row count whose total size is a multiple of 16 bytes (stream_rows below), so a
+// window never reaches outside the tensor: rounding only ever takes in bytes of a neighbouring row.
 struct CopyWindow {
   uintptr_t a0;    // start of the bulk copy (16-byte aligned)
   uint32_t lead;   // ga - a0: where the wanted bytes start inside the staged window
-  uint32_t bulk;   // bytes of the bulk copy (a multiple of 16, may be 0)
-  uint32_t tail;   // bytes after the bulk part to fetch with plain loads: [a0 + bulk, ge)
+  uint32_t bulk;   // bytes of the bulk copy (a multiple of 16)
 };
-__host__ __device__ inline CopyWindow copy_window(uintptr_t ga, uintptr_t ge, uintptr_t wend) {
+__host__ __device__ inline CopyWindow copy_window(uintptr_t ga, uintptr_t ge) {
   CopyWindow w;
   w.a0 = ga & ~(uintptr_t)15;
   w.lead = (uint32_t)(ga - w.a0);
-  uintptr_t e = (ge + 15) & ~(uintptr_t)15;
-  w.tail = 0;
-  if (e > wend) { e = ge & ~(uintptr_t)15; if (e < w.a0) e = w.a0; w.tail = (uint32_t)(ge - e); }
-  w.bulk = (uint32_t)(e - w.a0);
+  w.bulk = (uint32_t)(((ge + 15) & ~(uintptr_t)15) - w.a0);
   return w;
+}
+// Rows of an n-row tensor the streaming kernels may take: the largest count <= n whose byte size is a multiple of 16
+// (row sizes are even, so at most 7 rows are left over); the remaining rows go to the general kernel, which reads
+// with plain loads and exact bounds.
+inline int64_t stream_rows(int64_t n, int64_t rowbytes) {
+  int64_t r = n;
+  while (r > 0 && (r * rowbytes) % 16) --r;
+  return r;
 }
 
 // kernels (defined in the .cu files)

@@ -231,22 +231,15 @@ __global__ void __launch_bounds__(ROW_THREADS, 1) gemv_rows_kernel(const RowPara
   if (warp == ROW_WARPS) {
     // ------------------------------------------------------------------ producer (one lane is enough)
     if (lane == 0) {
-      const uintptr_t wend = (uintptr_t)(p.W + (size_t)p.n * p.rowbytes);
       auto issue_stage = [&](int q) {
         const int slot = q % S;
         const int ra = r0 + q * R;
         const int rb = (ra + R) < r1 ? (ra + R) : r1;
-        const uintptr_t ge = (uintptr_t)(p.W + (size_t)rb * p.rowbytes);
-        const CopyWindow cw = copy_window((uintptr_t)(p.W + (size_t)ra * p.rowbytes), ge, wend);
-        uint8_t* dst = ring + (size_t)slot * p.stage_bytes;
-        if (cw.tail) {   // the tensor ends inside a 16-byte unit: its last bytes come by plain loads (last stage only)
-          const uint16_t* src = reinterpret_cast<const uint16_t*>(ge - cw.tail);
-          uint16_t* d16 = reinterpret_cast<uint16_t*>(dst + cw.bulk);
-          for (uint32_t i = 0; i < cw.tail / 2; ++i) d16[i] = src[i];
-          __threadfence_block();   // ordered before the arrive below, which releases them to the consumers
-        }
+        // whole rows [ra, rb): one bulk copy (the host passes only row counts whose byte size is a multiple of 16,
+        // so the rounded window stays inside the tensor)
+        const CopyWindow cw = copy_window((uintptr_t)(p.W + (size_t)ra * p.rowbytes), (uintptr_t)(p.W + (size_t)rb * p.rowbytes));
         mbar_expect_tx(bar_full + 8 * slot, cw.bulk);
-        if (cw.bulk) bulk_g2s(smem_u32(dst), (const void*)cw.a0, cw.bulk, bar_full + 8 * slot);
+        bulk_g2s(smem_u32(ring + (size_t)slot * p.stage_bytes), (const void*)cw.a0, cw.bulk, bar_full + 8 * slot);
         __threadfence_block();
         *s_issued = q + 1;
       };

@@ -472,43 +472,32 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
     const int contig = p.contig;
     int slot = 0;          // ring position of the next stage to issue
     uint32_t eph = 1;      // parity that shows the slot's previous contents consumed (passes at once on the first lap)
-    const uintptr_t wend = (uintptr_t)(p.W + (size_t)p.n * p.rowbytes);
-    // the last bytes of the tensor, when it ends inside a 16-byte unit, come by plain 2-byte loads (see copy_window)
-    auto fetch_tail = [&](uint8_t* dst_generic, const CopyWindow& cw, uintptr_t ge) {
-      const uint16_t* src = reinterpret_cast<const uint16_t*>(ge - cw.tail);
-      uint16_t* d16 = reinterpret_cast<uint16_t*>(dst_generic + cw.bulk);
-      for (uint32_t i = 0; i < cw.tail / 2; ++i) d16[i] = src[i];
-      __threadfence_block();
-    };
+    // every window is rounded out to 16-byte units; the host passes only row counts whose byte size is a multiple of
+    // 16 (and a 16-byte aligned base), so the rounding never reaches outside the tensor
     auto issue_stage = [&](int q) {
       const int row0 = (rt0 + q) * TL_ROWS;
-      uint8_t* dstg = ring + (size_t)slot * p.stage_bytes;
-      const uint32_t dst = s_u32(dstg);
+      const uint32_t dst = s_u32(ring + (size_t)slot * p.stage_bytes);
       const uint32_t bar = bar_full + 8 * slot;
       if (contig) {
         if (lane == 0) {
           const int rows = (p.n - row0) < TL_ROWS ? (p.n - row0) : TL_ROWS;
           const uintptr_t ga = (uintptr_t)(p.W + (size_t)row0 * p.rowbytes);
-          const uintptr_t ge = ga + (size_t)rows * p.rowbytes;
-          const CopyWindow cw = copy_window(ga, ge, wend);
-          if (cw.tail) fetch_tail(dstg, cw, ge);
+          const CopyWindow cw = copy_window(ga, ga + (size_t)rows * p.rowbytes);
           bar_expect_tx(bar, cw.bulk);
-          if (cw.bulk) copy_g2s(dst, (const void*)cw.a0, cw.bulk, bar);
+          copy_g2s(dst, (const void*)cw.a0, cw.bulk, bar);
         }
       } else {
         CopyWindow cw;
-        cw.a0 = 0; cw.lead = 0; cw.bulk = 0; cw.tail = 0;
+        cw.a0 = 0; cw.lead = 0; cw.bulk = 0;
         const int row = row0 + lane;
         if (lane < TL_ROWS && row < p.n) {
           const uintptr_t ga = (uintptr_t)(p.W + (size_t)row * p.rowbytes + seg0);
-          cw = copy_window(ga, ga + seglen, wend);
-          if (cw.tail) fetch_tail(dstg + (size_t)lane * p.row_stride, cw, ga + seglen);
+          cw = copy_window(ga, ga + seglen);
         }
         uint32_t total = cw.bulk;
 #pragma unroll
         for (int mask = 4; mask > 0; mask >>= 1) total += __shfl_xor_sync(0xffffffffu, total, mask);
-        __syncwarp();                               // the tail stores above are ordered before the arrive
-        if (lane == 0) bar_expect_tx(bar, total);
+        if (lane == 0) bar_expect_tx(bar, total);   // row0 < n, so total > 0
         __syncwarp();
         if (cw.bulk) copy_g2s(dst + (uint32_t)lane * p.row_stride, (const void*)cw.a0, cw.bulk, bar);
       }

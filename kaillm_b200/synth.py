@@ -19,10 +19,15 @@ from __future__ import annotations
 import numpy as np
 
 Q4_0, Q8_0, Q2_K, Q4_K, Q6_K, IQ3_S = 2, 8, 10, 12, 14, 21
-BLOCK = {Q4_0: (32, 18), Q8_0: (32, 34), Q2_K: (256, 84), Q4_K: (256, 144), Q6_K: (256, 210), IQ3_S: (256, 110)}
-NAMES = {Q4_0: "Q4_0", Q8_0: "Q8_0", Q2_K: "Q2_K", Q4_K: "Q4_K", Q6_K: "Q6_K", IQ3_S: "IQ3_S"}
+Q4_1, Q5_0, Q5_1, Q3_K, Q5_K, IQ4_NL, IQ4_XS = 3, 6, 7, 11, 13, 20, 23
+BLOCK = {Q4_0: (32, 18), Q8_0: (32, 34), Q2_K: (256, 84), Q4_K: (256, 144), Q6_K: (256, 210), IQ3_S: (256, 110),
+         Q4_1: (32, 20), Q5_0: (32, 22), Q5_1: (32, 24), Q3_K: (256, 110), Q5_K: (256, 176), IQ4_NL: (32, 18),
+         IQ4_XS: (256, 136)}
+NAMES = {Q4_0: "Q4_0", Q8_0: "Q8_0", Q2_K: "Q2_K", Q4_K: "Q4_K", Q6_K: "Q6_K", IQ3_S: "IQ3_S", Q4_1: "Q4_1",
+         Q5_0: "Q5_0", Q5_1: "Q5_1", Q3_K: "Q3_K", Q5_K: "Q5_K", IQ4_NL: "IQ4_NL", IQ4_XS: "IQ4_XS"}
 # byte offsets of the fp16 scale fields inside one block
-SCALE_FIELDS = {Q4_0: (0,), Q8_0: (0,), Q2_K: (80, 82), Q4_K: (0, 2), Q6_K: (208,), IQ3_S: (0,)}
+SCALE_FIELDS = {Q4_0: (0,), Q8_0: (0,), Q2_K: (80, 82), Q4_K: (0, 2), Q6_K: (208,), IQ3_S: (0,), Q4_1: (0, 2), Q5_0: (0,),
+                Q5_1: (0, 2), Q3_K: (108,), Q5_K: (0, 2), IQ4_NL: (0,), IQ4_XS: (0,)}
 
 
 def row_bytes(qtype: int, k: int) -> int:

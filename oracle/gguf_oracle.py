@@ -37,12 +37,23 @@ from __future__ import annotations
 import numpy as np
 
 Q4_0, Q8_0, Q2_K, Q4_K, Q6_K, IQ3_S = 2, 8, 10, 12, 14, 21
-QTYPES = (Q4_0, Q8_0, Q2_K, Q4_K, Q6_K, IQ3_S)
-NAMES = {Q4_0: "Q4_0", Q8_0: "Q8_0", Q2_K: "Q2_K", Q4_K: "Q4_K", Q6_K: "Q6_K", IQ3_S: "IQ3_S"}
+Q4_1, Q5_0, Q5_1, Q3_K, Q5_K, IQ4_NL, IQ4_XS = 3, 6, 7, 11, 13, 20, 23
+QTYPES = (Q4_0, Q8_0, Q2_K, Q4_K, Q6_K, IQ3_S)                       # the benchmark's six formats
+MORE_QTYPES = (Q4_1, Q5_0, Q5_1, Q3_K, Q5_K, IQ4_NL, IQ4_XS)         # the other formats of real mixed checkpoints
+ALL_QTYPES = QTYPES + MORE_QTYPES
+NAMES = {Q4_0: "Q4_0", Q8_0: "Q8_0", Q2_K: "Q2_K", Q4_K: "Q4_K", Q6_K: "Q6_K", IQ3_S: "IQ3_S", Q4_1: "Q4_1",
+         Q5_0: "Q5_0", Q5_1: "Q5_1", Q3_K: "Q3_K", Q5_K: "Q5_K", IQ4_NL: "IQ4_NL", IQ4_XS: "IQ4_XS"}
 # (weights per block, bytes per block) - gguf-reader/gguf/constants.py:5958
-BLOCK = {Q4_0: (32, 18), Q8_0: (32, 34), Q2_K: (256, 84), Q4_K: (256, 144), Q6_K: (256, 210), IQ3_S: (256, 110)}
+BLOCK = {Q4_0: (32, 18), Q8_0: (32, 34), Q2_K: (256, 84), Q4_K: (256, 144), Q6_K: (256, 210), IQ3_S: (256, 110),
+         Q4_1: (32, 20), Q5_0: (32, 22), Q5_1: (32, 24), Q3_K: (256, 110), Q5_K: (256, 176), IQ4_NL: (32, 18),
+         IQ4_XS: (256, 136)}
 # weights per integer-dot group (one weight-side scale per group)
-GROUP = {Q4_0: 32, Q8_0: 32, Q2_K: 16, Q4_K: 32, Q6_K: 16, IQ3_S: 32}
+GROUP = {Q4_0: 32, Q8_0: 32, Q2_K: 16, Q4_K: 32, Q6_K: 16, IQ3_S: 32, Q4_1: 32, Q5_0: 32, Q5_1: 32, Q3_K: 16, Q5_K: 32,
+         IQ4_NL: 32, IQ4_XS: 32}
+# types without an MMQ kernel in the reference (quantization/utils.py: MMQ_QUANT_TYPES has no i-matrix formats)
+NO_MMQ = (IQ3_S, IQ4_NL, IQ4_XS)
+# the 16 code values of IQ4_NL / IQ4_XS (ggml-common.h:1060)
+KVALUES_IQ4NL = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], dtype=np.int16)
 
 
 def row_bytes(qtype: int, k: int) -> int:
@@ -267,6 +278,74 @@ def unpack(wire: np.ndarray, qtype: int, iq3s_top: int = 62) -> dict:
         out["q"] = np.where(sg == 1, -g, g).astype(np.int16).reshape(n, -1)
         s = np.stack([scales & 15, scales >> 4], axis=-1)      # [n,nblk,4,2] -> ib = 2*i + e
         out["sc"] = s.reshape(n, -1)
+    elif qtype == Q4_1:                                          # ggml-common.h: block_q4_1 {half2 dm; qs[16]}
+        out["d"] = _h(b[..., 0:2])
+        out["m"] = _h(b[..., 2:4])
+        qs = b[..., 4:20].astype(np.int16)
+        out["q"] = np.concatenate([qs & 15, qs >> 4], axis=-1).reshape(n, -1)
+    elif qtype in (Q5_0, Q5_1):                                  # block_q5_0 {half d; qh[4]; qs[16]}, q5_1 {half2 dm; ...}
+        o = 2 if qtype == Q5_0 else 4
+        out["d"] = _h(b[..., 0:2])
+        if qtype == Q5_1:
+            out["m"] = _h(b[..., 2:4])
+        qh = np.ascontiguousarray(b[..., o:o + 4]).view(np.uint32)[..., 0].astype(np.int64)     # [n,nblk]
+        qs = b[..., o + 4:o + 20].astype(np.int16)
+        bits = ((qh[..., None] >> np.arange(32)) & 1).astype(np.int16)                          # [n,nblk,32]
+        lo = (qs & 15) | (bits[..., 0:16] << 4)
+        hi = (qs >> 4) | (bits[..., 16:32] << 4)
+        out["q"] = np.concatenate([lo, hi], axis=-1).reshape(n, -1)                             # 0..31, unsigned
+    elif qtype == Q3_K:                                          # block_q3_K {hmask[32]; qs[64]; scales[12]; half d}
+        hm = b[..., 0:32].astype(np.int16)
+        qs = b[..., 32:96].astype(np.int16).reshape(n, nblk, 2, 32)
+        scb = b[..., 96:108].astype(np.int32)
+        out["d"] = _h(b[..., 108:110])
+        q = np.empty((n, nblk, 2, 4, 32), np.int16)
+        for nn in range(2):
+            for j in range(4):
+                low = (qs[:, :, nn, :] >> (2 * j)) & 3
+                has = (hm >> (4 * nn + j)) & 1
+                q[:, :, nn, j, :] = low - np.where(has == 1, 0, 4)      # dequantize.cuh:150 -> -4..3
+        out["q"] = q.reshape(n, -1)
+        sc = np.empty((n, nblk, 16), np.int32)
+        for i in range(16):                                      # dequantize.cuh:139-142, minus 32
+            if i < 4:
+                us = (scb[..., i] & 15) | (((scb[..., i + 8] >> 0) & 3) << 4)
+            elif i < 8:
+                us = (scb[..., i] & 15) | (((scb[..., i + 4] >> 2) & 3) << 4)
+            elif i < 12:
+                us = (scb[..., i - 8] >> 4) | (((scb[..., i] >> 4) & 3) << 4)
+            else:
+                us = (scb[..., i - 8] >> 4) | (((scb[..., i - 4] >> 6) & 3) << 4)
+            sc[..., i] = us - 32
+        out["sc"] = sc.reshape(n, -1)
+    elif qtype == Q5_K:                                          # block_q5_K {half2 dm; scales[12]; qh[32]; qs[128]}
+        out["d"] = _h(b[..., 0:2])
+        out["dmin"] = _h(b[..., 2:4])
+        sc, mn = q4k_scale_min(b[..., 4:16])
+        qh = b[..., 16:48].astype(np.int16)                                  # [n,nblk,32]
+        qs = b[..., 48:176].astype(np.int16).reshape(n, nblk, 4, 32)
+        parts = []
+        for il in range(4):
+            lo = (qs[:, :, il, :] & 15) | (((qh >> (2 * il)) & 1) << 4)
+            hi = (qs[:, :, il, :] >> 4) | (((qh >> (2 * il + 1)) & 1) << 4)
+            parts += [lo, hi]
+        out["q"] = np.stack(parts, axis=2).reshape(n, -1)                    # 0..31
+        out["sc"] = sc.reshape(n, -1)
+        out["mn"] = mn.reshape(n, -1)
+    elif qtype == IQ4_NL:                                        # block_iq4_nl {half d; qs[16]}
+        out["d"] = _h(b[..., 0:2])
+        qs = b[..., 2:18].astype(np.int16)
+        out["q"] = KVALUES_IQ4NL[np.concatenate([qs & 15, qs >> 4], axis=-1)].reshape(n, -1)
+    elif qtype == IQ4_XS:                                        # block_iq4_xs {half d; u16 scales_h; scales_l[4]; qs[128]}
+        out["d"] = _h(b[..., 0:2])
+        sh = np.ascontiguousarray(b[..., 2:4]).view(np.uint16)[..., 0].astype(np.int32)         # [n,nblk]
+        sl = b[..., 4:8].astype(np.int32)
+        qs = b[..., 8:136].astype(np.int16).reshape(n, nblk, 8, 16)
+        out["q"] = KVALUES_IQ4NL[np.concatenate([qs & 15, qs >> 4], axis=-1)].reshape(n, -1)
+        ls = np.empty((n, nblk, 8), np.int32)
+        for ib in range(8):
+            ls[..., ib] = ((sl[..., ib // 2] >> (4 * (ib % 2))) & 15) | (((sh >> (2 * ib)) & 3) << 4)
+        out["sc"] = (ls - 32).reshape(n, -1)
     else:
         raise ValueError(f"unsupported GGML type {qtype}")
     return out
@@ -304,8 +383,8 @@ def mul_mat(wire: np.ndarray, qtype: int, x: np.ndarray, semantics: str = "mmvq"
     """
     if semantics not in ("mmvq", "mmq"):
         raise ValueError(semantics)
-    if semantics == "mmq" and qtype == IQ3_S:
-        raise ValueError("the reference has no MMQ kernel for IQ3_S")
+    if semantics == "mmq" and qtype in NO_MMQ:
+        raise ValueError("the reference has no MMQ kernel for the i-matrix formats")
     x = np.asarray(x, dtype=np.float32)
     m, k = x.shape
     act = quantize_q8_1(x)
@@ -325,7 +404,20 @@ def mul_mat(wire: np.ndarray, qtype: int, x: np.ndarray, semantics: str = "mmvq"
         y = np.einsum("nb,mnb->mn", d, d8[:, None, :] * I - 8.0 * s8[:, None, :])
     elif qtype == Q8_0:
         y = np.einsum("nb,mb,mnb->mn", d, d8, I, optimize=True)
-    elif qtype == Q6_K:
+    elif qtype == IQ4_NL:                                         # vecdotq.cuh: vec_dot_iq4_nl_q8_1
+        y = np.einsum("nb,mb,mnb->mn", d, d8, I, optimize=True)
+    elif qtype in (Q4_1, Q5_1):
+        # vecdotq.cuh:71-92 / 131-160: the products d*d8 and m*s8 are formed in fp16 (__hmul2), then used in fp32
+        mw = w["m"]
+        dd = h2d(hmul(w["d"][None, :, :], act["d"][:, None, :nb8]))      # [m,n,b]
+        ms = h2d(hmul(mw[None, :, :], act["s"][:, None, :nb8]))
+        y = (dd * I + ms).sum(-1)
+    elif qtype == Q5_0:
+        if semantics == "mmq":                                    # load_tiles_q5_0 subtracts 16 from the codes: exact
+            y = np.einsum("nb,mnb->mn", d, d8[:, None, :] * (I - 16.0 * S[:, None, :]))
+        else:                                                     # vecdotq.cuh:94-126: -16 through the fp16 raw sum
+            y = np.einsum("nb,mnb->mn", d, d8[:, None, :] * I - 16.0 * s8[:, None, :])
+    elif qtype in (Q6_K, Q3_K, IQ4_XS):
         sc = w["sc"].astype(np.float64)
         t = (I * sc[None] * d8g[:, None, :]).reshape(m, -1, k // blk, gpb).sum(-1)
         y = (t * d[None]).sum(-1)
@@ -333,12 +425,12 @@ def mul_mat(wire: np.ndarray, qtype: int, x: np.ndarray, semantics: str = "mmvq"
         sc = (0.5 + w["sc"].astype(np.float64)) * 0.5
         t = (I * sc[None] * d8g[:, None, :]).reshape(m, -1, k // blk, gpb).sum(-1)
         y = (t * d[None]).sum(-1)
-    elif qtype in (Q2_K, Q4_K):
+    elif qtype in (Q2_K, Q4_K, Q5_K):
         sc = w["sc"].astype(np.float64)
         mn = w["mn"].astype(np.float64)
         dmin = h2d(w["dmin"])
         td = (I * sc[None] * d8g[:, None, :]).reshape(m, -1, k // blk, gpb).sum(-1)
-        if qtype == Q4_K and semantics == "mmq":
+        if qtype in (Q4_K, Q5_K) and semantics == "mmq":
             tm = (mn[None] * s8[:, None, :]).reshape(m, -1, k // blk, gpb).sum(-1)
         else:
             tm = (mn[None] * (S * d8g)[:, None, :]).reshape(m, -1, k // blk, gpb).sum(-1)
@@ -368,9 +460,13 @@ def dequantize_f32(wire: np.ndarray, qtype: int, iq3s_top: int = 62) -> np.ndarr
     d = np.repeat(w["d"].astype(np.float32), blk, axis=1)
     if qtype == Q4_0:
         return d * (q - np.float32(8))
-    if qtype == Q8_0:
+    if qtype == Q5_0:
+        return d * (q - np.float32(16))
+    if qtype in (Q4_1, Q5_1):
+        return d * q + np.repeat(w["m"].astype(np.float32), blk, axis=1)
+    if qtype in (Q8_0, IQ4_NL):
         return d * q
-    if qtype == Q6_K:
+    if qtype in (Q6_K, Q3_K, IQ4_XS):
         sc = np.repeat(w["sc"].astype(np.float32), grp, axis=1)
         return (d * sc) * q
     if qtype == IQ3_S:
@@ -407,6 +503,26 @@ def dequantize(wire: np.ndarray, qtype: int, dtype: str = "f16", half_fma: int =
     d = np.repeat(w["d"], blk, axis=1)                      # fp16
     if qtype == Q4_0:
         v = hmul(hsub(f2h(q), np.float16(8)), d)            # dequantize.cuh:10-15
+    elif qtype == Q5_0:
+        v = hmul(hsub(f2h(q), np.float16(16)), d)           # dequantize.cuh:35-50
+    elif qtype in (Q4_1, Q5_1):                             # dequantize.cuh:18-33, 52-67: hmul2 then hadd2
+        mm = np.repeat(w["m"], blk, axis=1)
+        v = f2h(h2d(f2h(q)) * h2d(d) + h2d(mm)) if half_fma else f2h(h2d(hmul(f2h(q), d)) + h2d(mm))
+    elif qtype == Q3_K:                                     # dequantize.cuh:143-151
+        sc = np.repeat(w["sc"], grp, axis=1)
+        v = hmul(hmul(d, f2h(sc)), f2h(q))
+    elif qtype == Q5_K:                                     # dequantize.cuh:198-230
+        sc = np.repeat(w["sc"], grp, axis=1)
+        mn = np.repeat(w["mn"], grp, axis=1)
+        dmin = np.repeat(w["dmin"], blk, axis=1)
+        d1 = hmul(d, f2h(sc))
+        m1 = hmul(dmin, f2h(mn))
+        v = hfma_sub(d1, f2h(q), m1) if half_fma else hsub(hmul(d1, f2h(q)), m1)
+    elif qtype in (IQ4_NL, IQ4_XS):                         # dequantize.cuh:401-437: fp32, then conversion to dst
+        df = d.astype(np.float32)
+        if qtype == IQ4_XS:
+            df = (df * np.repeat(w["sc"], grp, axis=1).astype(np.float32)).astype(np.float32)
+        return round_to_dtype((df * q.astype(np.float32)).astype(np.float32), dtype)
     elif qtype == Q8_0:
         v = hmul(f2h(q), d)                                 # dequantize.cuh:74-77
     elif qtype == Q2_K:

@@ -121,35 +121,38 @@ def test_torch_extension_registers_reference_schemas():
     assert hasattr(torch.ops._C_gguf, "ggml_moe_a8") and hasattr(torch.ops._C_gguf, "ggml_moe_a8_vec")
 
 
-@pytest.mark.parametrize("rowbytes", [18 * 3, 34 * 5, 210 * 20, 110 * 8, 144 * 20, 84 * 7, 210])
+@pytest.mark.parametrize("rowbytes", [18 * 3, 34 * 5, 210 * 20, 110 * 8, 144 * 20, 84 * 7, 210, 22, 136 * 3])
 @pytest.mark.parametrize("n", [1, 2, 7, 8, 9, 33])
-def test_streaming_kernels_never_read_past_the_tensor(rowbytes, n):
-    """Host arithmetic of the bulk-copy windows (the kernels call the same function): for tensors whose byte size is
-    not a multiple of 16 no bulk range or plain-load tail may end beyond base + n * rowbytes, the bulk range stays
-    16-byte aligned, and bulk + tail together cover the wanted bytes."""
+def test_streaming_kernels_never_read_outside_the_tensor(rowbytes, n):
+    """Host arithmetic of the dispatch and of the bulk-copy windows (the kernels call the same functions): the
+    streaming kernels get only rows whose total size is a multiple of 16 bytes, at most 7 rows are left to the general
+    kernel, and no 16-byte rounded window of whole rows or of row segments leaves [base, base + n * rowbytes)."""
     base = 0x7F0000001000
     end = base + n * rowbytes
+    ns, _, _ = capi.copy_window(base, n, rowbytes, 0, 1)
+    assert 0 <= n - ns <= 7 and (ns * rowbytes) % 16 == 0
+    assert ns == n or ((ns + 1) * rowbytes) % 16 != 0 or ns + 1 > n
     cases = []
     for rows in (1, 2, 8, 16):
-        for a in range(0, n, rows):
-            cases.append((a, min(a + rows, n), 0, 0))
+        for a in range(0, ns, rows):
+            cases.append((a, min(a + rows, ns), 0, 0))
     seg = max(2, (rowbytes // 4) // 2 * 2)
-    for r in range(n):
+    for r in range(ns):
         for off in range(0, rowbytes, seg):
             cases.append((r, r + 1, off, min(seg, rowbytes - off)))
     for a, b, off, ln in cases:
-        start, bulk, tail = capi.copy_window(base, n, rowbytes, a, b, off, ln)
+        _, start, bulk = capi.copy_window(base, n, rowbytes, a, b, off, ln)
         ga = base + a * rowbytes + off
         ge = ga + ln if ln else base + b * rowbytes
-        assert start % 16 == 0 and bulk % 16 == 0 and tail < 16 and tail % 2 == 0
-        assert base <= start <= ga
-        assert start + bulk + tail >= ge and start + bulk <= end and start + bulk + tail <= end
-        if tail:
-            assert start + bulk + tail == ge
+        assert start % 16 == 0 and bulk % 16 == 0 and bulk > 0
+        assert base <= start <= ga and start + bulk >= ge and start + bulk <= end
+    # rows beyond the streamed part have no window
+    if ns < n:
+        assert capi.copy_window(base, n, rowbytes, ns, n)[1:] == (0, 0)
 
 
 def test_copy_window_rejects_bad_arguments():
     with pytest.raises(capi.KqError):
-        capi.copy_window(4096, 4, 144, 3, 5)
+        capi.copy_window(4096 + 2, 4, 144, 0, 1)
     with pytest.raises(capi.KqError):
         capi.copy_window(4096, 4, 144, 0, 1, 100, 80)

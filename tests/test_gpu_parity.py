@@ -190,7 +190,10 @@ def test_in_kernel_quantization_equals_quantizer_launch(qt, n, k, m, dt):
         capi.set_option("fuse_q8", 1)
         capi.set_option("gemv_impl", 0)
     assert torch.equal(y1, y0)
-    assert plain_launches == fused_launches + 1
+    if wt.numel() % 16 == 0:
+        assert plain_launches == fused_launches + 1
+    else:   # a tensor that ends inside a 16-byte unit leaves its last rows to the general kernel, which needs the quantizer
+        assert plain_launches == fused_launches
     assert rel_l2(to_np(y1), O.mul_mat(w, qt, x, "mmvq")) < TIGHT
 
 
