@@ -14,7 +14,8 @@
  *
  * Weight tensors are GGUF wire bytes: uint8 [n, k/blk * block_bytes], rows contiguous, blocks
  * consecutive along k (vllm_gguf_plugin/csrc/gguf/ggml-common.h:20-150).  Supported GGML type ids:
- * 2 (Q4_0), 8 (Q8_0), 10 (Q2_K), 12 (Q4_K), 14 (Q6_K), 21 (IQ3_S); any other id is KQ_EUNSUPPORTED.
+ * 2 (Q4_0), 8 (Q8_0), 10 (Q2_K), 12 (Q4_K), 14 (Q6_K), 21 (IQ3_S) on every path, and 3 (Q4_1), 6 (Q5_0), 7 (Q5_1),
+ * 11 (Q3_K), 13 (Q5_K), 20 (IQ4_NL), 23 (IQ4_XS) on the general paths; any other id is KQ_EUNSUPPORTED.
  */
 #ifndef KQ_GGUF_H
 #define KQ_GGUF_H
@@ -45,6 +46,15 @@ extern "C" {
 #define KQ_TYPE_Q4_K 12
 #define KQ_TYPE_Q6_K 14
 #define KQ_TYPE_IQ3_S 21
+/* the other formats of real mixed-precision checkpoints: served by the general kernels (row-streaming / dp4a GEMV at
+ * every m, dequantize), not by the tensor-core paths */
+#define KQ_TYPE_Q4_1 3
+#define KQ_TYPE_Q5_0 6
+#define KQ_TYPE_Q5_1 7
+#define KQ_TYPE_Q3_K 11
+#define KQ_TYPE_Q5_K 13
+#define KQ_TYPE_IQ4_NL 20
+#define KQ_TYPE_IQ4_XS 23
 
 /* Thread-local text of the last error returned on this thread ("" if none). */
 const char* kq_last_error(void);
@@ -186,7 +196,8 @@ int kq_debug_copy_window(uint64_t base, int64_t n, int64_t rowbytes, int64_t row
 
 /* Runtime knobs for tests and profiling (process-wide, not thread-safe against concurrent launches):
  *   "gemv_impl"   0 = choose by shape (default), 1 = general dp4a kernel, 3 = row-streaming dp4a kernel,
- *                 4 = the same without the specialised Q4_K / Q6_K consumers, 6 = shared-stage int8-mma kernel;
+ *                 4 = the same without the specialised Q4_K / Q6_K consumers, 6 = shared-stage int8-mma kernel,
+ *                 7 = register-resident int8-mma kernel;
  *                 a forced kernel that does not cover the type or shape returns KQ_EUNSUPPORTED
  *   "tc_min_m"    smallest m that the shared-stage int8-mma kernel takes in mode 0 (default 3)
  *   "pdl"         0 = plain launches; p > 0 (default 2) = the quantizer and the streaming kernels are launched
@@ -196,6 +207,8 @@ int kq_debug_copy_window(uint64_t base, int64_t n, int64_t rowbytes, int64_t row
  *   "fuse_q8"     1 (default) = calls of 1-2 tokens on large matrices skip the quantizer launch: the row-streaming
  *                 kernel quantizes the activations itself, bit-identically, while its first weight stages are in
  *                 flight; 2 = wherever that kernel runs (tests); 0 = always launch the quantizer
+ *   "kres"        1 (default) = passes of 3..8 tokens use the register-resident kernel where it covers the type and
+ *                 shape, 2 = passes of 9..16 tokens too, 0 = never (the shared-stage kernel instead)
  *   "gemm_min_m"  smallest m that goes to the tcgen05 GEMM (default 81: m <= 80 keeps exact integer dots)
  *   "half_fma"    1 = K-quant dequantize contracts fp16 mul+sub into one fma (default), 0 = two roundings
  * Returns KQ_EINVAL for an unknown name. */

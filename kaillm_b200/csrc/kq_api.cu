@@ -22,7 +22,7 @@ int cuda_fail(cudaError_t e, const char* what) {
 }
 
 Options& options() {
-  static Options o = {0, 3, 81, 2, 1, 0, 0, 1};
+  static Options o = {0, 3, 81, 2, 1, 0, 0, 1, 1};
   return o;
 }
 
@@ -50,7 +50,8 @@ static int validate(const char* fn, const void* W, int type, int64_t n, int64_t 
                     int64_t m, int64_t stride_x, const void* scratch, size_t scratch_bytes, Problem& p,
                     bool need_w = true, bool need_x = true) {
   if (!type_geometry(type, &p.blk, &p.bytes)) {
-    set_error("%s: GGML type %d is not supported (supported: 2 Q4_0, 8 Q8_0, 10 Q2_K, 12 Q4_K, 14 Q6_K, 21 IQ3_S)", fn, type);
+    set_error("%s: GGML type %d is not supported (supported: 2 Q4_0, 3 Q4_1, 6 Q5_0, 7 Q5_1, 8 Q8_0, 10 Q2_K, 11 Q3_K, 12 Q4_K, "
+              "13 Q5_K, 14 Q6_K, 20 IQ4_NL, 21 IQ3_S, 23 IQ4_XS)", fn, type);
     return KQ_EUNSUPPORTED;
   }
   if (need_x && !dtype_ok(x_dtype)) { set_error("%s: unsupported activation dtype %d", fn, x_dtype); return KQ_EUNSUPPORTED; }
@@ -82,7 +83,10 @@ static int mul_mat(const char* fn, bool mmq, const void* W, int type, int64_t n,
     if (m < options().gemm_min_m) P.xh = nullptr;
     return launch_quantize(x, x_dtype, m, k, stride_x, &P, nullptr, p.L.kpad, (cudaStream_t)stream);
   }
-  if (mmq && type == KQ_TYPE_IQ3_S) { set_error("%s: IQ3_S has no MMQ kernel (use dequantize + matmul or mul_mat_vec)", fn); return KQ_EUNSUPPORTED; }
+  if (mmq && (type == KQ_TYPE_IQ3_S || type == KQ_TYPE_IQ4_NL || type == KQ_TYPE_IQ4_XS)) {
+    set_error("%s: the i-matrix formats have no MMQ kernel (use dequantize + matmul or mul_mat_vec)", fn);
+    return KQ_EUNSUPPORTED;
+  }
   if (!dtype_ok(y_dtype)) { set_error("%s: unsupported output dtype %d", fn, y_dtype); return KQ_EUNSUPPORTED; }
   if (!y || stride_y < n) { set_error("%s: bad output (null or stride_y < n)", fn); return KQ_EINVAL; }
   if ((uintptr_t)y % dtype_size(y_dtype)) { set_error("%s: misaligned output pointer", fn); return KQ_EINVAL; }
@@ -117,10 +121,6 @@ static int mul_mat(const char* fn, bool mmq, const void* W, int type, int64_t n,
       if (rc) return rc;
     }
     if (ns == n) return KQ_OK;
-    if (impl < 2)
-      return launch_gemv_dp4a((const uint8_t*)W + ns * p.rowbytes, type, n - ns, k, P.ds, P.qs, p.L.kpad, m,
-                              (uint8_t*)y + ns * dtype_size(y_dtype), y_dtype, stride_y, mmq, nullptr, nullptr, st);
-    if (ns == 0) { set_error("%s: the streaming GEMV does not cover this shape/alignment", fn); return KQ_EUNSUPPORTED; }
     return launch_gemv_dp4a((const uint8_t*)W + ns * p.rowbytes, type, n - ns, k, P.ds, P.qs, p.L.kpad, m,
                             (uint8_t*)y + ns * dtype_size(y_dtype), y_dtype, stride_y, mmq, nullptr, nullptr, st);
   }
@@ -321,6 +321,7 @@ int kq_set_option(const char* name, int value) {
   if (name && !strcmp(name, "tile_segments")) { options().tile_segments = value != 0; return KQ_OK; }
   if (name && !strcmp(name, "fuse_q8")) { options().fuse_q8 = value < 0 ? 0 : (value > 2 ? 2 : value); return KQ_OK; }
   if (name && !strcmp(name, "pdl")) { options().pdl = value < 0 ? 0 : value; return KQ_OK; }
+  if (name && !strcmp(name, "kres")) { options().kres = value < 0 ? 0 : (value > 2 ? 2 : value); return KQ_OK; }
   set_error("kq_set_option: unknown option");
   return KQ_EINVAL;
 }
@@ -333,6 +334,7 @@ int kq_get_option(const char* name, int* value) {
   if (name && value && !strcmp(name, "tile_segments")) { *value = options().tile_segments; return KQ_OK; }
   if (name && value && !strcmp(name, "fuse_q8")) { *value = options().fuse_q8; return KQ_OK; }
   if (name && value && !strcmp(name, "pdl")) { *value = options().pdl; return KQ_OK; }
+  if (name && value && !strcmp(name, "kres")) { *value = options().kres; return KQ_OK; }
   if (name && value && !strcmp(name, "launch_count")) { *value = (int)(options().launches & 0x7fffffff); return KQ_OK; }
   set_error("kq_get_option: unknown option");
   return KQ_EINVAL;

@@ -46,6 +46,8 @@ struct Options {
   long long launches;  // kernels launched by this library so far (host-side count)
   int tile_segments;   // 1: the tile GEMV fetches row segments even when its K slice is the whole row
   int fuse_q8;         // 1: calls of 1-2 tokens quantize the activations inside the row-streaming kernel (no quantizer launch)
+  int kres;            // 1: passes of 3..8 tokens use the register-resident kernel where it covers the type and shape;
+                       // 2: passes of 9..16 tokens as well (slower than the shared-stage kernel today); 0: never
 };
 Options& options();
 
@@ -57,6 +59,28 @@ template <> struct Fmt<KQ_TYPE_Q2_K> { static constexpr int BLK = 256, BYTES = 8
 template <> struct Fmt<KQ_TYPE_Q4_K> { static constexpr int BLK = 256, BYTES = 144, GROUP = 32; static constexpr bool HAS_MIN = true; };
 template <> struct Fmt<KQ_TYPE_Q6_K> { static constexpr int BLK = 256, BYTES = 210, GROUP = 16; static constexpr bool HAS_MIN = false; };
 template <> struct Fmt<KQ_TYPE_IQ3_S> { static constexpr int BLK = 256, BYTES = 110, GROUP = 32; static constexpr bool HAS_MIN = false; };
+template <> struct Fmt<KQ_TYPE_Q4_1> { static constexpr int BLK = 32, BYTES = 20, GROUP = 32; static constexpr bool HAS_MIN = true; };
+template <> struct Fmt<KQ_TYPE_Q5_0> { static constexpr int BLK = 32, BYTES = 22, GROUP = 32; static constexpr bool HAS_MIN = true; };
+template <> struct Fmt<KQ_TYPE_Q5_1> { static constexpr int BLK = 32, BYTES = 24, GROUP = 32; static constexpr bool HAS_MIN = true; };
+template <> struct Fmt<KQ_TYPE_Q3_K> { static constexpr int BLK = 256, BYTES = 110, GROUP = 16; static constexpr bool HAS_MIN = false; };
+template <> struct Fmt<KQ_TYPE_Q5_K> { static constexpr int BLK = 256, BYTES = 176, GROUP = 32; static constexpr bool HAS_MIN = true; };
+template <> struct Fmt<KQ_TYPE_IQ4_NL> { static constexpr int BLK = 32, BYTES = 18, GROUP = 32; static constexpr bool HAS_MIN = false; };
+template <> struct Fmt<KQ_TYPE_IQ4_XS> { static constexpr int BLK = 256, BYTES = 136, GROUP = 32; static constexpr bool HAS_MIN = false; };
+// Q4_1 / Q5_1: the reference forms d * d8 and m * s8 in fp16 (__hmul2) before using them in fp32
+// (vecdotq.cuh:71-92, 131-160); wb carries -m, z is the raw fp16 block sum
+template <int QT> struct HalfProd { static constexpr bool value = QT == KQ_TYPE_Q4_1 || QT == KQ_TYPE_Q5_1; };
+// min term from the fp16 RAW block sum (true) or from d8 * (sum of the codes) (false), per format and flavour:
+// Q4_0 always raw (vecdotq.cuh:46-66); Q4_K / Q5_K raw in the MMQ flavour only (:353-379, :405-445); Q5_0 raw in the
+// MMVQ flavour (:94-126) and exact in MMQ (its tile loader subtracts 16 from the codes)
+template <int QT, bool MMQ> struct RawSum {
+  static constexpr bool value = QT == KQ_TYPE_Q4_0 || HalfProd<QT>::value ||
+                                ((QT == KQ_TYPE_Q4_K || QT == KQ_TYPE_Q5_K) && MMQ) || (QT == KQ_TYPE_Q5_0 && !MMQ);
+};
+// the six formats every kernel covers; the others go through the general kernels only
+inline bool type_is_core(int type) {
+  return type == KQ_TYPE_Q4_0 || type == KQ_TYPE_Q8_0 || type == KQ_TYPE_Q2_K || type == KQ_TYPE_Q4_K ||
+         type == KQ_TYPE_Q6_K || type == KQ_TYPE_IQ3_S;
+}
 
 inline bool type_geometry(int type, int* blk, int* bytes) {
   switch (type) {
@@ -66,10 +90,17 @@ inline bool type_geometry(int type, int* blk, int* bytes) {
     case KQ_TYPE_Q4_K: *blk = 256; *bytes = 144; return true;
     case KQ_TYPE_Q6_K: *blk = 256; *bytes = 210; return true;
     case KQ_TYPE_IQ3_S: *blk = 256; *bytes = 110; return true;
+    case KQ_TYPE_Q4_1: *blk = 32; *bytes = 20; return true;
+    case KQ_TYPE_Q5_0: *blk = 32; *bytes = 22; return true;
+    case KQ_TYPE_Q5_1: *blk = 32; *bytes = 24; return true;
+    case KQ_TYPE_Q3_K: *blk = 256; *bytes = 110; return true;
+    case KQ_TYPE_Q5_K: *blk = 256; *bytes = 176; return true;
+    case KQ_TYPE_IQ4_NL: *blk = 32; *bytes = 18; return true;
+    case KQ_TYPE_IQ4_XS: *blk = 256; *bytes = 136; return true;
     default: return false;
   }
 }
-inline int type_group(int type) { return (type == KQ_TYPE_Q2_K || type == KQ_TYPE_Q6_K) ? 16 : 32; }
+inline int type_group(int type) { return (type == KQ_TYPE_Q2_K || type == KQ_TYPE_Q6_K || type == KQ_TYPE_Q3_K) ? 16 : 32; }
 
 // ------------------------------------------------------------------ quantized activation scratch
 // Activations are quantized to q8_1 (gguf_kernel.cu:32-69 of the reference) into a split layout:
@@ -184,6 +215,10 @@ bool gemv_tile_supported(const void* W, int type, int64_t n, int64_t k, int mtok
 int gemv_tile_splits(int type, int64_t n, int64_t k, int mtok);
 int launch_gemv_tile(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m0, int mcount, void* y,
                      int y_dtype, int64_t stride_y, bool mmq, cudaStream_t st);
+bool gemv_kres_supported(const void* W, int type, int64_t n, int64_t k, int mtok);
+int gemv_kres_splits(int type, int64_t n, int64_t k, int mtok);
+int launch_gemv_kres(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m0, int mcount, void* y,
+                     int y_dtype, int64_t stride_y, bool mmq, cudaStream_t st);
 int launch_p2p_allgather(const void* src, size_t bytes, void* const* peer_dst, uint32_t* const* peer_flags,
                          uint32_t* epoch, uint32_t* done, int slot, int rank, int world, int* status, cudaStream_t st);
 bool gemm_tc_supported(const void* W, int type, int64_t n, int64_t k);
@@ -256,6 +291,24 @@ __device__ __forceinline__ uint32_t iq3s_expand(uint32_t code, uint32_t top) {
     r |= b << (8 * j);
   }
   return r;
+}
+// per-byte (v - 4) for bytes in 0..7, no carries between bytes
+__device__ __forceinline__ uint32_t sub4_bytes(uint32_t v) {
+  return ((v | 0x80808080u) - 0x04040404u) ^ 0x80808080u;
+}
+// four 4-bit indices (low nibble of each byte of x) -> the four int8 code values of IQ4_NL / IQ4_XS
+// (kvalues_iq4nl, ggml-common.h:1060: -127 -104 -83 -65 -49 -35 -22 -10 1 13 25 38 53 69 89 113), by two byte permutes
+// over the table halves and a per-byte select on bit 3
+__device__ __forceinline__ uint32_t iq4nl_lookup(uint32_t x) {
+  const uint32_t sel = (x & 0x7u) | ((x >> 4) & 0x70u) | ((x >> 8) & 0x700u) | ((x >> 12) & 0x7000u);
+  const uint32_t lo = __byte_perm(0xBFAD9881u, 0xF6EADDCFu, sel);   // entries 0..7
+  const uint32_t hi = __byte_perm(0x26190D01u, 0x71594535u, sel);   // entries 8..15
+  const uint32_t m = ((x >> 3) & 0x01010101u) * 0xFFu;
+  return (lo & ~m) | (hi & m);
+}
+// bits 0..3 of `nib` -> 0x10 in byte j if bit j is set (the fifth bit of four 5-bit codes)
+__device__ __forceinline__ uint32_t nibble_to_bit4(uint32_t nib) {
+  return ((nib * 0x00204081u) & 0x01010101u) << 4;
 }
 #ifndef KQ_IQ3S_TOP
 #define KQ_IQ3S_TOP 62  // top magnitude byte of the codebook as the reference's CUDA table has it
@@ -347,6 +400,87 @@ __device__ __forceinline__ void decode_subblock(const uint8_t* __restrict__ row,
     }
     const uint32_t s4 = (b[106 + (ib >> 1)] >> (4 * (ib & 1))) & 15u;
     o.wa[0] = d * (0.5f + (float)s4) * 0.5f; o.wb[0] = 0.f; o.wa[1] = 0.f; o.wb[1] = 0.f;
+  } else if constexpr (QT == KQ_TYPE_Q4_1) {            // {half d, half m, qs[16]}: w = d*q + m
+    const uint8_t* b = row + (size_t)sb * 20;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t w = ld_u32(b + 4 + 4 * i);
+      o.v[i] = w & 0x0F0F0F0Fu;
+      o.v[i + 4] = (w >> 4) & 0x0F0F0F0Fu;
+    }
+    o.wa[0] = ld_h(b); o.wb[0] = -ld_h(b + 2); o.wa[1] = 0.f; o.wb[1] = 0.f;
+  } else if constexpr (QT == KQ_TYPE_Q5_0 || QT == KQ_TYPE_Q5_1) {   // {half d, [half m,] qh[4], qs[16]}: 5-bit codes
+    constexpr int HDR = QT == KQ_TYPE_Q5_0 ? 2 : 4;
+    const uint8_t* b = row + (size_t)sb * (QT == KQ_TYPE_Q5_0 ? 22 : 24);
+    const uint32_t qh = ld_u16x2(b + HDR);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t w = ld_u16x2(b + HDR + 4 + 4 * i);
+      o.v[i] = (w & 0x0F0F0F0Fu) | nibble_to_bit4((qh >> (4 * i)) & 15u);
+      o.v[i + 4] = ((w >> 4) & 0x0F0F0F0Fu) | nibble_to_bit4((qh >> (16 + 4 * i)) & 15u);
+    }
+    const float d = ld_h(b);
+    if constexpr (QT == KQ_TYPE_Q5_0) { o.wa[0] = d; o.wb[0] = 16.0f * d; }
+    else { o.wa[0] = d; o.wb[0] = -ld_h(b + 2); }
+    o.wa[1] = 0.f; o.wb[1] = 0.f;
+  } else if constexpr (QT == KQ_TYPE_Q3_K) {             // {hmask[32], qs[64], scales[12], half d}: 3-bit codes - 4
+    const uint8_t* b = row + (size_t)(sb >> 3) * 110;
+    const int j = sb & 7, n = j >> 2, jj = j & 3;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t lo = (ld_u16x2(b + 32 + 32 * n + 4 * i) >> (2 * jj)) & 0x03030303u;
+      const uint32_t hb = (ld_u16x2(b + 4 * i) >> (4 * n + jj)) & 0x01010101u;
+      o.v[i] = sub4_bytes(lo | (hb << 2));
+    }
+    const float d = ld_h(b + 108);
+    const uint8_t* sc = b + 96;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {                        // 6-bit scales of the two 16-weight groups (dequantize.cuh:139-142)
+      const int is = 2 * j + h;
+      int us;
+      if (is < 4) us = (sc[is] & 15) | (((sc[is + 8] >> 0) & 3) << 4);
+      else if (is < 8) us = (sc[is] & 15) | (((sc[is + 4] >> 2) & 3) << 4);
+      else if (is < 12) us = (sc[is - 8] >> 4) | (((sc[is] >> 4) & 3) << 4);
+      else us = (sc[is - 8] >> 4) | (((sc[is - 4] >> 6) & 3) << 4);
+      o.wa[h] = d * (float)(us - 32);
+      o.wb[h] = 0.f;
+    }
+  } else if constexpr (QT == KQ_TYPE_Q5_K) {             // {half d, half dmin, scales[12], qh[32], qs[128]}
+    const uint8_t* b = row + (size_t)(sb >> 3) * 176;
+    const int j = sb & 7, il = j >> 1, e = j & 1;
+    const float d = ld_h(b), dmin = ld_h(b + 2);
+    const uint8_t* q = b + 4;
+    uint32_t sc, mn;
+    if (j < 4) { sc = q[j] & 63u; mn = q[j + 4] & 63u; }
+    else { sc = (q[j + 4] & 15u) | ((q[j - 4] >> 6) << 4); mn = (q[j + 4] >> 4) | ((q[j] >> 6) << 4); }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t lo = (ld_u32(b + 48 + 32 * il + 4 * i) >> (4 * e)) & 0x0F0F0F0Fu;
+      const uint32_t hb = (ld_u32(b + 16 + 4 * i) >> j) & 0x01010101u;
+      o.v[i] = lo | (hb << 4);
+    }
+    o.wa[0] = d * (float)sc; o.wb[0] = dmin * (float)mn; o.wa[1] = 0.f; o.wb[1] = 0.f;
+  } else if constexpr (QT == KQ_TYPE_IQ4_NL) {           // {half d, qs[16]}: 4-bit indices into 16 code values
+    const uint8_t* b = row + (size_t)sb * 18;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t w = ld_u16x2(b + 2 + 4 * i);
+      o.v[i] = iq4nl_lookup(w & 0x0F0F0F0Fu);
+      o.v[i + 4] = iq4nl_lookup((w >> 4) & 0x0F0F0F0Fu);
+    }
+    o.wa[0] = ld_h(b); o.wb[0] = 0.f; o.wa[1] = 0.f; o.wb[1] = 0.f;
+  } else if constexpr (QT == KQ_TYPE_IQ4_XS) {           // {half d, u16 scales_h, scales_l[4], qs[128]}
+    const uint8_t* b = row + (size_t)(sb >> 3) * 136;
+    const int ib = sb & 7;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t w = ld_u32(b + 8 + 16 * ib + 4 * i);
+      o.v[i] = iq4nl_lookup(w & 0x0F0F0F0Fu);
+      o.v[i + 4] = iq4nl_lookup((w >> 4) & 0x0F0F0F0Fu);
+    }
+    const uint32_t sh = *reinterpret_cast<const uint16_t*>(b + 2);
+    const int ls = (int)(((b[4 + (ib >> 1)] >> (4 * (ib & 1))) & 15u) | (((sh >> (2 * ib)) & 3u) << 4));
+    o.wa[0] = ld_h(b) * (float)(ls - 32); o.wb[0] = 0.f; o.wa[1] = 0.f; o.wb[1] = 0.f;
   }
 }
 #endif  // __CUDACC__

@@ -112,6 +112,81 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restri
       const float mag = __fmul_rn(d, (float)gb);
       res[j] = from_f32<OutT>((signs >> j) & 1u ? -mag : mag);
     }
+  } else if constexpr (QT == KQ_TYPE_Q4_1 || QT == KQ_TYPE_Q5_1 || QT == KQ_TYPE_Q5_0) {
+    // dequantize.cuh:18-67: codes as fp16, then (q - 16) * d for Q5_0, q * d + m for Q4_1 / Q5_1 (the multiply-add pair
+    // is contracted like the multiply-subtract of the K-quants when `fma` is set)
+    constexpr int HDR = QT == KQ_TYPE_Q5_0 ? 2 : 4;
+    const __half d = __ushort_as_half(*reinterpret_cast<const uint16_t*>(b));
+    const __half m = __ushort_as_half(*reinterpret_cast<const uint16_t*>(b + 2));   // Q4_1 / Q5_1 only
+    uint32_t qh = 0;
+    if constexpr (QT != KQ_TYPE_Q4_1) qh = (uint32_t)b[HDR] | ((uint32_t)b[HDR + 1] << 8) | ((uint32_t)b[HDR + 2] << 16) | ((uint32_t)b[HDR + 3] << 24);
+    const uint8_t* qs = b + HDR + (QT == KQ_TYPE_Q4_1 ? 0 : 4);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int e = r0 + j;
+      int q = e < 16 ? (qs[e] & 15) : (qs[e - 16] >> 4);
+      if constexpr (QT != KQ_TYPE_Q4_1) q |= (int)((qh >> e) & 1u) << 4;
+      __half v;
+      if constexpr (QT == KQ_TYPE_Q5_0) v = __hmul_rn(__hsub_rn(__int2half_rn(q), __float2half_rn(16.0f)), d);
+      else v = fma ? __hfma(__int2half_rn(q), d, m) : __hadd_rn(__hmul_rn(__int2half_rn(q), d), m);
+      res[j] = half_to_out<OutT>(v);
+    }
+  } else if constexpr (QT == KQ_TYPE_Q3_K) {             // dequantize.cuh:123-152
+    const __half dall = __ushort_as_half(*reinterpret_cast<const uint16_t*>(b + 108));
+    const int n = r0 >> 7, jq = (r0 >> 5) & 3, l0 = r0 & 31;
+    const int is = 8 * n + 2 * jq + (l0 >> 4);
+    const uint8_t* sc = b + 96;
+    int us;
+    if (is < 4) us = (sc[is] & 15) | (((sc[is + 8] >> 0) & 3) << 4);
+    else if (is < 8) us = (sc[is] & 15) | (((sc[is + 4] >> 2) & 3) << 4);
+    else if (is < 12) us = (sc[is - 8] >> 4) | (((sc[is] >> 4) & 3) << 4);
+    else us = (sc[is - 8] >> 4) | (((sc[is - 4] >> 6) & 3) << 4);
+    const __half dl = __hmul_rn(dall, __int2half_rn(us - 32));
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int l = l0 + j;
+      const int q = ((b[32 + 32 * n + l] >> (2 * jq)) & 3) - (((b[l] >> (4 * n + jq)) & 1) ? 0 : 4);
+      res[j] = half_to_out<OutT>(__hmul_rn(dl, __int2half_rn(q)));
+    }
+  } else if constexpr (QT == KQ_TYPE_Q5_K) {             // dequantize.cuh:198-230
+    const __half dall = __ushort_as_half(*reinterpret_cast<const uint16_t*>(b));
+    const __half dmin = __ushort_as_half(*reinterpret_cast<const uint16_t*>(b + 2));
+    const int il = r0 >> 6, hi = (r0 >> 5) & 1, l0 = r0 & 31;
+    const int jj = 2 * il + hi;
+    const uint8_t* q = b + 4;
+    int sc, mn;
+    if (jj < 4) { sc = q[jj] & 63; mn = q[jj + 4] & 63; }
+    else { sc = (q[jj + 4] & 15) | ((q[jj - 4] >> 6) << 4); mn = (q[jj + 4] >> 4) | ((q[jj] >> 6) << 4); }
+    const __half d1 = __hmul_rn(dall, __int2half_rn(sc));
+    const __half m1 = __hmul_rn(dmin, __int2half_rn(mn));
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int byte = b[48 + 32 * il + l0 + j];
+      const int qq = (hi ? (byte >> 4) : (byte & 15)) + (((b[16 + l0 + j] >> jj) & 1) ? 16 : 0);
+      res[j] = half_to_out<OutT>(mul_sub(d1, __int2half_rn(qq), m1, fma));
+    }
+  } else if constexpr (QT == KQ_TYPE_IQ4_NL || QT == KQ_TYPE_IQ4_XS) {   // dequantize.cuh:401-437: fp32 d * code value
+    constexpr int KV[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+    float d = ld_h(b);
+    const uint8_t* qs;
+    int e0b;                                             // position inside the 32-weight sub-block
+    if constexpr (QT == KQ_TYPE_IQ4_NL) { qs = b + 2; e0b = r0; }
+    else {
+      const int ib = r0 >> 5;
+      const uint32_t sh = *reinterpret_cast<const uint16_t*>(b + 2);
+      const int ls = (int)(((b[4 + (ib >> 1)] >> (4 * (ib & 1))) & 15u) | (((sh >> (2 * ib)) & 3u) << 4));
+      d = __fmul_rn(d, (float)(ls - 32));
+      qs = b + 8 + 16 * ib; e0b = r0 & 31;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int e = e0b + j;
+      const int idx = e < 16 ? (qs[e] & 15) : (qs[e - 16] >> 4);
+      int kv = KV[0];
+#pragma unroll
+      for (int i = 1; i < 16; ++i) kv = idx == i ? KV[i] : kv;
+      res[j] = from_f32<OutT>(__fmul_rn(d, (float)kv));
+    }
   }
   // 8 outputs = 16 (half/bf16) or 32 (float) contiguous, aligned bytes
   if constexpr (sizeof(OutT) == 2) {
@@ -147,6 +222,13 @@ int launch_dequantize(const void* W, int type, int64_t count, void* out, int out
     case KQ_TYPE_Q4_K: return run<KQ_TYPE_Q4_K>(W, count, out, out_dtype, fma, st);
     case KQ_TYPE_Q6_K: return run<KQ_TYPE_Q6_K>(W, count, out, out_dtype, fma, st);
     case KQ_TYPE_IQ3_S: return run<KQ_TYPE_IQ3_S>(W, count, out, out_dtype, fma, st);
+    case KQ_TYPE_Q4_1: return run<KQ_TYPE_Q4_1>(W, count, out, out_dtype, fma, st);
+    case KQ_TYPE_Q5_0: return run<KQ_TYPE_Q5_0>(W, count, out, out_dtype, fma, st);
+    case KQ_TYPE_Q5_1: return run<KQ_TYPE_Q5_1>(W, count, out, out_dtype, fma, st);
+    case KQ_TYPE_Q3_K: return run<KQ_TYPE_Q3_K>(W, count, out, out_dtype, fma, st);
+    case KQ_TYPE_Q5_K: return run<KQ_TYPE_Q5_K>(W, count, out, out_dtype, fma, st);
+    case KQ_TYPE_IQ4_NL: return run<KQ_TYPE_IQ4_NL>(W, count, out, out_dtype, fma, st);
+    case KQ_TYPE_IQ4_XS: return run<KQ_TYPE_IQ4_XS>(W, count, out, out_dtype, fma, st);
   }
   set_error("unsupported GGML type %d", type);
   return KQ_EUNSUPPORTED;

@@ -600,6 +600,7 @@ int launch_out(const GemmParams& p, const CUtensorMap& map, const CUtensorMap& s
 
 // The tensor-core GEMM needs whole 256-weight K steps and 16-byte aligned Q4_K blocks; everything else is general.
 bool gemm_tc_supported(const void* W, int type, int64_t n, int64_t k) {
+  if (!type_is_core(type)) return false;
   if (k % KSTEP) return false;
   if (type == KQ_TYPE_Q4_K && ((uintptr_t)W % 16)) return false;
   return encode_fn() != nullptr;

@@ -3,7 +3,8 @@
 // Lanes take 32-weight sub-blocks of the row round-robin, decode them to int8 words
 // (decode_subblock) and form the exact integer dots against the q8_1 activation codes with dp4a;
 // the fp32 combine per sub-block follows the reference's vec_dot_* functions
-// (vllm_gguf_plugin/csrc/gguf/vecdotq.cuh:46-66, 165-177, 204-230, 328-379, 447-465, 1649-1672).
+// (vllm_gguf_plugin/csrc/gguf/vecdotq.cuh:46-66, 165-177, 204-230, 328-379, 447-465, 1649-1672; the other formats:
+// 71-160 Q4_1/Q5_0/Q5_1, 269-326 Q3_K, 384-445 Q5_K, 1757-1811 IQ4_NL/IQ4_XS).
 // Plain global loads, so any row stride / alignment the wire format allows is accepted; this kernel
 // is the general path and the integer-dot export used by the tests.
 #include "kq_common.cuh"
@@ -55,10 +56,13 @@ gemv_dp4a_kernel(const uint8_t* __restrict__ W, int64_t rowbytes, int n, int nsb
           if (F::HAS_MIN) S[h] = __dp4a(0x01010101, (int)u[i], S[h]);
         }
         float c;
-        if constexpr (NG == 1) {
+        if constexpr (HalfProd<QT>::value) {
+          // d * d8 and m * s8 rounded to fp16 first, as the reference's __hmul2 does (wb holds -m)
+          c = __half2float(__float2half_rn(s.wa[0] * dsf.x)) * (float)I[0] - __half2float(__float2half_rn(s.wb[0] * dsf.y));
+        } else if constexpr (NG == 1) {
           c = s.wa[0] * (dsf.x * (float)I[0]);
           if constexpr (F::HAS_MIN) {
-            const float z = (QT == KQ_TYPE_Q4_0 || (QT == KQ_TYPE_Q4_K && MMQ)) ? dsf.y : dsf.x * (float)S[0];
+            const float z = RawSum<QT, MMQ>::value ? dsf.y : dsf.x * (float)S[0];
             c -= s.wb[0] * z;
           }
         } else {
@@ -148,6 +152,17 @@ int launch_gemv_dp4a(const void* W, int type, int64_t n, int64_t k, const void* 
                  : run_out<KQ_TYPE_Q4_K, false>(w, rb, n, k, ds, qs, kpad, m, y, y_dtype, stride_y, dd, dsum, st);
     case KQ_TYPE_Q6_K: return run_out<KQ_TYPE_Q6_K, false>(w, rb, n, k, ds, qs, kpad, m, y, y_dtype, stride_y, dd, dsum, st);
     case KQ_TYPE_IQ3_S: return run_out<KQ_TYPE_IQ3_S, false>(w, rb, n, k, ds, qs, kpad, m, y, y_dtype, stride_y, dd, dsum, st);
+    case KQ_TYPE_Q4_1: return run_out<KQ_TYPE_Q4_1, false>(w, rb, n, k, ds, qs, kpad, m, y, y_dtype, stride_y, dd, dsum, st);
+    case KQ_TYPE_Q5_0:
+      return mmq ? run_out<KQ_TYPE_Q5_0, true>(w, rb, n, k, ds, qs, kpad, m, y, y_dtype, stride_y, dd, dsum, st)
+                 : run_out<KQ_TYPE_Q5_0, false>(w, rb, n, k, ds, qs, kpad, m, y, y_dtype, stride_y, dd, dsum, st);
+    case KQ_TYPE_Q5_1: return run_out<KQ_TYPE_Q5_1, false>(w, rb, n, k, ds, qs, kpad, m, y, y_dtype, stride_y, dd, dsum, st);
+    case KQ_TYPE_Q3_K: return run_out<KQ_TYPE_Q3_K, false>(w, rb, n, k, ds, qs, kpad, m, y, y_dtype, stride_y, dd, dsum, st);
+    case KQ_TYPE_Q5_K:
+      return mmq ? run_out<KQ_TYPE_Q5_K, true>(w, rb, n, k, ds, qs, kpad, m, y, y_dtype, stride_y, dd, dsum, st)
+                 : run_out<KQ_TYPE_Q5_K, false>(w, rb, n, k, ds, qs, kpad, m, y, y_dtype, stride_y, dd, dsum, st);
+    case KQ_TYPE_IQ4_NL: return run_out<KQ_TYPE_IQ4_NL, false>(w, rb, n, k, ds, qs, kpad, m, y, y_dtype, stride_y, dd, dsum, st);
+    case KQ_TYPE_IQ4_XS: return run_out<KQ_TYPE_IQ4_XS, false>(w, rb, n, k, ds, qs, kpad, m, y, y_dtype, stride_y, dd, dsum, st);
   }
   return KQ_EUNSUPPORTED;
 }

@@ -467,7 +467,10 @@ __global__ void __launch_bounds__(ROW_THREADS, 1) gemv_rows_kernel(const RowPara
           I[hh] = __dp4a((int)s.v[j], (int)u[j], I[hh]);
         }
         float c;
-        if constexpr (NG == 1) {
+        if constexpr (HalfProd<QT>::value) {
+          // d * d8 and m * s8 rounded to fp16 first, as the reference's __hmul2 does (wb holds -m)
+          c = __half2float(__float2half_rn(s.wa[0] * d8)) * (float)I[0] - __half2float(__float2half_rn(s.wb[0] * dsf.y));
+        } else if constexpr (NG == 1) {
           c = s.wa[0] * (d8 * (float)I[0]);
           if constexpr (F::HAS_MIN) c -= s.wb[0] * (zmode == 1 ? dsf.y : sZ[(size_t)t * p.nb32tot + sb]);
         } else {
@@ -501,7 +504,8 @@ struct RowConfig {
 };
 
 int z_per_block(int type) {
-  return (type == KQ_TYPE_Q2_K) ? 2 : ((type == KQ_TYPE_Q4_K || type == KQ_TYPE_Q4_0) ? 1 : 0);
+  if (type == KQ_TYPE_Q2_K) return 2;
+  return (type == KQ_TYPE_Q4_K || type == KQ_TYPE_Q4_0 || type == KQ_TYPE_Q5_K || type == KQ_TYPE_Q5_0) ? 1 : 0;
 }
 
 constexpr int SMEM_LIMIT = 227 * 1024;
@@ -519,11 +523,12 @@ bool make_row_config(int type, int64_t n, int64_t k, int mt, bool pair, RowConfi
   c.rows_per_stage = R;
   c.stage_bytes = (int)((R * rowbytes + 32 + 127) / 128 * 128);
   const int64_t kpad = (k + 511) / 512 * 512;
-  const bool zr = type == KQ_TYPE_Q2_K || type == KQ_TYPE_Q4_K || (pair && type == KQ_TYPE_Q6_K);
+  const bool zr = type == KQ_TYPE_Q2_K || type == KQ_TYPE_Q4_K || type == KQ_TYPE_Q5_K || type == KQ_TYPE_Q5_0 ||
+                  (pair && type == KQ_TYPE_Q6_K);
   c.a_stride = pair ? (int)(k / 64) * 80 + 16 : (int)k + 32;
   c.a_bytes = (mt * c.a_stride + 127) / 128 * 128;
   c.d_bytes = (int)((mt * (kpad / 32) * 4 + 127) / 128 * 128);
-  c.z_bytes = zr ? (int)((mt * (kpad / 32) * 4 * (type == KQ_TYPE_Q4_K ? 1 : 2) + 127) / 128 * 128) : 0;
+  c.z_bytes = zr ? (int)((mt * (kpad / 32) * 4 * ((type == KQ_TYPE_Q2_K || type == KQ_TYPE_Q6_K) ? 2 : 1) + 127) / 128 * 128) : 0;
   (void)zpb;
   const int fixed = SMEM_HEADER + (type == KQ_TYPE_IQ3_S ? 2048 : 0) + c.a_bytes + c.d_bytes + c.z_bytes;
   if (fixed + 3 * (int64_t)c.stage_bytes > SMEM_LIMIT) return false;
@@ -596,6 +601,7 @@ bool gemv_mma_supported(const void* W, int type, int64_t n, int64_t k) {
 // near 4.2 TB/s, so whenever it needs no K split (K up to about 8K) the mma kernel takes 1-2 tokens as well: 27.2 ->
 // 21.0 us on 17408x5120, 352 -> 246 us on a 248320x5120 LM head; with a K split (5120x17408) the row kernel stays ahead.
 static int tile_min_tokens(int type, int64_t n, int64_t k) {
+  if (!type_is_core(type)) return 1 << 30;   // the other formats never leave the row-streaming kernel
   if (type == KQ_TYPE_Q4_0) return 9;
   if (type == KQ_TYPE_Q6_K && gemv_tile_splits(type, n, k, 8) == 1) return 1;
   if (type == KQ_TYPE_IQ3_S) return 2;   // its generic row decoder pays per token: 29.4 -> 27.0 us at 2 tokens
@@ -624,8 +630,20 @@ int launch_gemv_mma(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs&
     const int64_t left = m - m0;
     const bool tile_start = (m0 % 16) == 0;
     int rc, mcount;
-    // 3..16 tokens (and, per format, fewer): the shared-stage mma kernel (all warps of a CTA on every stage of 8 rows)
     const int tile_min = tile_min_tokens(type, n, k);
+    // 3..16 tokens: the register-resident mma kernel where it covers the type and shape
+    // (today it wins for up to 8 tokens; 9..16 tokens only on request: kres = 2 or gemv_impl = 7)
+    const int pass = (int)(left < 16 ? left : 16);
+    if (tile_start && (impl == 7 || (impl == 0 && left >= tile_min && (options().kres == 2 || (options().kres == 1 && pass <= 8)))) &&
+        gemv_kres_supported(W, type, n, k, pass)) {
+      mcount = (int)(left < 16 ? left : 16);
+      rc = launch_gemv_kres(W, type, n, k, P, m0, mcount, y, y_dtype, stride_y, mmq, st);
+      if (rc) return rc;
+      m0 += mcount;
+      continue;
+    }
+    if (impl == 7) { set_error("register-resident GEMV: type/shape not covered"); return KQ_EUNSUPPORTED; }
+    // otherwise the shared-stage mma kernel (all warps of a CTA on every stage of 8 rows)
     if (tile_start && (impl == 6 || (impl == 0 && left >= tile_min)) &&
         gemv_tile_supported(W, type, n, k, (int)(left < 16 ? left : 16))) {
       mcount = (int)(left < 16 ? left : 16);
@@ -650,8 +668,10 @@ int launch_gemv_mma(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs&
     p.a_stride = rcg.a_stride; p.a_bytes = rcg.a_bytes; p.d_bytes = rcg.d_bytes; p.z_bytes = rcg.z_bytes;
     p.qs = P.qs; p.qsp = pair ? P.qsp : nullptr; p.ds = P.ds; p.zpb = zpb; p.kpad = (int)P.kpad; p.nb32tot = (int)(P.kpad / 32); p.klen = (int)k;
     p.zr = nullptr; p.zmode = 0;
-    if (type == KQ_TYPE_Q4_0 || (type == KQ_TYPE_Q4_K && mmq)) p.zmode = 1;
-    else if (type == KQ_TYPE_Q4_K) { p.zmode = 2; p.zr = P.z32r; }
+    // min term: the fp16 raw block sum (mode 1) or d8 * (sum of the codes) from the token-major table (mode 2)
+    if (type == KQ_TYPE_Q4_0 || type == KQ_TYPE_Q4_1 || type == KQ_TYPE_Q5_1 || ((type == KQ_TYPE_Q4_K || type == KQ_TYPE_Q5_K) && mmq) ||
+        (type == KQ_TYPE_Q5_0 && !mmq)) p.zmode = 1;
+    else if (type == KQ_TYPE_Q4_K || type == KQ_TYPE_Q5_K || type == KQ_TYPE_Q5_0) { p.zmode = 2; p.zr = P.z32r; }
     else if (type == KQ_TYPE_Q2_K) { p.zmode = 3; p.zr = P.z16r; }
     else if (type == KQ_TYPE_Q6_K && pair) { p.zmode = 3; p.zr = P.z16r; p.zpb = 2; }   // -32 offset via group sums
     p.prefetch = options().pdl < rcg.stages ? options().pdl : rcg.stages;
@@ -663,7 +683,15 @@ int launch_gemv_mma(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs&
       case KQ_TYPE_Q2_K: rc = launch_typed<KQ_TYPE_Q2_K>(p, rcg, mt, y_dtype, st); break;
       case KQ_TYPE_Q4_K: rc = launch_typed<KQ_TYPE_Q4_K>(p, rcg, mt, y_dtype, st); break;
       case KQ_TYPE_Q6_K: rc = launch_typed<KQ_TYPE_Q6_K>(p, rcg, mt, y_dtype, st); break;
-      default: rc = launch_typed<KQ_TYPE_IQ3_S>(p, rcg, mt, y_dtype, st); break;
+      case KQ_TYPE_IQ3_S: rc = launch_typed<KQ_TYPE_IQ3_S>(p, rcg, mt, y_dtype, st); break;
+      case KQ_TYPE_Q4_1: rc = launch_typed<KQ_TYPE_Q4_1>(p, rcg, mt, y_dtype, st); break;
+      case KQ_TYPE_Q5_0: rc = launch_typed<KQ_TYPE_Q5_0>(p, rcg, mt, y_dtype, st); break;
+      case KQ_TYPE_Q5_1: rc = launch_typed<KQ_TYPE_Q5_1>(p, rcg, mt, y_dtype, st); break;
+      case KQ_TYPE_Q3_K: rc = launch_typed<KQ_TYPE_Q3_K>(p, rcg, mt, y_dtype, st); break;
+      case KQ_TYPE_Q5_K: rc = launch_typed<KQ_TYPE_Q5_K>(p, rcg, mt, y_dtype, st); break;
+      case KQ_TYPE_IQ4_NL: rc = launch_typed<KQ_TYPE_IQ4_NL>(p, rcg, mt, y_dtype, st); break;
+      case KQ_TYPE_IQ4_XS: rc = launch_typed<KQ_TYPE_IQ4_XS>(p, rcg, mt, y_dtype, st); break;
+      default: set_error("row-streaming GEMV: type %d not covered", type); return KQ_EUNSUPPORTED;
     }
     if (rc) return rc;
     m0 += mcount;

@@ -40,13 +40,11 @@ constexpr int TL_ROWS = 8;
 constexpr int TL_CW = 16;                         // consumer warps
 constexpr int TL_THREADS = (TL_CW + 2) * 32;      // + reducer + producer
 constexpr int TL_HEADER = 1024;
+constexpr int TL_TILE_BYTES = 768;                // the reducer's transpose tile: 16 tokens x 12 floats
 constexpr int TL_NRED = 2;                        // partial-tile buffers (a power of two)
 constexpr int TL_SLEEP_C = 64, TL_SLEEP_R = 200, TL_SLEEP_P = 400;   // ns between polls: consumers, reducer, producer
 constexpr int TL_MAX_STAGES = 16;
 constexpr int TL_SMEM_LIMIT = 232448;
-constexpr uint32_t TL_MAGIC_I = 0x4B400000u;      // bits of 12582912.0f
-constexpr float TL_MAGIC_F = 12582912.0f;
-constexpr long long TL_WAIT_LIMIT = 1ll << 27;
 
 __constant__ uint16_t c_iq3s_codes_t[512] = {
 #include "kq_iq3s_codes.inc"
@@ -76,94 +74,7 @@ struct TileConfig {
   int ks, grid, stages, row_stride, stage_bytes, contig, a_stride, a_bytes, d_bytes, z_bytes, smem;
 };
 
-__device__ __forceinline__ uint32_t s_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void bar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void bar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void bar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool bar_try(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(20000u)   // the thread may stay suspended this many ns before the test returns false
-      : "memory");
-  return ok != 0;
-}
-// bounded wait; SLEEP_NS between polls keeps a waiting warp out of the issue slots of the working ones
-template <int SLEEP_NS = 64>
-__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (bar_try(bar, parity)) return true;
-  const long long t0 = clock64();
-  for (int it = 1;; ++it) {
-    __nanosleep(SLEEP_NS);
-    if (bar_try(bar, parity)) return true;
-    if ((it & 63) == 0) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > TL_WAIT_LIMIT) { *abort_flag = 1; return false; }
-    }
-  }
-}
-__device__ __forceinline__ void copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-               "l"(src), "r"(bytes), "r"(bar)
-               : "memory");
-}
-
-// tokens (A, 16 x 32 s8) x weights (B, 32 x 8 s8) -> s32
-__device__ __forceinline__ void mma_i8_k32(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                           uint32_t b1) {
-  asm(
-      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
-}
-__device__ __forceinline__ void mma_i8_k16(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
-  asm("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
-               : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-               : "r"(a0), "r"(a1), "r"(b0), "r"(0));
-}
-// d += A (16 x 8 tf32) x B (8 x 8 tf32)
-__device__ __forceinline__ void mma_tf32_k8(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                            uint32_t b1) {
-  asm(
-      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ float magic_f(int v) { return __int_as_float(v + (int)TL_MAGIC_I) - TL_MAGIC_F; }
-__device__ __forceinline__ uint32_t byte_of(uint32_t w, int i) { return __byte_perm(w, 0u, 0x4440u | (uint32_t)i); }
-__device__ __forceinline__ int sbyte_of(uint32_t w, int i) {   // sign-extended byte i in one permute
-  uint32_t r;
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(w), "r"(0u), "r"((uint32_t)i | ((8u | (uint32_t)i) * 0x1110u)));
-  return (int)r;
-}
-
-// shared-memory loads by byte offset into the CTA's dynamic shared memory: ordinary loads (the compiler may
-// schedule them around the arithmetic, but never across an mbarrier wait, which clobbers memory)
-extern __shared__ __align__(128) uint8_t tl_smem[];
-__device__ __forceinline__ uint32_t lds32(uint32_t a) { return *reinterpret_cast<const uint32_t*>(tl_smem + a); }
-__device__ __forceinline__ uint2 lds64(uint32_t a) { return *reinterpret_cast<const uint2*>(tl_smem + a); }
-__device__ __forceinline__ uint4 lds128(uint32_t a) { return *reinterpret_cast<const uint4*>(tl_smem + a); }
-__device__ __forceinline__ float2 ldsf2(uint32_t a) { return *reinterpret_cast<const float2*>(tl_smem + a); }
-__device__ __forceinline__ float ldsf(uint32_t a) { return *reinterpret_cast<const float*>(tl_smem + a); }
-// 32 bits at a 2-byte aligned address.  AL = 0: the address is 4-byte aligned; 1: it is 2 mod 4; 2: either, decided
-// per lane without a branch (the callers sit between warp-wide mma instructions and must not diverge)
-template <int AL>
-__device__ __forceinline__ uint32_t lds32_h(uint32_t a) {
-  if constexpr (AL == 0) return lds32(a);
-  else if constexpr (AL == 1) return __funnelshift_r(lds32(a - 2), lds32(a + 2), 16);
-  else {
-    const uint32_t b = a & ~3u;
-    return __funnelshift_r(lds32(b), lds32(b + 4), (a & 2u) << 3);
-  }
-}
+#include "kq_tile_common.cuh"
 
 struct TileView {       // byte offsets (into the dynamic shared memory) of the CTA's activation slice
   uint32_t sA;          // [tokens][a_stride] codes
@@ -431,7 +342,8 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
   float* sD = reinterpret_cast<float*>(sA + p.a_bytes);
   float* sZ = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sD) + p.d_bytes);
   float4* sRed = reinterpret_cast<float4*>(reinterpret_cast<uint8_t*>(sZ) + p.z_bytes);   // [2][16 warps][32 lanes]
-  uint8_t* ring = reinterpret_cast<uint8_t*>(sRed) + TL_NRED * TL_CW * 512;
+  float* sT = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sRed) + TL_NRED * TL_CW * 512);   // [16 tokens][12]: transpose tile
+  uint8_t* ring = reinterpret_cast<uint8_t*>(sT) + TL_TILE_BYTES;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int S = p.stages;
@@ -545,6 +457,9 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
     OutT* y = reinterpret_cast<OutT*>(p.y);
     const int g = lane >> 2, t = lane & 3;
     const int nks = p.ks;
+    // 16-byte stores need 16-byte aligned rows of the output / of the partials
+    const bool vec_y = ((uintptr_t)p.y % 16) == 0 && ((p.stride_y * sizeof(OutT)) % 16) == 0 && (((size_t)p.m0 * p.stride_y * sizeof(OutT)) % 16) == 0;
+    const bool vec_part = (p.n % 4) == 0;
     for (int q = 0; q < nst; ++q) {
       const int buf = q & (TL_NRED - 1);
       if (!bar_wait<TL_SLEEP_R>(bar_rfull + 8 * buf, (uint32_t)((q / TL_NRED) & 1), s_abort)) { if (lane == 0) atomicExch(p.status, 5); return; }
@@ -558,12 +473,36 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
       if (lane == 0) bar_arrive(bar_rempty + 8 * buf);
       const int row0 = (rt0 + q) * TL_ROWS;
       const float vals[4] = {sum.x, sum.y, sum.z, sum.w};
+      // Transpose through a small shared tile so that one lane stores the 8 rows of one token with a 16-byte store
+      // (two for fp32): value (row g, token tl) -> sT[tl][g], row stride 12 floats (conflict-free).  The scattered
+      // 2-byte stores this replaces cost 1.6 us (8 tokens) to 4.4 us (16 tokens) of a 17408x5120 call.
+      __syncwarp();   // the previous stage's tile has been read
 #pragma unroll
-      for (int i = 0; i < 2 * NH; ++i) {
-        const int row = row0 + g, tl = 2 * t + (i & 1) + 8 * (i >> 1);
-        if (row < p.n && tl < p.mcount) {
-          if (nks == 1) y[(size_t)(p.m0 + tl) * p.stride_y + row] = from_f32<OutT>(vals[i]);
-          else __stcg(p.part + ((size_t)ks * 16 + tl) * p.n + row, vals[i]);   // published after the loop
+      for (int i = 0; i < 2 * NH; ++i) sT[(2 * t + (i & 1) + 8 * (i >> 1)) * 12 + g] = vals[i];
+      __syncwarp();
+      if (lane < p.mcount && row0 < p.n) {
+        const int tl = lane;
+        const float4 va = *reinterpret_cast<const float4*>(sT + tl * 12), vb = *reinterpret_cast<const float4*>(sT + tl * 12 + 4);
+        const float v8[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+        const bool whole = row0 + 8 <= p.n;
+        if (nks > 1) {
+          float* dst = p.part + ((size_t)ks * 16 + tl) * p.n + row0;   // published after the loop
+          if (whole && vec_part) { __stcg(reinterpret_cast<float4*>(dst), va); __stcg(reinterpret_cast<float4*>(dst) + 1, vb); }
+          else for (int i = 0; i < 8; ++i) if (row0 + i < p.n) __stcg(dst + i, v8[i]);
+        } else {
+          OutT* dst = y + (size_t)(p.m0 + tl) * p.stride_y + row0;
+          if (whole && vec_y) {
+            if constexpr (sizeof(OutT) == 4) {
+              reinterpret_cast<float4*>(dst)[0] = va; reinterpret_cast<float4*>(dst)[1] = vb;
+            } else {
+              OutT o[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) o[i] = from_f32<OutT>(v8[i]);
+              *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(o);
+            }
+          } else {
+            for (int i = 0; i < 8; ++i) if (row0 + i < p.n) dst[i] = from_f32<OutT>(v8[i]);
+          }
         }
       }
     }
@@ -660,7 +599,7 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
 // smallest K split whose activation slice leaves room for a ring of >= 4 stages
 bool make_tile_config(int type, int64_t n, int64_t k, int mtok, TileConfig& c) {
   int blk, bytes;
-  if (!type_geometry(type, &blk, &bytes)) return false;
+  if (!type_is_core(type) || !type_geometry(type, &blk, &bytes)) return false;
   if (k % 256) return false;
   bytes *= 256 / blk;   // the kernel's unit of K is 256 weights
   blk = 256;
@@ -688,7 +627,7 @@ bool make_tile_config(int type, int64_t n, int64_t k, int mtok, TileConfig& c) {
     const int a_bytes = (mtok * a_stride + 127) / 128 * 128;
     const int d_bytes = ((klen / 32) * 64 + 127) / 128 * 128;
     const int z_bytes = (type == KQ_TYPE_Q4_K || type == KQ_TYPE_Q4_0) ? d_bytes : (type == KQ_TYPE_Q2_K ? 2 * d_bytes : 0);
-    const int fixed = TL_HEADER + (type == KQ_TYPE_IQ3_S ? TL_GRID_BYTES : 0) + a_bytes + d_bytes + z_bytes + TL_NRED * TL_CW * 512;
+    const int fixed = TL_HEADER + (type == KQ_TYPE_IQ3_S ? TL_GRID_BYTES : 0) + a_bytes + d_bytes + z_bytes + TL_NRED * TL_CW * 512 + TL_TILE_BYTES;
     int stages = (TL_SMEM_LIMIT - fixed) / stage_bytes;
     if (stages > TL_MAX_STAGES) stages = TL_MAX_STAGES;
     if (stages < 3) continue;

@@ -12,9 +12,10 @@ import torch
 from . import ops
 from .synth import BLOCK
 
-IMATRIX_QUANT_TYPES = frozenset({21})           # of the supported set: IQ3_S
-MMVQ_QUANT_TYPES = frozenset({2, 8, 10, 12, 14, 21})
-MMQ_QUANT_TYPES = frozenset({2, 8, 10, 12, 14})
+# the reference's type sets (quantization/utils.py:45-75), restricted to the formats this library serves
+IMATRIX_QUANT_TYPES = frozenset({20, 21, 23})    # IQ4_NL, IQ3_S, IQ4_XS
+MMVQ_QUANT_TYPES = frozenset({2, 3, 6, 7, 8, 10, 11, 12, 13, 14, 20, 21, 23})
+MMQ_QUANT_TYPES = frozenset({2, 3, 6, 7, 8, 10, 11, 12, 13, 14})
 DEQUANT_TYPES = MMVQ_QUANT_TYPES
 
 

@@ -18,8 +18,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 EXT_PATH = os.path.join(_HERE, "_C_gguf.so")
 
 # GGML type ids served by the CUDA kernels (gguf-reader/gguf/constants.py:5763-5799)
-SUPPORTED_QUANT_TYPES = frozenset({2, 8, 10, 12, 14, 21})
-GEMM_QUANT_TYPES = frozenset({2, 8, 10, 12, 14})
+SUPPORTED_QUANT_TYPES = frozenset({2, 3, 6, 7, 8, 10, 11, 12, 13, 14, 20, 21, 23})
+GEMM_QUANT_TYPES = frozenset({2, 3, 6, 7, 8, 10, 11, 12, 13, 14})
 
 
 def _load_extension() -> None:

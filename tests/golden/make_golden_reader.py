@@ -26,7 +26,7 @@ synth = importlib.util.module_from_spec(spec)
 spec.loader.exec_module(synth)
 
 out = {}
-for qt in (2, 8, 10, 12, 14, 21):
+for qt in sorted(synth.BLOCK):
     blk, _ = synth.BLOCK[qt]
     w = synth.wire_numpy(qt, 6, 2 * max(blk, 256), seed=100 + qt)
     out[f"wire_{qt}"] = w

@@ -166,6 +166,39 @@ def test_shared_stage_mma_gemv_matches_oracle_and_dp4a(qt, n, k, m, mmq, segment
     assert rel_l2(to_np(y), to_np(y1)) < TIGHT          # every row, against the general kernel
 
 
+@pytest.mark.parametrize("qt", [12])
+@pytest.mark.parametrize("n,k,m", [(8, 256, 5), (17, 512, 8), (100, 1024, 9), (2368, 2048, 12), (4736, 5120, 16), (4736, 5120, 7),
+                                   (333, 4352, 16), (70, 17408, 5), (1190, 17408, 8), (48, 768, 33), (3000, 14336, 3),
+                                   (1000, 4096, 16), (1000, 8192, 16), (520, 8192, 6), (600, 11008, 11),
+                                   (400, 2816, 8), (1001, 5632, 16)])
+@pytest.mark.parametrize("mmq", [False, True])
+def test_register_resident_gemv_matches_oracle_and_dp4a(qt, n, k, m, mmq):
+    """gemv_impl=7: every consumer warp keeps the activations of its own K units in registers; split-K where a warp's
+    share would not fit.  Shapes the kernel does not cover are reported as such, never computed wrongly."""
+    _, wt = wire(qt, n, k, seed=n + k)
+    x, xt = act(m, k, seed=m, dt="bf16")
+    w = wt.cpu().numpy()
+    scratch = torch.empty(capi.workspace_bytes(qt, m, n, k), dtype=torch.uint8, device=dev())
+    capi.set_option("gemv_impl", 7)
+    try:
+        try:
+            y = capi.mul_mat(wt, xt, qt, mmq=mmq, out_dtype=torch.float32, scratch=scratch)
+        except capi.KqError as e:
+            assert e.code == capi.KQ_EUNSUPPORTED
+            pytest.skip("shape not covered by the register-resident kernel")
+        assert capi.read_status(qt, m, n, k, scratch) == 0
+        yb = capi.mul_mat(wt, xt, qt, mmq=mmq, out_dtype=torch.float32, scratch=scratch)   # counters self-reset
+        capi.set_option("gemv_impl", 1)
+        y1 = capi.mul_mat(wt, xt, qt, mmq=mmq, out_dtype=torch.float32)
+    finally:
+        capi.set_option("gemv_impl", 0)
+    rows = np.r_[0:min(n, 150), max(0, n - 150):n]
+    want = O.mul_mat(w[rows], qt, x, "mmq" if mmq else "mmvq")
+    assert rel_l2(to_np(y)[:, rows], want) < TIGHT
+    assert torch.equal(y, yb)
+    assert rel_l2(to_np(y), to_np(y1)) < TIGHT          # every row, against the general kernel
+
+
 @pytest.mark.parametrize("qt", QT)
 @pytest.mark.parametrize("n,k,m", [(64, 512, 1), (333, 2048, 2), (1200, 5120, 1), (100, 17408, 2), (17, 256, 1)])
 @pytest.mark.parametrize("dt", ["bf16", "f16", "f32"])

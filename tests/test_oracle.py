@@ -9,9 +9,10 @@ from oracle import gguf_oracle as O
 
 GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 QT = O.QTYPES
+ALL = O.ALL_QTYPES
 
 
-@pytest.mark.parametrize("qt", QT)
+@pytest.mark.parametrize("qt", ALL)
 def test_dequantize_matches_reference_reader_fixture(qt):
     g = np.load(os.path.join(GOLD, "reader_dequant.npz"))
     w, ref = g[f"wire_{qt}"], g[f"deq_{qt}"]
@@ -78,6 +79,39 @@ def test_q8_1_wire_layout():
     assert w[1, 3, 2:4].view(np.float16)[0] == a["s"][1, 3]
 
 
+@pytest.mark.parametrize("qt", O.MORE_QTYPES)
+def test_more_formats_equal_dense_product_of_dequantized_operands(qt):
+    """The same identity for the other formats.  Where the reference uses the fp16 raw block sum (Q5_0's MMVQ
+    flavour, Q5_K's MMQ flavour) or rounds scale products to fp16 (Q4_1, Q5_1) the agreement is to that effect."""
+    k = 1024
+    w = synth.wire_numpy(qt, 24, k, seed=qt)
+    x = synth.activations_numpy(5, k, seed=qt, dtype="bf16")
+    a = O.quantize_q8_1(x)
+    xq = a["q"][:, :k].astype(np.float64) * np.repeat(a["d"][:, : k // 32].astype(np.float64), 32, 1)
+    dense = xq @ O.dequantize_f32(w, qt).astype(np.float64).T
+    rel = lambda y: np.linalg.norm(y - dense) / np.linalg.norm(dense)   # noqa: E731
+    y = O.mul_mat(w, qt, x, "mmvq")
+    if qt in (O.Q4_1, O.Q5_1):
+        assert rel(y) < 3e-2               # m * (raw fp16 sum) instead of m * d8 * (sum of codes), fp16 products
+    elif qt == O.Q5_0:
+        assert rel(y) < 3e-2               # -16 through the raw fp16 sum
+    else:
+        assert rel(y) < 1e-6
+    if qt in O.NO_MMQ:
+        with pytest.raises(ValueError):
+            O.mul_mat(w, qt, x, "mmq")
+    else:
+        y2 = O.mul_mat(w, qt, x, "mmq")
+        if qt == O.Q5_0:
+            assert rel(y2) < 1e-6          # the MMQ tile loader subtracts 16 from the codes: exact
+        elif qt == O.Q5_K:
+            assert 1e-7 < rel(y2) < 5e-3   # raw-sum min term
+        elif qt == O.Q3_K:
+            assert rel(y2) < 1e-6
+        else:
+            np.testing.assert_array_equal(y2, y)
+
+
 @pytest.mark.parametrize("qt", QT)
 def test_mul_mat_equals_dense_product_of_dequantized_operands(qt):
     """The integer-dot formulation is algebraically the dense product of the dequantized weight with the
@@ -103,7 +137,7 @@ def test_mul_mat_equals_dense_product_of_dequantized_operands(qt):
             O.mul_mat(w, qt, x, "mmq")
 
 
-@pytest.mark.parametrize("qt", QT)
+@pytest.mark.parametrize("qt", ALL)
 def test_group_dots_shapes_and_linearity(qt):
     k = 512
     w = synth.wire_numpy(qt, 8, k, seed=1)
@@ -114,10 +148,13 @@ def test_group_dots_shapes_and_linearity(qt):
     np.testing.assert_array_equal(S, act["q"][:, :k].astype(np.int64).reshape(2, k // g, g).sum(-1))
     # doubling the activations leaves the codes unchanged and doubles d (power of two) -> y doubles exactly
     y2 = O.mul_mat(w, qt, 2 * x, "mmvq")
-    np.testing.assert_allclose(y2, 2 * y, rtol=1e-6)
+    if qt in (O.Q4_1, O.Q5_1):   # their fp16 scale products can be subnormal, where rounding is not scale-invariant
+        assert np.linalg.norm(y2 - 2 * y) / np.linalg.norm(y) < 1e-3
+    else:
+        np.testing.assert_allclose(y2, 2 * y, rtol=1e-6)
 
 
-@pytest.mark.parametrize("qt", QT)
+@pytest.mark.parametrize("qt", ALL)
 @pytest.mark.parametrize("dt", ["f16", "bf16", "f32"])
 def test_dequantize_half_path_close_to_f32_and_representable(qt, dt):
     w = synth.wire_numpy(qt, 16, 512, seed=qt + 7)
@@ -129,10 +166,10 @@ def test_dequantize_half_path_close_to_f32_and_representable(qt, dt):
 
 
 def test_dequantize_fma_mode_changes_only_kquants_with_min():
-    for qt in QT:
+    for qt in ALL:
         w = synth.wire_numpy(qt, 16, 512, seed=3)
         a, b = O.dequantize(w, qt, "f16", half_fma=0), O.dequantize(w, qt, "f16", half_fma=1)
-        if qt in (O.Q2_K, O.Q4_K):
+        if qt in (O.Q2_K, O.Q4_K, O.Q5_K, O.Q4_1, O.Q5_1):
             assert (a != b).any()
         else:
             np.testing.assert_array_equal(a, b)
@@ -144,4 +181,4 @@ def test_row_bytes_and_errors():
     with pytest.raises(ValueError):
         O.row_bytes(O.Q4_K, 5000)
     with pytest.raises(ValueError):
-        O.unpack(np.zeros((1, 18), np.uint8), 13)
+        O.unpack(np.zeros((1, 18), np.uint8), 16)

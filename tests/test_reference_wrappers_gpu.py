@@ -30,7 +30,7 @@ pytestmark = pytest.mark.gpu
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 STAGE = os.path.join(ROOT, "baseline", "_ref")
-ALL_TYPES = [2, 8, 10, 12, 14, 21]
+ALL_TYPES = [2, 8, 10, 12, 14, 21, 3, 6, 7, 11, 13, 20, 23]
 
 
 @pytest.fixture(scope="module")
@@ -70,10 +70,11 @@ def ref_cuda():
 
 def _flavour(qt, m, n):
     """Which branch quantization/linear.py:40-63 takes."""
-    safe = (8 if n > 5120 else 16) if qt == 21 else (2 if n > 5120 else 6)
+    imatrix = qt in (20, 21, 23)
+    safe = (8 if n > 5120 else 16) if imatrix else (2 if n > 5120 else 6)
     if m <= safe:
         return "mmvq"
-    return "mmq" if qt != 21 else "dense"
+    return "dense" if imatrix else "mmq"
 
 
 def _expect(w, qt, x, xdt, flavour):
@@ -92,7 +93,7 @@ def test_reference_ops_wrappers(plugin, qt):
     y = plugin.ops.ggml_mul_mat_vec_a8(wt, xt, qt, n)
     assert y.shape == (m, n) and y.dtype == torch.bfloat16
     assert rel_l2(to_np(y), O.round_to_dtype(O.mul_mat(w, qt, x, "mmvq"), "bf16")) < 3e-3
-    if qt != 21:
+    if qt not in (20, 21, 23):
         y = plugin.ops.ggml_mul_mat_a8(wt, xt, qt, n)
         assert rel_l2(to_np(y), O.round_to_dtype(O.mul_mat(w, qt, x, "mmq"), "bf16")) < 3e-3
     d = plugin.ops.ggml_dequantize(wt, qt, n, k, torch.float16)
