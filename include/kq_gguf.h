@@ -133,6 +133,21 @@ int kq_mul_mat_prepared(const void* W, int type, int64_t n, int64_t k, int64_t m
                         void* y, int y_dtype, int64_t stride_y, int mmq,
                         void* scratch, size_t scratch_bytes, void* stream);
 
+/* Fused producers for kq_mul_mat_prepared: the activation is computed from its inputs and quantized in ONE launch,
+ * bit-identically to running the elementwise / normalising kernel first and kq_prepare_q8 on its output (m <= 80).
+ *   kq_prepare_q8_rmsnorm  a = T(T(x * rsqrt(mean(x^2) + eps)) * gamma) with both roundings in the storage type T (the order
+ *                          of vLLM's rms_norm kernel); gamma: k values of x_dtype; y_norm (may be NULL): the normalised
+ *                          [m, k] tensor, row stride k, for consumers that need it dense
+ *   kq_prepare_q8_swiglu   a = T(silu(gate)) * up in T, gate = gate_up[:, 0:k], up = gate_up[:, k:2k] (row stride
+ *                          stride_gu >= 2k): vLLM's SiluAndMul on the merged gate/up output, feeding the down projection
+ * They take the place of the reference production backend's fused activation producers
+ * (vllm_gguf_plugin/native/kernels/kai_prepare_ext.cuh:1-10, quantization/native_fused.py:144-200), with this path's
+ * q8_1 arithmetic (gguf_kernel.cu:32-69) instead of that backend's own activation format. */
+int kq_prepare_q8_rmsnorm(int type, int64_t n, int64_t k, const void* x, int x_dtype, int64_t m, int64_t stride_x,
+                          const void* gamma, float eps, void* y_norm, void* scratch, size_t scratch_bytes, void* stream);
+int kq_prepare_q8_swiglu(int type, int64_t n, int64_t k, const void* gate_up, int x_dtype, int64_t m, int64_t stride_gu,
+                         void* scratch, size_t scratch_bytes, void* stream);
+
 /* Dense dequantization of `count` weights (count a multiple of the block size) to out_dtype, with
  * the reference kernels' fp16 intermediate roundings.
  * Replaces ggml_dequantize, vllm_gguf_plugin/csrc/gguf/gguf_kernel.cu:87-102
@@ -140,7 +155,7 @@ int kq_mul_mat_prepared(const void* W, int type, int64_t n, int64_t k, int64_t m
 int kq_dequantize(const void* W, int type, int64_t count, void* out, int out_dtype, void* stream);
 
 /* Test hook: exact integer dot products per weight scale group.
- * dots: int32 [m, n, k/G] with G = 32 (Q4_0, Q8_0, Q4_K, IQ3_S) or 16 (Q2_K, Q6_K);
+ * dots: int32 [m, n, k/G] with G = 16 for Q2_K, Q3_K and Q6_K (one weight scale per 16 weights) and 32 for the others;
  * sums: int32 [m, k/G] = sum of the activation codes of each group (may be NULL).
  * Uses the same scratch as the mul_mat entry points.  No counterpart in the reference (its kernels
  * never materialise the integer dots); exists so the bit-exactness of the integer path can be

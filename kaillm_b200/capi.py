@@ -22,7 +22,7 @@ EXPORTS = (
     "kq_last_error", "kq_abi_version", "kq_block_geometry", "kq_workspace_bytes", "kq_quantize_q8_1",
     "kq_mul_mat_vec_a8", "kq_mul_mat_a8", "kq_dequantize", "kq_debug_group_dots", "kq_set_option",
     "kq_get_option", "kq_prepare_q8", "kq_mul_mat_prepared", "kq_read_status", "kq_mul_mat_vec_a8_static",
-    "kq_p2p_allgather", "kq_read_status_static", "kq_debug_copy_window",
+    "kq_p2p_allgather", "kq_read_status_static", "kq_debug_copy_window", "kq_prepare_q8_rmsnorm", "kq_prepare_q8_swiglu",
 )
 
 
@@ -50,6 +50,8 @@ def _load() -> ctypes.CDLL:
     lib.kq_mul_mat_vec_a8.argtypes = mm
     lib.kq_mul_mat_a8.argtypes = mm
     lib.kq_prepare_q8.argtypes = [i32, i64, i64, vp, i32, i64, i64, vp, sz, vp]
+    lib.kq_prepare_q8_rmsnorm.argtypes = [i32, i64, i64, vp, i32, i64, i64, vp, ctypes.c_float, vp, vp, sz, vp]
+    lib.kq_prepare_q8_swiglu.argtypes = [i32, i64, i64, vp, i32, i64, i64, vp, sz, vp]
     lib.kq_mul_mat_prepared.argtypes = [vp, i32, i64, i64, i64, vp, i32, i64, i32, vp, sz, vp]
     lib.kq_mul_mat_vec_a8_static.argtypes = [vp, i32, i64, i64, vp, i32, i64, i64, vp, i32, i64, vp]
     lib.kq_dequantize.argtypes = [vp, i32, i64, vp, i32, vp]
@@ -137,6 +139,24 @@ def prepare_q8(x: torch.Tensor, qtype: int, n: int, scratch: torch.Tensor) -> No
                                  scratch.numel(), _stream(x.device)))
 
 
+def prepare_q8_rmsnorm(x: torch.Tensor, gamma: torch.Tensor, eps: float, qtype: int, n: int, scratch: torch.Tensor,
+                       y_norm: torch.Tensor | None = None) -> None:
+    """RMSNorm(x) * gamma quantized into `scratch` in one launch (kq_prepare_q8_rmsnorm)."""
+    m, k = x.shape
+    with torch.cuda.device(x.device):
+        _check(lib.kq_prepare_q8_rmsnorm(qtype, n, k, x.data_ptr(), _DT[x.dtype], m, x.stride(0), gamma.data_ptr(), eps,
+                                         y_norm.data_ptr() if y_norm is not None else None, scratch.data_ptr(),
+                                         scratch.numel(), _stream(x.device)))
+
+
+def prepare_q8_swiglu(gate_up: torch.Tensor, qtype: int, n: int, scratch: torch.Tensor) -> None:
+    """silu(gate) * up of a merged [m, 2k] gate/up output quantized into `scratch` in one launch (kq_prepare_q8_swiglu)."""
+    m, k2 = gate_up.shape
+    with torch.cuda.device(gate_up.device):
+        _check(lib.kq_prepare_q8_swiglu(qtype, n, k2 // 2, gate_up.data_ptr(), _DT[gate_up.dtype], m, gate_up.stride(0),
+                                        scratch.data_ptr(), scratch.numel(), _stream(gate_up.device)))
+
+
 def mul_mat_prepared(W: torch.Tensor, qtype: int, m: int, k: int, out: torch.Tensor, scratch: torch.Tensor,
                      *, mmq: bool = False) -> torch.Tensor:
     """y = activations held in `scratch` times W (kq_mul_mat_prepared)."""
@@ -205,7 +225,7 @@ def dequantize(W: torch.Tensor, qtype: int, count: int, dtype=torch.float16) -> 
 def debug_group_dots(W: torch.Tensor, x: torch.Tensor, qtype: int):
     m, k = x.shape
     n = W.shape[0]
-    g = 16 if qtype in (10, 14) else 32
+    g = 16 if qtype in (10, 11, 14) else 32
     dots = torch.empty((m, n, k // g), dtype=torch.int32, device=x.device)
     sums = torch.empty((m, k // g), dtype=torch.int32, device=x.device)
     ws = workspace_bytes(qtype, m, n, k)

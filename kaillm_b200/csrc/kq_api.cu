@@ -181,6 +181,37 @@ int kq_prepare_q8(int type, int64_t n, int64_t k, const void* x, int x_dtype, in
                  scratch_bytes, stream, false, true);
 }
 
+// shared validation of the fused producers: same checks as kq_prepare_q8, then the scratch pointers
+static int prepare_common(const char* fn, int type, int64_t n, int64_t k, const void* x, int x_dtype, int64_t m, int64_t stride_x,
+                          int64_t min_stride, void* scratch, size_t scratch_bytes, Q8Ptrs* P) {
+  t_err[0] = 0;
+  Problem p;
+  int rc = validate(fn, nullptr, type, n, k, x, x_dtype, m, stride_x < k ? k : stride_x, scratch, scratch_bytes, p, false, true);
+  if (rc) return rc;
+  if (stride_x < min_stride) { set_error("%s: row stride %lld < %lld", fn, (long long)stride_x, (long long)min_stride); return KQ_EINVAL; }
+  if (m > 80) { set_error("%s: the fused producers serve the decode path (m <= 80)", fn); return KQ_ELIMIT; }
+  *P = q8_ptrs(scratch, p.L, n);
+  P->xh = nullptr;
+  return KQ_OK;
+}
+
+int kq_prepare_q8_rmsnorm(int type, int64_t n, int64_t k, const void* x, int x_dtype, int64_t m, int64_t stride_x,
+                          const void* gamma, float eps, void* y_norm, void* scratch, size_t scratch_bytes, void* stream) {
+  Q8Ptrs P;
+  int rc = prepare_common("kq_prepare_q8_rmsnorm", type, n, k, x, x_dtype, m, stride_x, k, scratch, scratch_bytes, &P);
+  if (rc) return rc;
+  if (!gamma) { set_error("kq_prepare_q8_rmsnorm: null gamma"); return KQ_EINVAL; }
+  return launch_prepare_rmsnorm(x, x_dtype, m, k, stride_x, gamma, eps, y_norm, P, (cudaStream_t)stream);
+}
+
+int kq_prepare_q8_swiglu(int type, int64_t n, int64_t k, const void* gate_up, int x_dtype, int64_t m, int64_t stride_gu,
+                         void* scratch, size_t scratch_bytes, void* stream) {
+  Q8Ptrs P;
+  int rc = prepare_common("kq_prepare_q8_swiglu", type, n, k, gate_up, x_dtype, m, stride_gu, 2 * k, scratch, scratch_bytes, &P);
+  if (rc) return rc;
+  return launch_prepare_swiglu(gate_up, x_dtype, m, k, stride_gu, P, (cudaStream_t)stream);
+}
+
 int kq_mul_mat_prepared(const void* W, int type, int64_t n, int64_t k, int64_t m, void* y, int y_dtype,
                         int64_t stride_y, int mmq, void* scratch, size_t scratch_bytes, void* stream) {
   return mul_mat("kq_mul_mat_prepared", mmq != 0, W, type, n, k, nullptr, KQ_F32, m, k, y, y_dtype, stride_y, scratch,

@@ -201,6 +201,10 @@ inline int64_t stream_rows(int64_t n, int64_t rowbytes) {
 // P may be null (then only the reference 36-byte block layout `wire36` is written)
 int launch_quantize(const void* x, int x_dtype, int64_t m, int64_t k, int64_t stride_x,
                     const Q8Ptrs* P, void* wire36, int64_t kpad, cudaStream_t st);
+int launch_prepare_rmsnorm(const void* x, int x_dtype, int64_t m, int64_t k, int64_t stride_x, const void* gamma, float eps,
+                           void* y_norm, const Q8Ptrs& P, cudaStream_t st);
+int launch_prepare_swiglu(const void* gate_up, int x_dtype, int64_t m, int64_t k, int64_t stride_gu, const Q8Ptrs& P,
+                          cudaStream_t st);
 int launch_gemv_dp4a(const void* W, int type, int64_t n, int64_t k, const void* ds, const void* qs,
                      int64_t kpad, int64_t m, void* y, int y_dtype, int64_t stride_y, bool mmq,
                      int32_t* dbg_dots, int32_t* dbg_sums, cudaStream_t st);

@@ -11,33 +11,12 @@
 
 namespace kq {
 
-// One warp per (token, 32-block).  Tokens m..16*ceil(m/16)-1 only zero-fill the transposed scale tables.
-template <typename T>
-__global__ void __launch_bounds__(256) quantize_q8_1_kernel(const T* __restrict__ x, int64_t stride_x, int k,
-                                                            int kpad, int64_t m, int64_t mpad, Q8Ptrs P,
-                                                            uint8_t* __restrict__ wire36) {
-  pdl_trigger();   // a GEMV launched behind this kernel may set up and prefetch its weights meanwhile
-  pdl_wait();      // the scratch this kernel rewrites may still be read by the launch before it
-  const int lane = threadIdx.x & 31;
+// One 32-block of one token, one value per lane (the whole warp calls this): d = amax / 127, codes, the fp32 butterfly
+// sum, and every table of the scratch layout.  tslot: index of (token tile, block, token in tile) in the transposed tables.
+__device__ __forceinline__ void quantize_block(float xi, int64_t row, int b, int lane, int kpad, int64_t tslot, const Q8Ptrs& P,
+                                               uint8_t* __restrict__ wire36) {
   const int nb = kpad >> 5;
-  const int64_t gthread = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (P.cnt != nullptr && gthread < P.ncnt) P.cnt[gthread] = 0;   // split-K counters start at zero
-  if (P.status != nullptr && gthread == 0) P.status[0] = 0;
-  const int64_t blk = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);  // global 32-block index over padded tokens
-  if (blk >= mpad * nb) return;
-  const int64_t row = blk / nb;
-  const int b = (int)(blk - row * nb);
-  const int64_t tslot = ((row >> 4) * nb + b) * 16 + (row & 15);      // [token tile][block][token in tile]
-  if (row >= m) {
-    if (P.dT != nullptr && lane == 0) {
-      P.dT[tslot] = 0.f; P.z32[tslot] = 0.f; P.zs8[tslot] = 0.f;
-      const int64_t t16 = ((row >> 4) * 2 * nb + 2 * b) * 16 + (row & 15);
-      P.z16[t16] = 0.f; P.z16[t16 + 16] = 0.f;
-    }
-    return;
-  }
   const int col = b * 32 + lane;
-  const float xi = col < k ? to_f32<T>(x[row * stride_x + col]) : 0.0f;
   float amax = fabsf(xi);
   float sum = xi;
 #pragma unroll
@@ -80,6 +59,132 @@ __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const T* __restrict_
     if (P.xh) P.s8h[row * nb + b] = sh;
     if (wire36) *reinterpret_cast<__half2*>(wire36 + (row * nb + b) * 36) = v;
   }
+}
+
+// One warp per (token, 32-block).  Tokens m..16*ceil(m/16)-1 only zero-fill the transposed scale tables.
+template <typename T>
+__global__ void __launch_bounds__(256) quantize_q8_1_kernel(const T* __restrict__ x, int64_t stride_x, int k,
+                                                            int kpad, int64_t m, int64_t mpad, Q8Ptrs P,
+                                                            uint8_t* __restrict__ wire36) {
+  pdl_trigger();   // a GEMV launched behind this kernel may set up and prefetch its weights meanwhile
+  pdl_wait();      // the scratch this kernel rewrites may still be read by the launch before it
+  const int lane = threadIdx.x & 31;
+  const int nb = kpad >> 5;
+  const int64_t gthread = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (P.cnt != nullptr && gthread < P.ncnt) P.cnt[gthread] = 0;   // split-K counters start at zero
+  if (P.status != nullptr && gthread == 0) P.status[0] = 0;
+  const int64_t blk = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);  // global 32-block index over padded tokens
+  if (blk >= mpad * nb) return;
+  const int64_t row = blk / nb;
+  const int b = (int)(blk - row * nb);
+  const int64_t tslot = ((row >> 4) * nb + b) * 16 + (row & 15);      // [token tile][block][token in tile]
+  if (row >= m) {
+    if (P.dT != nullptr && lane == 0) {
+      P.dT[tslot] = 0.f; P.z32[tslot] = 0.f; P.zs8[tslot] = 0.f;
+      const int64_t t16 = ((row >> 4) * 2 * nb + 2 * b) * 16 + (row & 15);
+      P.z16[t16] = 0.f; P.z16[t16 + 16] = 0.f;
+    }
+    return;
+  }
+  const int col = b * 32 + lane;
+  const float xi = col < k ? to_f32<T>(x[row * stride_x + col]) : 0.0f;
+  quantize_block(xi, row, b, lane, kpad, tslot, P, wire36);
+}
+
+// ---------------------------------------------------------------------------------------------- fused producers
+// The activation of a projection group is usually the output of a small elementwise or normalising kernel.  These
+// producers compute that output and quantize it in one launch, with the same per-block arithmetic as above (the
+// reference's production backend fuses the same two producers into its own activation format:
+// vllm_gguf_plugin/native/kernels/kai_prepare_ext.cuh:1-10, quantization/native_fused.py:144-200):
+//   MODE 1  RMSNorm:  a = T(T(x * rsqrt(mean(x^2) + eps)) * gamma), both roundings in the storage type T, the order of
+//                     vLLM's rms_norm kernel; optionally also stored as a dense [m, k] tensor (y_norm)
+//   MODE 2  SwiGLU:   a = T(silu(gate)) * up in T, gate = gu[:, 0:k], up = gu[:, k:2k] - vLLM's SiluAndMul
+// One CTA of 8 warps per token; tokens m..16*ceil(m/16)-1 only zero-fill the transposed scale tables.
+template <typename T> __device__ __forceinline__ T mul_in_type(T a, T b);
+template <> __device__ __forceinline__ float mul_in_type<float>(float a, float b) { return a * b; }
+template <> __device__ __forceinline__ __half mul_in_type<__half>(__half a, __half b) { return __hmul(a, b); }
+template <> __device__ __forceinline__ __nv_bfloat16 mul_in_type<__nv_bfloat16>(__nv_bfloat16 a, __nv_bfloat16 b) { return __hmul(a, b); }
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256) prepare_fused_kernel(const T* __restrict__ x, int64_t stride_x, int k, int kpad,
+                                                            int64_t m, const T* __restrict__ gamma, float eps,
+                                                            T* __restrict__ y_norm, Q8Ptrs P) {
+  pdl_trigger();
+  pdl_wait();      // the scratch this kernel rewrites, and x, may still be in use by the launch before it
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nb = kpad >> 5;
+  const int64_t row = blockIdx.x;
+  const int64_t gthread = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (int64_t i = gthread; i < P.ncnt; i += (int64_t)gridDim.x * blockDim.x) P.cnt[i] = 0;
+  if (gthread == 0) P.status[0] = 0;
+  if (row >= m) {
+    for (int b = threadIdx.x; b < nb; b += blockDim.x) {
+      const int64_t tslot = ((row >> 4) * nb + b) * 16 + (row & 15);
+      P.dT[tslot] = 0.f; P.z32[tslot] = 0.f; P.zs8[tslot] = 0.f;
+      const int64_t t16 = ((row >> 4) * 2 * nb + 2 * b) * 16 + (row & 15);
+      P.z16[t16] = 0.f; P.z16[t16 + 16] = 0.f;
+    }
+    return;
+  }
+  const T* xr = x + row * stride_x;
+  float inv = 1.0f;
+  if constexpr (MODE == 1) {
+    __shared__ float s_part[8];
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < k; c += blockDim.x) { const float v = to_f32<T>(xr[c]); ss = fmaf(v, v, ss); }
+#pragma unroll
+    for (int mask = 16; mask > 0; mask >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, mask);
+    if (lane == 0) s_part[warp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) tot += s_part[w];
+    inv = rsqrtf(tot / (float)k + eps);
+  }
+  for (int b = warp; b < nb; b += 8) {
+    const int col = b * 32 + lane;
+    float xi = 0.0f;
+    if (col < k) {
+      T a;
+      if constexpr (MODE == 1) {
+        a = mul_in_type<T>(from_f32<T>(to_f32<T>(xr[col]) * inv), gamma[col]);
+        if (y_norm != nullptr) y_norm[row * k + col] = a;
+      } else {
+        const float g = to_f32<T>(xr[col]);
+        a = mul_in_type<T>(from_f32<T>(g / (1.0f + expf(-g))), xr[k + col]);
+      }
+      xi = to_f32<T>(a);
+    }
+    const int64_t tslot = ((row >> 4) * nb + b) * 16 + (row & 15);
+    quantize_block(xi, row, b, lane, kpad, tslot, P, nullptr);
+  }
+}
+
+template <int MODE>
+static int launch_prepare_fused(const void* x, int x_dtype, int64_t m, int64_t k, int64_t stride_x, const void* gamma,
+                                float eps, void* y_norm, const Q8Ptrs& P, cudaStream_t st) {
+  const int64_t mpad = (m + 15) / 16 * 16;
+  const bool pdl = options().pdl != 0;
+  cudaError_t rc;
+  switch (x_dtype) {
+    case KQ_F32: rc = launch_pdl(prepare_fused_kernel<float, MODE>, dim3((unsigned)mpad), dim3(256), 0, st, pdl, (const float*)x, stride_x, (int)k, (int)P.kpad, m, (const float*)gamma, eps, (float*)y_norm, P); break;
+    case KQ_F16: rc = launch_pdl(prepare_fused_kernel<__half, MODE>, dim3((unsigned)mpad), dim3(256), 0, st, pdl, (const __half*)x, stride_x, (int)k, (int)P.kpad, m, (const __half*)gamma, eps, (__half*)y_norm, P); break;
+    case KQ_BF16: rc = launch_pdl(prepare_fused_kernel<__nv_bfloat16, MODE>, dim3((unsigned)mpad), dim3(256), 0, st, pdl, (const __nv_bfloat16*)x, stride_x, (int)k, (int)P.kpad, m, (const __nv_bfloat16*)gamma, eps, (__nv_bfloat16*)y_norm, P); break;
+    default: set_error("unsupported activation dtype %d", x_dtype); return KQ_EUNSUPPORTED;
+  }
+  KQ_CUDA_TRY(rc);
+  options().launches += 1;
+  KQ_CUDA_TRY(cudaGetLastError());
+  return KQ_OK;
+}
+
+int launch_prepare_rmsnorm(const void* x, int x_dtype, int64_t m, int64_t k, int64_t stride_x, const void* gamma, float eps,
+                           void* y_norm, const Q8Ptrs& P, cudaStream_t st) {
+  return launch_prepare_fused<1>(x, x_dtype, m, k, stride_x, gamma, eps, y_norm, P, st);
+}
+int launch_prepare_swiglu(const void* gate_up, int x_dtype, int64_t m, int64_t k, int64_t stride_gu, const Q8Ptrs& P,
+                          cudaStream_t st) {
+  return launch_prepare_fused<2>(gate_up, x_dtype, m, k, stride_gu, nullptr, 0.f, nullptr, P, st);
 }
 
 // GEMM-only flavour (large M): one LANE per (token, 32-block).  Writes only what the tcgen05 GEMM reads: the fp16

@@ -39,10 +39,13 @@ def test_geometry_and_workspace():
     assert capi.block_geometry(10) == (256, 84) and capi.block_geometry(12) == (256, 144)
     assert capi.block_geometry(14) == (256, 210) and capi.block_geometry(21) == (256, 110)
     with pytest.raises(capi.KqError) as e:
-        capi.block_geometry(13)
-    assert e.value.code == capi.KQ_EUNSUPPORTED and "13" in str(e.value)
+        capi.block_geometry(16)
+    assert e.value.code == capi.KQ_EUNSUPPORTED and "16" in str(e.value)
+    assert capi.block_geometry(3) == (32, 20) and capi.block_geometry(6) == (32, 22) and capi.block_geometry(7) == (32, 24)
+    assert capi.block_geometry(11) == (256, 110) and capi.block_geometry(13) == (256, 176)
+    assert capi.block_geometry(20) == (32, 18) and capi.block_geometry(23) == (256, 136)
     assert capi.workspace_bytes(12, 16, 17408, 5120) >= 16 * 5120 + 16 * 160 * 4
-    assert capi.workspace_bytes(13, 1, 1, 256) == 0
+    assert capi.workspace_bytes(16, 1, 1, 256) == 0
     assert capi.workspace_bytes(12, 1, 64, 300) >= 512 + 64     # k padded to 512
 
 
@@ -53,7 +56,7 @@ def _mm(fn, W=0x1000, qt=12, n=8, k=256, x=0x2000, xdt=0, m=1, sx=256, y=0x3000,
 @pytest.mark.parametrize("fn", ["kq_mul_mat_vec_a8", "kq_mul_mat_a8"])
 def test_mul_mat_argument_validation(fn):
     f = getattr(capi.lib, fn)
-    assert _mm(f, qt=13) == capi.KQ_EUNSUPPORTED
+    assert _mm(f, qt=16) == capi.KQ_EUNSUPPORTED
     assert "not supported" in capi.lib.kq_last_error().decode()
     assert _mm(f, k=200, sx=200) == capi.KQ_EINVAL
     assert "multiple of the block" in capi.lib.kq_last_error().decode()
@@ -73,9 +76,10 @@ def test_mul_mat_argument_validation(fn):
     assert "scratch too small" in capi.lib.kq_last_error().decode()
 
 
-def test_iq3s_has_no_mmq():
-    assert _mm(capi.lib.kq_mul_mat_a8, qt=21) == capi.KQ_EUNSUPPORTED
-    assert "IQ3_S" in capi.lib.kq_last_error().decode()
+def test_imatrix_formats_have_no_mmq():
+    for qt in (21, 20, 23):
+        assert _mm(capi.lib.kq_mul_mat_a8, qt=qt, k=256, sx=256) == capi.KQ_EUNSUPPORTED
+        assert "no MMQ kernel" in capi.lib.kq_last_error().decode()
 
 
 def test_dequantize_and_quantize_validation():

@@ -340,7 +340,7 @@ def test_unsupported_type_raises_on_gpu_too():
     _, wt = wire(12, 8, 256, seed=0)
     _, xt = act(1, 256, seed=0, dt="f32")
     with pytest.raises(capi.KqError) as e:
-        capi.mul_mat(wt, xt, 13)
+        capi.mul_mat(wt, xt, 16)
     assert e.value.code == capi.KQ_EUNSUPPORTED
 
 
