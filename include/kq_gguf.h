@@ -188,6 +188,14 @@ int kq_debug_group_dots(const void* W, int type, int64_t n, int64_t k,
 int kq_p2p_allgather(const void* src, size_t bytes, void* const* peer_dst, uint32_t* const* peer_flags,
                      uint32_t* epoch, uint32_t* done, int slot, int rank, int world, int* status, void* stream);
 
+/* The same gather into ROW-MAJOR [M, N] buffers: this rank's slice is [rows][row_bytes] (contiguous) and lands as
+ * columns rank * row_bytes .. (rank + 1) * row_bytes of every rank's buffer, whose rows are dst_row_stride bytes apart
+ * (>= world * row_bytes).  When the kernel has completed, the local buffer is the layer's full output as the next
+ * layer reads it, with no transposing copy.  Everything else as kq_p2p_allgather. */
+int kq_p2p_allgather_2d(const void* src, int64_t rows, size_t row_bytes, void* const* peer_dst, size_t dst_row_stride,
+                        uint32_t* const* peer_flags, uint32_t* epoch, uint32_t* done, int slot, int rank, int world,
+                        int* status, void* stream);
+
 /* Diagnostics: copies the device-side status word of a scratch buffer to the host (SYNCHRONISES with the
  * device; not for the serving path).  0 = every kernel that used the scratch finished normally; non-zero = a
  * bounded wait inside a kernel gave up and the kernel returned early (its outputs are then undefined).

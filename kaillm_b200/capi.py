@@ -23,6 +23,7 @@ EXPORTS = (
     "kq_mul_mat_vec_a8", "kq_mul_mat_a8", "kq_dequantize", "kq_debug_group_dots", "kq_set_option",
     "kq_get_option", "kq_prepare_q8", "kq_mul_mat_prepared", "kq_read_status", "kq_mul_mat_vec_a8_static",
     "kq_p2p_allgather", "kq_read_status_static", "kq_debug_copy_window", "kq_prepare_q8_rmsnorm", "kq_prepare_q8_swiglu",
+    "kq_p2p_allgather_2d",
 )
 
 
@@ -61,6 +62,7 @@ def _load() -> ctypes.CDLL:
     lib.kq_read_status_static.argtypes = [ctypes.POINTER(i32)]
     u64p = ctypes.POINTER(ctypes.c_uint64)
     lib.kq_debug_copy_window.argtypes = [ctypes.c_uint64, i64, i64, i64, i64, i64, i64, ctypes.POINTER(i64), u64p, u64p]
+    lib.kq_p2p_allgather_2d.argtypes = [vp, i64, sz, ctypes.POINTER(vp), sz, ctypes.POINTER(vp), vp, vp, i32, i32, i32, vp, vp]
     lib.kq_set_option.argtypes = [ctypes.c_char_p, i32]
     lib.kq_get_option.argtypes = [ctypes.c_char_p, ctypes.POINTER(i32)]
     return lib
@@ -213,6 +215,20 @@ def p2p_allgather(src: torch.Tensor, peer_dst: list[int], peer_flags: list[int],
     with torch.cuda.device(src.device):
         _check(lib.kq_p2p_allgather(src.data_ptr(), src.numel() * src.element_size(), dst, flg, epoch.data_ptr(),
                                     done.data_ptr(), slot, rank, world, status.data_ptr(), _stream(src.device)))
+
+
+def p2p_allgather_2d(src: torch.Tensor, peer_dst: list[int], dst_row_stride: int, peer_flags: list[int], epoch: torch.Tensor,
+                     done: torch.Tensor, slot: int, rank: int, status: torch.Tensor) -> None:
+    """kq_p2p_allgather_2d: `src` [M, N/world] (contiguous) becomes columns rank*N/world.. of every rank's row-major
+    [M, N] buffer (rows `dst_row_stride` bytes apart)."""
+    world = len(peer_dst)
+    dst = (ctypes.c_void_p * world)(*peer_dst)
+    flg = (ctypes.c_void_p * world)(*peer_flags)
+    rows, per = src.shape
+    with torch.cuda.device(src.device):
+        _check(lib.kq_p2p_allgather_2d(src.data_ptr(), rows, per * src.element_size(), dst, dst_row_stride, flg,
+                                       epoch.data_ptr(), done.data_ptr(), slot, rank, world, status.data_ptr(),
+                                       _stream(src.device)))
 
 
 def dequantize(W: torch.Tensor, qtype: int, count: int, dtype=torch.float16) -> torch.Tensor:

@@ -316,7 +316,18 @@ int kq_p2p_allgather(const void* src, size_t bytes, void* const* peer_dst, uint3
     set_error("kq_p2p_allgather: null pointer argument");
     return KQ_EINVAL;
   }
-  return launch_p2p_allgather(src, bytes, peer_dst, peer_flags, epoch, done, slot, rank, world, status, (cudaStream_t)stream);
+  return launch_p2p_allgather(src, bytes, 0, 0, peer_dst, peer_flags, epoch, done, slot, rank, world, status, (cudaStream_t)stream);
+}
+
+int kq_p2p_allgather_2d(const void* src, int64_t rows, size_t row_bytes, void* const* peer_dst, size_t dst_row_stride,
+                        uint32_t* const* peer_flags, uint32_t* epoch, uint32_t* done, int slot, int rank, int world,
+                        int* status, void* stream) {
+  if (!src || !peer_dst || !peer_flags || !epoch || !done || !status || rows <= 0) {
+    set_error("kq_p2p_allgather_2d: null pointer or non-positive row count");
+    return KQ_EINVAL;
+  }
+  return launch_p2p_allgather(src, (size_t)rows * row_bytes, rows, dst_row_stride, peer_dst, peer_flags, epoch, done, slot, rank,
+                              world, status, (cudaStream_t)stream);
 }
 
 int kq_debug_copy_window(uint64_t base, int64_t n, int64_t rowbytes, int64_t row_a, int64_t row_b, int64_t seg_off,

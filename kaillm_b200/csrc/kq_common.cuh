@@ -223,8 +223,9 @@ bool gemv_kres_supported(const void* W, int type, int64_t n, int64_t k, int mtok
 int gemv_kres_splits(int type, int64_t n, int64_t k, int mtok);
 int launch_gemv_kres(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m0, int mcount, void* y,
                      int y_dtype, int64_t stride_y, bool mmq, cudaStream_t st);
-int launch_p2p_allgather(const void* src, size_t bytes, void* const* peer_dst, uint32_t* const* peer_flags,
-                         uint32_t* epoch, uint32_t* done, int slot, int rank, int world, int* status, cudaStream_t st);
+int launch_p2p_allgather(const void* src, size_t bytes, int64_t rows, size_t dst_stride, void* const* peer_dst,
+                         uint32_t* const* peer_flags, uint32_t* epoch, uint32_t* done, int slot, int rank, int world,
+                         int* status, cudaStream_t st);
 bool gemm_tc_supported(const void* W, int type, int64_t n, int64_t k);
 int launch_gemm_tc(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m, void* y, int y_dtype,
                    int64_t stride_y, bool mmq, cudaStream_t st);

@@ -438,6 +438,8 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
         cdst[i] = smem_u32(sW + r * SROW + part * PIECE_B);
       }
     }
+    const bool holds_last_row = (row_tile + 1) * RT * BM >= p.n;   // rows past n are clamped to row n - 1
+    const int last_sblk = p.k / 256 - 1;
     auto stage_block = [&](int sblk) {                          // issue the copies of super-block column sblk
       if constexpr (QT == KQ_TYPE_Q4_K) {
 #pragma unroll
@@ -447,16 +449,23 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
       }
       if constexpr (QT == KQ_TYPE_Q6_K) {
         const size_t col = ((size_t)sblk * 210) & ~(size_t)7;   // rows and W are 8-byte aligned: the same for every row
-        // the aligned window of the last block of the last row may reach up to 6 bytes past the tensor: such a piece
-        // reads only the bytes that exist (the rest of its 8 bytes is zero-filled)
-        const uint8_t* wend = p.W + (size_t)p.n * p.rowbytes;
+        // The aligned window of the LAST block of the LAST row may reach up to 6 bytes past the tensor.  Only a CTA
+        // that holds that row, and only at that block, takes the careful path, where a piece reads just the bytes
+        // that exist (the rest of its 8 bytes is zero-filled); everywhere else the plain 8-byte copies run.
+        if (holds_last_row && sblk == last_sblk) {
+          const uint8_t* wend = p.W + (size_t)p.n * p.rowbytes;
 #pragma unroll
-        for (int i = 0; i < NCHUNK; ++i)
-          if (csrc[i]) {
-            const uint8_t* src = csrc[i] + col;
-            const uint32_t have = src + 8 <= wend ? 8u : (src < wend ? (uint32_t)(wend - src) : 0u);
-            asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(cdst[i]), "l"(src), "r"(have) : "memory");
-          }
+          for (int i = 0; i < NCHUNK; ++i)
+            if (csrc[i]) {
+              const uint8_t* src = csrc[i] + col;
+              const uint32_t have = src + 8 <= wend ? 8u : (src < wend ? (uint32_t)(wend - src) : 0u);
+              asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(cdst[i]), "l"(src), "r"(have) : "memory");
+            }
+        } else {
+#pragma unroll
+          for (int i = 0; i < NCHUNK; ++i)
+            if (csrc[i]) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(cdst[i]), "l"(csrc[i] + col) : "memory");
+        }
         asm volatile("cp.async.commit_group;" ::: "memory");
       }
     };

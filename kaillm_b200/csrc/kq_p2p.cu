@@ -27,7 +27,10 @@ constexpr long long P2P_WAIT_LIMIT = 1ll << 32;
 
 struct P2PParams {
   const uint8_t* src;
-  size_t bytes;
+  size_t bytes;                       // of the whole slice (rows * row_bytes)
+  size_t row_bytes;                   // bytes per row of the slice (== bytes for the rank-major layout)
+  size_t dst_stride;                  // bytes between rows in the destination buffers
+  size_t dst_off;                     // where this rank's first row starts in every destination buffer
   uint8_t* dst[P2P_MAX_RANKS];        // each rank's gather buffer (world * bytes)
   uint32_t* flags[P2P_MAX_RANKS];     // each rank's flag array [slots][P2P_MAX_RANKS]
   uint32_t* epoch;                    // local: calls made so far per slot
@@ -49,16 +52,18 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 __global__ void __launch_bounds__(1024) p2p_allgather_kernel(const P2PParams p) {
   const size_t nvec = p.bytes / 16;
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nthr = (size_t)gridDim.x * blockDim.x;
-  const size_t off0 = (size_t)p.rank * p.bytes;
+  // byte i of the slice = (row i / row_bytes, column i % row_bytes) -> dst_off + row * dst_stride + column
   if (p.vec16) {
     for (size_t i = tid; i < nvec; i += nthr) {
-      const uint4 v = *reinterpret_cast<const uint4*>(p.src + i * 16);
-      for (int r = 0; r < p.world; ++r) *reinterpret_cast<uint4*>(p.dst[r] + off0 + i * 16) = v;
+      const size_t b = i * 16, row = b / p.row_bytes, col = b - row * p.row_bytes;
+      const uint4 v = *reinterpret_cast<const uint4*>(p.src + b);
+      for (int r = 0; r < p.world; ++r) *reinterpret_cast<uint4*>(p.dst[r] + p.dst_off + row * p.dst_stride + col) = v;
     }
   } else {
     for (size_t i = tid; i < p.bytes; i += nthr) {
+      const size_t row = i / p.row_bytes, col = i - row * p.row_bytes;
       const uint8_t v = p.src[i];
-      for (int r = 0; r < p.world; ++r) p.dst[r][off0 + i] = v;
+      for (int r = 0; r < p.world; ++r) p.dst[r][p.dst_off + row * p.dst_stride + col] = v;
     }
   }
   __syncthreads();
@@ -96,8 +101,11 @@ __global__ void __launch_bounds__(1024) p2p_allgather_kernel(const P2PParams p) 
 
 }  // namespace
 
-int launch_p2p_allgather(const void* src, size_t bytes, void* const* peer_dst, uint32_t* const* peer_flags,
-                         uint32_t* epoch, uint32_t* done, int slot, int rank, int world, int* status, cudaStream_t st) {
+// rows == 0: the rank-major layout (the slice lands at rank * bytes of every buffer); rows > 0: the slice is
+// [rows][row_bytes] and lands as columns rank * row_bytes .. of row-major buffers with row stride dst_stride
+int launch_p2p_allgather(const void* src, size_t bytes, int64_t rows, size_t dst_stride, void* const* peer_dst,
+                         uint32_t* const* peer_flags, uint32_t* epoch, uint32_t* done, int slot, int rank, int world,
+                         int* status, cudaStream_t st) {
   if (world < 1 || world > P2P_MAX_RANKS || rank < 0 || rank >= world || slot < 0) {
     set_error("kq_p2p_allgather: world %d (max %d), rank %d, slot %d", world, P2P_MAX_RANKS, rank, slot);
     return KQ_EINVAL;
@@ -106,7 +114,15 @@ int launch_p2p_allgather(const void* src, size_t bytes, void* const* peer_dst, u
   P2PParams p;
   p.src = (const uint8_t*)src; p.bytes = bytes; p.epoch = epoch; p.done = done; p.status = status;
   p.slot = slot; p.rank = rank; p.world = world;
-  uintptr_t bits = (uintptr_t)src | (uintptr_t)bytes;   // rank * bytes is then aligned as well
+  if (rows > 0) {
+    if (bytes % (size_t)rows) { set_error("kq_p2p_allgather_2d: bytes is not a multiple of rows"); return KQ_EINVAL; }
+    p.row_bytes = bytes / (size_t)rows; p.dst_stride = dst_stride; p.dst_off = (size_t)rank * p.row_bytes;
+    if (dst_stride < (size_t)world * p.row_bytes) { set_error("kq_p2p_allgather_2d: destination row stride too small"); return KQ_EINVAL; }
+  } else {
+    p.row_bytes = bytes; p.dst_stride = 0; p.dst_off = (size_t)rank * bytes;
+  }
+  // 16-byte stores: source, slice and row size, destination stride and every buffer aligned
+  uintptr_t bits = (uintptr_t)src | (uintptr_t)bytes | (uintptr_t)p.row_bytes | (uintptr_t)p.dst_stride;
   for (int r = 0; r < P2P_MAX_RANKS; ++r) {
     p.dst[r] = r < world ? (uint8_t*)peer_dst[r] : nullptr;
     p.flags[r] = r < world ? peer_flags[r] : nullptr;

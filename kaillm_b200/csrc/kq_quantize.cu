@@ -99,7 +99,9 @@ __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const T* __restrict_
 //   MODE 1  RMSNorm:  a = T(T(x * rsqrt(mean(x^2) + eps)) * gamma), both roundings in the storage type T, the order of
 //                     vLLM's rms_norm kernel; optionally also stored as a dense [m, k] tensor (y_norm)
 //   MODE 2  SwiGLU:   a = T(silu(gate)) * up in T, gate = gu[:, 0:k], up = gu[:, k:2k] - vLLM's SiluAndMul
-// One CTA of 8 warps per token; tokens m..16*ceil(m/16)-1 only zero-fill the transposed scale tables.
+// Grid = (tokens padded to 16, chunks of 8 blocks): one warp per 32-block, as in the plain quantizer; every CTA of an
+// RMSNorm row recomputes the row's sum of squares (k loads per CTA, from L2).  Tokens m..16*ceil(m/16)-1 only
+// zero-fill the transposed scale tables.
 template <typename T> __device__ __forceinline__ T mul_in_type(T a, T b);
 template <> __device__ __forceinline__ float mul_in_type<float>(float a, float b) { return a * b; }
 template <> __device__ __forceinline__ __half mul_in_type<__half>(__half a, __half b) { return __hmul(a, b); }
@@ -114,11 +116,12 @@ __global__ void __launch_bounds__(256) prepare_fused_kernel(const T* __restrict_
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nb = kpad >> 5;
   const int64_t row = blockIdx.x;
-  const int64_t gthread = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  for (int64_t i = gthread; i < P.ncnt; i += (int64_t)gridDim.x * blockDim.x) P.cnt[i] = 0;
+  const int b = blockIdx.y * 8 + warp;                 // this warp's 32-block
+  const int64_t gthread = ((int64_t)blockIdx.y * gridDim.x + blockIdx.x) * blockDim.x + threadIdx.x;
+  for (int64_t i = gthread; i < P.ncnt; i += (int64_t)gridDim.x * gridDim.y * blockDim.x) P.cnt[i] = 0;
   if (gthread == 0) P.status[0] = 0;
   if (row >= m) {
-    for (int b = threadIdx.x; b < nb; b += blockDim.x) {
+    if (b < nb && lane == 0) {
       const int64_t tslot = ((row >> 4) * nb + b) * 16 + (row & 15);
       P.dT[tslot] = 0.f; P.z32[tslot] = 0.f; P.zs8[tslot] = 0.f;
       const int64_t t16 = ((row >> 4) * 2 * nb + 2 * b) * 16 + (row & 15);
@@ -141,7 +144,7 @@ __global__ void __launch_bounds__(256) prepare_fused_kernel(const T* __restrict_
     for (int w = 0; w < 8; ++w) tot += s_part[w];
     inv = rsqrtf(tot / (float)k + eps);
   }
-  for (int b = warp; b < nb; b += 8) {
+  if (b < nb) {
     const int col = b * 32 + lane;
     float xi = 0.0f;
     if (col < k) {
@@ -165,11 +168,12 @@ static int launch_prepare_fused(const void* x, int x_dtype, int64_t m, int64_t k
                                 float eps, void* y_norm, const Q8Ptrs& P, cudaStream_t st) {
   const int64_t mpad = (m + 15) / 16 * 16;
   const bool pdl = options().pdl != 0;
+  const dim3 grid((unsigned)mpad, (unsigned)((P.kpad / 32 + 7) / 8));
   cudaError_t rc;
   switch (x_dtype) {
-    case KQ_F32: rc = launch_pdl(prepare_fused_kernel<float, MODE>, dim3((unsigned)mpad), dim3(256), 0, st, pdl, (const float*)x, stride_x, (int)k, (int)P.kpad, m, (const float*)gamma, eps, (float*)y_norm, P); break;
-    case KQ_F16: rc = launch_pdl(prepare_fused_kernel<__half, MODE>, dim3((unsigned)mpad), dim3(256), 0, st, pdl, (const __half*)x, stride_x, (int)k, (int)P.kpad, m, (const __half*)gamma, eps, (__half*)y_norm, P); break;
-    case KQ_BF16: rc = launch_pdl(prepare_fused_kernel<__nv_bfloat16, MODE>, dim3((unsigned)mpad), dim3(256), 0, st, pdl, (const __nv_bfloat16*)x, stride_x, (int)k, (int)P.kpad, m, (const __nv_bfloat16*)gamma, eps, (__nv_bfloat16*)y_norm, P); break;
+    case KQ_F32: rc = launch_pdl(prepare_fused_kernel<float, MODE>, grid, dim3(256), 0, st, pdl, (const float*)x, stride_x, (int)k, (int)P.kpad, m, (const float*)gamma, eps, (float*)y_norm, P); break;
+    case KQ_F16: rc = launch_pdl(prepare_fused_kernel<__half, MODE>, grid, dim3(256), 0, st, pdl, (const __half*)x, stride_x, (int)k, (int)P.kpad, m, (const __half*)gamma, eps, (__half*)y_norm, P); break;
+    case KQ_BF16: rc = launch_pdl(prepare_fused_kernel<__nv_bfloat16, MODE>, grid, dim3(256), 0, st, pdl, (const __nv_bfloat16*)x, stride_x, (int)k, (int)P.kpad, m, (const __nv_bfloat16*)gamma, eps, (__nv_bfloat16*)y_norm, P); break;
     default: set_error("unsupported activation dtype %d", x_dtype); return KQ_EUNSUPPORTED;
   }
   KQ_CUDA_TRY(rc);

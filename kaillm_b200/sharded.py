@@ -99,6 +99,20 @@ class P2PGather:
         off = self.flag_bytes + b * self.buf_bytes
         return self.mem[off:off + self.world * nbytes].view(y_local.dtype).view(self.world, m, per)
 
+    def gather_cols(self, y_local: torch.Tensor, b: int) -> torch.Tensor:
+        """One kernel launch; returns the local buffer viewed as the row-major [M, N] output (rank r wrote columns
+        r*N/world ..), ready to be read by the next layer without a transposing copy."""
+        m, per = y_local.shape
+        y_local = y_local.contiguous()
+        nbytes = y_local.numel() * y_local.element_size()
+        if nbytes > self.max_bytes or not 0 <= b < self.nbuf:
+            raise ValueError(f"slice of {nbytes} bytes / buffer {b} outside what this P2PGather was sized for")
+        dst = [p + b * self.buf_bytes for p in self.data_ptrs]
+        row_stride = self.world * per * y_local.element_size()
+        self._capi.p2p_allgather_2d(y_local, dst, row_stride, self.flag_ptrs, self.epoch, self.done, b, self.rank, self.status)
+        off = self.flag_bytes + b * self.buf_bytes
+        return self.mem[off:off + self.world * nbytes].view(y_local.dtype).view(m, self.world * per)
+
     def check(self) -> None:
         """Synchronises; raises if any gather's bounded wait for a peer ran out."""
         st = int(self.status.item())
@@ -126,3 +140,96 @@ class ShardedGGUFLinear:
 
     def apply(self, x: torch.Tensor) -> torch.Tensor:
         return gather_columns(self.local(x), self.group)
+
+
+class DecoderStack:
+    """The linear layers of a decoder stack, row-sharded, chained through the fused activation producers.
+
+    Per layer, in the order a transformer runs them (attention itself is not part of this path and is left out):
+
+        h  -> RMSNorm -> q8_1 -> merged q/k/v projection  [M, 8192]   -> all-gather
+           -> q8_1 of the first `hidden` columns -> o projection [M, hidden] -> all-gather
+           -> RMSNorm -> q8_1 -> merged gate/up projection [M, 2*ffn] -> all-gather
+           -> silu(gate) * up -> q8_1 -> down projection [M, hidden]  -> all-gather -> h of the next layer
+
+    Merged projections are ONE weight tensor and ONE call, as the reference runs same-type merged layers
+    (quantization/linear.py:377-381); every projection is sharded on its output rows (quantization/params.py:230-247), so
+    each call ends in an all-gather of `[M, N/world]` slices into a row-major `[M, N]` buffer that the next producer
+    reads in place.  Each projection group costs one producer launch (activation + quantization), one GEMV launch and,
+    with more than one rank, one gather launch.
+
+    weights: per layer a dict {"qkv", "o", "gate_up", "down"} -> (local shard uint8 [N/world, rowbytes], type, N, K).
+    """
+
+    GROUPS = ("qkv", "o", "gate_up", "down")
+
+    def __init__(self, weights: list[dict], m: int, hidden: int, device: torch.device, p2p: "P2PGather | None" = None,
+                 group=None, eps: float = 1e-6, dtype: torch.dtype = torch.bfloat16):
+        from . import capi
+        self._capi = capi
+        self.w = weights
+        self.m, self.hidden, self.eps, self.dtype = m, hidden, eps, dtype
+        self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        self.group = group
+        self.p2p = p2p
+        self.dev = device
+        self.gamma = torch.ones(hidden, dtype=dtype, device=device)
+        ws = 0
+        self.nfull = {}
+        for name in self.GROUPS:
+            _, qt, n, k = weights[0][name]
+            self.nfull[name] = n
+            ws = max(ws, capi.workspace_bytes(qt, m, n // self.world, k))
+        self.scratch = torch.empty(ws, dtype=torch.uint8, device=device)
+        self.ylocal = {name: torch.empty((m, self.nfull[name] // self.world), dtype=dtype, device=device) for name in self.GROUPS}
+        # world == 1: the GEMV writes the full output itself; otherwise the gather buffers (slot = index in GROUPS)
+        self.yfull = {name: torch.empty((m, self.nfull[name]), dtype=dtype, device=device) for name in self.GROUPS} if self.world == 1 else {}
+        self.nccl_buf = {}
+        if self.world > 1 and p2p is None:
+            self.nccl_buf = {name: torch.empty((self.world, m, self.nfull[name] // self.world), dtype=dtype, device=device)
+                             for name in self.GROUPS}
+
+    def _project(self, name: str, W: torch.Tensor, qt: int, n: int, k: int, check=None) -> torch.Tensor:
+        """GEMV on the activations held in self.scratch, then the gather; returns the row-major [M, N] output."""
+        capi = self._capi
+        if self.world == 1:
+            out = self.yfull[name]
+            capi.mul_mat_prepared(W, qt, self.m, k, out, self.scratch)
+            return out
+        yl = self.ylocal[name]
+        capi.mul_mat_prepared(W, qt, self.m, k, yl, self.scratch)
+        if self.p2p is not None:
+            return self.p2p.gather_cols(yl, self.GROUPS.index(name))
+        buf = self.nccl_buf[name]
+        dist.all_gather_into_tensor(buf, yl, group=self.group)
+        return buf.permute(1, 0, 2).reshape(self.m, n)     # a transposing copy: the baseline the peer-store gather removes
+
+    def forward(self, h: torch.Tensor, on_output=None) -> torch.Tensor:
+        """One pass over all layers.  on_output(layer, name, full_output, prepare): hook for verification - `prepare(s)`
+        re-runs this group's producer into another scratch `s`."""
+        capi = self._capi
+        m, hid = self.m, self.hidden
+        for li, layer in enumerate(self.w):
+            W, qt, n, k = layer["qkv"]
+            prep = lambda s, n_=n, qt_=qt, h_=h: capi.prepare_q8_rmsnorm(h_, self.gamma, self.eps, qt_, n_, s)   # noqa: E731
+            capi.prepare_q8_rmsnorm(h, self.gamma, self.eps, qt, n // self.world, self.scratch)
+            qkv = self._project("qkv", W, qt, n, k)
+            if on_output: on_output(li, "qkv", qkv, prep)
+            W, qt, n, k = layer["o"]
+            a = qkv[:, :hid]                                   # stands in for the attention output: [M, hidden], row stride 8192
+            prep = lambda s, n_=n, qt_=qt, a_=a: capi.prepare_q8(a_, qt_, n_, s)   # noqa: E731
+            capi.prepare_q8(a, qt, n // self.world, self.scratch)
+            o = self._project("o", W, qt, n, k)
+            if on_output: on_output(li, "o", o, prep)
+            W, qt, n, k = layer["gate_up"]
+            prep = lambda s, n_=n, qt_=qt, o_=o: capi.prepare_q8_rmsnorm(o_, self.gamma, self.eps, qt_, n_, s)   # noqa: E731
+            capi.prepare_q8_rmsnorm(o, self.gamma, self.eps, qt, n // self.world, self.scratch)
+            gu = self._project("gate_up", W, qt, n, k)
+            if on_output: on_output(li, "gate_up", gu, prep)
+            W, qt, n, k = layer["down"]
+            prep = lambda s, n_=n, qt_=qt, gu_=gu: capi.prepare_q8_swiglu(gu_, qt_, n_, s)   # noqa: E731
+            capi.prepare_q8_swiglu(gu, qt, n // self.world, self.scratch)
+            h = self._project("down", W, qt, n, k)
+            if on_output: on_output(li, "down", h, prep)
+        return h

