@@ -275,7 +275,10 @@ def run_multi(args, torch, dist, dev, rank, world, local):
         try:
             maxb = C3_M * max(n for _, _, n, _ in C3_GROUPS) // world * 2
             p2p = sharded.P2PGather(max_bytes=maxb, nbuf=4, device=dev)
-            gather_how = "kq_p2p_allgather_2d (peer stores over NVLink into row-major buffers)"
+            gather_how = "kq_mul_mat_prepared_gather: 16-byte peer stores over NVLink from the GEMV's own epilogue into every rank's row-major buffer"
+            if args.no_fused_gather:
+                capi.set_option("no_fused_gather", 1)
+                gather_how = "kq_mul_mat_prepared_gather, two kernels (GEMV, then peer-store gather kernel)"
         except Exception as e:  # noqa: BLE001 - keep the NCCL path
             print(f"[bench] symmetric memory unavailable ({e!r}); using NCCL", file=sys.stderr)
     stack = sharded.DecoderStack(weights, C3_M, K_HID, dev, p2p=p2p)
@@ -322,8 +325,7 @@ def run_multi(args, torch, dist, dev, rank, world, local):
         barrier()                                   # every rank has set up its buffers before the first peer store
         h_ref = stack.forward(x0, on_output=on_output).clone()
         torch.cuda.synchronize()
-        if p2p is not None:
-            p2p.check()
+        stack.check()
         # every rank must hold the same gathered bits: compare a checksum of the final hidden state across ranks
         cs = h_ref.view(torch.int16).to(torch.int64).sum().reshape(1)
         lo, hi = cs.clone(), cs.clone()
@@ -384,15 +386,15 @@ def run_multi(args, torch, dist, dev, rank, world, local):
         t2 = torch.tensor([e0.elapsed_time(e1)], device=dev)
         dist.all_reduce(t2, op=dist.ReduceOp.MAX)
         ms_e2e = float(t2.item()) / esteps
-    if p2p is not None:
-        p2p.check()
+    stack.check()
     nbytes = c3_bytes(layers)
     value = nbytes / (ms_step * 1e-3) / 1e9
     if rank == 0:
         cfg = workload_config(world)
         cfg.update({"layers": layers, "bytes_per_step": nbytes, "gather": gather_how,
-                    "launch": "cuda graph replay" if captured else "eager",
-                    "per_layer": "4 x (activation producer + GEMV + gather): RMSNorm->q8_1, q8_1, RMSNorm->q8_1, SwiGLU->q8_1"})
+                    "launch": "cuda graph replay" if captured else "eager", "launches_per_step": launches_step,
+                    "gemv_and_gather_in_one_kernel": dict(stack.fused),
+                    "per_layer": "4 x (activation producer + GEMV with gather): RMSNorm->q8_1, q8_1, RMSNorm->q8_1, SwiGLU->q8_1"})
         print(json.dumps({
             "metric": "quantized GEMV HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
@@ -706,6 +708,7 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=0, help="layers of the stack (default: 16 MLP blocks at N=1, 64 decoder layers at N>1)")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-fused-gather", action="store_true", help="N>1: GEMV and peer-store gather as two kernels")
     ap.add_argument("--nccl", action="store_true", help="N>1: gather with NCCL instead of the library's peer-store kernel")
     ap.add_argument("--quick", action="store_true", help="N=1: only the main workload, roofline and e2e (no further legs)")
     args = ap.parse_args()

@@ -196,6 +196,28 @@ int kq_p2p_allgather_2d(const void* src, int64_t rows, size_t row_bytes, void* c
                         uint32_t* const* peer_flags, uint32_t* epoch, uint32_t* done, int slot, int rank, int world,
                         int* status, void* stream);
 
+/* A row(N)-sharded linear layer and the all-gather that follows it, as ONE kernel where that is possible: this rank's
+ * [n_local, k] slice of the weight matrix times the prepared activations (kq_prepare_q8*), with the outputs stored as
+ * columns rank * n_local .. of every rank's row-major [m, stride_y] buffer by plain 16-byte peer stores from the GEMV's
+ * own epilogue; the CTA that finishes last raises flag[slot][rank] on every rank and waits (bounded, about two seconds)
+ * for theirs, so when the kernel has completed the local buffer is the layer's whole output.  It replaces the pair
+ * "ggml_mul_mat_vec_a8 on the rank's shard + tensor_model_parallel_all_gather" of vLLM's column-parallel GGUF layers
+ * (shards: vllm_gguf_plugin/quantization/params.py:230-247); the reference has no such kernel.
+ *   peer_y       HOST array of `world` device pointers: every rank's output buffer, mapped into this process
+ *   stride_y     elements between rows of those buffers (>= world * n_local)
+ *   peer_flags, epoch, done, slot, rank, world   as kq_p2p_allgather (the two entries may share flag arrays)
+ *   peer_status  LOCAL device int, as `status` of kq_p2p_allgather: set non-zero when the bounded wait for a peer's
+ *                flag ran out (16 + rank of the silent peer from the fused kernel, 1 + rank from the gather kernel); the
+ *                library never clears it, so one word can watch a whole sequence of calls
+ *   fused        out, may be NULL: 1 = one kernel; 0 = two (the usual kernel dispatch into this rank's own columns, then
+ *                the gather kernel) - taken for m > 16, for shapes the shared-stage kernel does not cover, for buffers
+ *                whose rows are not 16-byte aligned, and with option "no_fused_gather"
+ * world == 1 degenerates to kq_mul_mat_prepared. */
+int kq_mul_mat_prepared_gather(const void* W, int type, int64_t n_local, int64_t k, int64_t m, int y_dtype, int mmq,
+                               void* scratch, size_t scratch_bytes, void* const* peer_y, int64_t stride_y,
+                               uint32_t* const* peer_flags, uint32_t* epoch, uint32_t* done, int slot, int rank,
+                               int world, int* peer_status, int* fused, void* stream);
+
 /* Diagnostics: copies the device-side status word of a scratch buffer to the host (SYNCHRONISES with the
  * device; not for the serving path).  0 = every kernel that used the scratch finished normally; non-zero = a
  * bounded wait inside a kernel gave up and the kernel returned early (its outputs are then undefined).

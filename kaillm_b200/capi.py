@@ -23,7 +23,7 @@ EXPORTS = (
     "kq_mul_mat_vec_a8", "kq_mul_mat_a8", "kq_dequantize", "kq_debug_group_dots", "kq_set_option",
     "kq_get_option", "kq_prepare_q8", "kq_mul_mat_prepared", "kq_read_status", "kq_mul_mat_vec_a8_static",
     "kq_p2p_allgather", "kq_read_status_static", "kq_debug_copy_window", "kq_prepare_q8_rmsnorm", "kq_prepare_q8_swiglu",
-    "kq_p2p_allgather_2d",
+    "kq_p2p_allgather_2d", "kq_mul_mat_prepared_gather",
 )
 
 
@@ -63,6 +63,8 @@ def _load() -> ctypes.CDLL:
     u64p = ctypes.POINTER(ctypes.c_uint64)
     lib.kq_debug_copy_window.argtypes = [ctypes.c_uint64, i64, i64, i64, i64, i64, i64, ctypes.POINTER(i64), u64p, u64p]
     lib.kq_p2p_allgather_2d.argtypes = [vp, i64, sz, ctypes.POINTER(vp), sz, ctypes.POINTER(vp), vp, vp, i32, i32, i32, vp, vp]
+    lib.kq_mul_mat_prepared_gather.argtypes = [vp, i32, i64, i64, i64, i32, i32, vp, sz, ctypes.POINTER(vp), i64,
+                                               ctypes.POINTER(vp), vp, vp, i32, i32, i32, vp, ctypes.POINTER(i32), vp]
     lib.kq_set_option.argtypes = [ctypes.c_char_p, i32]
     lib.kq_get_option.argtypes = [ctypes.c_char_p, ctypes.POINTER(i32)]
     return lib
@@ -229,6 +231,23 @@ def p2p_allgather_2d(src: torch.Tensor, peer_dst: list[int], dst_row_stride: int
         _check(lib.kq_p2p_allgather_2d(src.data_ptr(), rows, per * src.element_size(), dst, dst_row_stride, flg,
                                        epoch.data_ptr(), done.data_ptr(), slot, rank, world, status.data_ptr(),
                                        _stream(src.device)))
+
+
+def mul_mat_prepared_gather(W: torch.Tensor, qtype: int, m: int, k: int, scratch: torch.Tensor, peer_y: list[int],
+                            stride_y: int, dtype, peer_flags: list[int], epoch: torch.Tensor, done: torch.Tensor,
+                            slot: int, rank: int, status: torch.Tensor, mmq: bool = False) -> bool:
+    """kq_mul_mat_prepared_gather: this rank's weight slice `W` [N/world, row bytes] times the activations prepared in
+    `scratch`, written as columns rank*N/world.. of every rank's row-major buffer (`peer_y`: device addresses, rows
+    `stride_y` elements apart).  Returns True when GEMV and gather ran as one kernel."""
+    world = len(peer_y)
+    ys = (ctypes.c_void_p * world)(*peer_y)
+    flg = (ctypes.c_void_p * world)(*peer_flags)
+    fused = ctypes.c_int(0)
+    with torch.cuda.device(W.device):
+        _check(lib.kq_mul_mat_prepared_gather(W.data_ptr(), qtype, W.shape[0], k, m, _DT[dtype], int(mmq), scratch.data_ptr(),
+                                              scratch.numel(), ys, stride_y, flg, epoch.data_ptr(), done.data_ptr(), slot,
+                                              rank, world, status.data_ptr(), ctypes.byref(fused), _stream(W.device)))
+    return bool(fused.value)
 
 
 def dequantize(W: torch.Tensor, qtype: int, count: int, dtype=torch.float16) -> torch.Tensor:

@@ -22,7 +22,7 @@ int cuda_fail(cudaError_t e, const char* what) {
 }
 
 Options& options() {
-  static Options o = {0, 3, 81, 2, 1, 0, 0, 1, 1};
+  static Options o = {0, 3, 81, 2, 1, 0, 0, 1, 1, 0, 1, 1, 0};
   return o;
 }
 
@@ -106,7 +106,7 @@ static int mul_mat(const char* fn, bool mmq, const void* W, int type, int64_t n,
   if (x) {
     Q8Ptrs Pq = P;
     if (gemm) {   // the GEMM reads only the fp16 activations and raw block sums: skip the GEMV-side tables
-      Pq.qs = nullptr; Pq.qsp = nullptr; Pq.ds = nullptr; Pq.dT = nullptr;
+      Pq.qs = nullptr; Pq.qsp = nullptr; Pq.ds = nullptr; Pq.dT = nullptr; Pq.qsu = nullptr;
     }
     rc = launch_quantize(x, x_dtype, m, k, stride_x, &Pq, nullptr, p.L.kpad, st);
     if (rc) return rc;
@@ -222,7 +222,7 @@ int kq_mul_mat_prepared(const void* W, int type, int64_t n, int64_t k, int64_t m
 // Scratch for kq_mul_mat_vec_a8_static: a file-scope device array, one copy per GPU that loads the library.
 // Sized for the stated limits m <= 16, n <= 32768, k <= 32768 (layout of q8_layout at those maxima, rounded up).
 constexpr int64_t KQ_STATIC_MAX_M = 16, KQ_STATIC_MAX_N = 32768, KQ_STATIC_MAX_K = 32768;
-constexpr size_t KQ_STATIC_BYTES = 14u << 20;
+constexpr size_t KQ_STATIC_BYTES = 16u << 20;
 static __device__ __align__(256) unsigned char g_static_scratch[KQ_STATIC_BYTES];
 
 // The array's name is only a host-side handle; kernels need its device address, looked up once per device.
@@ -330,6 +330,56 @@ int kq_p2p_allgather_2d(const void* src, int64_t rows, size_t row_bytes, void* c
                               world, status, (cudaStream_t)stream);
 }
 
+int kq_mul_mat_prepared_gather(const void* W, int type, int64_t n_local, int64_t k, int64_t m, int y_dtype, int mmq,
+                               void* scratch, size_t scratch_bytes, void* const* peer_y, int64_t stride_y,
+                               uint32_t* const* peer_flags, uint32_t* epoch, uint32_t* done, int slot, int rank,
+                               int world, int* peer_status, int* fused, void* stream) {
+  t_err[0] = 0;
+  const char* fn = "kq_mul_mat_prepared_gather";
+  if (fused) *fused = 0;
+  if (!peer_y || !peer_flags || !epoch || !done || !peer_status) { set_error("%s: null pointer argument", fn); return KQ_EINVAL; }
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || slot < 0) {
+    set_error("%s: world %d (max 8), rank %d, slot %d", fn, world, rank, slot);
+    return KQ_EINVAL;
+  }
+  if (!dtype_ok(y_dtype)) { set_error("%s: unsupported output dtype %d", fn, y_dtype); return KQ_EUNSUPPORTED; }
+  if (n_local <= 0 || stride_y < (int64_t)world * n_local) { set_error("%s: stride_y < world * n_local", fn); return KQ_EINVAL; }
+  const size_t esz = dtype_size(y_dtype);
+  uintptr_t bits = (uintptr_t)((size_t)n_local * esz) | (uintptr_t)((size_t)stride_y * esz);
+  for (int r = 0; r < world; ++r) {
+    if (!peer_y[r] || !peer_flags[r]) { set_error("%s: null buffer or flag pointer for rank %d", fn, r); return KQ_EINVAL; }
+    if ((uintptr_t)peer_flags[r] % 4 || (uintptr_t)peer_y[r] % esz) { set_error("%s: misaligned buffer or flag array of rank %d", fn, r); return KQ_EINVAL; }
+    bits |= (uintptr_t)peer_y[r];
+  }
+  Problem p;
+  int rc = validate(fn, W, type, n_local, k, nullptr, KQ_F32, m, k, scratch, scratch_bytes, p, true, false);
+  if (rc) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  Q8Ptrs P = q8_ptrs(scratch, p.L, n_local);
+  const int64_t col0 = (int64_t)rank * n_local;
+  // one kernel: the shared-stage kernel takes the whole call (<= 16 tokens, all rows streamable) and every 16-byte
+  // output store is aligned in every rank's buffer
+  const bool one = world > 1 && options().gemv_impl == 0 && !options().no_fused_gather && m <= 16 && (bits & 15) == 0 &&
+                   !(mmq && (type == KQ_TYPE_IQ3_S || type == KQ_TYPE_IQ4_NL || type == KQ_TYPE_IQ4_XS)) &&
+                   gemv_mma_supported(W, type, n_local, k) && stream_rows(n_local, p.rowbytes) == n_local &&
+                   gemv_tile_supported(W, type, n_local, k, (int)m);
+  if (one) {
+    GatherArgs ga;
+    for (int r = 0; r < 8; ++r) { ga.peer_y[r] = r < world ? peer_y[r] : nullptr; ga.peer_flags[r] = r < world ? peer_flags[r] : nullptr; }
+    ga.epoch = epoch; ga.done = done; ga.status = peer_status; ga.slot = slot; ga.rank = rank; ga.world = world; ga.col0 = col0;
+    rc = launch_gemv_tile(W, type, n_local, k, P, 0, (int)m, peer_y[rank], y_dtype, stride_y, mmq != 0, st, &ga);
+    if (rc == KQ_OK && fused) *fused = 1;
+    return rc;
+  }
+  // two kernels: the usual dispatch writes this rank's columns of its own buffer, the gather kernel pushes them out
+  uint8_t* mine = (uint8_t*)peer_y[rank] + (size_t)col0 * esz;
+  rc = mul_mat(fn, mmq != 0, W, type, n_local, k, nullptr, KQ_F32, m, k, mine, y_dtype, stride_y, scratch, scratch_bytes, stream,
+               true, false);
+  if (rc || world == 1) return rc;
+  return launch_p2p_allgather(mine, (size_t)m * n_local * esz, m, (size_t)stride_y * esz, peer_y, peer_flags, epoch, done, slot,
+                              rank, world, peer_status, st, (size_t)stride_y * esz);
+}
+
 int kq_debug_copy_window(uint64_t base, int64_t n, int64_t rowbytes, int64_t row_a, int64_t row_b, int64_t seg_off,
                          int64_t seg_len, int64_t* streamed_rows, uint64_t* bulk_start, uint64_t* bulk_bytes) {
   t_err[0] = 0;
@@ -364,6 +414,10 @@ int kq_set_option(const char* name, int value) {
   if (name && !strcmp(name, "fuse_q8")) { options().fuse_q8 = value < 0 ? 0 : (value > 2 ? 2 : value); return KQ_OK; }
   if (name && !strcmp(name, "pdl")) { options().pdl = value < 0 ? 0 : value; return KQ_OK; }
   if (name && !strcmp(name, "kres")) { options().kres = value < 0 ? 0 : (value > 2 ? 2 : value); return KQ_OK; }
+  if (name && !strcmp(name, "no_fused_gather")) { options().no_fused_gather = value != 0; return KQ_OK; }
+  if (name && !strcmp(name, "umma")) { options().umma = value != 0; return KQ_OK; }
+  if (name && !strcmp(name, "umma_min_m")) { options().umma_min_m = value; return KQ_OK; }
+  if (name && !strcmp(name, "umma_box")) { options().umma_box = value != 0; return KQ_OK; }
   set_error("kq_set_option: unknown option");
   return KQ_EINVAL;
 }
@@ -377,6 +431,10 @@ int kq_get_option(const char* name, int* value) {
   if (name && value && !strcmp(name, "fuse_q8")) { *value = options().fuse_q8; return KQ_OK; }
   if (name && value && !strcmp(name, "pdl")) { *value = options().pdl; return KQ_OK; }
   if (name && value && !strcmp(name, "kres")) { *value = options().kres; return KQ_OK; }
+  if (name && value && !strcmp(name, "no_fused_gather")) { *value = options().no_fused_gather; return KQ_OK; }
+  if (name && value && !strcmp(name, "umma")) { *value = options().umma; return KQ_OK; }
+  if (name && value && !strcmp(name, "umma_min_m")) { *value = options().umma_min_m; return KQ_OK; }
+  if (name && value && !strcmp(name, "umma_box")) { *value = options().umma_box; return KQ_OK; }
   if (name && value && !strcmp(name, "launch_count")) { *value = (int)(options().launches & 0x7fffffff); return KQ_OK; }
   set_error("kq_get_option: unknown option");
   return KQ_EINVAL;

@@ -48,6 +48,10 @@ struct Options {
   int fuse_q8;         // 1: calls of 1-2 tokens quantize the activations inside the row-streaming kernel (no quantizer launch)
   int kres;            // 1: passes of 3..8 tokens use the register-resident kernel where it covers the type and shape;
                        // 2: passes of 9..16 tokens as well (slower than the shared-stage kernel today); 0: never
+  int umma;            // 1: the tensor-memory decode kernel takes the passes it covers (auto mode)
+  int umma_min_m;      // ... from this many tokens on
+  int umma_box;        // 1: its weight bytes arrive by tiled TMA copies where the rows are 16-byte aligned (else cp.async)
+  int no_fused_gather; // 1: kq_mul_mat_prepared_gather always runs as two kernels (GEMV, then the gather kernel)
 };
 Options& options();
 
@@ -118,16 +122,23 @@ inline int type_group(int type) { return (type == KQ_TYPE_Q2_K || type == KQ_TYP
 //   s8h   half  [m][kpad/32]        the fp16 raw block sums alone (second B operand of the GEMM)
 //   z32r  float [m][kpad/32]        same values as z32, token-major (row-streaming kernel)
 //   z16r  float [m][kpad/16]        same values as z16, token-major
+//   qsu   bytes [mt][kpad/256][6656]  per unit of 256 weights everything the tensor-memory decode kernel stages for it,
+//                                   contiguous (one bulk copy): the codes in the tensor core's K-major core-matrix
+//                                   order [16 chunks of 16 weights][16 tokens][16] (4096 B), then float [8 blocks][16
+//                                   tokens] of d8 (512 B), of d8 * code sum (512 B), of the raw fp16 sum (512 B), and
+//                                   float [16 half blocks][16 tokens] of d8 * code sum per 16 weights (1024 B)
 //   part  float [4][16][n]          split-K partial sums of one 16-token pass
 //   cnt   int   [KQ_CNT_SLOTS]      split-K arrival counters, one per 8-row tile (the quantizer zeroes the first
 //                                   ceil(n/8) of them, the kernel that used them resets them)
 //   status int  [64]                device-side error word (bounded waits that gave up)
 // Only `part` (which needs no initialisation) and the total depend on n, and `part` comes last: a scratch prepared
 // for n_max rows is laid out identically for every weight tensor of n <= n_max rows that shares it.
+constexpr int KQ_UNIT_TABLE = 4096 + 3 * 512 + 1024;   // bytes of qsu per (16-token pass, 256 weights)
+constexpr int KQ_PART_SLOTS = 4;      // partial-sum slots of a split row tile
 constexpr int KQ_CNT_SLOTS = 65536;   // 8-row tiles a split-K launch may have (n <= 524288); larger n runs unsplit
 struct Q8Layout {
   int64_t kpad, mt;
-  size_t off_ds, off_qs, off_qsp, off_xh, off_s8h, off_dT, off_z32, off_zs8, off_z16, off_z32r, off_z16r, off_part, off_cnt, off_status, total;
+  size_t off_ds, off_qs, off_qsp, off_xh, off_s8h, off_dT, off_z32, off_zs8, off_z16, off_z32r, off_z16r, off_qsu, off_part, off_cnt, off_status, total;
 };
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 inline Q8Layout q8_layout(int64_t m, int64_t n, int64_t k) {
@@ -149,13 +160,14 @@ inline Q8Layout q8_layout(int64_t m, int64_t n, int64_t k) {
   L.off_z16 = p;    p = align_up(p + (size_t)L.mt * nb * 128, 256);
   L.off_z32r = p;   p = align_up(p + (size_t)m * nb * 4, 256);
   L.off_z16r = p;   p = align_up(p + (size_t)m * nb * 8, 256);
-  L.off_part = p;   p = align_up(p + (size_t)4 * 16 * n * 4, 256);
+  L.off_qsu = p;    p = align_up(p + (size_t)L.mt * (L.kpad / 256) * KQ_UNIT_TABLE, 256);
+  L.off_part = p;   p = align_up(p + (size_t)KQ_PART_SLOTS * 16 * n * 4, 256);
   L.total = p;
   return L;
 }
 
 struct Q8Ptrs {  // device pointers into one scratch buffer
-  __half2* ds; int8_t* qs; int8_t* qsp; __half* xh; __half* s8h; float *dT, *z32, *zs8, *z16, *z32r, *z16r, *part; int *cnt, *status;
+  __half2* ds; int8_t* qs; int8_t* qsp; __half* xh; __half* s8h; float *dT, *z32, *zs8, *z16, *z32r, *z16r, *part; int8_t* qsu; int *cnt, *status;
   int64_t kpad; int ncnt;
 };
 inline Q8Ptrs q8_ptrs(void* scratch, const Q8Layout& L, int64_t n) {
@@ -165,6 +177,9 @@ inline Q8Ptrs q8_ptrs(void* scratch, const Q8Layout& L, int64_t n) {
   P.dT = (float*)(s + L.off_dT); P.z32 = (float*)(s + L.off_z32); P.zs8 = (float*)(s + L.off_zs8);
   P.z16 = (float*)(s + L.off_z16); P.z32r = (float*)(s + L.off_z32r); P.z16r = (float*)(s + L.off_z16r);
   P.part = (float*)(s + L.off_part);
+  // the unit tables are only written (and read) while the tensor-memory decode kernel is switched on: set the option
+  // before the activations are prepared
+  P.qsu = (options().umma || options().gemv_impl == 8) ? (int8_t*)(s + L.off_qsu) : nullptr;
   P.cnt = (int*)(s + L.off_cnt); P.status = (int*)(s + L.off_status);
   P.kpad = L.kpad;
   const int64_t tiles = (n + 7) / 8;
@@ -215,9 +230,23 @@ bool gemv_rows_only(int type, int64_t n, int64_t k, int64_t m);
 int launch_gemv_mma(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m, void* y,
                     int y_dtype, int64_t stride_y, bool mmq, cudaStream_t st, const void* fuse_x = nullptr,
                     int x_dtype = 0, int64_t stride_x = 0);
+// Fused all-gather of a row(N)-sharded layer: where the shared-stage kernel writes its outputs (every rank's [M, N]
+// buffer, this rank's columns from col0 on) and the flag arrays of the hand-shake that ends the kernel.
+struct GatherArgs {
+  void* peer_y[8];
+  uint32_t* peer_flags[8];
+  uint32_t* epoch;
+  uint32_t* done;
+  int* status;
+  int slot, rank, world;
+  int64_t col0;
+};
 bool gemv_tile_supported(const void* W, int type, int64_t n, int64_t k, int mtok);
 int gemv_tile_splits(int type, int64_t n, int64_t k, int mtok);
 int launch_gemv_tile(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m0, int mcount, void* y,
+                     int y_dtype, int64_t stride_y, bool mmq, cudaStream_t st, const GatherArgs* ga = nullptr);
+bool gemv_umma_supported(const void* W, int type, int64_t n, int64_t k);
+int launch_gemv_umma(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m0, int mcount, void* y,
                      int y_dtype, int64_t stride_y, bool mmq, cudaStream_t st);
 bool gemv_kres_supported(const void* W, int type, int64_t n, int64_t k, int mtok);
 int gemv_kres_splits(int type, int64_t n, int64_t k, int mtok);
@@ -225,7 +254,7 @@ int launch_gemv_kres(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs
                      int y_dtype, int64_t stride_y, bool mmq, cudaStream_t st);
 int launch_p2p_allgather(const void* src, size_t bytes, int64_t rows, size_t dst_stride, void* const* peer_dst,
                          uint32_t* const* peer_flags, uint32_t* epoch, uint32_t* done, int slot, int rank, int world,
-                         int* status, cudaStream_t st);
+                         int* status, cudaStream_t st, size_t src_stride = 0);
 bool gemm_tc_supported(const void* W, int type, int64_t n, int64_t k);
 int launch_gemm_tc(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m, void* y, int y_dtype,
                    int64_t stride_y, bool mmq, cudaStream_t st);

@@ -23,9 +23,8 @@
 //   A ring of 4 steps in TMEM (256 columns, beside the 256 accumulator columns) and a B ring of 3 steps in shared
 //   memory (192 KB) overlap dequantization, loads and MMAs.  Every mbarrier wait is bounded; on give-up a status
 //   word is set, TMEM is released and the CTA returns.
-#include <cuda.h>
-
 #include "kq_common.cuh"
+#include "kq_tma.cuh"
 
 namespace kq {
 namespace {
@@ -563,21 +562,6 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
 }
 
 // ------------------------------------------------------------------------------------------------ host
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(sym);
-  }
-  return fn;
-}
 
 template <int QT, bool CORR, typename OutT>
 int launch(const GemmParams& p, const CUtensorMap& map, const CUtensorMap& smap, int grid, cudaStream_t st) {

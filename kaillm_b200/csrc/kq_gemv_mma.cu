@@ -634,6 +634,15 @@ int launch_gemv_mma(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs&
     // 3..16 tokens: the register-resident mma kernel where it covers the type and shape
     // (today it wins for up to 8 tokens; 9..16 tokens only on request: kres = 2 or gemv_impl = 7)
     const int pass = (int)(left < 16 ? left : 16);
+    // the tensor-memory kernel (tcgen05 integer MMAs): on request for now (gemv_impl = 8, or option umma = 1 in auto mode)
+    if (tile_start && (impl == 8 || (impl == 0 && options().umma && left >= options().umma_min_m)) && gemv_umma_supported(W, type, n, k)) {
+      mcount = pass;
+      rc = launch_gemv_umma(W, type, n, k, P, m0, mcount, y, y_dtype, stride_y, mmq, st);
+      if (rc) return rc;
+      m0 += mcount;
+      continue;
+    }
+    if (impl == 8) { set_error("tensor-memory GEMV: type/shape not covered"); return KQ_EUNSUPPORTED; }
     if (tile_start && (impl == 7 || (impl == 0 && left >= tile_min && (options().kres == 2 || (options().kres == 1 && pass <= 8)))) &&
         gemv_kres_supported(W, type, n, k, pass)) {
       mcount = (int)(left < 16 ? left : 16);

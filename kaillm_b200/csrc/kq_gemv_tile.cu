@@ -68,6 +68,15 @@ struct TileParams {
   float* part;
   int* cnt;
   int* status;
+  // fused all-gather (g_world > 1): the outputs go, as columns g_col0 .., straight into every rank's row-major [M, N]
+  // buffer by plain peer stores; the last CTA to finish raises this call's flag on every rank and waits for theirs
+  void* peer_y[8];
+  uint32_t* peer_flags[8];
+  uint32_t* g_epoch;
+  uint32_t* g_done;
+  int* g_status;   // set (and never cleared here) when the wait for a peer's flag ran out
+  int g_slot, g_rank, g_world;
+  int64_t g_col0;
 };
 
 struct TileConfig {
@@ -327,6 +336,41 @@ __device__ __forceinline__ void unit_q2k(uint32_t pg, int b0, const TileView& A,
   }
 }
 
+// ---------------------------------------------------------------------------------------------- fused all-gather
+// Called by ONE whole warp of every CTA once all of the CTA's output stores are done and fenced at system scope (CTAs
+// without rows call it at once).  The CTA that arrives last advances the call's epoch, stores it into flag[slot][rank]
+// of every rank (release, system scope) and waits - bounded - until every rank's flag shows the same call: when the
+// kernel completes, this rank's [M, N] buffer holds all ranks' columns.  Same protocol and flag arrays as
+// kq_p2p_allgather; only plain loads and stores touch peer memory.
+constexpr long long TL_PEER_WAIT_LIMIT = 1ll << 32;   // a good two seconds: ranks may be skewed at their first call
+__device__ __forceinline__ void gather_finish(const TileParams& p, int lane) {
+  int last = 0;
+  if (lane == 0) last = atomicAdd(p.g_done + p.g_slot, 1u) == gridDim.x - 1;
+  last = __shfl_sync(0xffffffffu, last, 0);
+  if (!last) return;
+  uint32_t e = 0;
+  if (lane == 0) {
+    __threadfence_system();   // every CTA fenced its stores before it counted itself
+    p.g_done[p.g_slot] = 0;
+    e = p.g_epoch[p.g_slot] + 1;
+    p.g_epoch[p.g_slot] = e;
+  }
+  e = __shfl_sync(0xffffffffu, e, 0);
+  if (lane < p.g_world)
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.peer_flags[lane] + p.g_slot * 8 + p.g_rank), "r"(e) : "memory");
+  if (lane < p.g_world) {
+    const uint32_t* f = p.peer_flags[p.g_rank] + p.g_slot * 8 + lane;
+    const long long t0 = clock64();
+    for (;;) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+      if ((int32_t)(v - e) >= 0) break;
+      __nanosleep(100);
+      if (clock64() - t0 > TL_PEER_WAIT_LIMIT) { atomicExch(p.g_status, 16 + lane); break; }
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------- kernel
 // The kernel's unit of K is 256 weights: a super-block of the K-quants, eight blocks of Q8_0.
 template <int QT> struct TileUnit { static constexpr int BYTES = Fmt<QT>::BYTES * (256 / Fmt<QT>::BLK); };
@@ -351,7 +395,10 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
   const int grp = blockIdx.x / p.ks, ngrp = gridDim.x / p.ks;
   const int rt0 = (int)((int64_t)grp * p.ntiles / ngrp), rt1 = (int)((int64_t)(grp + 1) * p.ntiles / ngrp);
   pdl_trigger();
-  if (rt0 >= rt1) return;
+  if (rt0 >= rt1) {
+    if (p.g_world > 1 && warp == 0) { pdl_wait(); gather_finish(p, lane); }
+    return;
+  }
   const int nst = rt1 - rt0;
   const int blk0 = (int)((int64_t)ks * p.nblk / p.ks), blk1 = (int)((int64_t)(ks + 1) * p.nblk / p.ks);
   const int nsb = blk1 - blk0;
@@ -365,6 +412,7 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
     for (int b = 0; b < TL_NRED; ++b) { bar_init(bar_rfull + 8 * b, TL_CW); bar_init(bar_rempty + 8 * b, 1); }
     bar_init(bar_fin, 1);
     *s_abort = 0;
+    *reinterpret_cast<volatile int*>(smem + TL_HEADER - 16) = 0;   // consumer warps past the split-K finish (fused gather)
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -458,7 +506,9 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
     const int g = lane >> 2, t = lane & 3;
     const int nks = p.ks;
     // 16-byte stores need 16-byte aligned rows of the output / of the partials
-    const bool vec_y = ((uintptr_t)p.y % 16) == 0 && ((p.stride_y * sizeof(OutT)) % 16) == 0 && (((size_t)p.m0 * p.stride_y * sizeof(OutT)) % 16) == 0;
+    // (with the fused all-gather the host has checked every rank's buffer and the column offset)
+    const bool vec_y = (p.g_world > 1 || ((uintptr_t)p.y % 16) == 0) && ((p.stride_y * sizeof(OutT)) % 16) == 0 &&
+                       (((size_t)p.m0 * p.stride_y * sizeof(OutT)) % 16) == 0;
     const bool vec_part = (p.n % 4) == 0;
     for (int q = 0; q < nst; ++q) {
       const int buf = q & (TL_NRED - 1);
@@ -490,21 +540,30 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
           if (whole && vec_part) { __stcg(reinterpret_cast<float4*>(dst), va); __stcg(reinterpret_cast<float4*>(dst) + 1, vb); }
           else for (int i = 0; i < 8; ++i) if (row0 + i < p.n) __stcg(dst + i, v8[i]);
         } else {
-          OutT* dst = y + (size_t)(p.m0 + tl) * p.stride_y + row0;
-          if (whole && vec_y) {
-            if constexpr (sizeof(OutT) == 4) {
-              reinterpret_cast<float4*>(dst)[0] = va; reinterpret_cast<float4*>(dst)[1] = vb;
-            } else {
-              OutT o[8];
+          const int nd = p.g_world > 1 ? p.g_world : 1;
+          for (int r = 0; r < nd; ++r) {   // fused all-gather: the same 16 bytes to every rank's buffer
+            OutT* base = p.g_world > 1 ? reinterpret_cast<OutT*>(p.peer_y[r]) + p.g_col0 : y;
+            OutT* dst = base + (size_t)(p.m0 + tl) * p.stride_y + row0;
+            if (whole && vec_y) {
+              if constexpr (sizeof(OutT) == 4) {
+                reinterpret_cast<float4*>(dst)[0] = va; reinterpret_cast<float4*>(dst)[1] = vb;
+              } else {
+                OutT o[8];
 #pragma unroll
-              for (int i = 0; i < 8; ++i) o[i] = from_f32<OutT>(v8[i]);
-              *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(o);
+                for (int i = 0; i < 8; ++i) o[i] = from_f32<OutT>(v8[i]);
+                *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(o);
+              }
+            } else {
+              for (int i = 0; i < 8; ++i) if (row0 + i < p.n) dst[i] = from_f32<OutT>(v8[i]);
             }
-          } else {
-            for (int i = 0; i < 8; ++i) if (row0 + i < p.n) dst[i] = from_f32<OutT>(v8[i]);
           }
         }
       }
+    }
+    if (nks == 1 && p.g_world > 1) {
+      __threadfence_system();   // this warp issued all of the CTA's output stores
+      __syncwarp();
+      gather_finish(p, lane);
     }
     if (nks > 1) {
       // one fence and one round of counter updates for all tiles of this CTA.  The split that arrives last at a
@@ -588,10 +647,25 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
           float tot = v[0];
 #pragma unroll
           for (int sp = 1; sp < 4; ++sp) if (sp < nks) tot += v[sp];
-          y[(size_t)(p.m0 + tl) * p.stride_y + row] = from_f32<OutT>(tot);
+          const OutT o = from_f32<OutT>(tot);
+          if (p.g_world > 1) {
+            for (int r = 0; r < p.g_world; ++r)
+              (reinterpret_cast<OutT*>(p.peer_y[r]) + p.g_col0)[(size_t)(p.m0 + tl) * p.stride_y + row] = o;
+          } else {
+            y[(size_t)(p.m0 + tl) * p.stride_y + row] = o;
+          }
         }
       }
       if (lane == 0) p.cnt[rt] = 0;   // ready for the next launch on this scratch
+    }
+    if (p.g_world > 1) {
+      // the consumer warps issued this CTA's output stores: the last of them to get here hands the CTA over
+      int* s_warps = reinterpret_cast<int*>(smem + TL_HEADER - 16);
+      __threadfence_system();
+      __syncwarp();
+      int mine_last = 0;
+      if (lane == 0) mine_last = atomicAdd(s_warps, 1) == TL_CW - 1;
+      if (__shfl_sync(0xffffffffu, mine_last, 0)) gather_finish(p, lane);
     }
   }
 }
@@ -683,7 +757,7 @@ int gemv_tile_splits(int type, int64_t n, int64_t k, int mtok) {
 
 // one pass of up to 16 tokens starting at m0 (a multiple of 16)
 int launch_gemv_tile(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m0, int mcount, void* y,
-                     int y_dtype, int64_t stride_y, bool mmq, cudaStream_t st) {
+                     int y_dtype, int64_t stride_y, bool mmq, cudaStream_t st, const GatherArgs* ga) {
   const int nh = mcount > 8 ? 2 : 1;
   TileConfig c;
   if (!make_tile_config(type, n, k, 8 * nh, c)) { set_error("tile GEMV: shape not covered"); return KQ_EUNSUPPORTED; }
@@ -699,6 +773,14 @@ int launch_gemv_tile(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs
   p.kpad = (int)P.kpad; p.nb32tot = (int)(P.kpad / 32); p.m0 = (int)m0; p.mcount = mcount;
   p.prefetch = options().pdl < c.stages ? options().pdl : c.stages;
   p.y = y; p.stride_y = stride_y; p.part = P.part; p.cnt = P.cnt; p.status = P.status;
+  p.g_world = 0; p.g_slot = 0; p.g_rank = 0; p.g_col0 = 0; p.g_epoch = nullptr; p.g_done = nullptr; p.g_status = nullptr;
+  for (int r = 0; r < 8; ++r) { p.peer_y[r] = nullptr; p.peer_flags[r] = nullptr; }
+  if (ga && ga->world > 1) {
+    p.g_world = ga->world; p.g_slot = ga->slot; p.g_rank = ga->rank; p.g_col0 = ga->col0;
+    p.g_epoch = ga->epoch; p.g_done = ga->done; p.g_status = ga->status;
+    for (int r = 0; r < ga->world; ++r) { p.peer_y[r] = ga->peer_y[r]; p.peer_flags[r] = ga->peer_flags[r]; }
+    p.y = ga->peer_y[ga->rank];
+  }
   switch (type) {
     case KQ_TYPE_Q4_K: return launch_tile_typed<KQ_TYPE_Q4_K>(p, c, nh, y_dtype, st);
     case KQ_TYPE_Q6_K: return launch_tile_typed<KQ_TYPE_Q6_K>(p, c, nh, y_dtype, st);

@@ -31,6 +31,8 @@ struct P2PParams {
   size_t row_bytes;                   // bytes per row of the slice (== bytes for the rank-major layout)
   size_t dst_stride;                  // bytes between rows in the destination buffers
   size_t dst_off;                     // where this rank's first row starts in every destination buffer
+  size_t src_stride;                  // bytes between rows of the source (row_bytes when the slice is contiguous)
+  int skip_self;                      // the source IS this rank's columns of its own buffer: no store to itself
   uint8_t* dst[P2P_MAX_RANKS];        // each rank's gather buffer (world * bytes)
   uint32_t* flags[P2P_MAX_RANKS];     // each rank's flag array [slots][P2P_MAX_RANKS]
   uint32_t* epoch;                    // local: calls made so far per slot
@@ -56,14 +58,16 @@ __global__ void __launch_bounds__(1024) p2p_allgather_kernel(const P2PParams p) 
   if (p.vec16) {
     for (size_t i = tid; i < nvec; i += nthr) {
       const size_t b = i * 16, row = b / p.row_bytes, col = b - row * p.row_bytes;
-      const uint4 v = *reinterpret_cast<const uint4*>(p.src + b);
-      for (int r = 0; r < p.world; ++r) *reinterpret_cast<uint4*>(p.dst[r] + p.dst_off + row * p.dst_stride + col) = v;
+      const uint4 v = *reinterpret_cast<const uint4*>(p.src + row * p.src_stride + col);
+      for (int r = 0; r < p.world; ++r)
+        if (!(p.skip_self && r == p.rank)) *reinterpret_cast<uint4*>(p.dst[r] + p.dst_off + row * p.dst_stride + col) = v;
     }
   } else {
     for (size_t i = tid; i < p.bytes; i += nthr) {
       const size_t row = i / p.row_bytes, col = i - row * p.row_bytes;
-      const uint8_t v = p.src[i];
-      for (int r = 0; r < p.world; ++r) p.dst[r][p.dst_off + row * p.dst_stride + col] = v;
+      const uint8_t v = p.src[row * p.src_stride + col];
+      for (int r = 0; r < p.world; ++r)
+        if (!(p.skip_self && r == p.rank)) p.dst[r][p.dst_off + row * p.dst_stride + col] = v;
     }
   }
   __syncthreads();
@@ -105,7 +109,7 @@ __global__ void __launch_bounds__(1024) p2p_allgather_kernel(const P2PParams p) 
 // [rows][row_bytes] and lands as columns rank * row_bytes .. of row-major buffers with row stride dst_stride
 int launch_p2p_allgather(const void* src, size_t bytes, int64_t rows, size_t dst_stride, void* const* peer_dst,
                          uint32_t* const* peer_flags, uint32_t* epoch, uint32_t* done, int slot, int rank, int world,
-                         int* status, cudaStream_t st) {
+                         int* status, cudaStream_t st, size_t src_stride) {
   if (world < 1 || world > P2P_MAX_RANKS || rank < 0 || rank >= world || slot < 0) {
     set_error("kq_p2p_allgather: world %d (max %d), rank %d, slot %d", world, P2P_MAX_RANKS, rank, slot);
     return KQ_EINVAL;
@@ -121,8 +125,10 @@ int launch_p2p_allgather(const void* src, size_t bytes, int64_t rows, size_t dst
   } else {
     p.row_bytes = bytes; p.dst_stride = 0; p.dst_off = (size_t)rank * bytes;
   }
-  // 16-byte stores: source, slice and row size, destination stride and every buffer aligned
-  uintptr_t bits = (uintptr_t)src | (uintptr_t)bytes | (uintptr_t)p.row_bytes | (uintptr_t)p.dst_stride;
+  p.src_stride = src_stride ? src_stride : p.row_bytes;
+  p.skip_self = rank < world && peer_dst[rank] && (const uint8_t*)src == (const uint8_t*)peer_dst[rank] + p.dst_off;
+  // 16-byte stores: source, slice and row size, the strides and every buffer aligned
+  uintptr_t bits = (uintptr_t)src | (uintptr_t)bytes | (uintptr_t)p.row_bytes | (uintptr_t)p.dst_stride | (uintptr_t)p.src_stride;
   for (int r = 0; r < P2P_MAX_RANKS; ++r) {
     p.dst[r] = r < world ? (uint8_t*)peer_dst[r] : nullptr;
     p.flags[r] = r < world ? peer_flags[r] : nullptr;

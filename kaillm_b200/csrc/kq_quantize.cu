@@ -27,6 +27,8 @@ __device__ __forceinline__ void quantize_block(float xi, int64_t row, int b, int
   const float d = __fdiv_rn(amax, 127.0f);
   const int8_t q = amax == 0.0f ? (int8_t)0 : (int8_t)roundf(__fdiv_rn(xi, d));
   if (P.qs) P.qs[row * kpad + col] = q;
+  int8_t* unit = P.qsu ? P.qsu + ((row >> 4) * (kpad >> 8) + (b >> 3)) * (int64_t)KQ_UNIT_TABLE : nullptr;   // this pass's tables of the block's unit
+  if (unit) unit[((((col & 255) >> 4) * 16) + (row & 15)) * 16 + (col & 15)] = q;
   if (P.xh) P.xh[row * kpad + col] = __float2half_rn(__half2float(__float2half_rn(d)) * (float)q);
   if (P.qsp) {
     int8_t* pp = P.qsp + (row * (kpad >> 6) + (col >> 6)) * 80;
@@ -51,6 +53,11 @@ __device__ __forceinline__ void quantize_block(float xi, int64_t row, int b, int
       P.z32r[row * nb + b] = df * (float)(s16 + s16b);
       P.z16r[(row * nb + b) * 2] = df * (float)s16;
       P.z16r[(row * nb + b) * 2 + 1] = df * (float)s16b;
+      if (unit) {
+        float* ut = reinterpret_cast<float*>(unit + 4096) + (b & 7) * 16 + (row & 15);
+        ut[0] = df; ut[128] = df * (float)(s16 + s16b); ut[256] = __half2float(sh);
+        ut[384 + (b & 7) * 16] = df * (float)s16; ut[384 + (b & 7) * 16 + 16] = df * (float)s16b;   // [2 (b & 7) + half][16 tokens]
+      }
     }
   }
   if (lane == 0) {
@@ -59,6 +66,13 @@ __device__ __forceinline__ void quantize_block(float xi, int64_t row, int b, int
     if (P.xh) P.s8h[row * nb + b] = sh;
     if (wire36) *reinterpret_cast<__half2*>(wire36 + (row * nb + b) * 36) = v;
   }
+}
+
+// Padding tokens (m .. 16 * ceil(m / 16) - 1): zero scales in the unit tables (their codes may be anything)
+__device__ __forceinline__ void zero_unit_tables(const Q8Ptrs& P, int64_t row, int b, int kpad) {
+  if (!P.qsu) return;
+  float* ut = reinterpret_cast<float*>(P.qsu + ((row >> 4) * (kpad >> 8) + (b >> 3)) * (int64_t)KQ_UNIT_TABLE + 4096) + (b & 7) * 16 + (row & 15);
+  ut[0] = 0.f; ut[128] = 0.f; ut[256] = 0.f; ut[384 + (b & 7) * 16] = 0.f; ut[384 + (b & 7) * 16 + 16] = 0.f;
 }
 
 // One warp per (token, 32-block).  Tokens m..16*ceil(m/16)-1 only zero-fill the transposed scale tables.
@@ -83,6 +97,7 @@ __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const T* __restrict_
       P.dT[tslot] = 0.f; P.z32[tslot] = 0.f; P.zs8[tslot] = 0.f;
       const int64_t t16 = ((row >> 4) * 2 * nb + 2 * b) * 16 + (row & 15);
       P.z16[t16] = 0.f; P.z16[t16 + 16] = 0.f;
+      zero_unit_tables(P, row, b, kpad);
     }
     return;
   }
@@ -126,6 +141,7 @@ __global__ void __launch_bounds__(256) prepare_fused_kernel(const T* __restrict_
       P.dT[tslot] = 0.f; P.z32[tslot] = 0.f; P.zs8[tslot] = 0.f;
       const int64_t t16 = ((row >> 4) * 2 * nb + 2 * b) * 16 + (row & 15);
       P.z16[t16] = 0.f; P.z16[t16 + 16] = 0.f;
+      zero_unit_tables(P, row, b, kpad);
     }
     return;
   }
@@ -256,7 +272,7 @@ __global__ void __launch_bounds__(256) quantize_xh_kernel(const T* __restrict__ 
 int launch_quantize(const void* x, int x_dtype, int64_t m, int64_t k, int64_t stride_x, const Q8Ptrs* Pp,
                     void* wire36, int64_t kpad, cudaStream_t st) {
   Q8Ptrs P;
-  if (Pp) P = *Pp; else { P = Q8Ptrs(); P.ds = nullptr; P.qs = nullptr; P.qsp = nullptr; P.xh = nullptr; P.s8h = nullptr; P.dT = P.z32 = P.zs8 = P.z16 = P.z32r = P.z16r = P.part = nullptr; P.cnt = P.status = nullptr; P.kpad = kpad; P.ncnt = 0; }
+  if (Pp) P = *Pp; else { P = Q8Ptrs(); P.ds = nullptr; P.qs = nullptr; P.qsp = nullptr; P.xh = nullptr; P.s8h = nullptr; P.dT = P.z32 = P.zs8 = P.z16 = P.z32r = P.z16r = P.part = nullptr; P.qsu = nullptr; P.cnt = P.status = nullptr; P.kpad = kpad; P.ncnt = 0; }
   const bool pdl_on = options().pdl != 0;
   if (P.xh && P.s8h && !P.qs && !P.qsp && !P.ds && !P.dT && !wire36 && (k % 32) == 0 && m > 0) {
     // only the GEMM's operands are wanted (large M): lane-per-block kernel

@@ -113,11 +113,27 @@ class P2PGather:
         off = self.flag_bytes + b * self.buf_bytes
         return self.mem[off:off + self.world * nbytes].view(y_local.dtype).view(m, self.world * per)
 
+    def project(self, W: torch.Tensor, qtype: int, m: int, k: int, scratch: torch.Tensor, dtype: torch.dtype, b: int,
+                mmq: bool = False) -> tuple[torch.Tensor, bool]:
+        """This rank's weight slice times the activations prepared in `scratch`, gathered into buffer `b` by the
+        GEMV's own epilogue where the library can do that (kq_mul_mat_prepared_gather; otherwise GEMV + gather kernel).
+        Returns (local buffer viewed as the row-major [M, N] output, whether it was one kernel)."""
+        per = W.shape[0]
+        esz = torch.empty((), dtype=dtype).element_size()
+        nbytes = m * per * esz
+        if nbytes > self.max_bytes or not 0 <= b < self.nbuf:
+            raise ValueError(f"slice of {nbytes} bytes / buffer {b} outside what this P2PGather was sized for")
+        dst = [p + b * self.buf_bytes for p in self.data_ptrs]
+        fused = self._capi.mul_mat_prepared_gather(W, qtype, m, k, scratch, dst, self.world * per, dtype, self.flag_ptrs,
+                                                   self.epoch, self.done, b, self.rank, self.status, mmq)
+        off = self.flag_bytes + b * self.buf_bytes
+        return self.mem[off:off + self.world * nbytes].view(dtype).view(m, self.world * per), fused
+
     def check(self) -> None:
         """Synchronises; raises if any gather's bounded wait for a peer ran out."""
         st = int(self.status.item())
         if st:
-            raise RuntimeError(f"kq_p2p_allgather: wait for rank {st - 1} timed out")
+            raise RuntimeError(f"peer gather: wait for rank {st - 16 if st >= 16 else st - 1} timed out")
 
 
 class ShardedGGUFLinear:
@@ -155,8 +171,9 @@ class DecoderStack:
     Merged projections are ONE weight tensor and ONE call, as the reference runs same-type merged layers
     (quantization/linear.py:377-381); every projection is sharded on its output rows (quantization/params.py:230-247), so
     each call ends in an all-gather of `[M, N/world]` slices into a row-major `[M, N]` buffer that the next producer
-    reads in place.  Each projection group costs one producer launch (activation + quantization), one GEMV launch and,
-    with more than one rank, one gather launch.
+    reads in place.  Each projection group costs one producer launch (activation + quantization) and one GEMV launch
+    whose epilogue stores the slice into every rank's buffer (kq_mul_mat_prepared_gather); shapes that kernel does not
+    cover cost a separate gather launch.
 
     weights: per layer a dict {"qkv", "o", "gate_up", "down"} -> (local shard uint8 [N/world, rowbytes], type, N, K).
     """
@@ -186,6 +203,8 @@ class DecoderStack:
         # world == 1: the GEMV writes the full output itself; otherwise the gather buffers (slot = index in GROUPS)
         self.yfull = {name: torch.empty((m, self.nfull[name]), dtype=dtype, device=device) for name in self.GROUPS} if self.world == 1 else {}
         self.nccl_buf = {}
+        self.fused = {}     # per group: did the last call run GEMV + gather as one kernel
+        self.ws_shape = {name: (weights[0][name][1], m, self.nfull[name] // self.world, weights[0][name][3]) for name in self.GROUPS}
         if self.world > 1 and p2p is None:
             self.nccl_buf = {name: torch.empty((self.world, m, self.nfull[name] // self.world), dtype=dtype, device=device)
                              for name in self.GROUPS}
@@ -197,13 +216,24 @@ class DecoderStack:
             out = self.yfull[name]
             capi.mul_mat_prepared(W, qt, self.m, k, out, self.scratch)
             return out
+        if self.p2p is not None:
+            out, self.fused[name] = self.p2p.project(W, qt, self.m, k, self.scratch, self.dtype, self.GROUPS.index(name))
+            return out
         yl = self.ylocal[name]
         capi.mul_mat_prepared(W, qt, self.m, k, yl, self.scratch)
-        if self.p2p is not None:
-            return self.p2p.gather_cols(yl, self.GROUPS.index(name))
         buf = self.nccl_buf[name]
-        dist.all_gather_into_tensor(buf, yl, group=self.group)
+        dist.all_gather_into_tensor(buf.view(self.world * self.m, -1), yl, group=self.group)
         return buf.permute(1, 0, 2).reshape(self.m, n)     # a transposing copy: the baseline the peer-store gather removes
+
+    def check(self) -> None:
+        """Synchronises; raises if a bounded wait inside any kernel of the stack ran out."""
+        for name, (qt, m, n, k) in self.ws_shape.items():
+            st = self._capi.read_status(qt, m, n, k, self.scratch)
+            if st:
+                raise RuntimeError(f"decoder stack: kernel status {st} (a bounded wait inside the last GEMV ran out)")
+            break   # the status word sits at offset 0 for every shape
+        if self.p2p is not None:
+            self.p2p.check()
 
     def forward(self, h: torch.Tensor, on_output=None) -> torch.Tensor:
         """One pass over all layers.  on_output(layer, name, full_output, prepare): hook for verification - `prepare(s)`

@@ -199,6 +199,53 @@ def test_register_resident_gemv_matches_oracle_and_dp4a(qt, n, k, m, mmq):
     assert rel_l2(to_np(y), to_np(y1)) < TIGHT          # every row, against the general kernel
 
 
+@pytest.mark.parametrize("n,k,m", [(128, 256, 1), (256, 512, 5), (200, 1024, 16), (1000, 5120, 3), (17408, 5120, 16), (17408, 5120, 7),
+                                   (5120, 17408, 16), (640, 5120, 9), (130, 2048, 21), (4352, 5120, 16), (3000, 4096, 40)])
+@pytest.mark.parametrize("mmq", [False, True])
+@pytest.mark.parametrize("box", [1, 0])
+def test_tensor_memory_gemv_matches_oracle_and_dp4a(n, k, m, mmq, box):
+    """gemv_impl=8 (Q4_K): integer dots by tcgen05.mma.kind::i8 with the accumulators in tensor memory, weights staged by
+    tiled TMA copies (box=1) or cp.async (box=0); row tiles shared between CTAs meet through partial sums whose order
+    does not depend on timing, so two runs are bit-identical."""
+    qt = 12
+    _, wt = wire(qt, n, k, seed=n + k)
+    x, xt = act(m, k, seed=m, dt="bf16")
+    w = wt.cpu().numpy()
+    scratch = torch.empty(capi.workspace_bytes(qt, m, n, k), dtype=torch.uint8, device=dev())
+    capi.set_option("gemv_impl", 8)
+    capi.set_option("umma_box", box)
+    try:
+        l0 = capi.get_option("launch_count")
+        y = capi.mul_mat(wt, xt, qt, mmq=mmq, out_dtype=torch.float32, scratch=scratch)
+        assert capi.get_option("launch_count") - l0 == 1 + (m + 15) // 16      # quantizer + one launch per 16 tokens
+        assert capi.read_status(qt, m, n, k, scratch) == 0
+        yb = capi.mul_mat(wt, xt, qt, mmq=mmq, out_dtype=torch.float32, scratch=scratch)   # counters self-reset
+        yh = capi.mul_mat(wt, xt, qt, mmq=mmq, out_dtype=torch.bfloat16, scratch=scratch)
+        capi.set_option("gemv_impl", 1)
+        y1 = capi.mul_mat(wt, xt, qt, mmq=mmq, out_dtype=torch.float32)
+    finally:
+        capi.set_option("gemv_impl", 0)
+        capi.set_option("umma_box", 1)
+    rows = np.r_[0:min(n, 150), max(0, n - 150):n]
+    want = O.mul_mat(w[rows], qt, x, "mmq" if mmq else "mmvq")
+    assert rel_l2(to_np(y)[:, rows], want) < TIGHT
+    assert torch.equal(y, yb)
+    assert torch.equal(yh, y.to(torch.bfloat16))
+    assert rel_l2(to_np(y), to_np(y1)) < TIGHT          # every row, against the general kernel
+
+
+def test_tensor_memory_gemv_reports_what_it_does_not_cover():
+    _, wt = wire(14, 256, 512, seed=3)
+    _, xt = act(4, 512, seed=4, dt="bf16")
+    capi.set_option("gemv_impl", 8)
+    try:
+        with pytest.raises(capi.KqError) as e:
+            capi.mul_mat(wt, xt, 14, out_dtype=torch.float32)
+        assert e.value.code == capi.KQ_EUNSUPPORTED
+    finally:
+        capi.set_option("gemv_impl", 0)
+
+
 @pytest.mark.parametrize("qt", QT)
 @pytest.mark.parametrize("n,k,m", [(64, 512, 1), (333, 2048, 2), (1200, 5120, 1), (100, 17408, 2), (17, 256, 1)])
 @pytest.mark.parametrize("dt", ["bf16", "f16", "f32"])

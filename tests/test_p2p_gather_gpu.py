@@ -1,4 +1,5 @@
-"""kq_p2p_allgather on two GPUs: the pushed slices equal an NCCL all-gather, eagerly and in a replayed CUDA graph.
+"""kq_p2p_allgather and kq_mul_mat_prepared_gather on two GPUs: the pushed slices equal an NCCL all-gather, eagerly
+and in a replayed CUDA graph; the GEMV with the gather in its epilogue equals GEMV + NCCL gather bit for bit.
 
 Runs as two child processes (one per GPU, rendezvous on 127.0.0.1); skipped on a box with fewer than two GPUs."""
 import os
@@ -65,6 +66,112 @@ def test_p2p_allgather_matches_nccl():
         p.start()
     for p in procs:
         p.join(timeout=150)
+    res = {}
+    while not q.empty():
+        r, msg = q.get()
+        res[r] = msg
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+    assert res == {0: "ok", 1: "ok"}, res
+
+
+def _fused_worker(rank: int, world: int, port: int, q) -> None:
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+        sys.path.insert(0, ROOT)
+        import torch.distributed as dist
+
+        from kaillm_b200 import capi, sharded, synth
+        dev = torch.device(f"cuda:{rank}")
+        torch.cuda.set_device(dev)
+        dist.init_process_group("nccl", device_id=dev)
+        pg = sharded.P2PGather(max_bytes=20 * 8704 * 4, nbuf=4, device=dev)
+        bad = []
+        # (type, N, K, tokens, dtype, expect one kernel)
+        cases = [(12, 17408, 5120, 16, torch.bfloat16, True), (12, 17408, 5120, 5, torch.float16, True),
+                 (14, 5120, 17408, 16, torch.bfloat16, True), (14, 5120, 17408, 1, torch.float32, True),    # split-K finish
+                 (8, 8192, 5120, 16, torch.bfloat16, True), (2, 4096, 4096, 9, torch.bfloat16, True),
+                 (21, 2048, 2048, 3, torch.bfloat16, True), (10, 2048, 2048, 16, torch.float16, True),
+                 (12, 4096, 2048, 20, torch.bfloat16, False),      # more than one pass of 16 tokens: two kernels
+                 (13, 2048, 1024, 4, torch.bfloat16, False),       # a format only the general kernel covers
+                 (8, 2 * 1031, 512, 2, torch.float32, False)]      # slices whose rows are not 16-byte aligned
+        for ci, (qt, n, k, m, dt, want_fused) in enumerate(cases):
+            per = n // world
+            wfull = torch.from_numpy(synth.wire_numpy(qt, n, k, seed=50 + ci))
+            w = sharded.shard_rows(wfull, rank, world).contiguous().to(dev)
+            x = torch.from_numpy(synth.activations_numpy(m, k, seed=70 + ci)).to(dev).to(dt)
+            scratch = torch.empty(capi.workspace_bytes(qt, m, per, k), dtype=torch.uint8, device=dev)
+            yl = torch.empty((m, per), dtype=dt, device=dev)
+            capi.prepare_q8(x, qt, per, scratch)
+            if want_fused:
+                capi.set_option("gemv_impl", 6)      # the kernel the one-kernel path runs, on the same shard
+            capi.mul_mat_prepared(w, qt, m, k, yl, scratch)
+            capi.set_option("gemv_impl", 0)
+            want = sharded.gather_columns(yl)
+            for rep in range(3):
+                got, fused = pg.project(w, qt, m, k, scratch, dt, ci & 3)
+                torch.cuda.synchronize()
+                if fused != want_fused or not torch.equal(got, want):
+                    bad.append((ci, rep, fused, float((got.float() - want.float()).abs().max())))
+            if want_fused:                           # the option turns the epilogue off: same result from two kernels
+                capi.set_option("no_fused_gather", 1)
+                got, fused = pg.project(w, qt, m, k, scratch, dt, ci & 3)
+                capi.set_option("no_fused_gather", 0)
+                torch.cuda.synchronize()
+                if fused or float((got.float() - want.float()).abs().max()) > 1e-2 * float(want.float().abs().max()):
+                    bad.append((ci, "two-kernel", fused))
+            dist.barrier()
+        # a replayed graph of prepare + fused projection
+        qt, n, k, m, dt = 12, 17408, 5120, 16, torch.bfloat16
+        per = n // world
+        w = sharded.shard_rows(torch.from_numpy(synth.wire_numpy(qt, n, k, seed=9)), rank, world).contiguous().to(dev)
+        x = torch.from_numpy(synth.activations_numpy(m, k, seed=10)).to(dev).to(dt)
+        scratch = torch.empty(capi.workspace_bytes(qt, m, per, k), dtype=torch.uint8, device=dev)
+        yl = torch.empty((m, per), dtype=dt, device=dev)
+        capi.prepare_q8(x, qt, per, scratch)
+        capi.set_option("gemv_impl", 6)
+        capi.mul_mat_prepared(w, qt, m, k, yl, scratch)
+        capi.set_option("gemv_impl", 0)
+        want = sharded.gather_columns(yl)
+        st = torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(st):
+            capi.prepare_q8(x, qt, per, scratch)
+            pg.project(w, qt, m, k, scratch, dt, 0)
+            torch.cuda.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=st):
+                capi.prepare_q8(x, qt, per, scratch)
+                out, fused = pg.project(w, qt, m, k, scratch, dt, 0)
+            for _ in range(5):
+                gr.replay()
+            torch.cuda.synchronize()
+            if not fused or not torch.equal(out, want):
+                bad.append(("graph", fused))
+        pg.check()
+        if capi.read_status(qt, m, per, k, scratch):
+            bad.append(("status", capi.read_status(qt, m, per, k, scratch)))
+        dist.barrier()
+        q.put((rank, "ok" if not bad else f"mismatch: {bad[:6]}"))
+    except Exception as e:  # noqa: BLE001 - reported to the parent
+        import traceback
+        q.put((rank, f"error: {e!r} {traceback.format_exc()[-600:]}"))
+    finally:
+        os._exit(0)
+
+
+@pytest.mark.gpu
+def test_gemv_with_gather_in_its_epilogue_matches_gemv_plus_nccl():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    procs = [ctx.Process(target=_fused_worker, args=(r, 2, 29537, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=240)
     res = {}
     while not q.empty():
         r, msg = q.get()
