@@ -218,6 +218,41 @@ int kq_mul_mat_prepared_gather(const void* W, int type, int64_t n_local, int64_t
                                uint32_t* const* peer_flags, uint32_t* epoch, uint32_t* done, int slot, int rank,
                                int world, int* peer_status, int* fused, void* stream);
 
+/* Embedding lookup: out[i, :] = the dequantized row row_ids[i] of the [n, k] weight tensor, i < count - the
+ * torch.index_select + ggml_dequantize pair of the reference's GGUF embedding (quantization/vocal_embeds.py:38-55) in
+ * one kernel, without the gathered copy of the wire rows.  f32_math = 0: arithmetic of kq_dequantize; f32_math = 1, for
+ * Q4_K / Q5_K / Q6_K: (d * sc) * q - dmin * m with fp32 products, what gguf-reader computes and what the reference's
+ * embedding uses for these three formats (vocal_embeds.py:43-50, triton/dequantize/k_quant/q4_k.py:13-31); other formats
+ * ignore the flag.  row_ids: int64 on the device; an index outside [0, n) gives a row of zeros (the reference's
+ * index_select traps).  out: [count, k], 16-byte aligned. */
+int kq_dequantize_rows(const void* W, int type, int64_t n, int64_t k, const int64_t* row_ids, int64_t count, void* out,
+                       int out_dtype, int f32_math, void* stream);
+
+/* ggml_moe_a8_vec (vllm_gguf_plugin/csrc/gguf/gguf_kernel.cu:395-530, moe_vec.cuh:4-52): W holds `experts` matrices
+ * [n, k] back to back; output row z = token * top_k + j is W[topk_ids[z]] times the q8_1-quantized activations of token
+ * z / top_k, with the arithmetic of kq_mul_mat_vec_a8.  x [tokens, k], topk_ids int32 [tokens * top_k] (device), y
+ * [tokens * top_k, n].  Rows whose expert id is outside [0, experts) are left as the caller initialised them (the
+ * reference reads out of bounds for them).  Scratch: kq_workspace_bytes(type, tokens, n, k).  tokens * top_k <= 65535. */
+int kq_moe_a8_vec(const void* W, int type, int64_t experts, int64_t n, int64_t k, const void* x, int x_dtype, int64_t tokens,
+                  int64_t stride_x, const int32_t* topk_ids, int top_k, void* y, int y_dtype, int64_t stride_y, void* scratch,
+                  size_t scratch_bytes, void* stream);
+
+/* ggml_moe_a8 (gguf_kernel.cu:292-393, moe.cuh:9-128): the (token, expert) pairs sorted by expert in blocks of
+ * kq_moe_block_size(type) slots, as vLLM's moe_align_block_size lays them out: block b belongs to expert_ids[b]; slot s
+ * holds z = sorted_token_ids[s] (z >= tokens * top_k marks padding) and output row z is W[expert] times the activations
+ * of token z / top_k, with the arithmetic of kq_mul_mat_a8.  Blocks that start beyond num_tokens_post_padded[0] and blocks
+ * whose expert id is outside [0, experts) (the reference: outside [0, 255]) are skipped; rows nobody writes keep the
+ * caller's initialisation (the reference returns zeros).  All three index tensors are int32 on the device;
+ * num_sorted = entries of sorted_token_ids (at most 65535 blocks). */
+int kq_moe_a8(const void* W, int type, int64_t experts, int64_t n, int64_t k, const void* x, int x_dtype, int64_t tokens,
+              int64_t stride_x, const int32_t* sorted_token_ids, int64_t num_sorted, const int32_t* expert_ids,
+              const int32_t* num_tokens_post_padded, int top_k, void* y, int y_dtype, int64_t stride_y, void* scratch,
+              size_t scratch_bytes, void* stream);
+
+/* ggml_moe_get_block_size (gguf_kernel.cu:532-578): the block size kq_moe_a8 expects of moe_align_block_size (8 for every
+ * supported type; the reference's CUDA build answers 4), 0 for a type the library does not know. */
+int kq_moe_block_size(int type);
+
 /* Diagnostics: copies the device-side status word of a scratch buffer to the host (SYNCHRONISES with the
  * device; not for the serving path).  0 = every kernel that used the scratch finished normally; non-zero = a
  * bounded wait inside a kernel gave up and the kernel returned early (its outputs are then undefined).

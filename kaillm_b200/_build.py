@@ -19,7 +19,7 @@ ROOT = os.path.dirname(HERE)
 NVCC = os.environ.get("KQ_NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
-CU_SOURCES = ["kq_api.cu", "kq_quantize.cu", "kq_gemv_dp4a.cu", "kq_gemv_mma.cu", "kq_gemv_tile.cu", "kq_gemv_kres.cu", "kq_gemv_umma.cu", "kq_gemm_tc.cu", "kq_p2p.cu", "kq_dequant.cu"]
+CU_SOURCES = ["kq_api.cu", "kq_quantize.cu", "kq_gemv_dp4a.cu", "kq_gemv_mma.cu", "kq_gemv_tile.cu", "kq_gemv_kres.cu", "kq_gemv_umma.cu", "kq_moe.cu", "kq_gemm_tc.cu", "kq_p2p.cu", "kq_dequant.cu"]
 CU_DEPS = ["kq_common.cuh", "kq_tile_common.cuh", "kq_tma.cuh", "kq_iq3s_codes.inc", os.path.join(ROOT, "include", "kq_gguf.h")]
 
 

@@ -23,7 +23,7 @@ EXPORTS = (
     "kq_mul_mat_vec_a8", "kq_mul_mat_a8", "kq_dequantize", "kq_debug_group_dots", "kq_set_option",
     "kq_get_option", "kq_prepare_q8", "kq_mul_mat_prepared", "kq_read_status", "kq_mul_mat_vec_a8_static",
     "kq_p2p_allgather", "kq_read_status_static", "kq_debug_copy_window", "kq_prepare_q8_rmsnorm", "kq_prepare_q8_swiglu",
-    "kq_p2p_allgather_2d", "kq_mul_mat_prepared_gather",
+    "kq_p2p_allgather_2d", "kq_mul_mat_prepared_gather", "kq_moe_a8_vec", "kq_moe_a8", "kq_moe_block_size", "kq_dequantize_rows",
 )
 
 
@@ -65,6 +65,10 @@ def _load() -> ctypes.CDLL:
     lib.kq_p2p_allgather_2d.argtypes = [vp, i64, sz, ctypes.POINTER(vp), sz, ctypes.POINTER(vp), vp, vp, i32, i32, i32, vp, vp]
     lib.kq_mul_mat_prepared_gather.argtypes = [vp, i32, i64, i64, i64, i32, i32, vp, sz, ctypes.POINTER(vp), i64,
                                                ctypes.POINTER(vp), vp, vp, i32, i32, i32, vp, ctypes.POINTER(i32), vp]
+    lib.kq_moe_a8_vec.argtypes = [vp, i32, i64, i64, i64, vp, i32, i64, i64, vp, i32, vp, i32, i64, vp, sz, vp]
+    lib.kq_moe_a8.argtypes = [vp, i32, i64, i64, i64, vp, i32, i64, i64, vp, i64, vp, vp, i32, vp, i32, i64, vp, sz, vp]
+    lib.kq_moe_block_size.argtypes = [i32]
+    lib.kq_dequantize_rows.argtypes = [vp, i32, i64, i64, vp, i64, vp, i32, i32, vp]
     lib.kq_set_option.argtypes = [ctypes.c_char_p, i32]
     lib.kq_get_option.argtypes = [ctypes.c_char_p, ctypes.POINTER(i32)]
     return lib
@@ -250,11 +254,51 @@ def mul_mat_prepared_gather(W: torch.Tensor, qtype: int, m: int, k: int, scratch
     return bool(fused.value)
 
 
+def moe_a8_vec(W: torch.Tensor, x: torch.Tensor, topk_ids: torch.Tensor, qtype: int, out_dtype=None) -> torch.Tensor:
+    """kq_moe_a8_vec: W [E, n, row bytes], x [tokens, k], topk_ids int32 [tokens, top_k] -> [tokens * top_k, n]."""
+    experts, n = W.shape[0], W.shape[1]
+    tokens, k = x.shape
+    top_k = topk_ids.shape[1]
+    y = torch.zeros((tokens * top_k, n), dtype=out_dtype or x.dtype, device=x.device)
+    scratch = torch.empty(max(1, workspace_bytes(qtype, tokens, n, k)), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        _check(lib.kq_moe_a8_vec(W.data_ptr(), qtype, experts, n, k, x.data_ptr(), _DT[x.dtype], tokens, x.stride(0),
+                                 topk_ids.data_ptr(), top_k, y.data_ptr(), _DT[y.dtype], y.stride(0), scratch.data_ptr(),
+                                 scratch.numel(), _stream(x.device)))
+    return y
+
+
+def moe_a8(W: torch.Tensor, x: torch.Tensor, sorted_token_ids: torch.Tensor, expert_ids: torch.Tensor,
+           num_tokens_post_padded: torch.Tensor, top_k: int, qtype: int, out_dtype=None) -> torch.Tensor:
+    """kq_moe_a8: expert-sorted blocks of kq_moe_block_size slots -> [tokens * top_k, n] (rows nobody writes stay zero)."""
+    experts, n = W.shape[0], W.shape[1]
+    tokens, k = x.shape
+    y = torch.zeros((tokens * top_k, n), dtype=out_dtype or x.dtype, device=x.device)
+    scratch = torch.empty(max(1, workspace_bytes(qtype, tokens, n, k)), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        _check(lib.kq_moe_a8(W.data_ptr(), qtype, experts, n, k, x.data_ptr(), _DT[x.dtype], tokens, x.stride(0),
+                             sorted_token_ids.data_ptr(), sorted_token_ids.numel(), expert_ids.data_ptr(),
+                             num_tokens_post_padded.data_ptr(), top_k, y.data_ptr(), _DT[y.dtype], y.stride(0),
+                             scratch.data_ptr(), scratch.numel(), _stream(x.device)))
+    return y
+
+
 def dequantize(W: torch.Tensor, qtype: int, count: int, dtype=torch.float16) -> torch.Tensor:
     out = torch.empty(count, dtype=dtype, device=W.device)
     with torch.cuda.device(W.device):
         _check(lib.kq_dequantize(W.data_ptr(), qtype, count, out.data_ptr(), _DT[dtype], _stream(W.device)))
     return out
+
+
+def dequantize_rows(W: torch.Tensor, qtype: int, k: int, row_ids: torch.Tensor, dtype=torch.float16,
+                    f32_math: bool = False) -> torch.Tensor:
+    """kq_dequantize_rows: rows `row_ids` (int64, any shape) of the [n, row bytes] wire tensor W -> [*row_ids.shape, k]."""
+    ids = row_ids.reshape(-1).to(torch.int64).contiguous()
+    out = torch.empty((ids.numel(), k), dtype=dtype, device=W.device)
+    with torch.cuda.device(W.device):
+        _check(lib.kq_dequantize_rows(W.data_ptr(), qtype, W.shape[0], k, ids.data_ptr(), ids.numel(), out.data_ptr(),
+                                      _DT[dtype], int(f32_math), _stream(W.device)))
+    return out.view(*row_ids.shape, k)
 
 
 def debug_group_dots(W: torch.Tensor, x: torch.Tensor, qtype: int):

@@ -284,6 +284,19 @@ int kq_dequantize(const void* W, int type, int64_t count, void* out, int out_dty
   return launch_dequantize(W, type, count, out, out_dtype, (cudaStream_t)stream);
 }
 
+int kq_dequantize_rows(const void* W, int type, int64_t n, int64_t k, const int64_t* row_ids, int64_t count, void* out,
+                       int out_dtype, int f32_math, void* stream) {
+  t_err[0] = 0;
+  int b, s;
+  if (!type_geometry(type, &b, &s)) { set_error("kq_dequantize_rows: GGML type %d is not supported", type); return KQ_EUNSUPPORTED; }
+  if (!dtype_ok(out_dtype)) { set_error("kq_dequantize_rows: unsupported output dtype %d", out_dtype); return KQ_EUNSUPPORTED; }
+  if (n <= 0 || k <= 0 || k % b || count < 0) { set_error("kq_dequantize_rows: k=%lld must be a positive multiple of the block size %d", (long long)k, b); return KQ_EINVAL; }
+  if (count == 0) return KQ_OK;
+  if (!W || !out || !row_ids) { set_error("kq_dequantize_rows: null pointer"); return KQ_EINVAL; }
+  if ((uintptr_t)W % 2 || (uintptr_t)out % 16 || (uintptr_t)row_ids % 8) { set_error("kq_dequantize_rows: W must be 2-byte, out 16-byte, row_ids 8-byte aligned"); return KQ_EINVAL; }
+  return launch_dequantize(W, type, count * k, out, out_dtype, (cudaStream_t)stream, row_ids, k, n, f32_math != 0);
+}
+
 int kq_debug_group_dots(const void* W, int type, int64_t n, int64_t k, const void* x, int x_dtype, int64_t m,
                         int64_t stride_x, int32_t* dots, int32_t* sums, void* scratch, size_t scratch_bytes,
                         void* stream) {
@@ -378,6 +391,56 @@ int kq_mul_mat_prepared_gather(const void* W, int type, int64_t n_local, int64_t
   if (rc || world == 1) return rc;
   return launch_p2p_allgather(mine, (size_t)m * n_local * esz, m, (size_t)stride_y * esz, peer_y, peer_flags, epoch, done, slot,
                               rank, world, peer_status, st, (size_t)stride_y * esz);
+}
+
+// ---------------------------------------------------------------------------------------------- mixture of experts
+static int moe_common(const char* fn, bool block, const void* W, int type, int64_t experts, int64_t n, int64_t k, const void* x,
+                      int x_dtype, int64_t tokens, int64_t stride_x, const int32_t* ids, int64_t nslots, const int32_t* expert_ids,
+                      const int32_t* num_post_padded, int top_k, void* y, int y_dtype, int64_t stride_y, void* scratch,
+                      size_t scratch_bytes, void* stream) {
+  t_err[0] = 0;
+  if (experts <= 0 || top_k <= 0 || nslots < 0) { set_error("%s: experts, top_k must be positive", fn); return KQ_EINVAL; }
+  if (!ids || (block && (!expert_ids || !num_post_padded))) { set_error("%s: null index tensor", fn); return KQ_EINVAL; }
+  if (tokens == 0) return KQ_OK;
+  Problem p;
+  int rc = validate(fn, W, type, n, k, x, x_dtype, tokens, stride_x, scratch, scratch_bytes, p, true, true);
+  if (rc) return rc;
+  if (block && (type == KQ_TYPE_IQ3_S || type == KQ_TYPE_IQ4_NL || type == KQ_TYPE_IQ4_XS)) {
+    set_error("%s: the i-matrix formats have no MMQ kernel (use kq_moe_a8_vec)", fn);
+    return KQ_EUNSUPPORTED;
+  }
+  if (!dtype_ok(y_dtype)) { set_error("%s: unsupported output dtype %d", fn, y_dtype); return KQ_EUNSUPPORTED; }
+  if (!y || stride_y < n) { set_error("%s: bad output (null or stride_y < n)", fn); return KQ_EINVAL; }
+  if ((uintptr_t)y % dtype_size(y_dtype)) { set_error("%s: misaligned output pointer", fn); return KQ_EINVAL; }
+  if (tokens * top_k > 0x7fffffffll) { set_error("%s: tokens * top_k does not fit 31 bits", fn); return KQ_ELIMIT; }
+  cudaStream_t st = (cudaStream_t)stream;
+  Q8Ptrs P = q8_ptrs(scratch, p.L, n);
+  Q8Ptrs Pq = P;   // only the row-major codes and scales are read
+  Pq.qsp = nullptr; Pq.xh = nullptr; Pq.s8h = nullptr; Pq.dT = nullptr; Pq.qsu = nullptr;
+  rc = launch_quantize(x, x_dtype, tokens, k, stride_x, &Pq, nullptr, p.L.kpad, st);
+  if (rc) return rc;
+  return launch_moe(W, type, experts, n, k, P.ds, P.qs, p.L.kpad, tokens, top_k, ids, nslots, expert_ids, num_post_padded, block, y,
+                    y_dtype, stride_y, st);
+}
+
+int kq_moe_a8_vec(const void* W, int type, int64_t experts, int64_t n, int64_t k, const void* x, int x_dtype, int64_t tokens,
+                  int64_t stride_x, const int32_t* topk_ids, int top_k, void* y, int y_dtype, int64_t stride_y, void* scratch,
+                  size_t scratch_bytes, void* stream) {
+  return moe_common("kq_moe_a8_vec", false, W, type, experts, n, k, x, x_dtype, tokens, stride_x, topk_ids, tokens * (int64_t)top_k,
+                    nullptr, nullptr, top_k, y, y_dtype, stride_y, scratch, scratch_bytes, stream);
+}
+
+int kq_moe_a8(const void* W, int type, int64_t experts, int64_t n, int64_t k, const void* x, int x_dtype, int64_t tokens,
+              int64_t stride_x, const int32_t* sorted_token_ids, int64_t num_sorted, const int32_t* expert_ids,
+              const int32_t* num_tokens_post_padded, int top_k, void* y, int y_dtype, int64_t stride_y, void* scratch,
+              size_t scratch_bytes, void* stream) {
+  return moe_common("kq_moe_a8", true, W, type, experts, n, k, x, x_dtype, tokens, stride_x, sorted_token_ids, num_sorted, expert_ids,
+                    num_tokens_post_padded, top_k, y, y_dtype, stride_y, scratch, scratch_bytes, stream);
+}
+
+int kq_moe_block_size(int type) {
+  int b, sz;
+  return type_geometry(type, &b, &sz) ? KQ_MOE_BLOCK : 0;
 }
 
 int kq_debug_copy_window(uint64_t base, int64_t n, int64_t rowbytes, int64_t row_a, int64_t row_b, int64_t seg_off,

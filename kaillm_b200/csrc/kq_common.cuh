@@ -220,6 +220,10 @@ int launch_prepare_rmsnorm(const void* x, int x_dtype, int64_t m, int64_t k, int
                            void* y_norm, const Q8Ptrs& P, cudaStream_t st);
 int launch_prepare_swiglu(const void* gate_up, int x_dtype, int64_t m, int64_t k, int64_t stride_gu, const Q8Ptrs& P,
                           cudaStream_t st);
+constexpr int KQ_MOE_BLOCK = 8;   // slots per block of expert-sorted tokens (what kq_moe_block_size reports)
+int launch_moe(const void* W, int type, int64_t experts, int64_t n, int64_t k, const void* ds, const void* qs, int64_t kpad,
+               int64_t tokens, int top_k, const int32_t* ids, int64_t nslots, const int32_t* expert_ids,
+               const int32_t* num_post_padded, bool block, void* y, int y_dtype, int64_t stride_y, cudaStream_t st);
 int launch_gemv_dp4a(const void* W, int type, int64_t n, int64_t k, const void* ds, const void* qs,
                      int64_t kpad, int64_t m, void* y, int y_dtype, int64_t stride_y, bool mmq,
                      int32_t* dbg_dots, int32_t* dbg_sums, cudaStream_t st);
@@ -258,7 +262,8 @@ int launch_p2p_allgather(const void* src, size_t bytes, int64_t rows, size_t dst
 bool gemm_tc_supported(const void* W, int type, int64_t n, int64_t k);
 int launch_gemm_tc(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m, void* y, int y_dtype,
                    int64_t stride_y, bool mmq, cudaStream_t st);
-int launch_dequantize(const void* W, int type, int64_t count, void* out, int out_dtype, cudaStream_t st);
+int launch_dequantize(const void* W, int type, int64_t count, void* out, int out_dtype, cudaStream_t st,
+                      const int64_t* ids = nullptr, int64_t k = 0, int64_t nrows = 0, int f32math = 0);
 
 #ifdef __CUDACC__
 // ------------------------------------------------------------------ programmatic dependent launch

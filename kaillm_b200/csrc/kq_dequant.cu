@@ -28,13 +28,30 @@ __device__ __forceinline__ __half mul_sub(__half a, __half b, __half c, int fma)
   return fma ? __hfma(a, b, __hneg(c)) : __hsub_rn(__hmul_rn(a, b), c);
 }
 
+struct RowGather {
+  const int64_t* ids;   // nullptr: the blocks are taken in storage order
+  int64_t k, rowbytes, nrows;
+  int f32math;          // Q4_K / Q5_K / Q6_K: fp32 products as gguf-reader and the reference's embedding decoder form them
+};
+
 template <int QT, typename OutT>
 __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restrict__ W, int64_t count,
-                                                         OutT* __restrict__ out, int fma) {
+                                                         OutT* __restrict__ out, int fma, RowGather g) {
   using F = Fmt<QT>;
   const int64_t e0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (e0 >= count) return;
   const uint8_t* b = W + (e0 / F::BLK) * F::BYTES;
+  if (g.ids != nullptr) {
+    // output row r is weight row ids[r] (an embedding lookup); a row index outside the tensor gives zeros
+    const int64_t r = e0 / g.k, src = g.ids[r];
+    if (src < 0 || src >= g.nrows) {
+      const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+      reinterpret_cast<uint4*>(out + e0)[0] = z;
+      if constexpr (sizeof(OutT) == 4) reinterpret_cast<uint4*>(out + e0)[1] = z;
+      return;
+    }
+    b = W + src * g.rowbytes + ((e0 - r * g.k) / F::BLK) * F::BYTES;
+  }
   const int r0 = (int)(e0 % F::BLK);
   OutT res[8];
   if constexpr (QT == KQ_TYPE_Q4_0) {
@@ -81,7 +98,11 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restri
     for (int j = 0; j < 8; ++j) {
       const int byte = b[16 + 32 * il + l0 + j];
       const int qq = hi ? (byte >> 4) : (byte & 15);
-      res[j] = half_to_out<OutT>(mul_sub(d1, __int2half_rn(qq), m1, fma));
+      if (g.f32math)   // (d * sc) * q - dmin * m with every product and the difference rounded in fp32
+        res[j] = from_f32<OutT>(__fsub_rn(__fmul_rn(__fmul_rn(__half2float(dall), (float)sc), (float)qq),
+                                          __fmul_rn(__half2float(dmin), (float)mn)));
+      else
+        res[j] = half_to_out<OutT>(mul_sub(d1, __int2half_rn(qq), m1, fma));
     }
   } else if constexpr (QT == KQ_TYPE_Q6_K) {
     const __half d = __ushort_as_half(*reinterpret_cast<const uint16_t*>(b + 208));
@@ -93,7 +114,8 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restri
       const int nib = (q4 < 2) ? (lo & 15) : (lo >> 4);
       const int hb = (b[128 + 32 * ip + l0 + j] >> (2 * q4)) & 3;
       const int code = (nib | (hb << 4)) - 32;
-      res[j] = half_to_out<OutT>(__hmul_rn(d, __int2half_rn(sc * code)));
+      if (g.f32math) res[j] = from_f32<OutT>(__fmul_rn(__fmul_rn(__half2float(d), (float)sc), (float)code));   // (d * sc) * q
+      else res[j] = half_to_out<OutT>(__hmul_rn(d, __int2half_rn(sc * code)));
     }
   } else if constexpr (QT == KQ_TYPE_IQ3_S) {
     const float dh = ld_h(b);
@@ -163,7 +185,11 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restri
     for (int j = 0; j < 8; ++j) {
       const int byte = b[48 + 32 * il + l0 + j];
       const int qq = (hi ? (byte >> 4) : (byte & 15)) + (((b[16 + l0 + j] >> jj) & 1) ? 16 : 0);
-      res[j] = half_to_out<OutT>(mul_sub(d1, __int2half_rn(qq), m1, fma));
+      if (g.f32math)
+        res[j] = from_f32<OutT>(__fsub_rn(__fmul_rn(__fmul_rn(__half2float(dall), (float)sc), (float)qq),
+                                          __fmul_rn(__half2float(dmin), (float)mn)));
+      else
+        res[j] = half_to_out<OutT>(mul_sub(d1, __int2half_rn(qq), m1, fma));
     }
   } else if constexpr (QT == KQ_TYPE_IQ4_NL || QT == KQ_TYPE_IQ4_XS) {   // dequantize.cuh:401-437: fp32 d * code value
     constexpr int KV[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
@@ -198,14 +224,14 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restri
 }
 
 template <int QT>
-static int run(const void* W, int64_t count, void* out, int out_dtype, int fma, cudaStream_t st) {
+static int run(const void* W, int64_t count, void* out, int out_dtype, int fma, cudaStream_t st, const RowGather& g) {
   const int64_t threads = count / 8;
   const unsigned grid = (unsigned)((threads + 255) / 256);
   if (grid == 0) return KQ_OK;
   switch (out_dtype) {
-    case KQ_F16: dequantize_kernel<QT, __half><<<grid, 256, 0, st>>>((const uint8_t*)W, count, (__half*)out, fma); break;
-    case KQ_BF16: dequantize_kernel<QT, __nv_bfloat16><<<grid, 256, 0, st>>>((const uint8_t*)W, count, (__nv_bfloat16*)out, fma); break;
-    case KQ_F32: dequantize_kernel<QT, float><<<grid, 256, 0, st>>>((const uint8_t*)W, count, (float*)out, fma); break;
+    case KQ_F16: dequantize_kernel<QT, __half><<<grid, 256, 0, st>>>((const uint8_t*)W, count, (__half*)out, fma, g); break;
+    case KQ_BF16: dequantize_kernel<QT, __nv_bfloat16><<<grid, 256, 0, st>>>((const uint8_t*)W, count, (__nv_bfloat16*)out, fma, g); break;
+    case KQ_F32: dequantize_kernel<QT, float><<<grid, 256, 0, st>>>((const uint8_t*)W, count, (float*)out, fma, g); break;
     default: set_error("unsupported output dtype %d", out_dtype); return KQ_EUNSUPPORTED;
   }
   options().launches += 1;
@@ -213,22 +239,30 @@ static int run(const void* W, int64_t count, void* out, int out_dtype, int fma, 
   return KQ_OK;
 }
 
-int launch_dequantize(const void* W, int type, int64_t count, void* out, int out_dtype, cudaStream_t st) {
+int launch_dequantize(const void* W, int type, int64_t count, void* out, int out_dtype, cudaStream_t st, const int64_t* ids,
+                      int64_t k, int64_t nrows, int f32math) {
   const int fma = options().half_fma;
+  RowGather g;
+  g.ids = ids; g.k = k; g.nrows = nrows; g.rowbytes = 0; g.f32math = f32math;
+  if (ids) {
+    int blk, bytes;
+    if (!type_geometry(type, &blk, &bytes)) { set_error("unsupported GGML type %d", type); return KQ_EUNSUPPORTED; }
+    g.rowbytes = k / blk * bytes;
+  }
   switch (type) {
-    case KQ_TYPE_Q4_0: return run<KQ_TYPE_Q4_0>(W, count, out, out_dtype, fma, st);
-    case KQ_TYPE_Q8_0: return run<KQ_TYPE_Q8_0>(W, count, out, out_dtype, fma, st);
-    case KQ_TYPE_Q2_K: return run<KQ_TYPE_Q2_K>(W, count, out, out_dtype, fma, st);
-    case KQ_TYPE_Q4_K: return run<KQ_TYPE_Q4_K>(W, count, out, out_dtype, fma, st);
-    case KQ_TYPE_Q6_K: return run<KQ_TYPE_Q6_K>(W, count, out, out_dtype, fma, st);
-    case KQ_TYPE_IQ3_S: return run<KQ_TYPE_IQ3_S>(W, count, out, out_dtype, fma, st);
-    case KQ_TYPE_Q4_1: return run<KQ_TYPE_Q4_1>(W, count, out, out_dtype, fma, st);
-    case KQ_TYPE_Q5_0: return run<KQ_TYPE_Q5_0>(W, count, out, out_dtype, fma, st);
-    case KQ_TYPE_Q5_1: return run<KQ_TYPE_Q5_1>(W, count, out, out_dtype, fma, st);
-    case KQ_TYPE_Q3_K: return run<KQ_TYPE_Q3_K>(W, count, out, out_dtype, fma, st);
-    case KQ_TYPE_Q5_K: return run<KQ_TYPE_Q5_K>(W, count, out, out_dtype, fma, st);
-    case KQ_TYPE_IQ4_NL: return run<KQ_TYPE_IQ4_NL>(W, count, out, out_dtype, fma, st);
-    case KQ_TYPE_IQ4_XS: return run<KQ_TYPE_IQ4_XS>(W, count, out, out_dtype, fma, st);
+    case KQ_TYPE_Q4_0: return run<KQ_TYPE_Q4_0>(W, count, out, out_dtype, fma, st, g);
+    case KQ_TYPE_Q8_0: return run<KQ_TYPE_Q8_0>(W, count, out, out_dtype, fma, st, g);
+    case KQ_TYPE_Q2_K: return run<KQ_TYPE_Q2_K>(W, count, out, out_dtype, fma, st, g);
+    case KQ_TYPE_Q4_K: return run<KQ_TYPE_Q4_K>(W, count, out, out_dtype, fma, st, g);
+    case KQ_TYPE_Q6_K: return run<KQ_TYPE_Q6_K>(W, count, out, out_dtype, fma, st, g);
+    case KQ_TYPE_IQ3_S: return run<KQ_TYPE_IQ3_S>(W, count, out, out_dtype, fma, st, g);
+    case KQ_TYPE_Q4_1: return run<KQ_TYPE_Q4_1>(W, count, out, out_dtype, fma, st, g);
+    case KQ_TYPE_Q5_0: return run<KQ_TYPE_Q5_0>(W, count, out, out_dtype, fma, st, g);
+    case KQ_TYPE_Q5_1: return run<KQ_TYPE_Q5_1>(W, count, out, out_dtype, fma, st, g);
+    case KQ_TYPE_Q3_K: return run<KQ_TYPE_Q3_K>(W, count, out, out_dtype, fma, st, g);
+    case KQ_TYPE_Q5_K: return run<KQ_TYPE_Q5_K>(W, count, out, out_dtype, fma, st, g);
+    case KQ_TYPE_IQ4_NL: return run<KQ_TYPE_IQ4_NL>(W, count, out, out_dtype, fma, st, g);
+    case KQ_TYPE_IQ4_XS: return run<KQ_TYPE_IQ4_XS>(W, count, out, out_dtype, fma, st, g);
   }
   set_error("unsupported GGML type %d", type);
   return KQ_EUNSUPPORTED;

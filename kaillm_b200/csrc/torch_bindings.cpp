@@ -88,17 +88,65 @@ at::Tensor ggml_dequantize(const at::Tensor& W, int64_t type, c10::SymInt m_, c1
   return DW;
 }
 
-at::Tensor ggml_moe_a8(const at::Tensor&, const at::Tensor&, const at::Tensor&, const at::Tensor&, const at::Tensor&,
-                       int64_t, c10::SymInt, c10::SymInt, c10::SymInt) {
-  TORCH_CHECK(false, "ggml_moe_a8: mixture-of-experts GGUF kernels are not part of this library");
+// W: [E, row, row bytes] (or any contiguous uint8 tensor holding E matrices back to back)
+at::Tensor moe_impl(bool block, const at::Tensor& X, const at::Tensor& W, const at::Tensor& ids, const at::Tensor* expert_ids,
+                    const at::Tensor* num_post_padded, int64_t type, int64_t row, int64_t top_k, int64_t tokens) {
+  const char* fn = block ? "ggml_moe_a8" : "ggml_moe_a8_vec";
+  check_weight(W, fn);
+  TORCH_CHECK(X.is_cuda() && X.dim() == 2, fn, ": X must be a 2-D CUDA tensor");
+  TORCH_CHECK(X.get_device() == W.get_device(), fn, ": W and X are on different devices");
+  TORCH_CHECK(X.stride(1) == 1, fn, ": X must be contiguous along its last dimension");
+  TORCH_CHECK(tokens >= 0 && tokens <= X.size(0), fn, ": `tokens` exceeds X.size(0)");
+  TORCH_CHECK(top_k > 0 && row >= 0, fn, ": top_k must be positive");
+  const int64_t k = X.size(1);
+  const int xdt = kq_dtype_of(X.scalar_type(), fn);
+  int blk = 0, bytes = 0;
+  TORCH_CHECK(kq_block_geometry((int)type, &blk, &bytes) == KQ_OK, fn, ": ", kq_last_error());
+  TORCH_CHECK(k % blk == 0, fn, ": X.size(1)=", k, " is not a multiple of the block size ", blk);
+  const int64_t per_expert = row * (k / blk) * bytes;
+  TORCH_CHECK(per_expert > 0 && W.numel() % per_expert == 0, fn, ": W is not a whole number of [row, K] matrices");
+  const int64_t experts = W.numel() / per_expert;
+  auto as_i32 = [&](const at::Tensor& t, const char* name) {
+    TORCH_CHECK(t.is_cuda() && t.get_device() == X.get_device(), fn, ": ", name, " must be on X's device");
+    return t.scalar_type() == at::kInt && t.is_contiguous() ? t : t.to(at::kInt).contiguous();
+  };
+  const c10::cuda::CUDAGuard guard(X.device());
+  at::Tensor Y = at::zeros({tokens * top_k, row}, X.options());   // rows nobody writes read as zero, as in the reference
+  if (tokens == 0 || row == 0) return Y;
+  const at::Tensor ids32 = as_i32(ids, block ? "sorted_token_ids" : "topk_ids");
+  const size_t ws = kq_workspace_bytes((int)type, tokens, row, k);
+  at::Tensor scratch = at::empty({(int64_t)ws}, W.options());
+  auto stream = at::cuda::getCurrentCUDAStream(X.get_device()).stream();
+  int rc;
+  if (block) {
+    const at::Tensor e32 = as_i32(*expert_ids, "expert_ids"), n32 = as_i32(*num_post_padded, "num_tokens_post_padded");
+    TORCH_CHECK(n32.numel() >= 1, fn, ": num_tokens_post_padded is empty");
+    TORCH_CHECK(e32.numel() * kq_moe_block_size((int)type) >= ids32.numel(), fn, ": expert_ids has fewer entries than blocks of sorted tokens");
+    rc = kq_moe_a8(W.data_ptr(), (int)type, experts, row, k, X.data_ptr(), xdt, tokens, X.stride(0), ids32.data_ptr<int32_t>(),
+                   ids32.numel(), e32.data_ptr<int32_t>(), n32.data_ptr<int32_t>(), (int)top_k, Y.data_ptr(), xdt, Y.stride(0),
+                   scratch.data_ptr(), ws, (void*)stream);
+  } else {
+    TORCH_CHECK(ids32.numel() >= tokens * top_k, fn, ": topk_ids has fewer than tokens * top_k entries");
+    rc = kq_moe_a8_vec(W.data_ptr(), (int)type, experts, row, k, X.data_ptr(), xdt, tokens, X.stride(0), ids32.data_ptr<int32_t>(),
+                       (int)top_k, Y.data_ptr(), xdt, Y.stride(0), scratch.data_ptr(), ws, (void*)stream);
+  }
+  TORCH_CHECK(rc == KQ_OK, fn, ": ", kq_last_error());
+  return Y;
 }
 
-at::Tensor ggml_moe_a8_vec(const at::Tensor&, const at::Tensor&, const at::Tensor&, int64_t, int64_t, c10::SymInt,
-                           c10::SymInt) {
-  TORCH_CHECK(false, "ggml_moe_a8_vec: mixture-of-experts GGUF kernels are not part of this library");
+at::Tensor ggml_moe_a8(const at::Tensor& X, const at::Tensor& W, const at::Tensor& sorted_token_ids, const at::Tensor& expert_ids,
+                       const at::Tensor& num_tokens_post_padded, int64_t type, c10::SymInt row, c10::SymInt top_k,
+                       c10::SymInt tokens) {
+  return moe_impl(true, X, W, sorted_token_ids, &expert_ids, &num_tokens_post_padded, type, row.expect_int(), top_k.expect_int(),
+                  tokens.expect_int());
 }
 
-int64_t ggml_moe_get_block_size(int64_t) { return 0; }
+at::Tensor ggml_moe_a8_vec(const at::Tensor& X, const at::Tensor& W, const at::Tensor& topk_ids, int64_t top_k, int64_t type,
+                           c10::SymInt row, c10::SymInt tokens) {
+  return moe_impl(false, X, W, topk_ids, nullptr, nullptr, type, row.expect_int(), top_k, tokens.expect_int());
+}
+
+int64_t ggml_moe_get_block_size(int64_t type) { return kq_moe_block_size((int)type); }
 
 }  // namespace
 

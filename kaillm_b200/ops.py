@@ -45,3 +45,21 @@ def ggml_mul_mat_vec_a8(W: torch.Tensor, X: torch.Tensor, quant_type: int, row: 
 
 def ggml_mul_mat_a8(W: torch.Tensor, X: torch.Tensor, quant_type: int, row: int) -> torch.Tensor:
     return torch.ops._C_gguf.ggml_mul_mat_a8(W, X, quant_type, row)
+
+
+def ggml_moe_a8(X: torch.Tensor, W: torch.Tensor, sorted_token_ids: torch.Tensor, expert_ids: torch.Tensor,
+                num_tokens_post_padded: torch.Tensor, quant_type: int, row: int, top_k: int, tokens: int) -> torch.Tensor:
+    """vllm_gguf_plugin/ops.py:211-246."""
+    return torch.ops._C_gguf.ggml_moe_a8(X, W, sorted_token_ids, expert_ids, num_tokens_post_padded, quant_type, row, top_k,
+                                         tokens)
+
+
+def ggml_moe_a8_vec(X: torch.Tensor, W: torch.Tensor, topk_ids: torch.Tensor, top_k: int, quant_type: int, row: int,
+                    tokens: int) -> torch.Tensor:
+    """vllm_gguf_plugin/ops.py:249-278."""
+    return torch.ops._C_gguf.ggml_moe_a8_vec(X, W, topk_ids, top_k, quant_type, row, tokens)
+
+
+def ggml_moe_get_block_size(quant_type: int) -> int:
+    """vllm_gguf_plugin/ops.py:281-284."""
+    return torch.ops._C_gguf.ggml_moe_get_block_size(quant_type)

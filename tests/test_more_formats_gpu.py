@@ -107,3 +107,26 @@ def test_dequantize_bit_identical_to_reference(ref_ops, qt, dt):
     ref = ref_ops.ggml_dequantize(wt, qt, n, k, TDT[dt])
     mine = torch.ops._C_gguf.ggml_dequantize(wt, qt, n, k, TDT[dt])
     assert torch.equal(mine, ref)
+
+
+@pytest.mark.parametrize("qt", O.ALL_QTYPES)
+@pytest.mark.parametrize("dt", ["f16", "bf16", "f32"])
+def test_embedding_rows_match_oracle(qt, dt):
+    """kq_dequantize_rows / linear.apply_gguf_embedding: the selected rows, read in place, equal the dequantized gather
+    (vllm_gguf_plugin/quantization/vocal_embeds.py:29-58); Q4_K / Q5_K / Q6_K with fp32 products (gguf-reader's
+    arithmetic), the others with ggml_dequantize's."""
+    from kaillm_b200 import linear
+    vocab, hidden = 300, 1024
+    w, wt = wire(qt, vocab, hidden, seed=9 + qt)
+    ids = torch.tensor([[5, 299, 0], [17, 5, 123]], dtype=torch.long, device=dev())
+    out = linear.apply_gguf_embedding(ids, wt, qt, hidden, TDT[dt])
+    assert out.shape == (2, 3, hidden) and out.dtype == TDT[dt]
+    rows = w[ids.flatten().cpu().numpy()]
+    if qt in (12, 13, 14):
+        want = O.round_to_dtype(O.dequantize_f32(rows, qt), dt)
+    else:
+        want = O.dequantize(rows, qt, dt, half_fma=capi.get_option("half_fma"))
+    np.testing.assert_array_equal(to_np(out).reshape(-1, hidden), want)
+    bad = torch.tensor([0, vocab, -1, 7], dtype=torch.long, device=dev())
+    got = capi.dequantize_rows(wt, qt, hidden, bad, TDT[dt], f32_math=qt in (12, 13, 14))
+    assert not got[1].any() and not got[2].any() and torch.equal(got[3], capi.dequantize_rows(wt, qt, hidden, bad[3:], TDT[dt], f32_math=qt in (12, 13, 14))[0])

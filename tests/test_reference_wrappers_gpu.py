@@ -240,3 +240,27 @@ def test_reference_embedding_over_the_dequantize_op(plugin, qt):
     assert out.shape == (2, 3, hidden) and out.dtype == torch.float16
     want = O.dequantize(w[ids.flatten().cpu().numpy()], qt, "f16", half_fma=capi.get_option("half_fma"))
     np.testing.assert_array_equal(to_np(out).reshape(-1, hidden), want)
+
+
+# ------------------------------------------------------------------ mixture-of-experts wrappers
+@pytest.mark.parametrize("qt", [12, 14, 8, 21])
+def test_reference_moe_wrappers_reach_this_library(plugin, qt):
+    """`ops.ggml_moe_a8_vec / ggml_moe_a8 / ggml_moe_get_block_size` (vllm_gguf_plugin/ops.py:211-284) take their CUDA
+    branch on this repository's `_C_gguf` and return the oracle's per-pair results."""
+    e, n, k, tokens, top_k = 4, 64, 512, 9, 2
+    w = np.stack([synth.wire_numpy(qt, n, k, seed=qt + i) for i in range(e)])
+    wt = torch.from_numpy(w).to(dev())
+    x, xt = act(tokens, k, seed=31, dt="bf16")
+    rng = np.random.default_rng(qt)
+    ids = np.stack([rng.choice(e, size=top_k, replace=False) for _ in range(tokens)]).astype(np.int32)
+    idt = torch.from_numpy(ids).to(dev())
+    y = plugin.ops.ggml_moe_a8_vec(xt, wt, idt, top_k, qt, n, tokens)
+    want = np.stack([O.mul_mat(w[int(ids.reshape(-1)[z])], qt, x[z // top_k:z // top_k + 1], "mmvq")[0] for z in range(tokens * top_k)])
+    assert y.dtype == torch.bfloat16 and rel_l2(to_np(y), want) < 5e-3
+    if qt in (12, 14, 8):
+        bs = plugin.ops.ggml_moe_get_block_size(qt)
+        assert bs == capi.lib.kq_moe_block_size(qt) == 8
+        s, ex, tot = kq_linear.moe_align_block_size(idt, bs, e)
+        yb = plugin.ops.ggml_moe_a8(xt, wt, s, ex, tot, qt, n, top_k, tokens)
+        wantb = np.stack([O.mul_mat(w[int(ids.reshape(-1)[z])], qt, x[z // top_k:z // top_k + 1], "mmq")[0] for z in range(tokens * top_k)])
+        assert rel_l2(to_np(yb), wantb) < 5e-3
