@@ -281,7 +281,10 @@ def run_multi(args, torch, dist, dev, rank, world, local):
                 gather_how = "kq_mul_mat_prepared_gather, two kernels (GEMV, then peer-store gather kernel)"
         except Exception as e:  # noqa: BLE001 - keep the NCCL path
             print(f"[bench] symmetric memory unavailable ({e!r}); using NCCL", file=sys.stderr)
-    stack = sharded.DecoderStack(weights, C3_M, K_HID, dev, p2p=p2p)
+    stack = sharded.DecoderStack(weights, C3_M, K_HID, dev, p2p=p2p, wait_in_consumer=not args.flag_gather)
+    if stack.wait_in_consumer:
+        gather_how = ("kq_mul_mat_prepared_gather, wait_in_consumer: the GEMV's epilogue stores its slice into every rank's row-major "
+                      "buffer over NVLink; no hand-shake - the next producer polls the values against the arrival sentinel")
     g = torch.Generator(device=dev)
     g.manual_seed(1234)
     x0 = torch.randn((C3_M, K_HID), device=dev, generator=g).to(torch.bfloat16)
@@ -708,6 +711,7 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=0, help="layers of the stack (default: 16 MLP blocks at N=1, 64 decoder layers at N>1)")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--flag-gather", action="store_true", help="N>1: end every gather with the flag hand-shake instead of sentinel polling")
     ap.add_argument("--no-fused-gather", action="store_true", help="N>1: GEMV and peer-store gather as two kernels")
     ap.add_argument("--nccl", action="store_true", help="N>1: gather with NCCL instead of the library's peer-store kernel")
     ap.add_argument("--quick", action="store_true", help="N=1: only the main workload, roofline and e2e (no further legs)")

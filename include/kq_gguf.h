@@ -126,9 +126,13 @@ int kq_mul_mat_vec_a8_static(const void* W, int type, int64_t n, int64_t k,
  * Replace the quantize_row_q8_1_cuda call and the kernel launch inside ggml_mul_mat_vec_a8 /
  * ggml_mul_mat_a8, vllm_gguf_plugin/csrc/gguf/gguf_kernel.cu:116-118 and 119-215, 232-287; the
  * reference's production path shares the preparation the same way
- * (vllm_gguf_plugin/quantization/native_fused.py:282-347). */
+ * (vllm_gguf_plugin/quantization/native_fused.py:282-347).
+ * flags (also of the fused producers below): 0, or KQ_PREP_WAIT_ARRIVAL when x is a gather buffer that is being filled
+ * by kq_mul_mat_prepared_gather calls with wait_in_consumer = 1 (m <= 80): every element is then re-read until it is not
+ * the arrival sentinel (all bits set), bounded to about two seconds (status word 40 on give-up). */
+#define KQ_PREP_WAIT_ARRIVAL 1
 int kq_prepare_q8(int type, int64_t n, int64_t k, const void* x, int x_dtype, int64_t m, int64_t stride_x,
-                  void* scratch, size_t scratch_bytes, void* stream);
+                  void* scratch, size_t scratch_bytes, int flags, void* stream);
 int kq_mul_mat_prepared(const void* W, int type, int64_t n, int64_t k, int64_t m,
                         void* y, int y_dtype, int64_t stride_y, int mmq,
                         void* scratch, size_t scratch_bytes, void* stream);
@@ -144,9 +148,10 @@ int kq_mul_mat_prepared(const void* W, int type, int64_t n, int64_t k, int64_t m
  * (vllm_gguf_plugin/native/kernels/kai_prepare_ext.cuh:1-10, quantization/native_fused.py:144-200), with this path's
  * q8_1 arithmetic (gguf_kernel.cu:32-69) instead of that backend's own activation format. */
 int kq_prepare_q8_rmsnorm(int type, int64_t n, int64_t k, const void* x, int x_dtype, int64_t m, int64_t stride_x,
-                          const void* gamma, float eps, void* y_norm, void* scratch, size_t scratch_bytes, void* stream);
+                          const void* gamma, float eps, void* y_norm, void* scratch, size_t scratch_bytes, int flags,
+                          void* stream);
 int kq_prepare_q8_swiglu(int type, int64_t n, int64_t k, const void* gate_up, int x_dtype, int64_t m, int64_t stride_gu,
-                         void* scratch, size_t scratch_bytes, void* stream);
+                         void* scratch, size_t scratch_bytes, int flags, void* stream);
 
 /* Dense dequantization of `count` weights (count a multiple of the block size) to out_dtype, with
  * the reference kernels' fp16 intermediate roundings.
@@ -209,6 +214,17 @@ int kq_p2p_allgather_2d(const void* src, int64_t rows, size_t row_bytes, void* c
  *   peer_status  LOCAL device int, as `status` of kq_p2p_allgather: set non-zero when the bounded wait for a peer's
  *                flag ran out (16 + rank of the silent peer from the fused kernel, 1 + rank from the gather kernel); the
  *                library never clears it, so one word can watch a whole sequence of calls
+ *   wait_in_consumer  0: the hand-shake above.  1: NO hand-shake - the kernel only stores its outputs and returns; every
+ *                rank's buffer must hold the arrival sentinel (all bits set) in every element before any rank's call,
+ *                and whoever reads the buffer next polls the elements (kq_prepare_q8* with KQ_PREP_WAIT_ARRIVAL, or
+ *                kq_wait_arrival before a reader outside the library).  An output that would equal the sentinel (a NaN
+ *                with all bits set) is stored as the canonical NaN.  This takes the system-scope fence, the CTA counter
+ *                and the flag round trip off the critical path: what remains is the one-way latency of the stores.
+ *   reset_buf, reset_bytes  with wait_in_consumer: a LOCAL gather buffer (or NULL) that the producer of this call's
+ *                activations has finished reading; the kernel refills it with the sentinel so that its next use starts
+ *                from "nothing has arrived" (16-byte aligned and sized).  A buffer may be written again by the peers
+ *                only after they have consumed outputs of the call that refilled it - true for a chain of layers where
+ *                each call's activations are the previous call's gathered outputs.
  *   fused        out, may be NULL: 1 = one kernel; 0 = two (the usual kernel dispatch into this rank's own columns, then
  *                the gather kernel) - taken for m > 16, for shapes the shared-stage kernel does not cover, for buffers
  *                whose rows are not 16-byte aligned, and with option "no_fused_gather"
@@ -216,7 +232,19 @@ int kq_p2p_allgather_2d(const void* src, int64_t rows, size_t row_bytes, void* c
 int kq_mul_mat_prepared_gather(const void* W, int type, int64_t n_local, int64_t k, int64_t m, int y_dtype, int mmq,
                                void* scratch, size_t scratch_bytes, void* const* peer_y, int64_t stride_y,
                                uint32_t* const* peer_flags, uint32_t* epoch, uint32_t* done, int slot, int rank,
-                               int world, int* peer_status, int* fused, void* stream);
+                               int world, int* peer_status, int wait_in_consumer, void* reset_buf, size_t reset_bytes,
+                               int* fused, void* stream);
+
+/* Returns (on the stream) when no element of buf holds the arrival sentinel any more: the end of a chain of
+ * wait_in_consumer gathers, before something outside the library reads the buffer.  dtype = element type of the buffer
+ * (KQ_F32 / KQ_F16 / KQ_BF16); buf 16-byte aligned, bytes a multiple of 16; *status (local device int) becomes 41 when
+ * the bounded wait runs out. */
+int kq_wait_arrival(const void* buf, size_t bytes, int dtype, int* status, void* stream);
+
+/* Arrival polls that ran out (a peer is gone) set a flag on the GPU that makes every later poll on it give up at once
+ * instead of after its own two seconds.  This call copies the flag to *failed (SYNCHRONISES; may be NULL) and, with
+ * clear != 0, zeroes it.  0 = no poll has run out since the last clear. */
+int kq_arrival_status(int* failed, int clear);
 
 /* Embedding lookup: out[i, :] = the dequantized row row_ids[i] of the [n, k] weight tensor, i < count - the
  * torch.index_select + ggml_dequantize pair of the reference's GGUF embedding (quantization/vocal_embeds.py:38-55) in

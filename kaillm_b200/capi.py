@@ -23,7 +23,7 @@ EXPORTS = (
     "kq_mul_mat_vec_a8", "kq_mul_mat_a8", "kq_dequantize", "kq_debug_group_dots", "kq_set_option",
     "kq_get_option", "kq_prepare_q8", "kq_mul_mat_prepared", "kq_read_status", "kq_mul_mat_vec_a8_static",
     "kq_p2p_allgather", "kq_read_status_static", "kq_debug_copy_window", "kq_prepare_q8_rmsnorm", "kq_prepare_q8_swiglu",
-    "kq_p2p_allgather_2d", "kq_mul_mat_prepared_gather", "kq_moe_a8_vec", "kq_moe_a8", "kq_moe_block_size", "kq_dequantize_rows",
+    "kq_p2p_allgather_2d", "kq_mul_mat_prepared_gather", "kq_moe_a8_vec", "kq_moe_a8", "kq_moe_block_size", "kq_dequantize_rows", "kq_wait_arrival", "kq_arrival_status",
 )
 
 
@@ -50,9 +50,11 @@ def _load() -> ctypes.CDLL:
     mm = [vp, i32, i64, i64, vp, i32, i64, i64, vp, i32, i64, vp, sz, vp]
     lib.kq_mul_mat_vec_a8.argtypes = mm
     lib.kq_mul_mat_a8.argtypes = mm
-    lib.kq_prepare_q8.argtypes = [i32, i64, i64, vp, i32, i64, i64, vp, sz, vp]
-    lib.kq_prepare_q8_rmsnorm.argtypes = [i32, i64, i64, vp, i32, i64, i64, vp, ctypes.c_float, vp, vp, sz, vp]
-    lib.kq_prepare_q8_swiglu.argtypes = [i32, i64, i64, vp, i32, i64, i64, vp, sz, vp]
+    lib.kq_prepare_q8.argtypes = [i32, i64, i64, vp, i32, i64, i64, vp, sz, i32, vp]
+    lib.kq_prepare_q8_rmsnorm.argtypes = [i32, i64, i64, vp, i32, i64, i64, vp, ctypes.c_float, vp, vp, sz, i32, vp]
+    lib.kq_prepare_q8_swiglu.argtypes = [i32, i64, i64, vp, i32, i64, i64, vp, sz, i32, vp]
+    lib.kq_wait_arrival.argtypes = [vp, sz, i32, vp, vp]
+    lib.kq_arrival_status.argtypes = [ctypes.POINTER(i32), i32]
     lib.kq_mul_mat_prepared.argtypes = [vp, i32, i64, i64, i64, vp, i32, i64, i32, vp, sz, vp]
     lib.kq_mul_mat_vec_a8_static.argtypes = [vp, i32, i64, i64, vp, i32, i64, i64, vp, i32, i64, vp]
     lib.kq_dequantize.argtypes = [vp, i32, i64, vp, i32, vp]
@@ -64,7 +66,7 @@ def _load() -> ctypes.CDLL:
     lib.kq_debug_copy_window.argtypes = [ctypes.c_uint64, i64, i64, i64, i64, i64, i64, ctypes.POINTER(i64), u64p, u64p]
     lib.kq_p2p_allgather_2d.argtypes = [vp, i64, sz, ctypes.POINTER(vp), sz, ctypes.POINTER(vp), vp, vp, i32, i32, i32, vp, vp]
     lib.kq_mul_mat_prepared_gather.argtypes = [vp, i32, i64, i64, i64, i32, i32, vp, sz, ctypes.POINTER(vp), i64,
-                                               ctypes.POINTER(vp), vp, vp, i32, i32, i32, vp, ctypes.POINTER(i32), vp]
+                                               ctypes.POINTER(vp), vp, vp, i32, i32, i32, vp, i32, vp, sz, ctypes.POINTER(i32), vp]
     lib.kq_moe_a8_vec.argtypes = [vp, i32, i64, i64, i64, vp, i32, i64, i64, vp, i32, vp, i32, i64, vp, sz, vp]
     lib.kq_moe_a8.argtypes = [vp, i32, i64, i64, i64, vp, i32, i64, i64, vp, i64, vp, vp, i32, vp, i32, i64, vp, sz, vp]
     lib.kq_moe_block_size.argtypes = [i32]
@@ -139,30 +141,31 @@ def mul_mat(W: torch.Tensor, x: torch.Tensor, qtype: int, *, mmq: bool = False, 
     return out
 
 
-def prepare_q8(x: torch.Tensor, qtype: int, n: int, scratch: torch.Tensor) -> None:
-    """Quantize x [m,k] into `scratch` (kq_prepare_q8)."""
+def prepare_q8(x: torch.Tensor, qtype: int, n: int, scratch: torch.Tensor, wait_arrival: bool = False) -> None:
+    """Quantize x [m,k] into `scratch` (kq_prepare_q8).  wait_arrival: x is a gather buffer still being filled by the
+    peers; every element is polled against the arrival sentinel (KQ_PREP_WAIT_ARRIVAL)."""
     m, k = x.shape
     with torch.cuda.device(x.device):
         _check(lib.kq_prepare_q8(qtype, n, k, x.data_ptr(), _DT[x.dtype], m, x.stride(0), scratch.data_ptr(),
-                                 scratch.numel(), _stream(x.device)))
+                                 scratch.numel(), int(wait_arrival), _stream(x.device)))
 
 
 def prepare_q8_rmsnorm(x: torch.Tensor, gamma: torch.Tensor, eps: float, qtype: int, n: int, scratch: torch.Tensor,
-                       y_norm: torch.Tensor | None = None) -> None:
+                       y_norm: torch.Tensor | None = None, wait_arrival: bool = False) -> None:
     """RMSNorm(x) * gamma quantized into `scratch` in one launch (kq_prepare_q8_rmsnorm)."""
     m, k = x.shape
     with torch.cuda.device(x.device):
         _check(lib.kq_prepare_q8_rmsnorm(qtype, n, k, x.data_ptr(), _DT[x.dtype], m, x.stride(0), gamma.data_ptr(), eps,
                                          y_norm.data_ptr() if y_norm is not None else None, scratch.data_ptr(),
-                                         scratch.numel(), _stream(x.device)))
+                                         scratch.numel(), int(wait_arrival), _stream(x.device)))
 
 
-def prepare_q8_swiglu(gate_up: torch.Tensor, qtype: int, n: int, scratch: torch.Tensor) -> None:
+def prepare_q8_swiglu(gate_up: torch.Tensor, qtype: int, n: int, scratch: torch.Tensor, wait_arrival: bool = False) -> None:
     """silu(gate) * up of a merged [m, 2k] gate/up output quantized into `scratch` in one launch (kq_prepare_q8_swiglu)."""
     m, k2 = gate_up.shape
     with torch.cuda.device(gate_up.device):
         _check(lib.kq_prepare_q8_swiglu(qtype, n, k2 // 2, gate_up.data_ptr(), _DT[gate_up.dtype], m, gate_up.stride(0),
-                                        scratch.data_ptr(), scratch.numel(), _stream(gate_up.device)))
+                                        scratch.data_ptr(), scratch.numel(), int(wait_arrival), _stream(gate_up.device)))
 
 
 def mul_mat_prepared(W: torch.Tensor, qtype: int, m: int, k: int, out: torch.Tensor, scratch: torch.Tensor,
@@ -239,7 +242,8 @@ def p2p_allgather_2d(src: torch.Tensor, peer_dst: list[int], dst_row_stride: int
 
 def mul_mat_prepared_gather(W: torch.Tensor, qtype: int, m: int, k: int, scratch: torch.Tensor, peer_y: list[int],
                             stride_y: int, dtype, peer_flags: list[int], epoch: torch.Tensor, done: torch.Tensor,
-                            slot: int, rank: int, status: torch.Tensor, mmq: bool = False) -> bool:
+                            slot: int, rank: int, status: torch.Tensor, mmq: bool = False, wait_in_consumer: bool = False,
+                            reset_ptr: int = 0, reset_bytes: int = 0) -> bool:
     """kq_mul_mat_prepared_gather: this rank's weight slice `W` [N/world, row bytes] times the activations prepared in
     `scratch`, written as columns rank*N/world.. of every rank's row-major buffer (`peer_y`: device addresses, rows
     `stride_y` elements apart).  Returns True when GEMV and gather ran as one kernel."""
@@ -250,7 +254,8 @@ def mul_mat_prepared_gather(W: torch.Tensor, qtype: int, m: int, k: int, scratch
     with torch.cuda.device(W.device):
         _check(lib.kq_mul_mat_prepared_gather(W.data_ptr(), qtype, W.shape[0], k, m, _DT[dtype], int(mmq), scratch.data_ptr(),
                                               scratch.numel(), ys, stride_y, flg, epoch.data_ptr(), done.data_ptr(), slot,
-                                              rank, world, status.data_ptr(), ctypes.byref(fused), _stream(W.device)))
+                                              rank, world, status.data_ptr(), int(wait_in_consumer), reset_ptr or None, reset_bytes,
+                                              ctypes.byref(fused), _stream(W.device)))
     return bool(fused.value)
 
 
@@ -281,6 +286,20 @@ def moe_a8(W: torch.Tensor, x: torch.Tensor, sorted_token_ids: torch.Tensor, exp
                              num_tokens_post_padded.data_ptr(), top_k, y.data_ptr(), _DT[y.dtype], y.stride(0),
                              scratch.data_ptr(), scratch.numel(), _stream(x.device)))
     return y
+
+
+def wait_arrival(buf: torch.Tensor, status: torch.Tensor) -> None:
+    """kq_wait_arrival: on the current stream, until no element of the (contiguous) gather buffer holds the sentinel."""
+    with torch.cuda.device(buf.device):
+        _check(lib.kq_wait_arrival(buf.data_ptr(), buf.numel() * buf.element_size(), _DT[buf.dtype], status.data_ptr(),
+                                   _stream(buf.device)))
+
+
+def arrival_status(clear: bool = False) -> int:
+    """kq_arrival_status on the current device (synchronises): non-zero when an arrival poll has run out."""
+    v = ctypes.c_int()
+    _check(lib.kq_arrival_status(ctypes.byref(v), int(clear)))
+    return v.value
 
 
 def dequantize(W: torch.Tensor, qtype: int, count: int, dtype=torch.float16) -> torch.Tensor:

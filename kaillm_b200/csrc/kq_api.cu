@@ -73,7 +73,7 @@ static int validate(const char* fn, const void* W, int type, int64_t n, int64_t 
 
 static int mul_mat(const char* fn, bool mmq, const void* W, int type, int64_t n, int64_t k, const void* x,
                    int x_dtype, int64_t m, int64_t stride_x, void* y, int y_dtype, int64_t stride_y, void* scratch,
-                   size_t scratch_bytes, void* stream, bool need_w = true, bool need_x = true) {
+                   size_t scratch_bytes, void* stream, bool need_w = true, bool need_x = true, int wait_arrival = 0) {
   t_err[0] = 0;
   Problem p;
   int rc = validate(fn, W, type, n, k, x, x_dtype, m, stride_x, scratch, scratch_bytes, p, need_w, need_x);
@@ -81,7 +81,7 @@ static int mul_mat(const char* fn, bool mmq, const void* W, int type, int64_t n,
   if (!need_w) {
     Q8Ptrs P = q8_ptrs(scratch, p.L, n);
     if (m < options().gemm_min_m) P.xh = nullptr;
-    return launch_quantize(x, x_dtype, m, k, stride_x, &P, nullptr, p.L.kpad, (cudaStream_t)stream);
+    return launch_quantize(x, x_dtype, m, k, stride_x, &P, nullptr, p.L.kpad, (cudaStream_t)stream, wait_arrival);
   }
   if (mmq && (type == KQ_TYPE_IQ3_S || type == KQ_TYPE_IQ4_NL || type == KQ_TYPE_IQ4_XS)) {
     set_error("%s: the i-matrix formats have no MMQ kernel (use dequantize + matmul or mul_mat_vec)", fn);
@@ -176,9 +176,11 @@ int kq_mul_mat_a8(const void* W, int type, int64_t n, int64_t k, const void* x, 
 }
 
 int kq_prepare_q8(int type, int64_t n, int64_t k, const void* x, int x_dtype, int64_t m, int64_t stride_x,
-                  void* scratch, size_t scratch_bytes, void* stream) {
+                  void* scratch, size_t scratch_bytes, int flags, void* stream) {
+  if (flags & ~KQ_PREP_WAIT_ARRIVAL) { set_error("kq_prepare_q8: unknown flag bits %d", flags); return KQ_EINVAL; }
+  if ((flags & KQ_PREP_WAIT_ARRIVAL) && m > 80) { set_error("kq_prepare_q8: arrival polling serves the decode path (m <= 80)"); return KQ_ELIMIT; }
   return mul_mat("kq_prepare_q8", false, nullptr, type, n, k, x, x_dtype, m, stride_x, nullptr, KQ_F32, n, scratch,
-                 scratch_bytes, stream, false, true);
+                 scratch_bytes, stream, false, true, flags & KQ_PREP_WAIT_ARRIVAL);
 }
 
 // shared validation of the fused producers: same checks as kq_prepare_q8, then the scratch pointers
@@ -196,20 +198,23 @@ static int prepare_common(const char* fn, int type, int64_t n, int64_t k, const 
 }
 
 int kq_prepare_q8_rmsnorm(int type, int64_t n, int64_t k, const void* x, int x_dtype, int64_t m, int64_t stride_x,
-                          const void* gamma, float eps, void* y_norm, void* scratch, size_t scratch_bytes, void* stream) {
+                          const void* gamma, float eps, void* y_norm, void* scratch, size_t scratch_bytes, int flags,
+                          void* stream) {
   Q8Ptrs P;
   int rc = prepare_common("kq_prepare_q8_rmsnorm", type, n, k, x, x_dtype, m, stride_x, k, scratch, scratch_bytes, &P);
   if (rc) return rc;
   if (!gamma) { set_error("kq_prepare_q8_rmsnorm: null gamma"); return KQ_EINVAL; }
-  return launch_prepare_rmsnorm(x, x_dtype, m, k, stride_x, gamma, eps, y_norm, P, (cudaStream_t)stream);
+  if (flags & ~KQ_PREP_WAIT_ARRIVAL) { set_error("kq_prepare_q8_rmsnorm: unknown flag bits %d", flags); return KQ_EINVAL; }
+  return launch_prepare_rmsnorm(x, x_dtype, m, k, stride_x, gamma, eps, y_norm, P, (cudaStream_t)stream, flags & KQ_PREP_WAIT_ARRIVAL);
 }
 
 int kq_prepare_q8_swiglu(int type, int64_t n, int64_t k, const void* gate_up, int x_dtype, int64_t m, int64_t stride_gu,
-                         void* scratch, size_t scratch_bytes, void* stream) {
+                         void* scratch, size_t scratch_bytes, int flags, void* stream) {
   Q8Ptrs P;
   int rc = prepare_common("kq_prepare_q8_swiglu", type, n, k, gate_up, x_dtype, m, stride_gu, 2 * k, scratch, scratch_bytes, &P);
   if (rc) return rc;
-  return launch_prepare_swiglu(gate_up, x_dtype, m, k, stride_gu, P, (cudaStream_t)stream);
+  if (flags & ~KQ_PREP_WAIT_ARRIVAL) { set_error("kq_prepare_q8_swiglu: unknown flag bits %d", flags); return KQ_EINVAL; }
+  return launch_prepare_swiglu(gate_up, x_dtype, m, k, stride_gu, P, (cudaStream_t)stream, flags & KQ_PREP_WAIT_ARRIVAL);
 }
 
 int kq_mul_mat_prepared(const void* W, int type, int64_t n, int64_t k, int64_t m, void* y, int y_dtype,
@@ -346,9 +351,12 @@ int kq_p2p_allgather_2d(const void* src, int64_t rows, size_t row_bytes, void* c
 int kq_mul_mat_prepared_gather(const void* W, int type, int64_t n_local, int64_t k, int64_t m, int y_dtype, int mmq,
                                void* scratch, size_t scratch_bytes, void* const* peer_y, int64_t stride_y,
                                uint32_t* const* peer_flags, uint32_t* epoch, uint32_t* done, int slot, int rank,
-                               int world, int* peer_status, int* fused, void* stream) {
+                               int world, int* peer_status, int wait_in_consumer, void* reset_buf, size_t reset_bytes,
+                               int* fused, void* stream) {
   t_err[0] = 0;
   const char* fn = "kq_mul_mat_prepared_gather";
+  if (reset_buf && ((uintptr_t)reset_buf % 16 || reset_bytes % 16)) { set_error("%s: reset_buf must be 16-byte aligned and sized", fn); return KQ_EINVAL; }
+  if (!wait_in_consumer) { reset_buf = nullptr; reset_bytes = 0; }
   if (fused) *fused = 0;
   if (!peer_y || !peer_flags || !epoch || !done || !peer_status) { set_error("%s: null pointer argument", fn); return KQ_EINVAL; }
   if (world < 1 || world > 8 || rank < 0 || rank >= world || slot < 0) {
@@ -380,11 +388,14 @@ int kq_mul_mat_prepared_gather(const void* W, int type, int64_t n_local, int64_t
     GatherArgs ga;
     for (int r = 0; r < 8; ++r) { ga.peer_y[r] = r < world ? peer_y[r] : nullptr; ga.peer_flags[r] = r < world ? peer_flags[r] : nullptr; }
     ga.epoch = epoch; ga.done = done; ga.status = peer_status; ga.slot = slot; ga.rank = rank; ga.world = world; ga.col0 = col0;
+    ga.ll = wait_in_consumer != 0; ga.reset = reset_buf; ga.reset_bytes = reset_bytes;
     rc = launch_gemv_tile(W, type, n_local, k, P, 0, (int)m, peer_y[rank], y_dtype, stride_y, mmq != 0, st, &ga);
     if (rc == KQ_OK && fused) *fused = 1;
     return rc;
   }
   // two kernels: the usual dispatch writes this rank's columns of its own buffer, the gather kernel pushes them out
+  // (with its hand-shake: the consumer's sentinel test then passes at once; the consumed buffer is refilled here)
+  if (reset_buf && reset_bytes) KQ_CUDA_TRY(cudaMemsetAsync(reset_buf, 0xFF, reset_bytes, st));
   uint8_t* mine = (uint8_t*)peer_y[rank] + (size_t)col0 * esz;
   rc = mul_mat(fn, mmq != 0, W, type, n_local, k, nullptr, KQ_F32, m, k, mine, y_dtype, stride_y, scratch, scratch_bytes, stream,
                true, false);
@@ -436,6 +447,19 @@ int kq_moe_a8(const void* W, int type, int64_t experts, int64_t n, int64_t k, co
               size_t scratch_bytes, void* stream) {
   return moe_common("kq_moe_a8", true, W, type, experts, n, k, x, x_dtype, tokens, stride_x, sorted_token_ids, num_sorted, expert_ids,
                     num_tokens_post_padded, top_k, y, y_dtype, stride_y, scratch, scratch_bytes, stream);
+}
+
+int kq_wait_arrival(const void* buf, size_t bytes, int dtype, int* status, void* stream) {
+  t_err[0] = 0;
+  if (!dtype_ok(dtype)) { set_error("kq_wait_arrival: unsupported dtype %d", dtype); return KQ_EUNSUPPORTED; }
+  if (bytes == 0) return KQ_OK;
+  if (!buf || !status || (uintptr_t)buf % 16 || bytes % 16) { set_error("kq_wait_arrival: null pointer, or buffer not 16-byte aligned and sized"); return KQ_EINVAL; }
+  return launch_wait_arrival(buf, bytes, (int)dtype_size(dtype), status, (cudaStream_t)stream);
+}
+
+int kq_arrival_status(int* failed, int clear) {
+  t_err[0] = 0;
+  return arrival_status(failed, clear);
 }
 
 int kq_moe_block_size(int type) {

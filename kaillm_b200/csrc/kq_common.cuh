@@ -215,11 +215,11 @@ inline int64_t stream_rows(int64_t n, int64_t rowbytes) {
 // kernels (defined in the .cu files)
 // P may be null (then only the reference 36-byte block layout `wire36` is written)
 int launch_quantize(const void* x, int x_dtype, int64_t m, int64_t k, int64_t stride_x,
-                    const Q8Ptrs* P, void* wire36, int64_t kpad, cudaStream_t st);
+                    const Q8Ptrs* P, void* wire36, int64_t kpad, cudaStream_t st, int wait_arrival = 0);
 int launch_prepare_rmsnorm(const void* x, int x_dtype, int64_t m, int64_t k, int64_t stride_x, const void* gamma, float eps,
-                           void* y_norm, const Q8Ptrs& P, cudaStream_t st);
+                           void* y_norm, const Q8Ptrs& P, cudaStream_t st, int wait_arrival = 0);
 int launch_prepare_swiglu(const void* gate_up, int x_dtype, int64_t m, int64_t k, int64_t stride_gu, const Q8Ptrs& P,
-                          cudaStream_t st);
+                          cudaStream_t st, int wait_arrival = 0);
 constexpr int KQ_MOE_BLOCK = 8;   // slots per block of expert-sorted tokens (what kq_moe_block_size reports)
 int launch_moe(const void* W, int type, int64_t experts, int64_t n, int64_t k, const void* ds, const void* qs, int64_t kpad,
                int64_t tokens, int top_k, const int32_t* ids, int64_t nslots, const int32_t* expert_ids,
@@ -244,6 +244,9 @@ struct GatherArgs {
   int* status;
   int slot, rank, world;
   int64_t col0;
+  int ll;               // 1: outputs only, no hand-shake (the consumer polls against the sentinel)
+  void* reset;          // ll: local buffer to refill with the sentinel, or null
+  size_t reset_bytes;   // a multiple of 16
 };
 bool gemv_tile_supported(const void* W, int type, int64_t n, int64_t k, int mtok);
 int gemv_tile_splits(int type, int64_t n, int64_t k, int mtok);
@@ -256,6 +259,8 @@ bool gemv_kres_supported(const void* W, int type, int64_t n, int64_t k, int mtok
 int gemv_kres_splits(int type, int64_t n, int64_t k, int mtok);
 int launch_gemv_kres(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m0, int mcount, void* y,
                      int y_dtype, int64_t stride_y, bool mmq, cudaStream_t st);
+int launch_wait_arrival(const void* buf, size_t bytes, int elem_bytes, int* status, cudaStream_t st);
+int arrival_status(int* failed, int clear);
 int launch_p2p_allgather(const void* src, size_t bytes, int64_t rows, size_t dst_stride, void* const* peer_dst,
                          uint32_t* const* peer_flags, uint32_t* epoch, uint32_t* done, int slot, int rank, int world,
                          int* status, cudaStream_t st, size_t src_stride = 0);

@@ -75,6 +75,9 @@ struct TileParams {
   uint32_t* g_epoch;
   uint32_t* g_done;
   int* g_status;   // set (and never cleared here) when the wait for a peer's flag ran out
+  int g_ll;        // 1: no hand-shake - the outputs are their own arrival flags (the consumer polls against the sentinel)
+  uint4* g_reset;  // g_ll: local buffer to refill with the sentinel (the one the previous producer consumed), or null
+  uint32_t g_reset_n;   // ... in 16-byte units
   int g_slot, g_rank, g_world;
   int64_t g_col0;
 };
@@ -342,7 +345,24 @@ __device__ __forceinline__ void unit_q2k(uint32_t pg, int b0, const TileView& A,
 // of every rank (release, system scope) and waits - bounded - until every rank's flag shows the same call: when the
 // kernel completes, this rank's [M, N] buffer holds all ranks' columns.  Same protocol and flag arrays as
 // kq_p2p_allgather; only plain loads and stores touch peer memory.
-constexpr long long TL_PEER_WAIT_LIMIT = 1ll << 32;   // a good two seconds: ranks may be skewed at their first call
+constexpr long long TL_PEER_WAIT_LIMIT = 1ll << 32;
+// two 16-bit outputs: a half word with all bits set (the arrival sentinel, a NaN) becomes the canonical NaN
+__device__ __forceinline__ uint32_t not_sentinel2(uint32_t w) { return w ^ (__vcmpeq2(w, 0xFFFFFFFFu) & 0x80008000u); }
+// one output of any type, same rule (ll = 0: unchanged)
+template <typename OutT>
+__device__ __forceinline__ OutT out_value(float v, int ll) {
+  OutT o = from_f32<OutT>(v);
+  if (ll) {
+    if constexpr (sizeof(OutT) == 2) {
+      unsigned short b = *reinterpret_cast<unsigned short*>(&o);
+      if (b == 0xFFFFu) { b = 0x7FFFu; o = *reinterpret_cast<OutT*>(&b); }
+    } else {
+      unsigned int b = *reinterpret_cast<unsigned int*>(&o);
+      if (b == 0xFFFFFFFFu) { b = 0x7FFFFFFFu; o = *reinterpret_cast<OutT*>(&b); }
+    }
+  }
+  return o;
+}   // a good two seconds: ranks may be skewed at their first call
 __device__ __forceinline__ void gather_finish(const TileParams& p, int lane) {
   int last = 0;
   if (lane == 0) last = atomicAdd(p.g_done + p.g_slot, 1u) == gridDim.x - 1;
@@ -395,8 +415,18 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
   const int grp = blockIdx.x / p.ks, ngrp = gridDim.x / p.ks;
   const int rt0 = (int)((int64_t)grp * p.ntiles / ngrp), rt1 = (int)((int64_t)(grp + 1) * p.ntiles / ngrp);
   pdl_trigger();
+  if (p.g_reset != nullptr && warp == TL_CW) {
+    // sentinel-polled gather: refill the buffer the producer of this call's activations has just consumed, so that its
+    // next use starts from "nothing has arrived".  After the predecessor (that producer) has completed; before any of
+    // this CTA's outputs, which is what lets a peer move on to the call that writes the buffer again.
+    pdl_wait();
+    const uint32_t a = (uint32_t)((uint64_t)blockIdx.x * p.g_reset_n / gridDim.x), b = (uint32_t)((uint64_t)(blockIdx.x + 1) * p.g_reset_n / gridDim.x);
+    const uint4 ones = make_uint4(0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu);
+    for (uint32_t i = a + lane; i < b; i += 32) p.g_reset[i] = ones;
+    __threadfence();
+  }
   if (rt0 >= rt1) {
-    if (p.g_world > 1 && warp == 0) { pdl_wait(); gather_finish(p, lane); }
+    if (p.g_world > 1 && !p.g_ll && warp == 0) { pdl_wait(); gather_finish(p, lane); }
     return;
   }
   const int nst = rt1 - rt0;
@@ -546,21 +576,28 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
             OutT* dst = base + (size_t)(p.m0 + tl) * p.stride_y + row0;
             if (whole && vec_y) {
               if constexpr (sizeof(OutT) == 4) {
-                reinterpret_cast<float4*>(dst)[0] = va; reinterpret_cast<float4*>(dst)[1] = vb;
+                if (p.g_ll) {
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) reinterpret_cast<float*>(dst)[i] = out_value<float>(v8[i], 1);
+                } else {
+                  reinterpret_cast<float4*>(dst)[0] = va; reinterpret_cast<float4*>(dst)[1] = vb;
+                }
               } else {
                 OutT o[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) o[i] = from_f32<OutT>(v8[i]);
-                *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(o);
+                uint4 w = *reinterpret_cast<const uint4*>(o);
+                if (p.g_ll) { w.x = not_sentinel2(w.x); w.y = not_sentinel2(w.y); w.z = not_sentinel2(w.z); w.w = not_sentinel2(w.w); }
+                *reinterpret_cast<uint4*>(dst) = w;
               }
             } else {
-              for (int i = 0; i < 8; ++i) if (row0 + i < p.n) dst[i] = from_f32<OutT>(v8[i]);
+              for (int i = 0; i < 8; ++i) if (row0 + i < p.n) dst[i] = out_value<OutT>(v8[i], p.g_ll);
             }
           }
         }
       }
     }
-    if (nks == 1 && p.g_world > 1) {
+    if (nks == 1 && p.g_world > 1 && !p.g_ll) {
       __threadfence_system();   // this warp issued all of the CTA's output stores
       __syncwarp();
       gather_finish(p, lane);
@@ -647,7 +684,7 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
           float tot = v[0];
 #pragma unroll
           for (int sp = 1; sp < 4; ++sp) if (sp < nks) tot += v[sp];
-          const OutT o = from_f32<OutT>(tot);
+          const OutT o = out_value<OutT>(tot, p.g_ll);
           if (p.g_world > 1) {
             for (int r = 0; r < p.g_world; ++r)
               (reinterpret_cast<OutT*>(p.peer_y[r]) + p.g_col0)[(size_t)(p.m0 + tl) * p.stride_y + row] = o;
@@ -658,7 +695,7 @@ __global__ void __launch_bounds__(TL_THREADS, 1) gemv_tile_kernel(const TilePara
       }
       if (lane == 0) p.cnt[rt] = 0;   // ready for the next launch on this scratch
     }
-    if (p.g_world > 1) {
+    if (p.g_world > 1 && !p.g_ll) {
       // the consumer warps issued this CTA's output stores: the last of them to get here hands the CTA over
       int* s_warps = reinterpret_cast<int*>(smem + TL_HEADER - 16);
       __threadfence_system();
@@ -773,11 +810,12 @@ int launch_gemv_tile(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs
   p.kpad = (int)P.kpad; p.nb32tot = (int)(P.kpad / 32); p.m0 = (int)m0; p.mcount = mcount;
   p.prefetch = options().pdl < c.stages ? options().pdl : c.stages;
   p.y = y; p.stride_y = stride_y; p.part = P.part; p.cnt = P.cnt; p.status = P.status;
-  p.g_world = 0; p.g_slot = 0; p.g_rank = 0; p.g_col0 = 0; p.g_epoch = nullptr; p.g_done = nullptr; p.g_status = nullptr;
+  p.g_world = 0; p.g_slot = 0; p.g_rank = 0; p.g_col0 = 0; p.g_epoch = nullptr; p.g_done = nullptr; p.g_status = nullptr; p.g_ll = 0; p.g_reset = nullptr; p.g_reset_n = 0;
   for (int r = 0; r < 8; ++r) { p.peer_y[r] = nullptr; p.peer_flags[r] = nullptr; }
   if (ga && ga->world > 1) {
     p.g_world = ga->world; p.g_slot = ga->slot; p.g_rank = ga->rank; p.g_col0 = ga->col0;
     p.g_epoch = ga->epoch; p.g_done = ga->done; p.g_status = ga->status;
+    p.g_ll = ga->ll; p.g_reset = (uint4*)ga->reset; p.g_reset_n = (uint32_t)(ga->reset_bytes / 16);
     for (int r = 0; r < ga->world; ++r) { p.peer_y[r] = ga->peer_y[r]; p.peer_flags[r] = ga->peer_flags[r]; }
     p.y = ga->peer_y[ga->rank];
   }

@@ -7,6 +7,9 @@
 //
 // Output goes to the split layout the GEMV/GEMM kernels read (half2 ds[m][kpad/32], int8 qs[m][kpad])
 // and/or to the reference's 36-byte block layout.
+#include <cstring>
+#include <type_traits>
+
 #include "kq_common.cuh"
 
 namespace kq {
@@ -68,6 +71,38 @@ __device__ __forceinline__ void quantize_block(float xi, int64_t row, int b, int
   }
 }
 
+// Activations that are the output of a sharded projection whose all-gather has no hand-shake (kq_mul_mat_prepared_gather
+// with `wait_in_consumer`): the buffer was filled with the sentinel (all bits set, a NaN no conversion produces) before
+// the ranks stored into it, so a value is its own arrival flag.  The load is repeated - bounded, about two seconds - until
+// it returns something else; it goes to L2 (system scope), where the peers' stores land.
+// Once a wait has run out (a peer is gone), g_arrival_failed makes every later poll on this GPU give up at once instead of
+// after its own two seconds; kq_arrival_status reads and clears it.
+constexpr long long KQ_ARRIVAL_WAIT = 1ll << 32;
+__device__ int g_arrival_failed = 0;
+template <typename T>
+__device__ __forceinline__ T load_arrived(const T* p, int* status) {
+  using Bits = typename std::conditional<sizeof(T) == 2, unsigned short, unsigned int>::type;
+  const Bits sentinel = (Bits)~(Bits)0;
+  const volatile Bits* q = reinterpret_cast<const volatile Bits*>(p);
+  Bits v = *q;
+  if (v == sentinel) {
+    const long long t0 = clock64();
+    do {
+      __nanosleep(40);
+      v = *q;
+      if (*(volatile int*)&g_arrival_failed) break;
+      if (clock64() - t0 > KQ_ARRIVAL_WAIT) { atomicExch(status, 40); atomicExch(&g_arrival_failed, 40); break; }
+    } while (v == sentinel);
+  }
+  T out;
+  memcpy(&out, &v, sizeof(T));
+  return out;
+}
+template <typename T>
+__device__ __forceinline__ float load_act(const T* p, int wait_arrival, int* status) {
+  return to_f32<T>(wait_arrival ? load_arrived<T>(p, status) : *p);
+}
+
 // Padding tokens (m .. 16 * ceil(m / 16) - 1): zero scales in the unit tables (their codes may be anything)
 __device__ __forceinline__ void zero_unit_tables(const Q8Ptrs& P, int64_t row, int b, int kpad) {
   if (!P.qsu) return;
@@ -79,7 +114,7 @@ __device__ __forceinline__ void zero_unit_tables(const Q8Ptrs& P, int64_t row, i
 template <typename T>
 __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const T* __restrict__ x, int64_t stride_x, int k,
                                                             int kpad, int64_t m, int64_t mpad, Q8Ptrs P,
-                                                            uint8_t* __restrict__ wire36) {
+                                                            uint8_t* __restrict__ wire36, int wait_arrival) {
   pdl_trigger();   // a GEMV launched behind this kernel may set up and prefetch its weights meanwhile
   pdl_wait();      // the scratch this kernel rewrites may still be read by the launch before it
   const int lane = threadIdx.x & 31;
@@ -102,7 +137,7 @@ __global__ void __launch_bounds__(256) quantize_q8_1_kernel(const T* __restrict_
     return;
   }
   const int col = b * 32 + lane;
-  const float xi = col < k ? to_f32<T>(x[row * stride_x + col]) : 0.0f;
+  const float xi = col < k ? load_act<T>(x + row * stride_x + col, wait_arrival, P.status) : 0.0f;
   quantize_block(xi, row, b, lane, kpad, tslot, P, wire36);
 }
 
@@ -125,7 +160,7 @@ template <> __device__ __forceinline__ __nv_bfloat16 mul_in_type<__nv_bfloat16>(
 template <typename T, int MODE>
 __global__ void __launch_bounds__(256) prepare_fused_kernel(const T* __restrict__ x, int64_t stride_x, int k, int kpad,
                                                             int64_t m, const T* __restrict__ gamma, float eps,
-                                                            T* __restrict__ y_norm, Q8Ptrs P) {
+                                                            T* __restrict__ y_norm, Q8Ptrs P, int wait_arrival) {
   pdl_trigger();
   pdl_wait();      // the scratch this kernel rewrites, and x, may still be in use by the launch before it
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -150,7 +185,7 @@ __global__ void __launch_bounds__(256) prepare_fused_kernel(const T* __restrict_
   if constexpr (MODE == 1) {
     __shared__ float s_part[8];
     float ss = 0.f;
-    for (int c = threadIdx.x; c < k; c += blockDim.x) { const float v = to_f32<T>(xr[c]); ss = fmaf(v, v, ss); }
+    for (int c = threadIdx.x; c < k; c += blockDim.x) { const float v = load_act<T>(xr + c, wait_arrival, P.status); ss = fmaf(v, v, ss); }
 #pragma unroll
     for (int mask = 16; mask > 0; mask >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, mask);
     if (lane == 0) s_part[warp] = ss;
@@ -166,11 +201,11 @@ __global__ void __launch_bounds__(256) prepare_fused_kernel(const T* __restrict_
     if (col < k) {
       T a;
       if constexpr (MODE == 1) {
-        a = mul_in_type<T>(from_f32<T>(to_f32<T>(xr[col]) * inv), gamma[col]);
+        a = mul_in_type<T>(from_f32<T>(load_act<T>(xr + col, wait_arrival, P.status) * inv), gamma[col]);
         if (y_norm != nullptr) y_norm[row * k + col] = a;
       } else {
-        const float g = to_f32<T>(xr[col]);
-        a = mul_in_type<T>(from_f32<T>(g / (1.0f + expf(-g))), xr[k + col]);
+        const float g = load_act<T>(xr + col, wait_arrival, P.status);
+        a = mul_in_type<T>(from_f32<T>(g / (1.0f + expf(-g))), wait_arrival ? load_arrived<T>(xr + k + col, P.status) : xr[k + col]);
       }
       xi = to_f32<T>(a);
     }
@@ -181,15 +216,15 @@ __global__ void __launch_bounds__(256) prepare_fused_kernel(const T* __restrict_
 
 template <int MODE>
 static int launch_prepare_fused(const void* x, int x_dtype, int64_t m, int64_t k, int64_t stride_x, const void* gamma,
-                                float eps, void* y_norm, const Q8Ptrs& P, cudaStream_t st) {
+                                float eps, void* y_norm, const Q8Ptrs& P, cudaStream_t st, int wait_arrival) {
   const int64_t mpad = (m + 15) / 16 * 16;
   const bool pdl = options().pdl != 0;
   const dim3 grid((unsigned)mpad, (unsigned)((P.kpad / 32 + 7) / 8));
   cudaError_t rc;
   switch (x_dtype) {
-    case KQ_F32: rc = launch_pdl(prepare_fused_kernel<float, MODE>, grid, dim3(256), 0, st, pdl, (const float*)x, stride_x, (int)k, (int)P.kpad, m, (const float*)gamma, eps, (float*)y_norm, P); break;
-    case KQ_F16: rc = launch_pdl(prepare_fused_kernel<__half, MODE>, grid, dim3(256), 0, st, pdl, (const __half*)x, stride_x, (int)k, (int)P.kpad, m, (const __half*)gamma, eps, (__half*)y_norm, P); break;
-    case KQ_BF16: rc = launch_pdl(prepare_fused_kernel<__nv_bfloat16, MODE>, grid, dim3(256), 0, st, pdl, (const __nv_bfloat16*)x, stride_x, (int)k, (int)P.kpad, m, (const __nv_bfloat16*)gamma, eps, (__nv_bfloat16*)y_norm, P); break;
+    case KQ_F32: rc = launch_pdl(prepare_fused_kernel<float, MODE>, grid, dim3(256), 0, st, pdl, (const float*)x, stride_x, (int)k, (int)P.kpad, m, (const float*)gamma, eps, (float*)y_norm, P, wait_arrival); break;
+    case KQ_F16: rc = launch_pdl(prepare_fused_kernel<__half, MODE>, grid, dim3(256), 0, st, pdl, (const __half*)x, stride_x, (int)k, (int)P.kpad, m, (const __half*)gamma, eps, (__half*)y_norm, P, wait_arrival); break;
+    case KQ_BF16: rc = launch_pdl(prepare_fused_kernel<__nv_bfloat16, MODE>, grid, dim3(256), 0, st, pdl, (const __nv_bfloat16*)x, stride_x, (int)k, (int)P.kpad, m, (const __nv_bfloat16*)gamma, eps, (__nv_bfloat16*)y_norm, P, wait_arrival); break;
     default: set_error("unsupported activation dtype %d", x_dtype); return KQ_EUNSUPPORTED;
   }
   KQ_CUDA_TRY(rc);
@@ -199,12 +234,54 @@ static int launch_prepare_fused(const void* x, int x_dtype, int64_t m, int64_t k
 }
 
 int launch_prepare_rmsnorm(const void* x, int x_dtype, int64_t m, int64_t k, int64_t stride_x, const void* gamma, float eps,
-                           void* y_norm, const Q8Ptrs& P, cudaStream_t st) {
-  return launch_prepare_fused<1>(x, x_dtype, m, k, stride_x, gamma, eps, y_norm, P, st);
+                           void* y_norm, const Q8Ptrs& P, cudaStream_t st, int wait_arrival) {
+  return launch_prepare_fused<1>(x, x_dtype, m, k, stride_x, gamma, eps, y_norm, P, st, wait_arrival);
 }
 int launch_prepare_swiglu(const void* gate_up, int x_dtype, int64_t m, int64_t k, int64_t stride_gu, const Q8Ptrs& P,
-                          cudaStream_t st) {
-  return launch_prepare_fused<2>(gate_up, x_dtype, m, k, stride_gu, nullptr, 0.f, nullptr, P, st);
+                          cudaStream_t st, int wait_arrival) {
+  return launch_prepare_fused<2>(gate_up, x_dtype, m, k, stride_gu, nullptr, 0.f, nullptr, P, st, wait_arrival);
+}
+
+// Waits until no element of buf[0 .. n16 * 16 bytes) holds the arrival sentinel (all bits of an element set): the end of
+// a chain of sentinel-polled gathers, before a consumer outside the library reads the buffer.
+__global__ void __launch_bounds__(256) wait_arrival_kernel(const uint4* buf, size_t n16, int elem_bytes, int* status) {
+  const size_t nthr = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += nthr) {
+    const volatile uint32_t* q = reinterpret_cast<const volatile uint32_t*>(buf + i);
+    const long long t0 = clock64();
+    for (;;) {
+      bool missing = false;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t w = q[j];
+        missing |= elem_bytes == 2 ? __vcmpeq2(w, 0xFFFFFFFFu) != 0u : w == 0xFFFFFFFFu;
+      }
+      if (!missing) break;
+      __nanosleep(100);
+      if (*(volatile int*)&g_arrival_failed) { atomicExch(status, 41); break; }
+      if (clock64() - t0 > KQ_ARRIVAL_WAIT) { atomicExch(status, 41); atomicExch(&g_arrival_failed, 41); break; }
+    }
+  }
+}
+
+int launch_wait_arrival(const void* buf, size_t bytes, int elem_bytes, int* status, cudaStream_t st) {
+  if (bytes == 0) return KQ_OK;
+  const size_t n16 = bytes / 16;
+  size_t blocks = (n16 + 255) / 256;
+  if (blocks > 592) blocks = 592;
+  wait_arrival_kernel<<<(unsigned)blocks, 256, 0, st>>>((const uint4*)buf, n16, elem_bytes, status);
+  options().launches += 1;
+  KQ_CUDA_TRY(cudaGetLastError());
+  return KQ_OK;
+}
+
+// (failed != nullptr) copies the flag to the host - synchronises; clear != 0 zeroes it afterwards
+int arrival_status(int* failed, int clear) {
+  int v = 0;
+  KQ_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_arrival_failed, sizeof(int)));
+  if (failed) *failed = v;
+  if (clear && v) { const int z = 0; KQ_CUDA_TRY(cudaMemcpyToSymbol(g_arrival_failed, &z, sizeof(int))); }
+  return KQ_OK;
 }
 
 // GEMM-only flavour (large M): one LANE per (token, 32-block).  Writes only what the tcgen05 GEMM reads: the fp16
@@ -270,7 +347,7 @@ __global__ void __launch_bounds__(256) quantize_xh_kernel(const T* __restrict__ 
 }
 
 int launch_quantize(const void* x, int x_dtype, int64_t m, int64_t k, int64_t stride_x, const Q8Ptrs* Pp,
-                    void* wire36, int64_t kpad, cudaStream_t st) {
+                    void* wire36, int64_t kpad, cudaStream_t st, int wait_arrival) {
   Q8Ptrs P;
   if (Pp) P = *Pp; else { P = Q8Ptrs(); P.ds = nullptr; P.qs = nullptr; P.qsp = nullptr; P.xh = nullptr; P.s8h = nullptr; P.dT = P.z32 = P.zs8 = P.z16 = P.z32r = P.z16r = P.part = nullptr; P.qsu = nullptr; P.cnt = P.status = nullptr; P.kpad = kpad; P.ncnt = 0; }
   const bool pdl_on = options().pdl != 0;
@@ -301,15 +378,15 @@ int launch_quantize(const void* x, int x_dtype, int64_t m, int64_t k, int64_t st
   switch (x_dtype) {
     case KQ_F32:
       lrc = launch_pdl(quantize_q8_1_kernel<float>, dim3(grid), dim3(256), 0, st, pdl, (const float*)x, stride_x, (int)k,
-                       (int)kpad, m, mpad, P, (uint8_t*)wire36);
+                       (int)kpad, m, mpad, P, (uint8_t*)wire36, wait_arrival);
       break;
     case KQ_F16:
       lrc = launch_pdl(quantize_q8_1_kernel<__half>, dim3(grid), dim3(256), 0, st, pdl, (const __half*)x, stride_x, (int)k,
-                       (int)kpad, m, mpad, P, (uint8_t*)wire36);
+                       (int)kpad, m, mpad, P, (uint8_t*)wire36, wait_arrival);
       break;
     case KQ_BF16:
       lrc = launch_pdl(quantize_q8_1_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, pdl, (const __nv_bfloat16*)x, stride_x, (int)k,
-                       (int)kpad, m, mpad, P, (uint8_t*)wire36);
+                       (int)kpad, m, mpad, P, (uint8_t*)wire36, wait_arrival);
       break;
     default:
       set_error("unsupported activation dtype %d", x_dtype);

@@ -71,6 +71,7 @@ class P2PGather:
         total = flag_bytes + nbuf * self.buf_bytes
         self.mem = symm.empty((total,), dtype=torch.uint8, device=device)
         self.mem.zero_()
+        self.mem[flag_bytes:].fill_(0xFF)       # data buffers start as "nothing has arrived" (the arrival sentinel)
         torch.cuda.synchronize(device)
         self.hdl = symm.rendezvous(self.mem, group.group_name)
         self.hdl.barrier()                      # every rank's flags are zero before anyone publishes
@@ -113,11 +114,20 @@ class P2PGather:
         off = self.flag_bytes + b * self.buf_bytes
         return self.mem[off:off + self.world * nbytes].view(y_local.dtype).view(m, self.world * per)
 
+    def buffer(self, b: int, m: int, n: int, dtype: torch.dtype) -> torch.Tensor:
+        """Gather buffer `b` viewed as a row-major [m, n] tensor."""
+        nbytes = m * n * torch.empty((), dtype=dtype).element_size()
+        off = self.flag_bytes + b * self.buf_bytes
+        return self.mem[off:off + nbytes].view(dtype).view(m, n)
+
     def project(self, W: torch.Tensor, qtype: int, m: int, k: int, scratch: torch.Tensor, dtype: torch.dtype, b: int,
-                mmq: bool = False) -> tuple[torch.Tensor, bool]:
+                mmq: bool = False, wait_in_consumer: bool = False, reset: torch.Tensor | None = None) -> tuple[torch.Tensor, bool]:
         """This rank's weight slice times the activations prepared in `scratch`, gathered into buffer `b` by the
         GEMV's own epilogue where the library can do that (kq_mul_mat_prepared_gather; otherwise GEMV + gather kernel).
-        Returns (local buffer viewed as the row-major [M, N] output, whether it was one kernel)."""
+        Returns (local buffer viewed as the row-major [M, N] output, whether it was one kernel).
+        wait_in_consumer: no hand-shake; the buffer's next reader polls the elements against the arrival sentinel
+        (prepare_q8*(wait_arrival=True) or capi.wait_arrival), and `reset` - the gather buffer the producer of this call's
+        activations has consumed - is refilled with the sentinel for its next use."""
         per = W.shape[0]
         esz = torch.empty((), dtype=dtype).element_size()
         nbytes = m * per * esz
@@ -125,7 +135,9 @@ class P2PGather:
             raise ValueError(f"slice of {nbytes} bytes / buffer {b} outside what this P2PGather was sized for")
         dst = [p + b * self.buf_bytes for p in self.data_ptrs]
         fused = self._capi.mul_mat_prepared_gather(W, qtype, m, k, scratch, dst, self.world * per, dtype, self.flag_ptrs,
-                                                   self.epoch, self.done, b, self.rank, self.status, mmq)
+                                                   self.epoch, self.done, b, self.rank, self.status, mmq, wait_in_consumer,
+                                                   reset.data_ptr() if reset is not None else 0,
+                                                   (reset.numel() * reset.element_size() + 15) // 16 * 16 if reset is not None else 0)
         off = self.flag_bytes + b * self.buf_bytes
         return self.mem[off:off + self.world * nbytes].view(dtype).view(m, self.world * per), fused
 
@@ -133,7 +145,8 @@ class P2PGather:
         """Synchronises; raises if any gather's bounded wait for a peer ran out."""
         st = int(self.status.item())
         if st:
-            raise RuntimeError(f"peer gather: wait for rank {st - 16 if st >= 16 else st - 1} timed out")
+            who = "the gathered values (sentinel poll)" if st >= 40 else f"rank {st - 16 if st >= 16 else st - 1}"
+            raise RuntimeError(f"peer gather: wait for {who} timed out (status {st})")
 
 
 class ShardedGGUFLinear:
@@ -181,7 +194,7 @@ class DecoderStack:
     GROUPS = ("qkv", "o", "gate_up", "down")
 
     def __init__(self, weights: list[dict], m: int, hidden: int, device: torch.device, p2p: "P2PGather | None" = None,
-                 group=None, eps: float = 1e-6, dtype: torch.dtype = torch.bfloat16):
+                 group=None, eps: float = 1e-6, dtype: torch.dtype = torch.bfloat16, wait_in_consumer: bool = True):
         from . import capi
         self._capi = capi
         self.w = weights
@@ -191,6 +204,8 @@ class DecoderStack:
         self.group = group
         self.p2p = p2p
         self.dev = device
+        # gathers without a hand-shake: the next producer polls the gathered values against the arrival sentinel
+        self.wait_in_consumer = bool(wait_in_consumer) and p2p is not None
         self.gamma = torch.ones(hidden, dtype=dtype, device=device)
         ws = 0
         self.nfull = {}
@@ -217,7 +232,13 @@ class DecoderStack:
             capi.mul_mat_prepared(W, qt, self.m, k, out, self.scratch)
             return out
         if self.p2p is not None:
-            out, self.fused[name] = self.p2p.project(W, qt, self.m, k, self.scratch, self.dtype, self.GROUPS.index(name))
+            slot = self.GROUPS.index(name)
+            reset = None
+            if self.wait_in_consumer:      # the buffer this call's activations came from has been consumed: refill it
+                prev = self.GROUPS[slot - 1]
+                reset = self.p2p.buffer((slot - 1) % len(self.GROUPS), self.m, self.nfull[prev], self.dtype)
+            out, self.fused[name] = self.p2p.project(W, qt, self.m, k, self.scratch, self.dtype, slot,
+                                                     wait_in_consumer=self.wait_in_consumer, reset=reset)
             return out
         yl = self.ylocal[name]
         capi.mul_mat_prepared(W, qt, self.m, k, yl, self.scratch)
@@ -234,32 +255,51 @@ class DecoderStack:
             break   # the status word sits at offset 0 for every shape
         if self.p2p is not None:
             self.p2p.check()
+            if self.wait_in_consumer:
+                with torch.cuda.device(self.dev):
+                    st = self._capi.arrival_status()
+                if st:
+                    raise RuntimeError(f"decoder stack: an arrival poll ran out (status {st}): a rank stopped storing its outputs")
 
     def forward(self, h: torch.Tensor, on_output=None) -> torch.Tensor:
         """One pass over all layers.  on_output(layer, name, full_output, prepare): hook for verification - `prepare(s)`
         re-runs this group's producer into another scratch `s`."""
         capi = self._capi
         m, hid = self.m, self.hidden
+        wa = self.wait_in_consumer
+
+        def seen(name, buf):      # the hook reads the buffer with ordinary kernels: everything must have arrived
+            if on_output:
+                if wa:
+                    capi.wait_arrival(buf, self.p2p.status)
+                return True
+            return False
+
+        def keep(t):              # the hook's `prepare` re-reads a producer's input after the buffer has been refilled
+            return t.clone() if (on_output and wa) else t
+
         for li, layer in enumerate(self.w):
             W, qt, n, k = layer["qkv"]
-            prep = lambda s, n_=n, qt_=qt, h_=h: capi.prepare_q8_rmsnorm(h_, self.gamma, self.eps, qt_, n_, s)   # noqa: E731
-            capi.prepare_q8_rmsnorm(h, self.gamma, self.eps, qt, n // self.world, self.scratch)
+            prep = lambda s, n_=n, qt_=qt, h_=keep(h): capi.prepare_q8_rmsnorm(h_, self.gamma, self.eps, qt_, n_, s)   # noqa: E731
+            capi.prepare_q8_rmsnorm(h, self.gamma, self.eps, qt, n // self.world, self.scratch, wait_arrival=wa and li > 0)
             qkv = self._project("qkv", W, qt, n, k)
-            if on_output: on_output(li, "qkv", qkv, prep)
+            if seen("qkv", qkv): on_output(li, "qkv", qkv, prep)
             W, qt, n, k = layer["o"]
             a = qkv[:, :hid]                                   # stands in for the attention output: [M, hidden], row stride 8192
-            prep = lambda s, n_=n, qt_=qt, a_=a: capi.prepare_q8(a_, qt_, n_, s)   # noqa: E731
-            capi.prepare_q8(a, qt, n // self.world, self.scratch)
+            prep = lambda s, n_=n, qt_=qt, a_=keep(a): capi.prepare_q8(a_, qt_, n_, s)   # noqa: E731
+            capi.prepare_q8(a, qt, n // self.world, self.scratch, wait_arrival=wa)
             o = self._project("o", W, qt, n, k)
-            if on_output: on_output(li, "o", o, prep)
+            if seen("o", o): on_output(li, "o", o, prep)
             W, qt, n, k = layer["gate_up"]
-            prep = lambda s, n_=n, qt_=qt, o_=o: capi.prepare_q8_rmsnorm(o_, self.gamma, self.eps, qt_, n_, s)   # noqa: E731
-            capi.prepare_q8_rmsnorm(o, self.gamma, self.eps, qt, n // self.world, self.scratch)
+            prep = lambda s, n_=n, qt_=qt, o_=keep(o): capi.prepare_q8_rmsnorm(o_, self.gamma, self.eps, qt_, n_, s)   # noqa: E731
+            capi.prepare_q8_rmsnorm(o, self.gamma, self.eps, qt, n // self.world, self.scratch, wait_arrival=wa)
             gu = self._project("gate_up", W, qt, n, k)
-            if on_output: on_output(li, "gate_up", gu, prep)
+            if seen("gate_up", gu): on_output(li, "gate_up", gu, prep)
             W, qt, n, k = layer["down"]
-            prep = lambda s, n_=n, qt_=qt, gu_=gu: capi.prepare_q8_swiglu(gu_, qt_, n_, s)   # noqa: E731
-            capi.prepare_q8_swiglu(gu, qt, n // self.world, self.scratch)
+            prep = lambda s, n_=n, qt_=qt, gu_=keep(gu): capi.prepare_q8_swiglu(gu_, qt_, n_, s)   # noqa: E731
+            capi.prepare_q8_swiglu(gu, qt, n // self.world, self.scratch, wait_arrival=wa)
             h = self._project("down", W, qt, n, k)
-            if on_output: on_output(li, "down", h, prep)
+            if seen("down", h): on_output(li, "down", h, prep)
+        if wa:
+            capi.wait_arrival(h, self.p2p.status)      # the caller reads h with kernels that do not poll
         return h

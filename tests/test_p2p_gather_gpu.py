@@ -1,5 +1,6 @@
 """kq_p2p_allgather and kq_mul_mat_prepared_gather on two GPUs: the pushed slices equal an NCCL all-gather, eagerly
-and in a replayed CUDA graph; the GEMV with the gather in its epilogue equals GEMV + NCCL gather bit for bit.
+and in a replayed CUDA graph; the GEMV with the gather in its epilogue equals GEMV + NCCL gather bit for bit; a decoder
+stack gives the same bits with NCCL gathers, with the flag hand-shake and with sentinel-polled gathers.
 
 Runs as two child processes (one per GPU, rendezvous on 127.0.0.1); skipped on a box with fewer than two GPUs."""
 import os
@@ -152,6 +153,51 @@ def _fused_worker(rank: int, world: int, port: int, q) -> None:
         if capi.read_status(qt, m, per, k, scratch):
             bad.append(("status", capi.read_status(qt, m, per, k, scratch)))
         dist.barrier()
+        # ---- a small decoder stack three ways: NCCL gathers, flag hand-shake in the GEMV, sentinel-polled gathers
+        hidden, ffn, mm, layers = 2048, 4096, 16, 3
+        groups = [("qkv", 8, 3072, hidden), ("o", 8, hidden, hidden), ("gate_up", 12, 2 * ffn, hidden), ("down", 14, hidden, ffn)]
+        weights = []
+        for li in range(layers):
+            d = {}
+            for gi, (name, qt_, n_, k_) in enumerate(groups):
+                wf = torch.from_numpy(synth.wire_numpy(qt_, n_, k_, seed=300 + 10 * li + gi))
+                d[name] = (sharded.shard_rows(wf, rank, world).contiguous().to(dev), qt_, n_, k_)
+            weights.append(d)
+        h0 = (torch.from_numpy(synth.activations_numpy(mm, hidden, seed=77)).to(dev) * 0.5).to(torch.bfloat16)
+        pg2 = sharded.P2PGather(max_bytes=mm * 2 * ffn // world * 2, nbuf=4, device=dev)
+        pg3 = sharded.P2PGather(max_bytes=mm * 2 * ffn // world * 2, nbuf=4, device=dev)
+        ref = sharded.DecoderStack(weights, mm, hidden, dev).forward(h0).clone()
+        flag = sharded.DecoderStack(weights, mm, hidden, dev, p2p=pg2, wait_in_consumer=False)
+        poll = sharded.DecoderStack(weights, mm, hidden, dev, p2p=pg3, wait_in_consumer=True)
+        for name, stk in (("flag", flag), ("poll", poll)):
+            for rep in range(3):                 # buffers are reused from the second pass on
+                out = stk.forward(h0).clone()
+                torch.cuda.synchronize()
+                if not torch.equal(out, ref):
+                    bad.append((name, rep, float((out.float() - ref.float()).abs().max())))
+            stk.check()
+            if not all(stk.fused.values()):
+                bad.append((name, "not fused", dict(stk.fused)))
+            seen = []
+            stk.forward(h0, on_output=lambda li, nm, y, prep: seen.append(bool(torch.isfinite(y.float()).all())))
+            if len(seen) != 4 * layers or not all(seen):
+                bad.append((name, "hook", seen))
+        dist.barrier()
+        with torch.cuda.stream(st):
+            poll.forward(h0)
+            torch.cuda.synchronize()
+            gr2 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr2, stream=st):
+                out = poll.forward(h0)
+            for _ in range(4):
+                gr2.replay()
+            torch.cuda.synchronize()
+            if not torch.equal(out, ref):
+                bad.append(("poll graph", float((out.float() - ref.float()).abs().max())))
+        poll.check()
+        if capi.arrival_status():
+            bad.append(("arrival flag", capi.arrival_status()))
+        dist.barrier()
         q.put((rank, "ok" if not bad else f"mismatch: {bad[:6]}"))
     except Exception as e:  # noqa: BLE001 - reported to the parent
         import traceback
@@ -171,7 +217,7 @@ def test_gemv_with_gather_in_its_epilogue_matches_gemv_plus_nccl():
     for p in procs:
         p.start()
     for p in procs:
-        p.join(timeout=240)
+        p.join(timeout=400)
     res = {}
     while not q.empty():
         r, msg = q.get()

@@ -79,14 +79,14 @@ class _OracleCapi:
         self.workspace_bytes = real.workspace_bytes
         self.act = None
 
-    def prepare_q8_rmsnorm(self, h, gamma, eps, qt, n, scratch):
+    def prepare_q8_rmsnorm(self, h, gamma, eps, qt, n, scratch, **kw):
         x = h.float()
         self.act = (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)).to(h.dtype).float() * gamma.float()
 
-    def prepare_q8(self, a, qt, n, scratch):
+    def prepare_q8(self, a, qt, n, scratch, **kw):
         self.act = a.float()
 
-    def prepare_q8_swiglu(self, gu, qt, n, scratch):
+    def prepare_q8_swiglu(self, gu, qt, n, scratch, **kw):
         f = gu.shape[1] // 2
         self.act = torch.nn.functional.silu(gu[:, :f].float()) * gu[:, f:].float()
 
