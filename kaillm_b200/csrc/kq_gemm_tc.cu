@@ -11,18 +11,20 @@
 //   For those cases w^ is formed without the offset/min and extra K steps multiply the per-block coefficient
 //   c[row, b] (-8*d, or -dmin*m) with s8[tok, b] into the same accumulator.
 //
-//   CTA tile  128 weight rows (UMMA M, one TMEM lane per row) x BN = 256 tokens (UMMA N); K step = 128
-//   warps 0-7 thread = (weight row, one of the step's two 64-weight atoms): reads its wire bytes straight from
-//             global/L2 (prefetched one step ahead), dequantizes 64 weights to packed fp16 registers and writes them
-//             to TMEM with tcgen05.st - the A operand never touches shared memory.  After the K loop the same
-//             threads read the accumulators back (tcgen05.ld) and store y (lanes = consecutive rows: coalesced).
-//   warp 8    one lane fetches the x^ tile [BN x 128] of each K step with two TMA tiled loads (128-byte swizzle)
-//   warp 9    one lane issues the MMAs: per K step 8 x tcgen05.mma.kind::f16 (128 x 256 x 16), A from TMEM, B
-//             through a shared-memory descriptor; tcgen05.commit signals "buffers free" and, at the end,
-//             "accumulator complete".
-//   A ring of 4 steps in TMEM (256 columns, beside the 256 accumulator columns) and a B ring of 3 steps in shared
-//   memory (192 KB) overlap dequantization, loads and MMAs.  Every mbarrier wait is bounded; on give-up a status
-//   word is set, TMEM is released and the CTA returns.
+//   CTA tile  2 x 128 weight rows (two accumulators, UMMA M = 128: one TMEM lane per row) x BN = 128 tokens (UMMA N),
+//             both accumulators fed by the same activation tile; K step = 128
+//   warps 0-15 thread = (weight row of one of the two row tiles, one of the step's two 64-weight atoms): dequantizes 64
+//             weights to packed fp16 registers and writes them to TMEM with tcgen05.st - the A operand never touches
+//             shared memory.  Q4_K and Q6_K wire bytes reach the threads through a shared-memory stage filled with
+//             coalesced cp.async pieces (one super-block column of the CTA's 256 rows per stage); the other formats are
+//             read straight from global/L2, prefetched one step ahead.  After the K loop the same threads read the
+//             accumulators back (tcgen05.ld) and store y (lanes = consecutive rows: coalesced).
+//   warp 16   one lane fetches the x^ tile [BN x 128] of each K step with two TMA tiled loads (128-byte swizzle)
+//   warp 17   one lane issues the MMAs: per K step 8 x tcgen05.mma.kind::f16 (128 x 128 x 16) per row tile, A from TMEM,
+//             B through a shared-memory descriptor; tcgen05.commit signals "buffers free" and, at the end,
+//             "accumulators complete".
+//   TMEM: 256 accumulator columns (2 x 128) + an A ring of 2 slots x 128 columns; shared memory: a B ring of 5 steps x
+//   32 KB.  Every mbarrier wait is bounded; on give-up a status word is set, TMEM is released and the CTA returns.
 #include "kq_common.cuh"
 #include "kq_tma.cuh"
 

@@ -1,0 +1,56 @@
+"""Run one configuration of the decode / prefill path a few times - the unit a profiler captures.
+
+    python -m kaillm_b200.probe --type 12 --n 17408 --k 5120 --m 16 [--opt gemv_impl=6 ...] [--mats 4] [--mmq] [--full]
+
+`--mats` distinct weight matrices are generated from seeds (so the weights of a launch are never in L2 from the launch
+before), the activations are prepared once (`--full`: with every call, through kq_mul_mat_vec_a8 / kq_mul_mat_a8) and
+each matrix is multiplied once; the status word of the scratch is checked at the end.  Under `ncu` pick the kernel with
+`-k regex:...` and skip the first launch (`-s 1`).  Options are those of kq_set_option (gemv_impl, kres, umma, pdl ...).
+"""
+from __future__ import annotations
+
+import argparse
+import sys
+
+import torch
+
+from . import capi, synth
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("--type", type=int, default=12, help="GGML type id")
+    ap.add_argument("--n", type=int, default=17408)
+    ap.add_argument("--k", type=int, default=5120)
+    ap.add_argument("--m", type=int, default=1)
+    ap.add_argument("--mats", type=int, default=4)
+    ap.add_argument("--mmq", action="store_true", help="MMQ arithmetic (kq_mul_mat_a8)")
+    ap.add_argument("--full", action="store_true", help="quantize the activations with every call")
+    ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE")
+    args = ap.parse_args(argv)
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    for o in args.opt:
+        name, val = o.split("=")
+        capi.set_option(name, int(val))
+    qt, n, k, m = args.type, args.n, args.k, args.m
+    ws = [synth.wire_torch(qt, n, k, 100 + i, dev) for i in range(args.mats)]
+    x = torch.randn((m, k), device=dev).to(torch.bfloat16)
+    y = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    scratch = torch.empty(capi.workspace_bytes(qt, m, n, k), dtype=torch.uint8, device=dev)
+    torch.cuda.synchronize()
+    if not args.full:
+        capi.prepare_q8(x, qt, n, scratch)
+    for w in ws:
+        if args.full:
+            capi.mul_mat(w, x, qt, mmq=args.mmq, out=y, scratch=scratch)
+        else:
+            capi.mul_mat_prepared(w, qt, m, k, y, scratch, mmq=args.mmq)
+    torch.cuda.synchronize()
+    status = capi.read_status(qt, m, n, k, scratch)
+    print(f"type {qt} n {n} k {k} m {m}: {args.mats} matrices, status {status}, launches {capi.get_option('launch_count')}")
+    return 0 if status == 0 and bool(torch.isfinite(y.float()).all()) else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())
