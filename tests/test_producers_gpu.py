@@ -5,7 +5,7 @@ import pytest
 import torch
 
 from kaillm_b200 import capi
-from tests.gpu_util import TDT, dev, rel_l2, to_np, wire
+from tests.gpu_util import TDT, act, dev, rel_l2, to_np, wire
 
 pytestmark = pytest.mark.gpu
 
@@ -75,3 +75,40 @@ def test_producers_validate_arguments():
         capi.prepare_q8_rmsnorm(torch.zeros((90, 256), dtype=torch.bfloat16, device=dev()), x[0], 1e-6, 12, 8,
                                 torch.empty(capi.workspace_bytes(12, 90, 8, 256), dtype=torch.uint8, device=dev()))
     assert e.value.code == capi.KQ_ELIMIT
+
+
+def test_arrival_poll_gives_up_and_reports():
+    """KQ_PREP_WAIT_ARRIVAL on a buffer nobody fills: the bounded poll (about two seconds) runs out, the kernel returns,
+    the status word and the per-GPU flag say so, later polls give up at once, and after clearing the flag a buffer whose
+    values have arrived is read normally.  Nothing faults: the wait is a loop on ordinary loads with a clock limit."""
+    import time
+    m, k, qt = 2, 256, 12
+    empty = torch.full((m, k), -1, dtype=torch.int16, device=dev()).view(torch.bfloat16)      # every element = the sentinel
+    scratch = torch.zeros(capi.workspace_bytes(qt, m, 64, k), dtype=torch.uint8, device=dev())
+    assert capi.arrival_status(clear=True) in (0, 40, 41)
+    t0 = time.time()
+    capi.prepare_q8(empty, qt, 64, scratch, wait_arrival=True)
+    torch.cuda.synchronize()
+    first = time.time() - t0
+    assert capi.read_status(qt, m, 64, k, scratch) == 40 and capi.arrival_status() == 40
+    t0 = time.time()
+    capi.prepare_q8(empty, qt, 64, scratch, wait_arrival=True)      # gives up at once now
+    status = torch.zeros(1, dtype=torch.int32, device=dev())
+    capi.wait_arrival(empty, status)
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 0.5 * first + 0.2 and int(status.item()) == 41
+    assert capi.arrival_status(clear=True) != 0 and capi.arrival_status() == 0
+    # values that have arrived: identical to the plain preparation
+    x, xt = act(m, k, seed=3, dt="bf16")
+    s2 = torch.zeros_like(scratch)
+    capi.prepare_q8(xt, qt, 64, scratch, wait_arrival=True)
+    capi.prepare_q8(xt, qt, 64, s2)
+    capi.wait_arrival(xt, status.zero_())
+    torch.cuda.synchronize()
+    assert capi.read_status(qt, m, 64, k, scratch) == 0 and int(status.item()) == 0 and capi.arrival_status() == 0
+    _, wt = wire(qt, 64, k, seed=5)
+    y1 = torch.empty((m, 64), dtype=torch.float32, device=dev())
+    y2 = torch.empty_like(y1)
+    capi.mul_mat_prepared(wt, qt, m, k, y1, scratch)
+    capi.mul_mat_prepared(wt, qt, m, k, y2, s2)
+    assert torch.equal(y1, y2)
