@@ -305,7 +305,7 @@ int kq_debug_copy_window(uint64_t base, int64_t n, int64_t rowbytes, int64_t row
 /* Runtime knobs for tests and profiling (process-wide, not thread-safe against concurrent launches):
  *   "gemv_impl"   0 = choose by shape (default), 1 = general dp4a kernel, 3 = row-streaming dp4a kernel,
  *                 4 = the same without the specialised Q4_K / Q6_K consumers, 6 = shared-stage int8-mma kernel,
- *                 7 = register-resident int8-mma kernel;
+ *                 7 = register-resident int8-mma kernel, 8 = tensor-memory kernel (tcgen05 kind::i8 MMAs; Q4_K);
  *                 a forced kernel that does not cover the type or shape returns KQ_EUNSUPPORTED
  *   "tc_min_m"    smallest m that the shared-stage int8-mma kernel takes in mode 0 (default 3)
  *   "pdl"         0 = plain launches; p > 0 (default 2) = the quantizer and the streaming kernels are launched
@@ -317,6 +317,12 @@ int kq_debug_copy_window(uint64_t base, int64_t n, int64_t rowbytes, int64_t row
  *                 flight; 2 = wherever that kernel runs (tests); 0 = always launch the quantizer
  *   "kres"        1 (default) = passes of 3..8 tokens use the register-resident kernel where it covers the type and
  *                 shape, 2 = passes of 9..16 tokens too, 0 = never (the shared-stage kernel instead)
+ *   "umma"        1 = in mode 0 the tensor-memory kernel takes the passes it covers, from "umma_min_m" tokens on
+ *                 (default 0: it is slower than the default kernels today).  The per-unit activation tables it reads
+ *                 are only written while it is switched on ("umma" = 1 or "gemv_impl" = 8): set the option BEFORE
+ *                 the activations are prepared.  "umma_box" 1 (default) = its weight bytes arrive by tiled TMA copies
+ *                 where the rows are 16-byte aligned, 0 = by cp.async
+ *   "no_fused_gather" 1 = kq_mul_mat_prepared_gather always runs as two kernels (default 0)
  *   "gemm_min_m"  smallest m that goes to the tcgen05 GEMM (default 81: m <= 80 keeps exact integer dots)
  *   "half_fma"    1 = K-quant dequantize contracts fp16 mul+sub into one fma (default), 0 = two roundings
  * Returns KQ_EINVAL for an unknown name. */

@@ -38,6 +38,12 @@ template <int QT, typename OutT>
 __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restrict__ W, int64_t count,
                                                          OutT* __restrict__ out, int fma, RowGather g) {
   using F = Fmt<QT>;
+  // IQ3_S: the expanded codebook in shared memory (lanes look up different entries: the constant cache would serialise them)
+  __shared__ uint32_t s_grid[QT == KQ_TYPE_IQ3_S ? 512 : 1];
+  if constexpr (QT == KQ_TYPE_IQ3_S) {
+    for (int i = threadIdx.x; i < 512; i += blockDim.x) s_grid[i] = iq3s_expand(c_iq3s_codes_dq[i], KQ_IQ3S_TOP);
+    __syncthreads();
+  }
   const int64_t e0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (e0 >= count) return;
   const uint8_t* b = W + (e0 / F::BLK) * F::BYTES;
@@ -123,16 +129,15 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restri
     const uint32_t qh = b[66 + ib];
     const uint32_t i1 = b[2 + 8 * ib + 2 * il] | ((qh << (8 - 2 * il)) & 256u);
     const uint32_t i2 = b[2 + 8 * ib + 2 * il + 1] | ((qh << (7 - 2 * il)) & 256u);
-    const uint32_t g1 = iq3s_expand(c_iq3s_codes_dq[i1], KQ_IQ3S_TOP);
-    const uint32_t g2 = iq3s_expand(c_iq3s_codes_dq[i2], KQ_IQ3S_TOP);
+    const uint32_t g1 = s_grid[i1], g2 = s_grid[i2];
     const uint32_t signs = b[74 + 4 * ib + il];
     const uint32_t s4 = (b[106 + (ib >> 1)] >> (4 * (ib & 1))) & 15u;
     const float d = __fmul_rn(__fmul_rn(dh, 0.5f + (float)s4), 0.5f);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const uint32_t gb = ((j < 4 ? g1 : g2) >> (8 * (j & 3))) & 0xFFu;
-      const float mag = __fmul_rn(d, (float)gb);
-      res[j] = from_f32<OutT>((signs >> j) & 1u ? -mag : mag);
+      const float mag = __fmul_rn(d, __uint_as_float(gb | 0x4B000000u) - 8388608.0f);   // (float)gb without the conversion pipe
+      res[j] = from_f32<OutT>(__uint_as_float(__float_as_uint(mag) ^ (((signs >> j) & 1u) << 31)));
     }
   } else if constexpr (QT == KQ_TYPE_Q4_1 || QT == KQ_TYPE_Q5_1 || QT == KQ_TYPE_Q5_0) {
     // dequantize.cuh:18-67: codes as fp16, then (q - 16) * d for Q5_0, q * d + m for Q4_1 / Q5_1 (the multiply-add pair
@@ -192,7 +197,6 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restri
         res[j] = half_to_out<OutT>(mul_sub(d1, __int2half_rn(qq), m1, fma));
     }
   } else if constexpr (QT == KQ_TYPE_IQ4_NL || QT == KQ_TYPE_IQ4_XS) {   // dequantize.cuh:401-437: fp32 d * code value
-    constexpr int KV[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
     float d = ld_h(b);
     const uint8_t* qs;
     int e0b;                                             // position inside the 32-weight sub-block
@@ -204,14 +208,22 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restri
       d = __fmul_rn(d, (float)(ls - 32));
       qs = b + 8 + 16 * ib; e0b = r0 & 31;
     }
+    // the thread's 8 weights are the low (e0b < 16) or the high nibbles of 8 consecutive bytes; the code values come from
+    // two byte permutes per word (iq4nl_lookup), the int -> float conversion from the magic exponent
+    const int sh4 = e0b >= 16 ? 4 : 0;
+    const uint8_t* q8 = qs + (e0b & 15);
+    uint32_t w[2];
+    if constexpr (QT == KQ_TYPE_IQ4_NL) { w[0] = ld_u16x2(q8); w[1] = ld_u16x2(q8 + 4); }
+    else { w[0] = ld_u32(q8); w[1] = ld_u32(q8 + 4); }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int e = e0b + j;
-      const int idx = e < 16 ? (qs[e] & 15) : (qs[e - 16] >> 4);
-      int kv = KV[0];
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t kv4 = iq4nl_lookup((w[h] >> sh4) & 0x0F0F0F0Fu);
 #pragma unroll
-      for (int i = 1; i < 16; ++i) kv = idx == i ? KV[i] : kv;
-      res[j] = from_f32<OutT>(__fmul_rn(d, (float)kv));
+      for (int i = 0; i < 4; ++i) {
+        const int kv = (int)(int8_t)((kv4 >> (8 * i)) & 0xFFu);
+        const float kf = __int_as_float(kv + 0x4B400000) - 12582912.0f;
+        res[4 * h + i] = from_f32<OutT>(__fmul_rn(d, kf));
+      }
     }
   }
   // 8 outputs = 16 (half/bf16) or 32 (float) contiguous, aligned bytes

@@ -40,9 +40,6 @@ namespace {
 
 #include "kq_tile_common.cuh"
 
-#ifndef UM_EXP
-#define UM_EXP 0
-#endif
 // wait with the cycles spent in it added to a counter when built with -DUM_TRACE (diagnostic builds only)
 template <int SL>
 __device__ __forceinline__ bool um_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, long long& waited) {
@@ -298,7 +295,7 @@ __global__ void __launch_bounds__(UM_THREADS, 1) gemv_umma_kernel(const UmmaPara
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t baddr = s_u32(ring + (size_t)slot * STAGE_BYTES + RAW_BYTES);
 #pragma unroll
-        for (int bb = 0; bb < ((UM_EXP & 8) ? 0 : 8 / UM_MMA_WARPS); ++bb) {
+        for (int bb = 0; bb < 8 / UM_MMA_WARPS; ++bb) {
           const int b = w * (8 / UM_MMA_WARPS) + bb;
           const uint64_t bdesc = (uint64_t)(((baddr + b * 512) & 0x3FFFF) >> 4) | desc_hi;
           asm volatile(
@@ -336,8 +333,7 @@ __global__ void __launch_bounds__(UM_THREADS, 1) gemv_umma_kernel(const UmmaPara
           uint32_t o[32];
 #pragma unroll
           for (int jj = 0; jj < 2; ++jj) {
-            uint4 w0 = make_uint4(0, 0, 0, 0), w1 = w0;
-            if (!(UM_EXP & 2)) { w0 = lds128(raw + 16 + (hh * 2 + jj) * 32); w1 = lds128(raw + 32 + (hh * 2 + jj) * 32); }
+            const uint4 w0 = lds128(raw + 16 + (hh * 2 + jj) * 32), w1 = lds128(raw + 32 + (hh * 2 + jj) * 32);
             const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -345,12 +341,12 @@ __global__ void __launch_bounds__(UM_THREADS, 1) gemv_umma_kernel(const UmmaPara
               o[jj * 16 + 8 + i] = (w[i] >> 4) & 0x0F0F0F0Fu;
             }
           }
-          if (!(UM_EXP & 4)) um_tmem_st32(tbase + lane_base + UM_TMEM_A + a * 64 + hh * 32, o);
+          um_tmem_st32(tbase + lane_base + UM_TMEM_A + a * 64 + hh * 32, o);
         }
       }
       // the min terms of this unit, while the stores to tensor memory are on their way
       if constexpr (QT == KQ_TYPE_Q4_K) {
-        if (!(UM_EXP & 1)) {
+        {
           const uint4 hd = lds128(raw);
           const float dmin = __half2float(__ushort_as_half((unsigned short)(hd.x >> 16)));
           const uint32_t mlo = hd.z & 0x3F3F3F3Fu, mhi = ((hd.w >> 4) & 0x0F0F0F0Fu) | ((hd.z >> 2) & 0x30303030u);
@@ -444,7 +440,7 @@ __global__ void __launch_bounds__(UM_THREADS, 1) gemv_umma_kernel(const UmmaPara
           if (lane == 0) { bar_arrive(bar_dempty + 8 * d); bar_arrive(bar_empty + 8 * slot); }   // accumulators and stage read
         }
 #pragma unroll
-        for (int bb = 0; bb < ((UM_EXP & 1) ? 0 : 2); ++bb) {
+        for (int bb = 0; bb < 2; ++bb) {
           // float(I * sc) * d8: the integer multiply-add lands I * sc (< 2^22) on the magic exponent - conversion and
           // scaling in one instruction (measured: an integer add + a packed multiply by sc * d8 instead costs 9% more
           // instructions, the compiler turns the adds into multiply-adds on the same pipe)

@@ -98,6 +98,27 @@ __device__ __forceinline__ T load_arrived(const T* p, int* status) {
   memcpy(&out, &v, sizeof(T));
   return out;
 }
+// sixteen bytes of such a buffer at once (L2 load; re-read while any element still holds the sentinel)
+template <typename T>
+__device__ __forceinline__ uint4 load_vec_arrived(const uint4* p, int wait_arrival, int* status) {
+  uint4 v = __ldcg(p);
+  if (wait_arrival) {
+    auto missing = [](const uint4& w) {
+      if constexpr (sizeof(T) == 2) return (__vcmpeq2(w.x, 0xFFFFFFFFu) | __vcmpeq2(w.y, 0xFFFFFFFFu) | __vcmpeq2(w.z, 0xFFFFFFFFu) | __vcmpeq2(w.w, 0xFFFFFFFFu)) != 0u;
+      else return w.x == 0xFFFFFFFFu || w.y == 0xFFFFFFFFu || w.z == 0xFFFFFFFFu || w.w == 0xFFFFFFFFu;
+    };
+    if (missing(v)) {
+      const long long t0 = clock64();
+      do {
+        __nanosleep(40);
+        v = __ldcg(p);
+        if (*(volatile int*)&g_arrival_failed) break;
+        if (clock64() - t0 > KQ_ARRIVAL_WAIT) { atomicExch(status, 40); atomicExch(&g_arrival_failed, 40); break; }
+      } while (missing(v));
+    }
+  }
+  return v;
+}
 template <typename T>
 __device__ __forceinline__ float load_act(const T* p, int wait_arrival, int* status) {
   return to_f32<T>(wait_arrival ? load_arrived<T>(p, status) : *p);
@@ -185,7 +206,17 @@ __global__ void __launch_bounds__(256) prepare_fused_kernel(const T* __restrict_
   if constexpr (MODE == 1) {
     __shared__ float s_part[8];
     float ss = 0.f;
-    for (int c = threadIdx.x; c < k; c += blockDim.x) { const float v = load_act<T>(xr + c, wait_arrival, P.status); ss = fmaf(v, v, ss); }
+    constexpr int PER = 16 / (int)sizeof(T);   // elements per 16-byte load
+    if ((k % PER) == 0 && ((uintptr_t)xr % 16) == 0) {
+      for (int c = threadIdx.x * PER; c < k; c += blockDim.x * PER) {
+        const uint4 v = load_vec_arrived<T>(reinterpret_cast<const uint4*>(xr + c), wait_arrival, P.status);
+        const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+        for (int i = 0; i < PER; ++i) { const float f = to_f32<T>(e[i]); ss = fmaf(f, f, ss); }
+      }
+    } else {
+      for (int c = threadIdx.x; c < k; c += blockDim.x) { const float v = load_act<T>(xr + c, wait_arrival, P.status); ss = fmaf(v, v, ss); }
+    }
 #pragma unroll
     for (int mask = 16; mask > 0; mask >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, mask);
     if (lane == 0) s_part[warp] = ss;
