@@ -79,7 +79,8 @@ def test_p2p_allgather_matches_nccl():
 
 def _fused_worker(rank: int, world: int, port: int, q) -> None:
     try:
-        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                          NCCL_NVLS_ENABLE="0")
         sys.path.insert(0, ROOT)
         import torch.distributed as dist
 
@@ -197,6 +198,30 @@ def _fused_worker(rank: int, world: int, port: int, q) -> None:
         poll.check()
         if capi.arrival_status():
             bad.append(("arrival flag", capi.arrival_status()))
+        dist.barrier()
+        # ---- a peer that does not take part: the bounded wait of the flag hand-shake runs out (about two seconds), the
+        # kernel returns, the status word names the silent rank, and the context stays usable.  Rank 1 simply makes no
+        # call (it is alive and idle: nothing faults, nothing is killed).
+        pg4 = sharded.P2PGather(max_bytes=16 * 1024 * 2, nbuf=1, device=dev)
+        qt_, n_, k_, m_ = 12, 2048, 1024, 4
+        w_ = sharded.shard_rows(torch.from_numpy(synth.wire_numpy(qt_, n_, k_, seed=5)), rank, world).contiguous().to(dev)
+        x_ = torch.from_numpy(synth.activations_numpy(m_, k_, seed=6)).to(dev).to(torch.bfloat16)
+        sc_ = torch.empty(capi.workspace_bytes(qt_, m_, n_ // world, k_), dtype=torch.uint8, device=dev)
+        if rank == 0:
+            capi.prepare_q8(x_, qt_, n_ // world, sc_)
+            pg4.project(w_, qt_, m_, k_, sc_, torch.bfloat16, 0)
+            torch.cuda.synchronize()
+            try:
+                pg4.check()
+                bad.append(("silent peer not reported",))
+            except RuntimeError as e:
+                if "rank 1" not in str(e):
+                    bad.append(("wrong report", str(e)))
+            y_ = torch.empty((m_, n_ // world), dtype=torch.bfloat16, device=dev)
+            capi.mul_mat_prepared(w_, qt_, m_, k_, y_, sc_)          # the GPU still works
+            torch.cuda.synchronize()
+            if not bool(torch.isfinite(y_.float()).all()):
+                bad.append(("context unusable after the time-out",))
         dist.barrier()
         q.put((rank, "ok" if not bad else f"mismatch: {bad[:6]}"))
     except Exception as e:  # noqa: BLE001 - reported to the parent
