@@ -12,7 +12,7 @@
 
 namespace kq {
 
-__constant__ uint16_t c_iq3s_codes_dq[512] = {
+__device__ const uint16_t c_iq3s_codes_dq[512] = {
 #include "kq_iq3s_codes.inc"
 };
 

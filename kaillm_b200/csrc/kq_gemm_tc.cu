@@ -50,7 +50,7 @@ constexpr int W6_ROW = 232;                    // Q6_K: bytes per staged row (21
 constexpr int W6_STAGE_BYTES = RT * BM * W6_ROW;
 constexpr long long GEMM_WAIT_LIMIT = 1ll << 28;
 
-__constant__ uint16_t c_iq3s_codes_g[512] = {
+__device__ const uint16_t c_iq3s_codes_g[512] = {
 #include "kq_iq3s_codes.inc"
 };
 

@@ -11,7 +11,7 @@
 
 namespace kq {
 
-__constant__ uint16_t c_iq3s_codes[512] = {
+__device__ const uint16_t c_iq3s_codes[512] = {
 #include "kq_iq3s_codes.inc"
 };
 

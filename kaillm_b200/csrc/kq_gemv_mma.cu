@@ -19,7 +19,7 @@ constexpr long long WAIT_LIMIT = 1ll << 27;   // ~70 ms at 1.9 GHz; a healthy wa
 constexpr int SMEM_HEADER = 1024;
 constexpr int MAX_STAGES = 32;
 
-__constant__ uint16_t c_iq3s_codes_s[512] = {
+__device__ const uint16_t c_iq3s_codes_s[512] = {
 #include "kq_iq3s_codes.inc"
 };
 

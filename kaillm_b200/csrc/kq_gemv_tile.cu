@@ -46,7 +46,7 @@ constexpr int TL_SLEEP_C = 64, TL_SLEEP_R = 200, TL_SLEEP_P = 400;   // ns betwe
 constexpr int TL_MAX_STAGES = 16;
 constexpr int TL_SMEM_LIMIT = 232448;
 
-__constant__ uint16_t c_iq3s_codes_t[512] = {
+__device__ const uint16_t c_iq3s_codes_t[512] = {
 #include "kq_iq3s_codes.inc"
 };
 constexpr int TL_GRID_BYTES = 2048;               // IQ3_S: the expanded 512-entry codebook in shared memory

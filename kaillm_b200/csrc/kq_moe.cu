@@ -17,7 +17,7 @@ namespace kq {
 
 namespace {
 
-__constant__ uint16_t c_iq3s_codes_moe[512] = {
+__device__ const uint16_t c_iq3s_codes_moe[512] = {
 #include "kq_iq3s_codes.inc"
 };
 
