@@ -8,6 +8,8 @@
 // (fma = 0: two roundings; 1: the first product is fused; 2: Q2_K's second product is fused instead).
 //
 // One thread produces 8 consecutive weights (16 bytes of fp16 output), so a warp writes 512 contiguous bytes.
+#include <type_traits>
+
 #include "kq_common.cuh"
 
 namespace kq {
@@ -28,24 +30,43 @@ __device__ __forceinline__ __half mul_sub(__half a, __half b, __half c, int fma)
   return fma ? __hfma(a, b, __hneg(c)) : __hsub_rn(__hmul_rn(a, b), c);
 }
 
+// ---- two weights per instruction (the fp16 arithmetic of the reference, bit for bit: every step below is one correctly
+// rounded fp16 operation on exact inputs, as in the scalar formulas)
+// bytes i and i+1 of w (i = 0 or 2) as the halves (1024 + byte): fp16 1024..1279 has an ulp of 1, so OR-ing a byte into
+// the mantissa of 1024 is exact
+__device__ __forceinline__ __half2 bytes_to_h2_plus1024(uint32_t w, int i) {
+  const uint32_t v = __byte_perm(w, 0u, i == 0 ? 0x4140u : 0x4342u) | 0x64006400u;
+  return *reinterpret_cast<const __half2*>(&v);
+}
+// four fp16 pairs -> 8 outputs, one 16-byte (fp16 / bf16) or two (fp32) stores
+template <typename OutT>
+__device__ __forceinline__ void store8(OutT* dst, const __half2 (&h)[4]) {
+  if constexpr (sizeof(OutT) == 4) {
+    float4 a, b;
+    const float2 f0 = __half22float2(h[0]), f1 = __half22float2(h[1]), f2 = __half22float2(h[2]), f3 = __half22float2(h[3]);
+    a = make_float4(f0.x, f0.y, f1.x, f1.y); b = make_float4(f2.x, f2.y, f3.x, f3.y);
+    reinterpret_cast<float4*>(dst)[0] = a; reinterpret_cast<float4*>(dst)[1] = b;
+  } else if constexpr (std::is_same<OutT, __half>::value) {
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(h);
+  } else {
+    __nv_bfloat162 o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[i] = __float22bfloat162_rn(__half22float2(h[i]));
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(o);
+  }
+}
+
 struct RowGather {
   const int64_t* ids;   // nullptr: the blocks are taken in storage order
   int64_t k, rowbytes, nrows;
   int f32math;          // Q4_K / Q5_K / Q6_K: fp32 products as gguf-reader and the reference's embedding decoder form them
 };
 
+// eight consecutive weights starting at element e0
 template <int QT, typename OutT>
-__global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restrict__ W, int64_t count,
-                                                         OutT* __restrict__ out, int fma, RowGather g) {
+__device__ __forceinline__ void dequantize8(const uint8_t* __restrict__ W, int64_t e0, OutT* __restrict__ out, int fma,
+                                            const RowGather& g, const uint32_t* s_grid) {
   using F = Fmt<QT>;
-  // IQ3_S: the expanded codebook in shared memory (lanes look up different entries: the constant cache would serialise them)
-  __shared__ uint32_t s_grid[QT == KQ_TYPE_IQ3_S ? 512 : 1];
-  if constexpr (QT == KQ_TYPE_IQ3_S) {
-    for (int i = threadIdx.x; i < 512; i += blockDim.x) s_grid[i] = iq3s_expand(c_iq3s_codes_dq[i], KQ_IQ3S_TOP);
-    __syncthreads();
-  }
-  const int64_t e0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
-  if (e0 >= count) return;
   const uint8_t* b = W + (e0 / F::BLK) * F::BYTES;
   if (g.ids != nullptr) {
     // output row r is weight row ids[r] (an embedding lookup); a row index outside the tensor gives zeros
@@ -71,6 +92,17 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restri
     }
   } else if constexpr (QT == KQ_TYPE_Q8_0) {
     const __half d = __ushort_as_half(*reinterpret_cast<const uint16_t*>(b));
+    {   // int8 codes -> fp16 by the biased-byte trick: (code ^ 0x80) + 1024 - 1152 = code
+      const uint32_t w0 = ld_u16x2(b + 2 + r0) ^ 0x80808080u, w1 = ld_u16x2(b + 6 + r0) ^ 0x80808080u;
+      const __half2 bias = __floats2half2_rn(1152.0f, 1152.0f), d2 = __halves2half2(d, d);
+      __half2 h[4];
+      h[0] = __hmul2_rn(__hsub2_rn(bytes_to_h2_plus1024(w0, 0), bias), d2);
+      h[1] = __hmul2_rn(__hsub2_rn(bytes_to_h2_plus1024(w0, 2), bias), d2);
+      h[2] = __hmul2_rn(__hsub2_rn(bytes_to_h2_plus1024(w1, 0), bias), d2);
+      h[3] = __hmul2_rn(__hsub2_rn(bytes_to_h2_plus1024(w1, 2), bias), d2);
+      store8<OutT>(out + e0, h);
+      return;
+    }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const int q = (int8_t)b[2 + r0 + j];
@@ -100,6 +132,21 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restri
     else { sc = (q[jj + 4] & 15) | ((q[jj - 4] >> 6) << 4); mn = (q[jj + 4] >> 4) | ((q[jj] >> 6) << 4); }
     const __half d1 = __hmul_rn(dall, __int2half_rn(sc));
     const __half m1 = __hmul_rn(dmin, __int2half_rn(mn));
+    if (!g.f32math) {   // d1 * q - m1, two weights at a time
+      const uint8_t* q8 = b + 16 + 32 * il + l0;
+      const bool al4 = ((uintptr_t)q8 & 3) == 0;       // the tensor may start on a 2-byte boundary only
+      const uint32_t r0w = al4 ? ld_u32(q8) : ld_u16x2(q8), r1w = al4 ? ld_u32(q8 + 4) : ld_u16x2(q8 + 4);
+      const uint32_t w0 = (r0w >> (4 * hi)) & 0x0F0F0F0Fu, w1 = (r1w >> (4 * hi)) & 0x0F0F0F0Fu;
+      const __half2 k1024 = __floats2half2_rn(1024.0f, 1024.0f), d2 = __halves2half2(d1, d1), m2 = __halves2half2(m1, m1);
+      __half2 h[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const __half2 q = __hsub2_rn(bytes_to_h2_plus1024(i < 2 ? w0 : w1, (i & 1) * 2), k1024);
+        h[i] = fma ? __hfma2(d2, q, __hneg2(m2)) : __hsub2_rn(__hmul2_rn(d2, q), m2);
+      }
+      store8<OutT>(out + e0, h);
+      return;
+    }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const int byte = b[16 + 32 * il + l0 + j];
@@ -114,6 +161,25 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restri
     const __half d = __ushort_as_half(*reinterpret_cast<const uint16_t*>(b + 208));
     const int ip = r0 >> 7, q4 = (r0 >> 5) & 3, l0 = r0 & 31;
     const int sc = (int8_t)b[192 + 8 * ip + 2 * q4 + (l0 >> 4)];
+    if (!g.f32math) {   // d * half(sc * (code - 32)): sc and code - 32 are exact in fp16, so half(sc) * half(code - 32) rounds once, like the conversion of the integer product
+      const uint8_t* pl = b + 64 * ip + 32 * (q4 & 1) + l0;
+      const uint8_t* ph = b + 128 + 32 * ip + l0;
+      const uint32_t l0w = ld_u16x2(pl), l1w = ld_u16x2(pl + 4), h0w = ld_u16x2(ph), h1w = ld_u16x2(ph + 4);
+      const int sh = q4 < 2 ? 0 : 4;
+      const uint32_t c0 = ((l0w >> sh) & 0x0F0F0F0Fu) | (((h0w >> (2 * q4)) & 0x03030303u) << 4);
+      const uint32_t c1 = ((l1w >> sh) & 0x0F0F0F0Fu) | (((h1w >> (2 * q4)) & 0x03030303u) << 4);
+      const __half2 k1056 = __floats2half2_rn(1056.0f, 1056.0f), d2 = __halves2half2(d, d);
+      const __half sch = __int2half_rn(sc);
+      const __half2 s2 = __halves2half2(sch, sch);
+      __half2 h[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const __half2 q = __hsub2_rn(bytes_to_h2_plus1024(i < 2 ? c0 : c1, (i & 1) * 2), k1056);
+        h[i] = __hmul2_rn(d2, __hmul2_rn(s2, q));
+      }
+      store8<OutT>(out + e0, h);
+      return;
+    }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const int lo = b[64 * ip + 32 * (q4 & 1) + l0 + j];
@@ -235,10 +301,29 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restri
   }
 }
 
+// Grid-stride over chunks of eight weights (the launcher decides how many chunks a thread walks).
+template <int QT, typename OutT>
+__global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restrict__ W, int64_t count,
+                                                         OutT* __restrict__ out, int fma, RowGather g) {
+  // IQ3_S: the expanded codebook in shared memory (lanes look up different entries: the constant cache would serialise them)
+  __shared__ uint32_t s_grid[QT == KQ_TYPE_IQ3_S ? 512 : 1];
+  if constexpr (QT == KQ_TYPE_IQ3_S) {
+    for (int i = threadIdx.x; i < 512; i += blockDim.x) s_grid[i] = iq3s_expand(c_iq3s_codes_dq[i], KQ_IQ3S_TOP);
+    __syncthreads();
+  }
+  const int64_t step = (int64_t)gridDim.x * blockDim.x * 8;
+  for (int64_t e0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8; e0 < count; e0 += step)
+    dequantize8<QT, OutT>(W, e0, out, fma, g, s_grid);
+}
+
 template <int QT>
 static int run(const void* W, int64_t count, void* out, int out_dtype, int fma, cudaStream_t st, const RowGather& g) {
   const int64_t threads = count / 8;
-  const unsigned grid = (unsigned)((threads + 255) / 256);
+  int64_t blocks = (threads + 255) / 256;
+  // IQ3_S fills its codebook once per CTA: few CTAs that walk many chunks; the other formats run best with one chunk per thread
+  const int64_t cap = QT == KQ_TYPE_IQ3_S ? (int64_t)sm_count() * 16 : (int64_t)0x7fffffff;
+  if (blocks > cap) blocks = cap;
+  const unsigned grid = (unsigned)blocks;
   if (grid == 0) return KQ_OK;
   switch (out_dtype) {
     case KQ_F16: dequantize_kernel<QT, __half><<<grid, 256, 0, st>>>((const uint8_t*)W, count, (__half*)out, fma, g); break;

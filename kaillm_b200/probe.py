@@ -2,7 +2,7 @@
 
     python -m kaillm_b200.probe --type 12 --n 17408 --k 5120 --m 16 [--opt gemv_impl=6 ...] [--mats 4] [--mmq] [--full]
 
-`--mats` distinct weight matrices are generated from seeds (so the weights of a launch are never in L2 from the launch
+`--dequantize` runs kq_dequantize of each matrix instead.  `--mats` distinct weight matrices are generated from seeds (so the weights of a launch are never in L2 from the launch
 before), the activations are prepared once (`--full`: with every call, through kq_mul_mat_vec_a8 / kq_mul_mat_a8) and
 each matrix is multiplied once; the status word of the scratch is checked at the end.  Under `ncu` pick the kernel with
 `-k regex:...` and skip the first launch (`-s 1`).  Options are those of kq_set_option (gemv_impl, kres, umma, pdl ...).
@@ -26,6 +26,7 @@ def main(argv=None) -> int:
     ap.add_argument("--mats", type=int, default=4)
     ap.add_argument("--mmq", action="store_true", help="MMQ arithmetic (kq_mul_mat_a8)")
     ap.add_argument("--full", action="store_true", help="quantize the activations with every call")
+    ap.add_argument("--dequantize", action="store_true", help="run kq_dequantize of the matrices (to bf16) instead of the product")
     ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE")
     args = ap.parse_args(argv)
     dev = torch.device("cuda:0")
@@ -35,6 +36,12 @@ def main(argv=None) -> int:
         capi.set_option(name, int(val))
     qt, n, k, m = args.type, args.n, args.k, args.m
     ws = [synth.wire_torch(qt, n, k, 100 + i, dev) for i in range(args.mats)]
+    if args.dequantize:
+        outs = [capi.dequantize(w, qt, n * k, torch.bfloat16) for w in ws]
+        torch.cuda.synchronize()
+        ok = all(bool(torch.isfinite(o.float()).all()) for o in outs)
+        print(f"type {qt} n {n} k {k}: {args.mats} matrices dequantized to bf16, finite {ok}")
+        return 0 if ok else 1
     x = torch.randn((m, k), device=dev).to(torch.bfloat16)
     y = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
     scratch = torch.empty(capi.workspace_bytes(qt, m, n, k), dtype=torch.uint8, device=dev)
