@@ -83,13 +83,16 @@ __device__ __forceinline__ void dequantize8(const uint8_t* __restrict__ W, int64
   OutT res[8];
   if constexpr (QT == KQ_TYPE_Q4_0) {
     const __half d = __ushort_as_half(*reinterpret_cast<const uint16_t*>(b));
-    const __half eight = __float2half_rn(8.0f);
+    // the thread's 8 weights are the low (r0 < 16) or the high nibbles of 8 consecutive bytes; (q - 8) * d two at a time
+    const uint8_t* q8 = b + 2 + (r0 & 15);
+    const int sh = r0 >= 16 ? 4 : 0;
+    const uint32_t w0 = (ld_u16x2(q8) >> sh) & 0x0F0F0F0Fu, w1 = (ld_u16x2(q8 + 4) >> sh) & 0x0F0F0F0Fu;
+    const __half2 k1032 = __floats2half2_rn(1032.0f, 1032.0f), d2 = __halves2half2(d, d);
+    __half2 h[4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int e = r0 + j;
-      const int q = e < 16 ? (b[2 + e] & 15) : (b[2 + e - 16] >> 4);
-      res[j] = half_to_out<OutT>(__hmul_rn(__hsub_rn(__int2half_rn(q), eight), d));
-    }
+    for (int i = 0; i < 4; ++i) h[i] = __hmul2_rn(__hsub2_rn(bytes_to_h2_plus1024(i < 2 ? w0 : w1, (i & 1) * 2), k1032), d2);
+    store8<OutT>(out + e0, h);
+    return;
   } else if constexpr (QT == KQ_TYPE_Q8_0) {
     const __half d = __ushort_as_half(*reinterpret_cast<const uint16_t*>(b));
     {   // int8 codes -> fp16 by the biased-byte trick: (code ^ 0x80) + 1024 - 1152 = code
@@ -103,23 +106,29 @@ __device__ __forceinline__ void dequantize8(const uint8_t* __restrict__ W, int64
       store8<OutT>(out + e0, h);
       return;
     }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int q = (int8_t)b[2 + r0 + j];
-      res[j] = half_to_out<OutT>(__hmul_rn(__int2half_rn(q), d));
-    }
   } else if constexpr (QT == KQ_TYPE_Q2_K) {
     const __half dall = __ushort_as_half(*reinterpret_cast<const uint16_t*>(b + 80));
     const __half dmin = __ushort_as_half(*reinterpret_cast<const uint16_t*>(b + 82));
     const int n = r0 >> 7, j4 = (r0 >> 5) & 3, l0 = r0 & 31;
     const int s = b[8 * n + 2 * j4 + (l0 >> 4)];
     const __half mpart = __hmul_rn(dmin, __int2half_rn(s >> 4));
+    {   // two weights at a time: half(sc * q) = half(sc) * half(q) exactly (the product is at most 45)
+      const uint8_t* q8 = b + 16 + 32 * n + l0;
+      const bool al4 = ((uintptr_t)q8 & 3) == 0;
+      const uint32_t w0 = ((al4 ? ld_u32(q8) : ld_u16x2(q8)) >> (2 * j4)) & 0x03030303u;
+      const uint32_t w1 = ((al4 ? ld_u32(q8 + 4) : ld_u16x2(q8 + 4)) >> (2 * j4)) & 0x03030303u;
+      const __half2 k1024 = __floats2half2_rn(1024.0f, 1024.0f), d2 = __halves2half2(dall, dall), m2 = __halves2half2(mpart, mpart);
+      const __half sch = __int2half_rn(s & 15), mh = __int2half_rn(s >> 4);
+      const __half2 s2 = __halves2half2(sch, sch), ndmin2 = __halves2half2(__hneg(dmin), __hneg(dmin)), mh2 = __halves2half2(mh, mh);
+      __half2 h[4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int q = (b[16 + 32 * n + l0 + j] >> (2 * j4)) & 3;
-      const __half xq = __int2half_rn((s & 15) * q);
-      res[j] = half_to_out<OutT>(fma == 2 ? __hfma(__hneg(dmin), __int2half_rn(s >> 4), __hmul_rn(dall, xq))
-                                          : mul_sub(dall, xq, mpart, fma));
+      for (int i = 0; i < 4; ++i) {
+        const __half2 xq = __hmul2_rn(s2, __hsub2_rn(bytes_to_h2_plus1024(i < 2 ? w0 : w1, (i & 1) * 2), k1024));
+        h[i] = fma == 2 ? __hfma2(ndmin2, mh2, __hmul2_rn(d2, xq))
+                        : (fma ? __hfma2(d2, xq, __hneg2(m2)) : __hsub2_rn(__hmul2_rn(d2, xq), m2));
+      }
+      store8<OutT>(out + e0, h);
+      return;
     }
   } else if constexpr (QT == KQ_TYPE_Q4_K) {
     const __half dall = __ushort_as_half(*reinterpret_cast<const uint16_t*>(b));
@@ -252,6 +261,24 @@ __device__ __forceinline__ void dequantize8(const uint8_t* __restrict__ W, int64
     else { sc = (q[jj + 4] & 15) | ((q[jj - 4] >> 6) << 4); mn = (q[jj + 4] >> 4) | ((q[jj] >> 6) << 4); }
     const __half d1 = __hmul_rn(dall, __int2half_rn(sc));
     const __half m1 = __hmul_rn(dmin, __int2half_rn(mn));
+    if (!g.f32math) {   // as Q4_K, with the fifth bit of each code taken from qh
+      const uint8_t* q8 = b + 48 + 32 * il + l0;
+      const uint8_t* qh8 = b + 16 + l0;
+      const bool al4 = ((uintptr_t)q8 & 3) == 0;
+      const uint32_t r0w = al4 ? ld_u32(q8) : ld_u16x2(q8), r1w = al4 ? ld_u32(q8 + 4) : ld_u16x2(q8 + 4);
+      const uint32_t h0w = al4 ? ld_u32(qh8) : ld_u16x2(qh8), h1w = al4 ? ld_u32(qh8 + 4) : ld_u16x2(qh8 + 4);
+      const uint32_t w0 = ((r0w >> (4 * hi)) & 0x0F0F0F0Fu) | (((h0w >> jj) & 0x01010101u) << 4);
+      const uint32_t w1 = ((r1w >> (4 * hi)) & 0x0F0F0F0Fu) | (((h1w >> jj) & 0x01010101u) << 4);
+      const __half2 k1024 = __floats2half2_rn(1024.0f, 1024.0f), d2 = __halves2half2(d1, d1), m2 = __halves2half2(m1, m1);
+      __half2 h[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const __half2 q = __hsub2_rn(bytes_to_h2_plus1024(i < 2 ? w0 : w1, (i & 1) * 2), k1024);
+        h[i] = fma ? __hfma2(d2, q, __hneg2(m2)) : __hsub2_rn(__hmul2_rn(d2, q), m2);
+      }
+      store8<OutT>(out + e0, h);
+      return;
+    }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const int byte = b[48 + 32 * il + l0 + j];
@@ -292,12 +319,14 @@ __device__ __forceinline__ void dequantize8(const uint8_t* __restrict__ W, int64
       }
     }
   }
-  // 8 outputs = 16 (half/bf16) or 32 (float) contiguous, aligned bytes
-  if constexpr (sizeof(OutT) == 2) {
-    *reinterpret_cast<uint4*>(out + e0) = *reinterpret_cast<const uint4*>(res);
-  } else {
-    reinterpret_cast<uint4*>(out + e0)[0] = reinterpret_cast<const uint4*>(res)[0];
-    reinterpret_cast<uint4*>(out + e0)[1] = reinterpret_cast<const uint4*>(res)[1];
+  // 8 outputs = 16 (half/bf16) or 32 (float) contiguous, aligned bytes (Q4_0, Q8_0 and Q2_K have stored theirs already)
+  if constexpr (QT != KQ_TYPE_Q4_0 && QT != KQ_TYPE_Q8_0 && QT != KQ_TYPE_Q2_K) {
+    if constexpr (sizeof(OutT) == 2) {
+      *reinterpret_cast<uint4*>(out + e0) = *reinterpret_cast<const uint4*>(res);
+    } else {
+      reinterpret_cast<uint4*>(out + e0)[0] = reinterpret_cast<const uint4*>(res)[0];
+      reinterpret_cast<uint4*>(out + e0)[1] = reinterpret_cast<const uint4*>(res)[1];
+    }
   }
 }
 

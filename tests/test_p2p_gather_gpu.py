@@ -183,6 +183,14 @@ def _fused_worker(rank: int, world: int, port: int, q) -> None:
             stk.forward(h0, on_output=lambda li, nm, y, prep: seen.append(bool(torch.isfinite(y.float()).all())))
             if len(seen) != 4 * layers or not all(seen):
                 bad.append((name, "hook", seen))
+        # sentinel-polled stack with the gather as a second kernel (the fall-back of shapes the GEMV epilogue cannot carry)
+        capi.set_option("no_fused_gather", 1)
+        for rep in range(2):
+            out = poll.forward(h0).clone()
+            torch.cuda.synchronize()
+            if not torch.equal(out, ref) or any(poll.fused.values()):
+                bad.append(("poll, two kernels", rep, dict(poll.fused)))
+        capi.set_option("no_fused_gather", 0)
         dist.barrier()
         with torch.cuda.stream(st):
             poll.forward(h0)
