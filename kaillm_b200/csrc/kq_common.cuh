@@ -52,6 +52,7 @@ struct Options {
   int umma_min_m;      // ... from this many tokens on
   int umma_box;        // 1: its weight bytes arrive by tiled TMA copies where the rows are 16-byte aligned (else cp.async)
   int no_fused_gather; // 1: kq_mul_mat_prepared_gather always runs as two kernels (GEMV, then the gather kernel)
+  int gemm_wide;       // tcgen05 GEMM tile: 0 = 256 rows x 128 tokens, 2 = 128 rows x 256 tokens, 1 = the latter when m > 128
 };
 Options& options();
 

@@ -32,22 +32,33 @@ namespace kq {
 namespace {
 
 constexpr int BM = 128;         // UMMA M: weight rows per accumulator (one TMEM lane per row)
-constexpr int RT = 2;           // accumulators (row tiles) per CTA: the CTA covers RT * BM = 256 weight rows
-constexpr int BN = 128;         // tokens per CTA = UMMA N
 constexpr int KSTEP = 128;      // k per pipeline step (two swizzle atoms)
 constexpr int ATOM = 64;        // k per 128-byte swizzle atom (fp16)
-constexpr int NA = 2;           // A ring (TMEM): 2 slots x (RT x 64) columns
-constexpr int NB = 5;           // B ring (shared memory): 5 x 32 KB
-constexpr int DQ_WARPS = 16;    // dequantizing warps: warp w -> TMEM lanes 32*(w%4).., atom (w>>2)&1 of the step, row tile w>>3
+constexpr int DQ_WARPS = 16;    // dequantizing warps
 constexpr int GEMM_THREADS = (DQ_WARPS + 2) * 32;
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t TMEM_D = 0;                 // accumulators: row tile t in columns [t * BN, (t + 1) * BN)
-constexpr uint32_t TMEM_A = 256;               // A ring: slot ab, row tile t, atom a at 256 + ab * 128 + t * 64 + a * 32
-constexpr int A_SLOT_COLS = RT * 64;
-constexpr int B_STAGE_BYTES = BN * KSTEP * 2;  // 32 KB
-constexpr int W_STAGE_BYTES = RT * BM * 144;   // Q4_K: one super-block column of the CTA's 256 rows
+constexpr uint32_t TMEM_D = 0;                 // accumulators: 256 columns
+constexpr uint32_t TMEM_A = 256;               // A ring: 256 columns
 constexpr int W6_ROW = 232;                    // Q6_K: bytes per staged row (216-byte aligned window of a 210-byte block, padded)
-constexpr int W6_STAGE_BYTES = RT * BM * W6_ROW;
+
+// Two tile shapes, same TMEM budget (256 accumulator columns + 256 columns of A ring):
+//   narrow  2 row tiles x 128 tokens: warp w unpacks for row tile w>>3, atom (w>>2)&1 of EVERY step; an unpacked
+//           weight meets 128 tokens.  For m <= 128.
+//   wide    1 row tile x 256 tokens (UMMA N = 256): the two groups of 8 warps take alternate K steps (group w>>3
+//           serves the steps of its parity), so an unpacked weight meets 256 tokens - half the unpacking
+//           instructions per flop, twice the activation bytes per flop (64 KB per step through a ring of 3).
+template <bool WIDE>
+struct Tile {
+  static constexpr int RT = WIDE ? 1 : 2;          // accumulators (row tiles) per CTA
+  static constexpr int BN = WIDE ? 256 : 128;      // tokens per CTA = UMMA N
+  static constexpr int NA = WIDE ? 4 : 2;          // A ring slots
+  static constexpr int NB = WIDE ? 3 : 5;          // B ring stages
+  static constexpr int SLOT = RT * 64;             // TMEM columns per A slot: row tile t, atom a at t * 64 + a * 32
+  static constexpr int B_STAGE = BN * KSTEP * 2;   // 32 / 64 KB
+  static constexpr int A_ARRIVALS = WIDE ? DQ_WARPS / 2 : DQ_WARPS;
+  static constexpr int W4_STAGE = RT * BM * 144;   // Q4_K: one super-block column of the CTA's rows
+  static constexpr int W6_STAGE = RT * BM * W6_ROW;
+};
 constexpr long long GEMM_WAIT_LIMIT = 1ll << 28;
 
 __device__ const uint16_t c_iq3s_codes_g[512] = {
@@ -304,17 +315,19 @@ __device__ __forceinline__ void dequant_q6k_regs(const uint32_t (&ql)[16], const
 }
 
 // ------------------------------------------------------------------------------------------------ kernel
-template <int QT, bool CORR, typename OutT>
+template <int QT, bool CORR, typename OutT, bool WIDE>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap smap) {
   using F = Fmt<QT>;
+  using T = Tile<WIDE>;
+  constexpr int RT = T::RT, BN = T::BN, NA = T::NA, NB = T::NB, A_SLOT_COLS = T::SLOT, B_STAGE_BYTES = T::B_STAGE;
   extern __shared__ __align__(1024) uint8_t smem[];
-  uint8_t* sB = smem;                                            // NB x 64 KB; each atom [BN rows x 128 B] swizzled
+  uint8_t* sB = smem;                                            // NB stages; each atom [BN rows x 128 B] swizzled
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + NB * B_STAGE_BYTES);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 26);
   volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 27);
   uint32_t* s_grid = reinterpret_cast<uint32_t*>(bars + 32);     // IQ3_S codebook (2 KB)
-  uint8_t* sW = smem + NB * B_STAGE_BYTES + 4096;                // staged super-block column of the CTA's 256 rows (Q4_K 144 B, Q6_K 232 B per row)
+  uint8_t* sW = smem + NB * B_STAGE_BYTES + 4096;                // staged super-block column of the CTA's rows (Q4_K 144 B, Q6_K 232 B per row)
   const uint32_t bar_bfull = smem_u32(bars), bar_bempty = smem_u32(bars + 8), bar_afull = smem_u32(bars + 16),
                  bar_aempty = smem_u32(bars + 20), bar_dfull = smem_u32(bars + 24);
   static_assert(NB <= 8 && NA <= 4, "barrier layout");
@@ -326,7 +339,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
 
   if (tid == 0) {
     for (int i = 0; i < NB; ++i) { mbar_init(bar_bfull + 8 * i, 1); mbar_init(bar_bempty + 8 * i, 1); }
-    for (int i = 0; i < NA; ++i) { mbar_init(bar_afull + 8 * i, DQ_WARPS); mbar_init(bar_aempty + 8 * i, 1); }
+    for (int i = 0; i < NA; ++i) { mbar_init(bar_afull + 8 * i, T::A_ARRIVALS); mbar_init(bar_aempty + 8 * i, 1); }
     mbar_init(bar_dfull, 1);
     *s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -381,7 +394,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
           for (int kk = 0; kk < ATOM / 16; ++kk) {
             const uint32_t accum = (s > 0 || a > 0 || kk > 0) ? 1u : 0u;
 #pragma unroll
-            for (int t = 0; t < RT; ++t) {   // both row tiles against the same B tile
+            for (int t = 0; t < RT; ++t) {   // every row tile against the same B tile
               const uint32_t ta = tbase + TMEM_A + ab * A_SLOT_COLS + t * 64 + a * 32 + kk * 8;
               asm volatile(
                   "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
@@ -400,7 +413,8 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
     // -------------------------------------------------------------------------- dequantizers
     const int rloc = (warp & 3) * 32 + lane;          // row inside a row tile = TMEM lane
     const int half = (warp >> 2) & 1;                 // which of the step's two atoms
-    const int t = warp >> 3;                          // which of the CTA's row tiles
+    const int grp = warp >> 3;                        // narrow: which of the CTA's row tiles; wide: which step parity
+    const int t = WIDE ? 0 : grp;                     // row tile of this thread
     int row = (row_tile * RT + t) * BM + rloc;
     const bool row_ok = row < p.n;
     if (!row_ok) row = p.n - 1;                       // clamp: loads stay in bounds, the store is skipped
@@ -415,8 +429,9 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
     // 32-byte nibble runs of its two atoms into registers and the buffer is free for the next column while the two
     // K steps are unpacked.  The named barrier is reached by every dequantizing thread on every iteration, also
     // after a wait has given up (`ok` only guards the work), so it cannot be left waiting.
-    uint4 hdr4 = {}, qa[2][2] = {};
-    uint32_t q6l[2][16] = {}, q6h[2][8] = {}, q6s[2] = {};   // Q6_K: the thread's two atoms of the current column
+    constexpr int NE = WIDE ? 1 : 2;                  // atoms of a super-block column this thread unpacks
+    uint4 hdr4 = {}, qa[NE][2] = {};
+    uint32_t q6l[NE][16] = {}, q6h[NE][8] = {}, q6s[NE] = {};   // Q6_K: the thread's atoms of the current column
     __half q6d = __float2half_rn(0.f);
     const bool st6 = QT == KQ_TYPE_Q6_K && p.stage6 != 0;
     constexpr int DQ_THREADS = DQ_WARPS * 32;
@@ -472,54 +487,68 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
     };
     auto dq_barrier = [&]() { asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS) : "memory"); };
     if (QT == KQ_TYPE_Q4_K || st6) stage_block(0);
-    for (int s = 0; s < nsteps; ++s) {
+    // narrow: one iteration per step.  wide: one iteration per PAIR of steps (= super-block column); the thread
+    // unpacks for step 2 * it + grp only, but takes part in the staging of every column.
+    const int niter = WIDE ? (nsteps + 1) / 2 : nsteps;
+    for (int it = 0; it < niter; ++it) {
+      const int s = WIDE ? 2 * it + grp : it;
       const int ab = s % NA, fill = s / NA;
+      const bool new_col = WIDE ? (2 * it < nmain) : (s < nmain && (s & 1) == 0);
+      const int col = WIDE ? it : (s >> 1);           // super-block column
+      const int sel = WIDE ? 0 : (s & 1);             // which of the thread's pulled atoms this step uses
       // dequantize before waiting for the slot: the wire bytes do not depend on the pipeline state
       uint32_t v[32];
+      if constexpr (QT == KQ_TYPE_Q4_K) {
+        if (new_col) {
+          asm volatile("cp.async.wait_group 0;" ::: "memory");
+          dq_barrier();                               // the whole column has landed
+          const uint8_t* mine = sW + (t * BM + rloc) * 144;
+          hdr4 = *reinterpret_cast<const uint4*>(mine);
+#pragma unroll
+          for (int e = 0; e < NE; ++e) {              // narrow: atoms `half` (this step) and `half + 2` (next step); wide: atom 2 * grp + half
+            const int a4 = WIDE ? 2 * grp + half : half + 2 * e;
+            qa[e][0] = *reinterpret_cast<const uint4*>(mine + 16 + 32 * a4);
+            qa[e][1] = *reinterpret_cast<const uint4*>(mine + 32 + 32 * a4);
+          }
+          dq_barrier();                               // everyone has its bytes: the buffer may be refilled
+          if (2 * (col + 1) < nmain) stage_block(col + 1);
+        }
+      }
+      if constexpr (QT == KQ_TYPE_Q6_K) {
+        if (st6 && new_col) {
+          asm volatile("cp.async.wait_group 0;" ::: "memory");
+          dq_barrier();
+          const uint32_t off = (uint32_t)(((size_t)col * 210) & 7);        // where the block starts inside its window
+          const uint8_t* mine = sW + (t * BM + rloc) * W6_ROW + off;
+          const uint32_t fsh = ((uint32_t)(uintptr_t)mine & 2u) << 3;      // 0 or 16: the same for all rows
+          auto words = [&](const uint8_t* ptr, uint32_t* dst, int n) {     // n 32-bit words from a 2-byte aligned address
+            const uint32_t* q = reinterpret_cast<const uint32_t*>((uintptr_t)ptr & ~(uintptr_t)3);
+            uint32_t lo = q[0];
+#pragma unroll
+            for (int i = 0; i < n; ++i) { const uint32_t hi = q[i + 1]; dst[i] = __funnelshift_r(lo, hi, fsh); lo = hi; }
+          };
+#pragma unroll
+          for (int e = 0; e < NE; ++e) {              // half super-block: narrow e (this step, next step), wide grp
+            const int ip = WIDE ? grp : e;
+            words(mine + 64 * ip, q6l[e], 16);
+            words(mine + 128 + 32 * ip, q6h[e], 8);
+            words(mine + 192 + 8 * ip + 4 * half, &q6s[e], 1);
+          }
+          q6d = *reinterpret_cast<const __half*>(mine + 208);
+          dq_barrier();
+          if (2 * (col + 1) < nmain) stage_block(col + 1);
+        }
+      }
+      if (s >= nsteps) continue;                      // wide, odd number of steps: nothing left for this group
       if (s < nmain) {
         const int ga = s * (KSTEP / ATOM) + half;     // atom index along the row
         if constexpr (QT == KQ_TYPE_Q4_K) {
-          if ((s & 1) == 0) {                         // a new super-block column: steps s and s+1
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-            dq_barrier();                             // the whole column has landed
-            const uint8_t* mine = sW + (t * BM + rloc) * 144;
-            hdr4 = *reinterpret_cast<const uint4*>(mine);
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {             // atoms `half` (this step) and `half + 2` (next step)
-              qa[e][0] = *reinterpret_cast<const uint4*>(mine + 16 + 32 * (half + 2 * e));
-              qa[e][1] = *reinterpret_cast<const uint4*>(mine + 32 + 32 * (half + 2 * e));
-            }
-            dq_barrier();                             // everyone has its bytes: the buffer may be refilled
-            if (s + 2 < nmain) stage_block((s >> 1) + 1);
-          }
-          const bool odd = (s & 1) != 0;
-          const uint4 cur[3] = {hdr4, odd ? qa[1][0] : qa[0][0], odd ? qa[1][1] : qa[0][1]};
+          const bool second = NE > 1 && sel;
+          const uint4 cur[3] = {hdr4, second ? qa[NE - 1][0] : qa[0][0], second ? qa[NE - 1][1] : qa[0][1]};
           dequant_atom<QT, CORR>(nullptr, ga & 3, s_grid, p.half_fma, cur, v);
         } else if (st6) {
           if constexpr (QT == KQ_TYPE_Q6_K) {
-            if ((s & 1) == 0) {                       // a new super-block column: atoms `half` (now) and `half + 2` (next step)
-              asm volatile("cp.async.wait_group 0;" ::: "memory");
-              dq_barrier();
-              const uint32_t off = (uint32_t)(((size_t)(s >> 1) * 210) & 7);   // where the block starts inside its window
-              const uint8_t* mine = sW + (t * BM + rloc) * W6_ROW + off;
-              const uint32_t fsh = ((uint32_t)(uintptr_t)mine & 2u) << 3;      // 0 or 16: the same for all rows
-              auto words = [&](const uint8_t* ptr, uint32_t* dst, int n) {     // n 32-bit words from a 2-byte aligned address
-                const uint32_t* q = reinterpret_cast<const uint32_t*>((uintptr_t)ptr & ~(uintptr_t)3);
-                uint32_t lo = q[0];
-#pragma unroll
-                for (int i = 0; i < n; ++i) { const uint32_t hi = q[i + 1]; dst[i] = __funnelshift_r(lo, hi, fsh); lo = hi; }
-              };
-#pragma unroll
-              for (int e = 0; e < 2; ++e) {
-                words(mine + 64 * e, q6l[e], 16);
-                words(mine + 128 + 32 * e, q6h[e], 8);
-                words(mine + 192 + 8 * e + 4 * half, &q6s[e], 1);
-              }
-              q6d = *reinterpret_cast<const __half*>(mine + 208);
-              dq_barrier();
-              if (s + 2 < nmain) stage_block((s >> 1) + 1);
-            }
-            if (s & 1) dequant_q6k_regs(q6l[1], q6h[1], q6s[1], q6d, half, v);
+            if (NE > 1 && sel) dequant_q6k_regs(q6l[NE - 1], q6h[NE - 1], q6s[NE - 1], q6d, half, v);
             else dequant_q6k_regs(q6l[0], q6h[0], q6s[0], q6d, half, v);
           }
         } else {
@@ -540,18 +569,19 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
         if (lane == 0) mbar_arrive(bar_afull + 8 * ab);
       }
     }
-    // -------------------------------------------------------------------------- epilogue: warp w takes columns
-    // [64*half, 64*half+64) of its 32 lanes in its row tile's accumulator
+    // -------------------------------------------------------------------------- epilogue: warp w takes the 64
+    // accumulator columns [64 * (w >> 2), +64) of its 32 lanes (narrow: that is its own row tile's accumulator)
     if (ok && mbar_wait(bar_dfull, 0, s_abort)) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       OutT* y = reinterpret_cast<OutT*>(p.y);
+      const int cbase = (warp >> 2) * 64;
 #pragma unroll 1
-      for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32) {
+      for (int c0 = cbase; c0 < cbase + 64; c0 += 32) {
         uint32_t r[32];
-        tmem_ld32(tbase + TMEM_D + lane_base + t * BN + c0, r);
+        tmem_ld32(tbase + TMEM_D + lane_base + c0, r);
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-          const int tok = tok_tile * BN + c0 + j;
+          const int tok = tok_tile * BN + c0 - t * BN + j;
           if (row_ok && tok < p.m) y[(size_t)tok * p.stride_y + row] = from_f32<OutT>(__uint_as_float(r[j]));
         }
       }
@@ -565,10 +595,12 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
 
 // ------------------------------------------------------------------------------------------------ host
 
-template <int QT, bool CORR, typename OutT>
+template <int QT, bool CORR, typename OutT, bool WIDE>
 int launch(const GemmParams& p, const CUtensorMap& map, const CUtensorMap& smap, int grid, cudaStream_t st) {
-  auto kern = gemm_tc_kernel<QT, CORR, OutT>;
-  const int smem = NB * B_STAGE_BYTES + 4096 + (QT == KQ_TYPE_Q4_K ? W_STAGE_BYTES : (QT == KQ_TYPE_Q6_K ? W6_STAGE_BYTES : 0));
+  using T = Tile<WIDE>;
+  auto kern = gemm_tc_kernel<QT, CORR, OutT, WIDE>;
+  const int smem = T::NB * T::B_STAGE + 4096 + (QT == KQ_TYPE_Q4_K ? T::W4_STAGE : (QT == KQ_TYPE_Q6_K ? T::W6_STAGE : 0));
+  static_assert(T::NB * T::B_STAGE + 4096 + T::W6_STAGE <= 227 * 1024, "shared memory budget");
   static DeviceOnce attr_set;   // the attribute belongs to the (function, device) pair
   if (attr_set.first_time()) {
     KQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -581,11 +613,11 @@ int launch(const GemmParams& p, const CUtensorMap& map, const CUtensorMap& smap,
 }
 
 template <int QT, bool CORR>
-int launch_out(const GemmParams& p, const CUtensorMap& map, const CUtensorMap& smap, int grid, int y_dtype, cudaStream_t st) {
+int launch_out(const GemmParams& p, const CUtensorMap& map, const CUtensorMap& smap, int grid, int y_dtype, bool wide, cudaStream_t st) {
   switch (y_dtype) {
-    case KQ_F32: return launch<QT, CORR, float>(p, map, smap, grid, st);
-    case KQ_F16: return launch<QT, CORR, __half>(p, map, smap, grid, st);
-    case KQ_BF16: return launch<QT, CORR, __nv_bfloat16>(p, map, smap, grid, st);
+    case KQ_F32: return wide ? launch<QT, CORR, float, true>(p, map, smap, grid, st) : launch<QT, CORR, float, false>(p, map, smap, grid, st);
+    case KQ_F16: return wide ? launch<QT, CORR, __half, true>(p, map, smap, grid, st) : launch<QT, CORR, __half, false>(p, map, smap, grid, st);
+    case KQ_BF16: return wide ? launch<QT, CORR, __nv_bfloat16, true>(p, map, smap, grid, st) : launch<QT, CORR, __nv_bfloat16, false>(p, map, smap, grid, st);
   }
   set_error("unsupported output dtype %d", y_dtype);
   return KQ_EUNSUPPORTED;
@@ -611,7 +643,10 @@ int launch_gemm_tc(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& 
   CUtensorMap map;
   const cuuint64_t gdim[2] = {(cuuint64_t)k, (cuuint64_t)m};
   const cuuint64_t gstr[1] = {(cuuint64_t)P.kpad * 2};
-  const cuuint32_t box[2] = {ATOM, BN};
+  // tile shape: option gemm_wide 0 = always 128 tokens, 1 = 256 tokens when more than 128 tokens come, 2 = always 256
+  const bool wide = options().gemm_wide == 2 || (options().gemm_wide == 1 && m > 128);
+  const int BN = wide ? Tile<true>::BN : Tile<false>::BN, RT = wide ? Tile<true>::RT : Tile<false>::RT;
+  const cuuint32_t box[2] = {ATOM, (cuuint32_t)BN};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)P.xh, gdim, gstr, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -635,13 +670,13 @@ int launch_gemm_tc(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& 
   p.stage6 = type == KQ_TYPE_Q6_K && ((uintptr_t)W % 8) == 0 && (p.rowbytes % 8) == 0;
   const int grid = (int)((n + RT * BM - 1) / (RT * BM)) * p.ntok_tiles;
   switch (type) {
-    case KQ_TYPE_Q4_0: return launch_out<KQ_TYPE_Q4_0, true>(p, map, smap, grid, y_dtype, st);
-    case KQ_TYPE_Q8_0: return launch_out<KQ_TYPE_Q8_0, false>(p, map, smap, grid, y_dtype, st);
-    case KQ_TYPE_Q2_K: return launch_out<KQ_TYPE_Q2_K, false>(p, map, smap, grid, y_dtype, st);
-    case KQ_TYPE_Q4_K: return corr ? launch_out<KQ_TYPE_Q4_K, true>(p, map, smap, grid, y_dtype, st)
-                                   : launch_out<KQ_TYPE_Q4_K, false>(p, map, smap, grid, y_dtype, st);
-    case KQ_TYPE_Q6_K: return launch_out<KQ_TYPE_Q6_K, false>(p, map, smap, grid, y_dtype, st);
-    case KQ_TYPE_IQ3_S: return launch_out<KQ_TYPE_IQ3_S, false>(p, map, smap, grid, y_dtype, st);
+    case KQ_TYPE_Q4_0: return launch_out<KQ_TYPE_Q4_0, true>(p, map, smap, grid, y_dtype, wide, st);
+    case KQ_TYPE_Q8_0: return launch_out<KQ_TYPE_Q8_0, false>(p, map, smap, grid, y_dtype, wide, st);
+    case KQ_TYPE_Q2_K: return launch_out<KQ_TYPE_Q2_K, false>(p, map, smap, grid, y_dtype, wide, st);
+    case KQ_TYPE_Q4_K: return corr ? launch_out<KQ_TYPE_Q4_K, true>(p, map, smap, grid, y_dtype, wide, st)
+                                   : launch_out<KQ_TYPE_Q4_K, false>(p, map, smap, grid, y_dtype, wide, st);
+    case KQ_TYPE_Q6_K: return launch_out<KQ_TYPE_Q6_K, false>(p, map, smap, grid, y_dtype, wide, st);
+    case KQ_TYPE_IQ3_S: return launch_out<KQ_TYPE_IQ3_S, false>(p, map, smap, grid, y_dtype, wide, st);
   }
   return KQ_EUNSUPPORTED;
 }

@@ -38,9 +38,19 @@ def fp16_operand_product(w, qt, x, mmq):
     return xh @ wh.T
 
 
+@pytest.fixture(params=[0, 2], ids=["tile256x128", "tile128x256"])
+def tile_shape(request):
+    """Both tile shapes of the GEMM kernel (option gemm_wide), whatever the token count."""
+    old = capi.get_option("gemm_wide")
+    capi.set_option("gemm_wide", request.param)
+    yield request.param
+    capi.set_option("gemm_wide", old)
+
+
 @pytest.mark.parametrize("qt", O.QTYPES)
-@pytest.mark.parametrize("n,k,m", [(128, 256, 128), (256, 1024, 96), (200, 512, 81), (384, 2048, 300), (130, 768, 129)])
-def test_gemm_matches_fp16_operand_product_and_oracle(qt, n, k, m):
+@pytest.mark.parametrize("n,k,m", [(128, 256, 128), (256, 1024, 96), (200, 512, 81), (384, 2048, 300), (130, 768, 129),
+                                   (300, 1280, 520)])
+def test_gemm_matches_fp16_operand_product_and_oracle(qt, n, k, m, tile_shape):
     w, wt = wire(qt, n, k, seed=qt + n)
     x, xt = act(m, k, seed=k + m, dt="bf16")
     ws = capi.workspace_bytes(qt, m, n, k)
@@ -50,6 +60,20 @@ def test_gemm_matches_fp16_operand_product_and_oracle(qt, n, k, m):
     assert capi.read_status(qt, m, n, k, scratch) == 0
     assert rel_l2(y, fp16_operand_product(w, qt, x, mmq)) < 5e-6
     assert rel_l2(y, O.mul_mat(w, qt, x, "mmq" if mmq else "mmvq")) < GATE
+
+
+@pytest.mark.parametrize("qt", [2, 8])
+@pytest.mark.parametrize("n,k,m", [(136, 640, 260), (128, 128, 90), (260, 384, 257)])
+def test_gemm_odd_number_of_k_steps(qt, n, k, m, tile_shape):
+    """32-weight formats allow K = an odd multiple of 128: in the 128 x 256 tile the two unpacking groups take
+    alternate steps, so one of them has one step fewer (Q4_0 adds its correction step on top)."""
+    w, wt = wire(qt, n, k, seed=qt + k)
+    x, xt = act(m, k, seed=k + m, dt="bf16")
+    scratch = torch.empty(capi.workspace_bytes(qt, m, n, k), dtype=torch.uint8, device=dev())
+    y = to_np(capi.mul_mat(wt, xt, qt, mmq=True, out_dtype=torch.float32, scratch=scratch))
+    assert capi.read_status(qt, m, n, k, scratch) == 0
+    assert rel_l2(y, fp16_operand_product(w, qt, x, True)) < 5e-6
+    assert rel_l2(y, O.mul_mat(w, qt, x, "mmq")) < GATE
 
 
 def test_gemm_q4k_vec_flavour_folds_the_min_term():
