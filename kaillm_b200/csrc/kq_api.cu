@@ -22,7 +22,7 @@ int cuda_fail(cudaError_t e, const char* what) {
 }
 
 Options& options() {
-  static Options o = {0, 3, 81, 2, 1, 0, 0, 1, 1, 0, 1, 1, 0, 1};
+  static Options o = {0, 3, 81, 2, 1, 0, 0, 1, 1, 0, 1, 1, 0, 1, 1};
   return o;
 }
 
@@ -71,6 +71,20 @@ static int validate(const char* fn, const void* W, int type, int64_t n, int64_t 
   return KQ_OK;
 }
 
+// tcgen05 GEMM or passes of the integer GEMV?  From gemm_min_m tokens on always the GEMM.  Below that (17+ tokens,
+// i.e. two or more GEMV passes) the GEMM takes the call when its time, flat in m up to 256 tokens, beats the passes:
+// measured on Q4_K 17408x5120 38 us against 42 / 49 / 64 / 116 us at 17 / 32 / 33 / 80 tokens, on Q4_K 8192x2048
+// (64 row tiles) 20 us against 22 / 26 / 49 us at 32 / 33 / 80; on Q6_K 5120x17408 (40 row tiles of a long K) the
+// GEMV wins up to 80 tokens.
+static bool gemm_wanted(int type, int64_t n, int64_t k, int64_t m) {
+  const Options& o = options();
+  if (o.gemv_impl != 0) return false;
+  if (m >= o.gemm_min_m) return true;
+  if (!o.gemm_small_m || m <= 16 || !gemm_tc_staged(type)) return false;
+  const int64_t tiles = (n + 127) / 128;
+  return tiles >= 120 || (m >= 33 && tiles >= 60);
+}
+
 static int mul_mat(const char* fn, bool mmq, const void* W, int type, int64_t n, int64_t k, const void* x,
                    int x_dtype, int64_t m, int64_t stride_x, void* y, int y_dtype, int64_t stride_y, void* scratch,
                    size_t scratch_bytes, void* stream, bool need_w = true, bool need_x = true, int wait_arrival = 0) {
@@ -80,7 +94,7 @@ static int mul_mat(const char* fn, bool mmq, const void* W, int type, int64_t n,
   if (rc) return rc;
   if (!need_w) {
     Q8Ptrs P = q8_ptrs(scratch, p.L, n);
-    if (m < options().gemm_min_m) P.xh = nullptr;
+    if (!gemm_wanted(type, n, k, m)) P.xh = nullptr;
     return launch_quantize(x, x_dtype, m, k, stride_x, &P, nullptr, p.L.kpad, (cudaStream_t)stream, wait_arrival);
   }
   if (mmq && (type == KQ_TYPE_IQ3_S || type == KQ_TYPE_IQ4_NL || type == KQ_TYPE_IQ4_XS)) {
@@ -93,7 +107,7 @@ static int mul_mat(const char* fn, bool mmq, const void* W, int type, int64_t n,
   cudaStream_t st = (cudaStream_t)stream;
   Q8Ptrs P = q8_ptrs(scratch, p.L, n);
   const int impl = options().gemv_impl;
-  const bool gemm = impl == 0 && m >= options().gemm_min_m && gemm_tc_supported(W, type, n, k);
+  const bool gemm = gemm_wanted(type, n, k, m) && gemm_tc_supported(W, type, n, k);
   if (!gemm && need_x) P.xh = nullptr;   // the fp16 copy of the activations is only written for the GEMM
   // 1-2 tokens on the row-streaming kernel: its consumer warps quantize x themselves while the first weights arrive
   // (measured: it pays when all (token, 32-block) pairs fit one pass of the 512 consumer lanes and the matrix is big
@@ -193,7 +207,7 @@ static int prepare_common(const char* fn, int type, int64_t n, int64_t k, const 
   if (stride_x < min_stride) { set_error("%s: row stride %lld < %lld", fn, (long long)stride_x, (long long)min_stride); return KQ_EINVAL; }
   if (m > 80) { set_error("%s: the fused producers serve the decode path (m <= 80)", fn); return KQ_ELIMIT; }
   *P = q8_ptrs(scratch, p.L, n);
-  P->xh = nullptr;
+  if (!gemm_wanted(type, n, k, m)) P->xh = nullptr;   // the GEMM's fp16 operands only where the projection will be a GEMM
   return KQ_OK;
 }
 
@@ -503,6 +517,7 @@ int kq_set_option(const char* name, int value) {
   if (name && !strcmp(name, "kres")) { options().kres = value < 0 ? 0 : (value > 2 ? 2 : value); return KQ_OK; }
   if (name && !strcmp(name, "no_fused_gather")) { options().no_fused_gather = value != 0; return KQ_OK; }
   if (name && !strcmp(name, "gemm_wide")) { options().gemm_wide = value; return KQ_OK; }
+  if (name && !strcmp(name, "gemm_small_m")) { options().gemm_small_m = value != 0; return KQ_OK; }
   if (name && !strcmp(name, "umma")) { options().umma = value != 0; return KQ_OK; }
   if (name && !strcmp(name, "umma_min_m")) { options().umma_min_m = value; return KQ_OK; }
   if (name && !strcmp(name, "umma_box")) { options().umma_box = value != 0; return KQ_OK; }
@@ -521,6 +536,7 @@ int kq_get_option(const char* name, int* value) {
   if (name && value && !strcmp(name, "kres")) { *value = options().kres; return KQ_OK; }
   if (name && value && !strcmp(name, "no_fused_gather")) { *value = options().no_fused_gather; return KQ_OK; }
   if (name && value && !strcmp(name, "gemm_wide")) { *value = options().gemm_wide; return KQ_OK; }
+  if (name && value && !strcmp(name, "gemm_small_m")) { *value = options().gemm_small_m; return KQ_OK; }
   if (name && value && !strcmp(name, "umma")) { *value = options().umma; return KQ_OK; }
   if (name && value && !strcmp(name, "umma_min_m")) { *value = options().umma_min_m; return KQ_OK; }
   if (name && value && !strcmp(name, "umma_box")) { *value = options().umma_box; return KQ_OK; }

@@ -53,6 +53,9 @@ struct Options {
   int umma_box;        // 1: its weight bytes arrive by tiled TMA copies where the rows are 16-byte aligned (else cp.async)
   int no_fused_gather; // 1: kq_mul_mat_prepared_gather always runs as two kernels (GEMV, then the gather kernel)
   int gemm_wide;       // tcgen05 GEMM tile: 0 = 256 rows x 128 tokens, 2 = 128 rows x 256 tokens, 1 = the latter when m > 128
+                       // or the format's wire bytes are staged through shared memory (where it is faster at every m)
+  int gemm_small_m;    // 1: calls of 17..gemm_min_m-1 tokens also go to the tcgen05 GEMM where it beats the 16-token
+                       // GEMV passes (staged formats, enough 128-row tiles to fill the GPU)
 };
 Options& options();
 
@@ -266,6 +269,7 @@ int launch_p2p_allgather(const void* src, size_t bytes, int64_t rows, size_t dst
                          uint32_t* const* peer_flags, uint32_t* epoch, uint32_t* done, int slot, int rank, int world,
                          int* status, cudaStream_t st, size_t src_stride = 0);
 bool gemm_tc_supported(const void* W, int type, int64_t n, int64_t k);
+bool gemm_tc_staged(int type);   // the format's wire bytes reach the unpacking threads through shared memory
 int launch_gemm_tc(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& P, int64_t m, void* y, int y_dtype,
                    int64_t stride_y, bool mmq, cudaStream_t st);
 int launch_dequantize(const void* W, int type, int64_t count, void* out, int out_dtype, cudaStream_t st,

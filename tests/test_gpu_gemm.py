@@ -102,6 +102,39 @@ def test_config4_q4k_prefill(m):
     assert rel_l2(y32, want) < GATE
 
 
+@pytest.mark.parametrize("qt,n,k", [(12, 16384, 1024), (14, 15488, 512), (12, 7808, 1024)])
+@pytest.mark.parametrize("m", [17, 33, 80])
+def test_calls_of_17_to_80_tokens_take_the_gemm_where_it_is_faster(qt, n, k, m):
+    """Two or more 16-token GEMV passes against one GEMM launch: with enough 128-row tiles the GEMM takes the call
+    (option gemm_small_m).  Both paths must pass the gate; the fused producers must feed the GEMM as well."""
+    _, wt = wire(qt, n, k, seed=qt + m)
+    x, xt = act(m, k, seed=m, dt="bf16")
+    w = wt.cpu().numpy()
+    rows = np.r_[0:64, n - 64:n]
+    want = O.mul_mat(w[rows], qt, x, "mmvq")
+    y = capi.mul_mat(wt, xt, qt, out_dtype=torch.float32)
+    capi.set_option("gemm_small_m", 0)
+    try:
+        y_int = capi.mul_mat(wt, xt, qt, out_dtype=torch.float32)
+    finally:
+        capi.set_option("gemm_small_m", 1)
+    assert rel_l2(to_np(y_int)[:, rows], want) < 2e-5                # integer dots: fp32 rounding only
+    assert rel_l2(to_np(y)[:, rows], want) < GATE
+    tiles = (n + 127) // 128
+    takes_gemm = tiles >= 120 or (m >= 33 and tiles >= 60)
+    assert torch.equal(y, y_int) != takes_gemm                       # fp16 operands differ from integer dots in the last bits
+    # the same call in two halves, activations from the SwiGLU producer
+    g = torch.Generator(device=dev()); g.manual_seed(m)
+    gu = torch.randn((m, 2 * k), device=dev(), generator=g).to(torch.bfloat16)
+    a = (torch.nn.functional.silu(gu[:, :k]) * gu[:, k:]).contiguous()
+    scratch = torch.full((capi.workspace_bytes(qt, m, n, k),), 0xFF, dtype=torch.uint8, device=dev())
+    capi.prepare_q8_swiglu(gu, qt, n, scratch)
+    y2 = torch.empty((m, n), dtype=torch.float32, device=dev())
+    capi.mul_mat_prepared(wt, qt, m, k, y2, scratch)
+    assert capi.read_status(qt, m, n, k, scratch) == 0
+    assert rel_l2(to_np(y2)[:, rows], O.mul_mat(w[rows], qt, a.float().cpu().numpy(), "mmvq")) < GATE
+
+
 def test_gemm_and_gemv_paths_agree():
     qt, n, k, m = 14, 512, 2048, 96
     _, wt = wire(qt, n, k, seed=9)
