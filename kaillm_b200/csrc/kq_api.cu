@@ -80,7 +80,7 @@ static bool gemm_wanted(int type, int64_t n, int64_t k, int64_t m) {
   const Options& o = options();
   if (o.gemv_impl != 0) return false;
   if (m >= o.gemm_min_m) return true;
-  if (!o.gemm_small_m || m <= 16 || !gemm_tc_staged(type)) return false;
+  if (!o.gemm_small_m || m <= 16 || !gemm_tc_staged(type) || (k % 256) != 0) return false;
   const int64_t tiles = (n + 127) / 128;
   return tiles >= 120 || (m >= 33 && tiles >= 60);
 }

@@ -77,6 +77,7 @@ struct GemmParams {
   int* status;
   int half_fma;
   int stage6;         // Q6_K: rows and W are 8-byte aligned, the block columns go through shared memory
+  int stagew;         // Q8_0, Q4_0, Q2_K in the 128 x 256 tile: W is 16-byte aligned and k a multiple of 256, the columns go through shared memory
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -314,6 +315,85 @@ __device__ __forceinline__ void dequant_q6k_regs(const uint32_t (&ql)[16], const
   }
 }
 
+// Window staging of the 32-weight-block formats and Q2_K (128 x 256 tile only): per 256-weight column a row owns COLB wire
+// bytes; the 16-byte aligned window around them goes to shared memory in 16-byte pieces, each unpacking thread pulls the
+// words of its own 64-weight atom into registers and unpacks from there, two weights per fp16x2 instruction.
+template <int QT> struct Win { static constexpr bool ON = false; static constexpr int COLB = 16, PIECES = 1, SROW = 16, NG = 1; };
+template <> struct Win<KQ_TYPE_Q8_0> { static constexpr bool ON = true; static constexpr int COLB = 272, PIECES = 17, SROW = 272, NG = 17; };
+template <> struct Win<KQ_TYPE_Q4_0> { static constexpr bool ON = true; static constexpr int COLB = 144, PIECES = 9, SROW = 144, NG = 9; };
+// Q2_K blocks are 4-byte aligned (84 = 4 * 21): a block starts 0, 4, 8 or 12 bytes into its window of 6 pieces
+template <> struct Win<KQ_TYPE_Q2_K> { static constexpr bool ON = true; static constexpr int COLB = 84, PIECES = 6, SROW = 112, NG = 10; };
+
+// bytes (b0, b1) and (b2, b3) of `w`, each plus 1024, as fp16 pairs (the bytes land in the mantissas of 0x6400)
+__device__ __forceinline__ __half2 bytes01_plus1024(uint32_t w) { return bits_h2(__byte_perm(w, 0x64646464u, 0x4140)); }
+__device__ __forceinline__ __half2 bytes23_plus1024(uint32_t w) { return bits_h2(__byte_perm(w, 0x64646464u, 0x4342)); }
+
+// Q8_0 atom = two blocks = 68 bytes = 17 words g: block 0 {d at bytes 0-1, codes at 2-33}, block 1 {d at 34-35, codes at
+// 36-67 = words 9..16}.  Signed codes: c ^ 0x80 = c + 128 as an unsigned byte, so 1024 + byte - 1152 = c exactly.
+__device__ __forceinline__ void dequant_q8_0_regs(const uint32_t (&g)[17], uint32_t (&out)[32]) {
+  const __half2 k1152 = __half2half2(__ushort_as_half(0x6480));
+  const __half2 d0 = __half2half2(__low2half(bits_h2(g[0]))), d1 = __half2half2(__high2half(bits_h2(g[8])));
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint32_t c0 = __byte_perm(g[j], g[j + 1], 0x5432) ^ 0x80808080u, c1 = g[9 + j] ^ 0x80808080u;
+    out[2 * j] = h2_bits(__hmul2_rn(__hsub2(bytes01_plus1024(c0), k1152), d0));
+    out[2 * j + 1] = h2_bits(__hmul2_rn(__hsub2(bytes23_plus1024(c0), k1152), d0));
+    out[16 + 2 * j] = h2_bits(__hmul2_rn(__hsub2(bytes01_plus1024(c1), k1152), d1));
+    out[16 + 2 * j + 1] = h2_bits(__hmul2_rn(__hsub2(bytes23_plus1024(c1), k1152), d1));
+  }
+}
+
+// Q4_0 atom = two blocks = 36 bytes = 9 words: block 0 {d, qs at bytes 2-17}, block 1 {d at 18-19, qs at 20-35 = words
+// 5..8}; weight j = low nibble of qs[j], weight j + 16 = high nibble.  d * q without the -8 (applied by the correction steps).
+__device__ __forceinline__ void dequant_q4_0_regs(const uint32_t (&g)[9], uint32_t (&out)[32]) {
+  const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const __half2 d = __half2half2(e ? __high2half(bits_h2(g[4])) : __low2half(bits_h2(g[0])));
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t w = e ? g[5 + j] : __byte_perm(g[j], g[j + 1], 0x5432);
+      const uint32_t lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;
+      out[16 * e + 2 * j] = h2_bits(__hmul2_rn(__hsub2(bytes01_plus1024(lo), k1024), d));
+      out[16 * e + 2 * j + 1] = h2_bits(__hmul2_rn(__hsub2(bytes23_plus1024(lo), k1024), d));
+      out[16 * e + 8 + 2 * j] = h2_bits(__hmul2_rn(__hsub2(bytes01_plus1024(hi), k1024), d));
+      out[16 * e + 8 + 2 * j + 1] = h2_bits(__hmul2_rn(__hsub2(bytes23_plus1024(hi), k1024), d));
+    }
+  }
+}
+
+// Q2_K atom a4 of a super-block: half h = a4 >> 1 (qs bytes 32h..32h+31 = g[1..8]), 2-bit fields 2 * (a4 & 1) and
+// 2 * (a4 & 1) + 1; g[0] = its four scale bytes (sc | mn << 4, one per 16 weights), g[9] = {d, dmin}.
+// Same fp16 operations as the scalar path: half(sc * q) exact, then d * that minus dmin * mn in the order `fma` selects.
+__device__ __forceinline__ void dequant_q2_k_regs(const uint32_t (&g)[10], int odd, int fma, uint32_t (&out)[32]) {
+  const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
+  const __half2 dm = bits_h2(g[9]);
+  const __half2 d2 = __half2half2(__low2half(dm)), dmin2 = __half2half2(__high2half(dm));
+#pragma unroll
+  for (int run = 0; run < 2; ++run) {              // field 2 * odd + run: weights 32 * run .. + 31 of the atom
+    const int sh = 2 * (2 * odd + run);
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {               // 16 weights under one scale byte
+      const uint32_t sb = (g[0] >> (8 * (2 * run + hh))) & 0xFFu;
+      const __half2 sc2 = __half2half2(__int2half_rn((int)(sb & 15u))), mn2 = __half2half2(__int2half_rn((int)(sb >> 4)));
+      const __half2 mp2 = __hmul2_rn(dmin2, mn2);
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const uint32_t code = (g[1 + 4 * hh + w] >> sh) & 0x03030303u;
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const __half2 xq = __hmul2_rn(__hsub2(q ? bytes23_plus1024(code) : bytes01_plus1024(code), k1024), sc2);
+          __half2 r;
+          if (fma == 2) r = __hfma2(__hneg2(dmin2), mn2, __hmul2_rn(d2, xq));
+          else if (fma) r = __hfma2(d2, xq, __hneg2(mp2));
+          else r = __hsub2(__hmul2_rn(d2, xq), mp2);
+          out[16 * run + 8 * hh + 2 * w + q] = h2_bits(r);
+        }
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ kernel
 template <int QT, bool CORR, typename OutT, bool WIDE>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -327,7 +407,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 26);
   volatile int* s_abort = reinterpret_cast<volatile int*>(bars + 27);
   uint32_t* s_grid = reinterpret_cast<uint32_t*>(bars + 32);     // IQ3_S codebook (2 KB)
-  uint8_t* sW = smem + NB * B_STAGE_BYTES + 4096;                // staged super-block column of the CTA's rows (Q4_K 144 B, Q6_K 232 B per row)
+  uint8_t* sW = smem + NB * B_STAGE_BYTES + (QT == KQ_TYPE_IQ3_S ? 4096 : 1024);                // staged super-block column of the CTA's rows (Q4_K 144 B, Q6_K 232 B per row)
   const uint32_t bar_bfull = smem_u32(bars), bar_bempty = smem_u32(bars + 8), bar_afull = smem_u32(bars + 16),
                  bar_aempty = smem_u32(bars + 20), bar_dfull = smem_u32(bars + 24);
   static_assert(NB <= 8 && NA <= 4, "barrier layout");
@@ -434,29 +514,51 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
     uint32_t q6l[NE][16] = {}, q6h[NE][8] = {}, q6s[NE] = {};   // Q6_K: the thread's atoms of the current column
     __half q6d = __float2half_rn(0.f);
     const bool st6 = QT == KQ_TYPE_Q6_K && p.stage6 != 0;
+    using WN = Win<QT>;
+    constexpr bool WINQ = WIDE && WN::ON;              // a window-staged format in the tile shape that has room for it
+    const bool stw = WINQ && p.stagew != 0;
     constexpr int DQ_THREADS = DQ_WARPS * 32;
-    // pieces per row and column: Q4_K 9 x 16 B (the block), Q6_K 27 x 8 B (the 8-byte aligned window around the block)
-    constexpr int PIECES = QT == KQ_TYPE_Q6_K ? 27 : 9;
+    // pieces per row and column: Q4_K 9 x 16 B (the block), Q6_K 27 x 8 B (the 8-byte aligned window around the block),
+    // window formats: 16-byte pieces of the 16-byte aligned window
+    constexpr int PIECES = QT == KQ_TYPE_Q6_K ? 27 : WINQ ? WN::PIECES : 9;
     constexpr int PIECE_B = QT == KQ_TYPE_Q6_K ? 8 : 16;
-    constexpr int SROW = QT == KQ_TYPE_Q6_K ? W6_ROW : 144;
-    constexpr int NCHUNK = (QT == KQ_TYPE_Q4_K || QT == KQ_TYPE_Q6_K) ? (RT * BM * PIECES + DQ_THREADS - 1) / DQ_THREADS : 1;
+    constexpr int SROW = QT == KQ_TYPE_Q6_K ? W6_ROW : WINQ ? WN::SROW : 144;
+    constexpr int NCHUNK = (QT == KQ_TYPE_Q4_K || QT == KQ_TYPE_Q6_K || WINQ) ? (RT * BM * PIECES + DQ_THREADS - 1) / DQ_THREADS : 1;
     const int dq_tid = warp * 32 + lane;
     const uint8_t* csrc[NCHUNK];
     uint32_t cdst[NCHUNK];
-    if (QT == KQ_TYPE_Q4_K || st6) {
+    if (QT == KQ_TYPE_Q4_K || st6 || stw) {
 #pragma unroll
       for (int i = 0; i < NCHUNK; ++i) {
         const int c = dq_tid + i * DQ_THREADS;
         const int r = c / PIECES, part = c - PIECES * r;
         int grow = row_tile * RT * BM + r;
         if (grow >= p.n) grow = p.n - 1;
-        csrc[i] = c < RT * BM * PIECES ? p.W + (size_t)grow * p.rowbytes + part * PIECE_B : nullptr;
-        cdst[i] = smem_u32(sW + r * SROW + part * PIECE_B);
+        // window formats: the row's start (the window is aligned per column when the copies are issued); the piece
+        // index rides in the top byte of cdst
+        csrc[i] = c < RT * BM * PIECES ? p.W + (size_t)grow * p.rowbytes + (WINQ ? 0 : part * PIECE_B) : nullptr;
+        cdst[i] = smem_u32(sW + r * SROW + part * PIECE_B) | (WINQ ? (uint32_t)part << 24 : 0u);
       }
     }
     const bool holds_last_row = (row_tile + 1) * RT * BM >= p.n;   // rows past n are clamped to row n - 1
     const int last_sblk = p.k / 256 - 1;
     auto stage_block = [&](int sblk) {                          // issue the copies of super-block column sblk
+      if constexpr (WINQ) {
+        // The window of the LAST column of the LAST row may reach a few bytes past the tensor (Q2_K: up to 12).  Only a
+        // CTA that holds that row, and only there, takes the careful path, where a piece reads just the bytes that
+        // exist (the rest of its 16 bytes is zero-filled).
+        const size_t col = (size_t)sblk * WN::COLB;
+        const bool careful = holds_last_row && sblk == last_sblk;
+        const uint8_t* wend = p.W + (size_t)p.n * p.rowbytes;
+#pragma unroll
+        for (int i = 0; i < NCHUNK; ++i)
+          if (csrc[i]) {
+            const uint8_t* src = reinterpret_cast<const uint8_t*>((uintptr_t)(csrc[i] + col) & ~(uintptr_t)15) + ((cdst[i] >> 24) << 4);
+            const uint32_t have = (!careful || src + 16 <= wend) ? 16u : (src < wend ? (uint32_t)(wend - src) : 0u);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(cdst[i] & 0xFFFFFFu), "l"(src), "r"(have) : "memory");
+          }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+      }
       if constexpr (QT == KQ_TYPE_Q4_K) {
 #pragma unroll
         for (int i = 0; i < NCHUNK; ++i)
@@ -486,7 +588,8 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
       }
     };
     auto dq_barrier = [&]() { asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS) : "memory"); };
-    if (QT == KQ_TYPE_Q4_K || st6) stage_block(0);
+    uint32_t gq[WN::NG] = {};                         // window formats: the words of the thread's atom
+    if (QT == KQ_TYPE_Q4_K || st6 || stw) stage_block(0);
     // narrow: one iteration per step.  wide: one iteration per PAIR of steps (= super-block column); the thread
     // unpacks for step 2 * it + grp only, but takes part in the staging of every column.
     const int niter = WIDE ? (nsteps + 1) / 2 : nsteps;
@@ -539,6 +642,26 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
           if (2 * (col + 1) < nmain) stage_block(col + 1);
         }
       }
+      if constexpr (WINQ) {
+        if (stw && new_col) {
+          asm volatile("cp.async.wait_group 0;" ::: "memory");
+          dq_barrier();
+          const uint32_t off = (uint32_t)((uintptr_t)(wrow + (size_t)col * WN::COLB) & 15);   // where the column starts inside its window
+          const uint8_t* mine = sW + rloc * WN::SROW + off;
+          const int a4 = 2 * grp + half;
+          if constexpr (QT == KQ_TYPE_Q2_K) {
+            gq[0] = *reinterpret_cast<const uint32_t*>(mine + 4 * a4);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) gq[1 + i] = *reinterpret_cast<const uint32_t*>(mine + 16 + 32 * grp + 4 * i);
+            gq[9] = *reinterpret_cast<const uint32_t*>(mine + 80);
+          } else {
+#pragma unroll
+            for (int i = 0; i < WN::NG; ++i) gq[i] = *reinterpret_cast<const uint32_t*>(mine + (WN::COLB / 4) * a4 + 4 * i);
+          }
+          dq_barrier();
+          if (2 * (col + 1) < nmain) stage_block(col + 1);
+        }
+      }
       if (s >= nsteps) continue;                      // wide, odd number of steps: nothing left for this group
       if (s < nmain) {
         const int ga = s * (KSTEP / ATOM) + half;     // atom index along the row
@@ -551,6 +674,10 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
             if (NE > 1 && sel) dequant_q6k_regs(q6l[NE - 1], q6h[NE - 1], q6s[NE - 1], q6d, half, v);
             else dequant_q6k_regs(q6l[0], q6h[0], q6s[0], q6d, half, v);
           }
+        } else if (stw) {
+          if constexpr (WINQ && QT == KQ_TYPE_Q8_0) dequant_q8_0_regs(gq, v);
+          if constexpr (WINQ && QT == KQ_TYPE_Q4_0) dequant_q4_0_regs(gq, v);
+          if constexpr (WINQ && QT == KQ_TYPE_Q2_K) dequant_q2_k_regs(gq, half, p.half_fma, v);
         } else {
           const uint8_t* blk = F::BLK >= 256 ? wrow + (size_t)(ga / ATOMS_PER_BLK) * F::BYTES
                                              : wrow + (size_t)ga * 2 * F::BYTES;
@@ -599,8 +726,9 @@ template <int QT, bool CORR, typename OutT, bool WIDE>
 int launch(const GemmParams& p, const CUtensorMap& map, const CUtensorMap& smap, int grid, cudaStream_t st) {
   using T = Tile<WIDE>;
   auto kern = gemm_tc_kernel<QT, CORR, OutT, WIDE>;
-  const int smem = T::NB * T::B_STAGE + 4096 + (QT == KQ_TYPE_Q4_K ? T::W4_STAGE : (QT == KQ_TYPE_Q6_K ? T::W6_STAGE : 0));
-  static_assert(T::NB * T::B_STAGE + 4096 + T::W6_STAGE <= 227 * 1024, "shared memory budget");
+  constexpr int WSTAGE = QT == KQ_TYPE_Q4_K ? T::W4_STAGE : QT == KQ_TYPE_Q6_K ? T::W6_STAGE : (WIDE && Win<QT>::ON) ? BM * Win<QT>::SROW : 0;
+  constexpr int smem = T::NB * T::B_STAGE + (QT == KQ_TYPE_IQ3_S ? 4096 : 1024) + WSTAGE;   // barriers (+ IQ3_S codebook), then the weight stage
+  static_assert(smem <= 227 * 1024, "shared memory budget");
   static DeviceOnce attr_set;   // the attribute belongs to the (function, device) pair
   if (attr_set.first_time()) {
     KQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -625,7 +753,9 @@ int launch_out(const GemmParams& p, const CUtensorMap& map, const CUtensorMap& s
 
 }  // namespace
 
-bool gemm_tc_staged(int type) { return type == KQ_TYPE_Q4_K || type == KQ_TYPE_Q6_K; }
+bool gemm_tc_staged(int type) {
+  return type == KQ_TYPE_Q4_K || type == KQ_TYPE_Q6_K || type == KQ_TYPE_Q8_0 || type == KQ_TYPE_Q4_0 || type == KQ_TYPE_Q2_K;
+}
 
 // The tensor-core GEMM needs whole 256-weight K steps and 16-byte aligned Q4_K blocks; everything else is general.
 bool gemm_tc_supported(const void* W, int type, int64_t n, int64_t k) {
@@ -672,6 +802,7 @@ int launch_gemm_tc(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& 
   p.ntok_tiles = (int)((m + BN - 1) / BN);
   p.y = y; p.stride_y = stride_y; p.status = P.status; p.half_fma = options().half_fma;
   p.stage6 = type == KQ_TYPE_Q6_K && ((uintptr_t)W % 8) == 0 && (p.rowbytes % 8) == 0;
+  p.stagew = ((uintptr_t)W % 16) == 0 && (k % 256) == 0;
   const int grid = (int)((n + RT * BM - 1) / (RT * BM)) * p.ntok_tiles;
   switch (type) {
     case KQ_TYPE_Q4_0: return launch_out<KQ_TYPE_Q4_0, true>(p, map, smap, grid, y_dtype, wide, st);
