@@ -22,7 +22,8 @@ N > 1   the mixed-quant decoder stack: 64 layers, per layer merged q/k/v (Q8_0, 
         ranks and all-gathered; each projection consumes the gathered output of the one before it (RMSNorm / SwiGLU /
         plain q8_1 producers), so nothing overlaps artificially.  Total work is fixed (strong scaling).  Before the line
         is printed every rank's gathered outputs are compared with single-GPU results on the full matrices, and the
-        ranks' final outputs with each other.
+        ranks' final outputs with each other.  `same_workload_one_gpu`: the same stack, unsharded, timed on rank 0 in
+        the same run - the N = 1 line above measures another configuration, so this is what the N-GPU value compares with.
 
 --impl reference times the reference's CPU path (gguf-reader dequantize + torch matmul) on the host cores, on a
 bounded sample of the same configuration.
@@ -392,6 +393,23 @@ def run_multi(args, torch, dist, dev, rank, world, local):
     stack.check()
     nbytes = c3_bytes(layers)
     value = nbytes / (ms_step * 1e-3) / 1e9
+    # ---- the same workload on ONE GPU, measured in this run (rank 0, whole tensors, the other ranks wait): the N = 1
+    # line of this program measures another configuration, so this is the figure the N-GPU value divides by
+    one = None
+    if rank == 0 and not args.no_one_gpu:
+        try:
+            solo = sharded.DecoderStack(make_stack(torch, synth, dev, 0, 1, layers), C3_M, K_HID, dev, unsharded=True)
+            with torch.cuda.stream(stream):
+                solo.forward(x0)
+                r1, cap1 = tm.graph(lambda: solo.forward(x0))
+                ms1 = tm.time(r1, max(3, min(args.steps, 10)))
+            one = {"ms_per_step": ms1, "value": nbytes / (ms1 * 1e-3) / 1e9, "unit": "GB/s", "speedup_of_this_run": ms1 / ms_step,
+                   "launch": "cuda graph replay" if cap1 else "eager",
+                   "how": "rank 0 alone, unsharded weights from the same seeds, after the timed region of the sharded run"}
+            del solo, r1
+        except Exception as e:  # noqa: BLE001 - the comparison figure is optional
+            one = {"unavailable": repr(e)[:200]}
+    barrier()
     if rank == 0:
         cfg = workload_config(world)
         cfg.update({"layers": layers, "bytes_per_step": nbytes, "gather": gather_how,
@@ -404,6 +422,7 @@ def run_multi(args, torch, dist, dev, rank, world, local):
             "dtype": "int8", "data": "synthetic", "config": cfg,
             "frac_of_measured_hbm": value / (world * pk["hbm"]), "frac_of_nominal_8tbs": value / (world * 8000.0),
             "per_gpu_gbs": value / world, "us_per_projection": ms_step * 1e3 / (4 * layers),
+            "same_workload_one_gpu": one,
             "clocks": clocks, "gpu_launches": launches_step * args.steps,
             "verified": {"gathered_outputs_vs_single_gpu_full_matrices": "equal up to last-bit rounding flips",
                          "worst_rel_l2": checked.get("worst_rel"), "least_fraction_bit_equal": checked.get("least_equal"),
@@ -715,6 +734,7 @@ def main() -> None:
     ap.add_argument("--no-fused-gather", action="store_true", help="N>1: GEMV and peer-store gather as two kernels")
     ap.add_argument("--nccl", action="store_true", help="N>1: gather with NCCL instead of the library's peer-store kernel")
     ap.add_argument("--quick", action="store_true", help="N=1: only the main workload, roofline and e2e (no further legs)")
+    ap.add_argument("--no-one-gpu", action="store_true", help="N>1: skip the one-GPU run of the same workload on rank 0")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)

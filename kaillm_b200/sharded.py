@@ -194,12 +194,15 @@ class DecoderStack:
     GROUPS = ("qkv", "o", "gate_up", "down")
 
     def __init__(self, weights: list[dict], m: int, hidden: int, device: torch.device, p2p: "P2PGather | None" = None,
-                 group=None, eps: float = 1e-6, dtype: torch.dtype = torch.bfloat16, wait_in_consumer: bool = True):
+                 group=None, eps: float = 1e-6, dtype: torch.dtype = torch.bfloat16, wait_in_consumer: bool = True,
+                 unsharded: bool = False):
+        """`unsharded`: the weights are whole tensors and this process runs the stack alone, whatever process group
+        exists (a single-GPU baseline inside a multi-rank job)."""
         from . import capi
         self._capi = capi
         self.w = weights
         self.m, self.hidden, self.eps, self.dtype = m, hidden, eps, dtype
-        self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
+        self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized() and not unsharded) else 1
         self.rank = dist.get_rank(group) if self.world > 1 else 0
         self.group = group
         self.p2p = p2p
