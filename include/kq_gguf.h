@@ -323,7 +323,14 @@ int kq_debug_copy_window(uint64_t base, int64_t n, int64_t rowbytes, int64_t row
  *                 the activations are prepared.  "umma_box" 1 (default) = its weight bytes arrive by tiled TMA copies
  *                 where the rows are 16-byte aligned, 0 = by cp.async
  *   "no_fused_gather" 1 = kq_mul_mat_prepared_gather always runs as two kernels (default 0)
- *   "gemm_min_m"  smallest m that goes to the tcgen05 GEMM (default 81: m <= 80 keeps exact integer dots)
+ *   "gemm_min_m"  smallest m that always goes to the tcgen05 GEMM (default 81)
+ *   "gemm_small_m" 1 (default) = calls of 17..gemm_min_m-1 tokens go to the GEMM too where one launch beats the
+ *                 16-token GEMV passes (Q4_0, Q8_0, Q2_K, Q4_K, Q6_K; k a multiple of 256; at least 120 tiles of 128
+ *                 rows, or 60 from 33 tokens on); results then carry fp16-operand rounding (rel-L2 about 3e-4 to the
+ *                 integer path, inside the 1e-3 contract).  0 = m < gemm_min_m keeps exact integer dots.  Set it
+ *                 BEFORE the activations are prepared (kq_prepare_q8* write the GEMM's operands only when wanted)
+ *   "gemm_wide"   tile of the GEMM: 0 = 256 rows x 128 tokens, 2 = 128 rows x 256 tokens, 1 (default) = the latter
+ *                 whenever more than 128 tokens come or the format's wire bytes are staged through shared memory
  *   "half_fma"    1 = K-quant dequantize contracts fp16 mul+sub into one fma (default), 0 = two roundings
  * Returns KQ_EINVAL for an unknown name. */
 int kq_set_option(const char* name, int value);
