@@ -325,8 +325,9 @@ int kq_debug_copy_window(uint64_t base, int64_t n, int64_t rowbytes, int64_t row
  *   "no_fused_gather" 1 = kq_mul_mat_prepared_gather always runs as two kernels (default 0)
  *   "gemm_min_m"  smallest m that always goes to the tcgen05 GEMM (default 81)
  *   "gemm_small_m" 1 (default) = calls of 17..gemm_min_m-1 tokens go to the GEMM too where one launch beats the
- *                 16-token GEMV passes (Q4_0, Q8_0, Q2_K, Q4_K, Q6_K; k a multiple of 256; at least 120 tiles of 128
- *                 rows, or 60 from 33 tokens on); results then carry fp16-operand rounding (rel-L2 about 3e-4 to the
+ *                 16-token GEMV passes (Q4_0, Q8_0, Q2_K, Q4_K, Q6_K; k a multiple of 256; from 17 tokens with at least
+ *                 120 tiles of 128 rows, from 33 with 60, from 49 with 30; Q4_0 and Q6_K later); results then carry
+ *                 fp16-operand rounding (rel-L2 about 3e-4 to the
  *                 integer path, inside the 1e-3 contract).  0 = m < gemm_min_m keeps exact integer dots.  Set it
  *                 BEFORE the activations are prepared (kq_prepare_q8* write the GEMM's operands only when wanted)
  *   "gemm_wide"   tile of the GEMM: 0 = 256 rows x 128 tokens, 2 = 128 rows x 256 tokens, 1 (default) = the latter

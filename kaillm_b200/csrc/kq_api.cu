@@ -72,17 +72,24 @@ static int validate(const char* fn, const void* W, int type, int64_t n, int64_t 
 }
 
 // tcgen05 GEMM or passes of the integer GEMV?  From gemm_min_m tokens on always the GEMM.  Below that (17+ tokens,
-// i.e. two or more GEMV passes) the GEMM takes the call when its time, flat in m up to 256 tokens, beats the passes:
-// measured on Q4_K 17408x5120 38 us against 42 / 49 / 64 / 116 us at 17 / 32 / 33 / 80 tokens, on Q4_K 8192x2048
-// (64 row tiles) 20 us against 22 / 26 / 49 us at 32 / 33 / 80; on Q6_K 5120x17408 (40 row tiles of a long K) the
-// GEMV wins up to 80 tokens.
+// i.e. two or more GEMV passes) the GEMM takes the call when its time, flat in m up to 256 tokens, beats the passes.
+// Measured (us, whole call, GEMV passes at 17 / 33 / 48 / 80 tokens against the GEMM):
+//   Q4_K 17408x5120 (136 row tiles)  42 / 64 / 71 / 116   against  38
+//   Q8_0  8192x5120  (64)            34 / 53 / 61 /  99   against  54      Q2_K 8192x2048 (64)  21 / 31 / 35 / 57  against 23
+//   Q4_0  8192x5120  (64)            36 / 60 / 75 / 122   against  95  (its correction steps are slow)
+//   Q8_0  5120x5120  (40)            26 / 42 / 50 /  79   against  54      Q4_K 4096x4096 (32)  17 / 25 / 30 / 48  against 30
+//   Q6_K  5120x17408 (40, long K)    57 / 93 / 111 / 184  against 175
 static bool gemm_wanted(int type, int64_t n, int64_t k, int64_t m) {
   const Options& o = options();
   if (o.gemv_impl != 0) return false;
   if (m >= o.gemm_min_m) return true;
   if (!o.gemm_small_m || m <= 16 || !gemm_tc_staged(type) || (k % 256) != 0) return false;
   const int64_t tiles = (n + 127) / 128;
-  return tiles >= 120 || (m >= 33 && tiles >= 60);
+  const bool q40 = type == KQ_TYPE_Q4_0, q6k = type == KQ_TYPE_Q6_K;   // more time per K step than the others
+  if (tiles >= 120) return m >= (q40 ? 49 : 17);
+  if (tiles >= 60) return m >= (q40 ? 65 : q6k ? 49 : 33);
+  if (tiles >= 30) return !q40 && !q6k && m >= 49;
+  return false;
 }
 
 static int mul_mat(const char* fn, bool mmq, const void* W, int type, int64_t n, int64_t k, const void* x,

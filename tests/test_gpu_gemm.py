@@ -102,7 +102,19 @@ def test_config4_q4k_prefill(m):
     assert rel_l2(y32, want) < GATE
 
 
-@pytest.mark.parametrize("qt,n,k", [(12, 16384, 1024), (14, 15488, 512), (12, 7808, 1024)])
+def _takes_gemm(qt, n, m):
+    """The library's rule for 17..80 tokens (kq_api.cu: gemm_wanted), restated."""
+    tiles = (n + 127) // 128
+    if tiles >= 120:
+        return m >= (49 if qt == 2 else 17)
+    if tiles >= 60:
+        return m >= (65 if qt == 2 else 49 if qt == 14 else 33)
+    if tiles >= 30:
+        return qt not in (2, 14) and m >= 49
+    return False
+
+
+@pytest.mark.parametrize("qt,n,k", [(12, 16384, 1024), (14, 15488, 512), (12, 7808, 1024), (8, 4096, 512), (2, 7808, 512)])
 @pytest.mark.parametrize("m", [17, 33, 80])
 def test_calls_of_17_to_80_tokens_take_the_gemm_where_it_is_faster(qt, n, k, m):
     """Two or more 16-token GEMV passes against one GEMM launch: with enough 128-row tiles the GEMM takes the call
@@ -120,9 +132,7 @@ def test_calls_of_17_to_80_tokens_take_the_gemm_where_it_is_faster(qt, n, k, m):
         capi.set_option("gemm_small_m", 1)
     assert rel_l2(to_np(y_int)[:, rows], want) < 2e-5                # integer dots: fp32 rounding only
     assert rel_l2(to_np(y)[:, rows], want) < GATE
-    tiles = (n + 127) // 128
-    takes_gemm = tiles >= 120 or (m >= 33 and tiles >= 60)
-    assert torch.equal(y, y_int) != takes_gemm                       # fp16 operands differ from integer dots in the last bits
+    assert torch.equal(y, y_int) != _takes_gemm(qt, n, m)                      # fp16 operands differ from integer dots in the last bits
     # the same call in two halves, activations from the SwiGLU producer
     g = torch.Generator(device=dev()); g.manual_seed(m)
     gu = torch.randn((m, 2 * k), device=dev(), generator=g).to(torch.bfloat16)

@@ -38,10 +38,10 @@ def test_mul_mat_a8_matches_reference_kernels(ref_ops, qt, n, k, m):
 
 
 @pytest.mark.parametrize("qt", [2, 8, 10, 12, 14])
-@pytest.mark.parametrize("n,k,m", [(256, 1024, 200), (300, 2048, 130)])
+@pytest.mark.parametrize("n,k,m", [(256, 1024, 200), (300, 2048, 130), (7808, 512, 48), (15488, 256, 17)])
 def test_prefill_gemm_matches_reference_kernels(ref_ops, qt, n, k, m):
-    """More than 80 tokens: this library switches to the tcgen05 GEMM with fp16 operands; the reference stays on its
-    integer MMQ kernels.  The gate is the path's 1e-3."""
+    """More than 80 tokens - and from 17 tokens on matrices with enough 128-row tiles - this library switches to the
+    tcgen05 GEMM with fp16 operands; the reference stays on its integer MMQ kernels.  The gate is the path's 1e-3."""
     w, wt = wire(qt, n, k, seed=qt + 5)
     x, xt = act(m, k, seed=m + 5, dt="f32")          # fp32 in, fp32 out: no output rounding in the comparison
     ref = to_np(ref_ops.ggml_mul_mat_a8(wt, xt, qt, n))
