@@ -236,7 +236,9 @@ __global__ void __launch_bounds__(ROW_THREADS, 1) gemv_rows_kernel(const RowPara
         const int ra = r0 + q * R;
         const int rb = (ra + R) < r1 ? (ra + R) : r1;
         // whole rows [ra, rb): one bulk copy (the host passes only row counts whose byte size is a multiple of 16,
-        // so the rounded window stays inside the tensor)
+        // so the rounded window stays inside the tensor).  This lane's loop is the request rate of the SM: a request
+        // costs it ~0.25 us whatever its size, so stages are sized well above 16 KB (option row_stage_kb) and nothing
+        // else sits in the loop (splitting a stage among several lanes made it slower)
         const CopyWindow cw = copy_window((uintptr_t)(p.W + (size_t)ra * p.rowbytes), (uintptr_t)(p.W + (size_t)rb * p.rowbytes));
         mbar_expect_tx(bar_full + 8 * slot, cw.bulk);
         bulk_g2s(smem_u32(ring + (size_t)slot * p.stage_bytes), (const void*)cw.a0, cw.bulk, bar_full + 8 * slot);
@@ -516,9 +518,14 @@ bool make_row_config(int type, int64_t n, int64_t k, int mt, bool pair, RowConfi
   if (!type_geometry(type, &blk, &bytes)) return false;
   const int64_t rowbytes = k / blk * bytes;
   const int zpb = z_per_block(type);
-  int R = (int)(16384 / rowbytes);
+  // Stage size.  The producer lane's loop is the request rate of an SM, so the Q4_K row-pair kernel, whose 16 KB target
+  // gave 11.5 KB stages (an even number of 2880-byte rows), runs on 24 KB stages: 15.3 -> 13.1 us on 17408x5120 at one
+  // token, 28.2 -> 21.3 us on 34816x5120.  The one-row-per-warp kernels were not faster with larger stages (Q8_0
+  // 5120x5120 at two tokens: 10.3 -> 12.2 us), they keep 16 KB.
+  const int64_t stage_target = (pair && type == KQ_TYPE_Q4_K) ? (int64_t)options().row_stage_kb * 1024 : 16384;
+  int R = (int)(stage_target / rowbytes);
   if (R < 1) R = 1;
-  if (R > 16) R = 16;
+  if (R > 32) R = 32;
   if (pair) R = R < 2 ? 2 : (R & ~1);   // a warp's two rows never straddle stages
   c.rows_per_stage = R;
   c.stage_bytes = (int)((R * rowbytes + 32 + 127) / 128 * 128);
