@@ -326,7 +326,7 @@ int kq_debug_copy_window(uint64_t base, int64_t n, int64_t rowbytes, int64_t row
  *   "gemm_min_m"  smallest m that always goes to the tcgen05 GEMM (default 81)
  *   "gemm_small_m" 1 (default) = calls of 17..gemm_min_m-1 tokens go to the GEMM too where one launch beats the
  *                 16-token GEMV passes (Q4_0, Q8_0, Q2_K, Q4_K, Q6_K; k a multiple of 256; from 17 tokens with at least
- *                 120 tiles of 128 rows, from 33 with 60, from 49 with 30; Q4_0 and Q6_K later); results then carry
+ *                 120 tiles of 128 rows, from 33 with 60, from 49 with 30; Q4_0 and Q6_K a step later); results then carry
  *                 fp16-operand rounding (rel-L2 about 3e-4 to the
  *                 integer path, inside the 1e-3 contract).  0 = m < gemm_min_m keeps exact integer dots.  Set it
  *                 BEFORE the activations are prepared (kq_prepare_q8* write the GEMM's operands only when wanted)

@@ -65,7 +65,7 @@ static int validate(const char* fn, const void* W, int type, int64_t n, int64_t 
   if (wa % need) { set_error("%s: weight pointer must be %d-byte aligned for this type", fn, need); return KQ_EINVAL; }
   if (need_x && (uintptr_t)x % dtype_size(x_dtype)) { set_error("%s: misaligned activation pointer", fn); return KQ_EINVAL; }
   p.rowbytes = k / p.blk * p.bytes;
-  p.L = q8_layout(m, n, k);
+  p.L = q8_layout(m, n, k, type);
   if (!scratch || (uintptr_t)scratch % 256) { set_error("%s: scratch must be non-null and 256-byte aligned", fn); return KQ_ESCRATCH; }
   if (scratch_bytes < p.L.total) { set_error("%s: scratch too small (%zu < %zu)", fn, scratch_bytes, p.L.total); return KQ_ESCRATCH; }
   return KQ_OK;
@@ -76,7 +76,7 @@ static int validate(const char* fn, const void* W, int type, int64_t n, int64_t 
 // Measured (us, whole call, GEMV passes at 17 / 33 / 48 / 80 tokens against the GEMM):
 //   Q4_K 17408x5120 (136 row tiles)  42 / 64 / 71 / 116   against  38
 //   Q8_0  8192x5120  (64)            34 / 53 / 61 /  99   against  54      Q2_K 8192x2048 (64)  21 / 31 / 35 / 57  against 23
-//   Q4_0  8192x5120  (64)            36 / 60 / 75 / 122   against  95  (its correction steps are slow)
+//   Q4_0  8192x5120  (64)            36 / 60 / 75 / 122   against  58      Q4_0 17408x5120 (136)  50 / 75 / .. / ..  against 68
 //   Q8_0  5120x5120  (40)            26 / 42 / 50 /  79   against  54      Q4_K 4096x4096 (32)  17 / 25 / 30 / 48  against 30
 //   Q6_K  5120x17408 (40, long K)    57 / 93 / 111 / 184  against 175
 static bool gemm_wanted(int type, int64_t n, int64_t k, int64_t m) {
@@ -86,9 +86,9 @@ static bool gemm_wanted(int type, int64_t n, int64_t k, int64_t m) {
   if (!o.gemm_small_m || m <= 16 || !gemm_tc_staged(type) || (k % 256) != 0) return false;
   const int64_t tiles = (n + 127) / 128;
   const bool q40 = type == KQ_TYPE_Q4_0, q6k = type == KQ_TYPE_Q6_K;   // more time per K step than the others
-  if (tiles >= 120) return m >= (q40 ? 49 : 17);
-  if (tiles >= 60) return m >= (q40 ? 65 : q6k ? 49 : 33);
-  if (tiles >= 30) return !q40 && !q6k && m >= 49;
+  if (tiles >= 120) return m >= (q40 ? 33 : 17);
+  if (tiles >= 60) return m >= (q6k ? 49 : 33);
+  if (tiles >= 30) return !q6k && m >= 49;
   return false;
 }
 
@@ -169,7 +169,7 @@ int kq_block_geometry(int type, int* weights_per_block, int* bytes_per_block) {
 size_t kq_workspace_bytes(int type, int64_t m, int64_t n, int64_t k) {
   int b, s;
   if (!type_geometry(type, &b, &s) || m <= 0 || n <= 0 || k <= 0) return 0;
-  return q8_layout(m, n, k).total;
+  return q8_layout(m, n, k, type).total;
 }
 
 int kq_quantize_q8_1(const void* x, int x_dtype, int64_t m, int64_t k, int64_t stride_x, void* out_blocks, void* stream) {

@@ -143,10 +143,11 @@ constexpr int KQ_PART_SLOTS = 4;      // partial-sum slots of a split row tile
 constexpr int KQ_CNT_SLOTS = 65536;   // 8-row tiles a split-K launch may have (n <= 524288); larger n runs unsplit
 struct Q8Layout {
   int64_t kpad, mt;
-  size_t off_ds, off_qs, off_qsp, off_xh, off_s8h, off_dT, off_z32, off_zs8, off_z16, off_z32r, off_z16r, off_qsu, off_part, off_cnt, off_status, total;
+  size_t off_ds, off_qs, off_qsp, off_xh, off_s8h, off_dT, off_z32, off_zs8, off_z16, off_z32r, off_z16r, off_qsu, off_part, off_cnt, off_status, off_w16, total;
+  int64_t w16_stride;   // halves per row of the Q4_0 coefficient table (0: none)
 };
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
-inline Q8Layout q8_layout(int64_t m, int64_t n, int64_t k) {
+inline Q8Layout q8_layout(int64_t m, int64_t n, int64_t k, int type = 0) {
   Q8Layout L;
   L.kpad = (k + 511) / 512 * 512;
   L.mt = (m + 15) / 16;
@@ -167,12 +168,17 @@ inline Q8Layout q8_layout(int64_t m, int64_t n, int64_t k) {
   L.off_z16r = p;   p = align_up(p + (size_t)m * nb * 8, 256);
   L.off_qsu = p;    p = align_up(p + (size_t)L.mt * (L.kpad / 256) * KQ_UNIT_TABLE, 256);
   L.off_part = p;   p = align_up(p + (size_t)KQ_PART_SLOTS * 16 * n * 4, 256);
+  // Q4_0 calls that may go to the tensor-core GEMM: a dense fp16 table [n][k/32 rounded up to 128] of -8 * d per block,
+  // written per call, so that the GEMM's correction steps read 128 contiguous bytes per row instead of 64 scattered scales
+  L.w16_stride = (type == KQ_TYPE_Q4_0 && m > 16) ? (int64_t)((nb + 127) / 128 * 128) : 0;
+  L.off_w16 = p;    p = align_up(p + (size_t)n * L.w16_stride * 2, 256);
   L.total = p;
   return L;
 }
 
 struct Q8Ptrs {  // device pointers into one scratch buffer
   __half2* ds; int8_t* qs; int8_t* qsp; __half* xh; __half* s8h; float *dT, *z32, *zs8, *z16, *z32r, *z16r, *part; int8_t* qsu; int *cnt, *status;
+  __half* w16; int64_t w16_stride;   // Q4_0 coefficient table of the GEMM's correction steps (null: none)
   int64_t kpad; int ncnt;
 };
 inline Q8Ptrs q8_ptrs(void* scratch, const Q8Layout& L, int64_t n) {
@@ -182,6 +188,7 @@ inline Q8Ptrs q8_ptrs(void* scratch, const Q8Layout& L, int64_t n) {
   P.dT = (float*)(s + L.off_dT); P.z32 = (float*)(s + L.off_z32); P.zs8 = (float*)(s + L.off_zs8);
   P.z16 = (float*)(s + L.off_z16); P.z32r = (float*)(s + L.off_z32r); P.z16r = (float*)(s + L.off_z16r);
   P.part = (float*)(s + L.off_part);
+  P.w16 = L.w16_stride ? (__half*)(s + L.off_w16) : nullptr; P.w16_stride = L.w16_stride;
   // the unit tables are only written (and read) while the tensor-memory decode kernel is switched on: set the option
   // before the activations are prepared
   P.qsu = (options().umma || options().gemv_impl == 8) ? (int8_t*)(s + L.off_qsu) : nullptr;

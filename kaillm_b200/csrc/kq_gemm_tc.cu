@@ -77,6 +77,8 @@ struct GemmParams {
   int* status;
   int half_fma;
   int stage6;         // Q6_K: rows and W are 8-byte aligned, the block columns go through shared memory
+  const __half* ctab;  // Q4_0: dense table [n][ctab_stride] of -8 * d per 32-block (null: read the scales from W)
+  int64_t ctab_stride;
   int stagew;         // Q8_0, Q4_0, Q2_K in the 128 x 256 tile: W is 16-byte aligned and k a multiple of 256, the columns go through shared memory
 };
 
@@ -159,7 +161,28 @@ __device__ __forceinline__ __half corr_coef(const uint8_t* __restrict__ wrow, in
 }
 
 template <int QT>
-__device__ __forceinline__ void corr_atom(const uint8_t* __restrict__ wrow, int atom, int nb32, uint32_t (&out)[32]) {
+__device__ __noinline__ void corr_atom_scattered(const uint8_t* __restrict__ wrow, int atom, int nb32, uint32_t* out) {
+  for (int i = 0; i < 32; ++i) {
+    const int b = atom * 64 + 2 * i;
+    const __half c0 = b < nb32 ? corr_coef<QT>(wrow, b) : __float2half_rn(0.f);
+    const __half c1 = b + 1 < nb32 ? corr_coef<QT>(wrow, b + 1) : __float2half_rn(0.f);
+    out[i] = h2_bits(__halves2half2(c0, c1));
+  }
+}
+
+template <int QT>
+__device__ __forceinline__ void corr_atom(const uint8_t* __restrict__ wrow, int atom, int nb32, const __half* __restrict__ crow,
+                                          uint32_t (&out)[32]) {
+  if (QT == KQ_TYPE_Q4_0 && crow != nullptr) {
+    // the row's coefficients were laid out densely (zero past the last block) by q4_0_coef_kernel: 128 contiguous bytes
+    const uint4* c = reinterpret_cast<const uint4*>(crow + (size_t)atom * 64);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint4 v = __ldg(c + i);
+      out[4 * i] = v.x; out[4 * i + 1] = v.y; out[4 * i + 2] = v.z; out[4 * i + 3] = v.w;
+    }
+    return;
+  }
   if constexpr (QT == KQ_TYPE_Q4_K) {
     // 64 coefficients = 8 super-blocks x 8 sub-block mins; one 16-byte header load per super-block
 #pragma unroll
@@ -176,13 +199,12 @@ __device__ __forceinline__ void corr_atom(const uint8_t* __restrict__ wrow, int 
       }
     }
   } else {
+    // rare path (Q4_0 without its coefficient table): kept out of line so that its 64 scattered loads do not weigh on
+    // the register allocation of the K loop
+    uint32_t tmp[32];
+    corr_atom_scattered<QT>(wrow, atom, nb32, tmp);
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const int b = atom * 64 + 2 * i;
-      const __half c0 = b < nb32 ? corr_coef<QT>(wrow, b) : __float2half_rn(0.f);
-      const __half c1 = b + 1 < nb32 ? corr_coef<QT>(wrow, b + 1) : __float2half_rn(0.f);
-      out[i] = h2_bits(__halves2half2(c0, c1));
-    }
+    for (int i = 0; i < 32; ++i) out[i] = tmp[i];
   }
 }
 
@@ -684,7 +706,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
           dequant_atom<QT, CORR>(blk, F::BLK >= 256 ? (ga % ATOMS_PER_BLK) : 0, s_grid, p.half_fma, pre, v);
         }
       } else {
-        corr_atom<QT>(wrow, (s - nmain) * (KSTEP / ATOM) + half, p.nb32, v);
+        corr_atom<QT>(wrow, (s - nmain) * (KSTEP / ATOM) + half, p.nb32, p.ctab ? p.ctab + (size_t)row * p.ctab_stride : nullptr, v);
       }
       if (ok && fill > 0) ok = mbar_wait(bar_aempty + 8 * ab, (uint32_t)((fill - 1) & 1), s_abort);
       if (ok) {
@@ -718,6 +740,19 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, con
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tbase), "r"(TMEM_COLS));
+}
+
+// Q4_0: out[row][b] = -8 * d(row, b) as fp16 for b < nb, 0 up to `stride`.  One warp per row; consecutive lanes read
+// consecutive blocks' scales (18 bytes apart: every sector of the row is touched once).
+__global__ void __launch_bounds__(256) q4_0_coef_kernel(const uint8_t* __restrict__ W, int64_t rowbytes, int n, int nb,
+                                                        __half* __restrict__ out, int64_t stride) {
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= n) return;
+  const uint8_t* wrow = W + (size_t)row * rowbytes;
+  __half* o = out + (size_t)row * stride;
+  for (int b = lane; b < (int)stride; b += 32)
+    o[b] = b < nb ? __hmul_rn(__float2half_rn(-8.0f), __ushort_as_half(*reinterpret_cast<const uint16_t*>(wrow + (size_t)b * 18)))
+                  : __float2half_rn(0.f);
 }
 
 // ------------------------------------------------------------------------------------------------ host
@@ -803,6 +838,13 @@ int launch_gemm_tc(const void* W, int type, int64_t n, int64_t k, const Q8Ptrs& 
   p.y = y; p.stride_y = stride_y; p.status = P.status; p.half_fma = options().half_fma;
   p.stage6 = type == KQ_TYPE_Q6_K && ((uintptr_t)W % 8) == 0 && (p.rowbytes % 8) == 0;
   p.stagew = ((uintptr_t)W % 16) == 0 && (k % 256) == 0;
+  p.ctab = nullptr; p.ctab_stride = 0;
+  if (type == KQ_TYPE_Q4_0 && P.w16 != nullptr) {
+    q4_0_coef_kernel<<<(unsigned)((n + 7) / 8), 256, 0, st>>>((const uint8_t*)W, p.rowbytes, (int)n, p.nb32, P.w16, P.w16_stride);
+    options().launches += 1;
+    KQ_CUDA_TRY(cudaGetLastError());
+    p.ctab = P.w16; p.ctab_stride = P.w16_stride;
+  }
   const int grid = (int)((n + RT * BM - 1) / (RT * BM)) * p.ntok_tiles;
   switch (type) {
     case KQ_TYPE_Q4_0: return launch_out<KQ_TYPE_Q4_0, true>(p, map, smap, grid, y_dtype, wide, st);

@@ -106,11 +106,11 @@ def _takes_gemm(qt, n, m):
     """The library's rule for 17..80 tokens (kq_api.cu: gemm_wanted), restated."""
     tiles = (n + 127) // 128
     if tiles >= 120:
-        return m >= (49 if qt == 2 else 17)
+        return m >= (33 if qt == 2 else 17)
     if tiles >= 60:
-        return m >= (65 if qt == 2 else 49 if qt == 14 else 33)
+        return m >= (49 if qt == 14 else 33)
     if tiles >= 30:
-        return qt not in (2, 14) and m >= 49
+        return qt != 14 and m >= 49
     return False
 
 
