@@ -340,7 +340,7 @@ __device__ __forceinline__ void dequant_q6k_regs(const uint32_t (&ql)[16], const
 // Window staging of the 32-weight-block formats and Q2_K (128 x 256 tile only): per 256-weight column a row owns COLB wire
 // bytes; the 16-byte aligned window around them goes to shared memory in 16-byte pieces, each unpacking thread pulls the
 // words of its own 64-weight atom into registers and unpacks from there, two weights per fp16x2 instruction.
-template <int QT> struct Win { static constexpr bool ON = false; static constexpr int COLB = 16, PIECES = 1, SROW = 16, NG = 1; };
+template <int QT> struct Win { static constexpr bool ON = false; enum { COLB = 16, PIECES = 1, SROW = 16, NG = 1 }; };
 template <> struct Win<KQ_TYPE_Q8_0> { static constexpr bool ON = true; static constexpr int COLB = 272, PIECES = 17, SROW = 272, NG = 17; };
 template <> struct Win<KQ_TYPE_Q4_0> { static constexpr bool ON = true; static constexpr int COLB = 144, PIECES = 9, SROW = 144, NG = 9; };
 // Q2_K blocks are 4-byte aligned (84 = 4 * 21): a block starts 0, 4, 8 or 12 bytes into its window of 6 pieces

@@ -433,7 +433,7 @@ __global__ void __launch_bounds__(ROW_THREADS, 1) gemv_rows_kernel(const RowPara
         y[(size_t)(p.m0 + (lane & 15)) * p.stride_y + row] = from_f32<OutT>(mine);
     }
     return;
-  }
+  } else {
   for (int i = warp; r0 + i < r1; i += ROW_WARPS) {
     const int row = r0 + i;
     const int q = i / R, slot = q % S;
@@ -496,6 +496,7 @@ __global__ void __launch_bounds__(ROW_THREADS, 1) gemv_rows_kernel(const RowPara
 #pragma unroll
     for (int t = 0; t < MT; ++t) if (lane == t) mine = acc[t];
     if (lane < MT && lane < p.mcount) y[(size_t)(p.m0 + lane) * p.stride_y + row] = from_f32<OutT>(mine);
+  }
   }
 }
 

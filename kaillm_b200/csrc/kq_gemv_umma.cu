@@ -117,11 +117,6 @@ __device__ __forceinline__ f2 add2p(f2 a, f2 b) {
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
   return r;
 }
-__device__ __forceinline__ f2 mul2p(f2 a, f2 b) {
-  f2 r;
-  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
 // (float)v0, (float)v1 for |v| < 2^22: integer add onto the magic exponent, then one packed subtraction
 __device__ __forceinline__ f2 int2_to_f2(int v0, int v1, f2 neg_magic) {
   return add2p(pki(v0 + (int)TL_MAGIC_I, v1 + (int)TL_MAGIC_I), neg_magic);
@@ -365,7 +360,6 @@ __global__ void __launch_bounds__(UM_THREADS, 1) gemv_umma_kernel(const UmmaPara
               um[v * 2 + 1] = fma2p(m2, z8.y, um[v * 2 + 1]);
             }
           }
-#pragma unroll
           const f2 nd2 = pk(-dmin, -dmin);
 #pragma unroll
           for (int i = 0; i < 2 * NV; ++i) accm[i] = fma2p(nd2, um[i], accm[i]);
@@ -453,7 +447,6 @@ __global__ void __launch_bounds__(UM_THREADS, 1) gemv_umma_kernel(const UmmaPara
         }
       }
       if (!ok) break;
-#pragma unroll
       {
         const f2 dd2 = pk(dd, dd);
 #pragma unroll
