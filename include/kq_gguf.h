@@ -123,6 +123,8 @@ int kq_mul_mat_vec_a8_static(const void* W, int type, int64_t n, int64_t k,
  * against the activations already held there (mmq != 0 selects the MMQ arithmetic).  n passed to
  * kq_prepare_q8 must be >= every n used with that scratch (it sizes the split-K area; everything the preparation
  * writes sits at offsets that do not depend on n, so weight tensors of different n share one preparation).
+ * Tensors of different GGML types may share it too when their blocks have the same number of weights; size the scratch
+ * with the largest kq_workspace_bytes over the types (Q4_0 above 16 tokens adds a per-call table).
  * Replace the quantize_row_q8_1_cuda call and the kernel launch inside ggml_mul_mat_vec_a8 /
  * ggml_mul_mat_a8, vllm_gguf_plugin/csrc/gguf/gguf_kernel.cu:116-118 and 119-215, 232-287; the
  * reference's production path shares the preparation the same way

@@ -92,6 +92,13 @@ static bool gemm_wanted(int type, int64_t n, int64_t k, int64_t m) {
   return false;
 }
 
+// A preparation does not know which weight tensors (type, n) will be multiplied against it: it writes the GEMM's fp16
+// operands whenever some tensor could take the GEMM at this token count.
+static bool prepare_writes_gemm_operands(int64_t m) {
+  const Options& o = options();
+  return o.gemv_impl == 0 && (m >= o.gemm_min_m || (o.gemm_small_m && m > 16));
+}
+
 static int mul_mat(const char* fn, bool mmq, const void* W, int type, int64_t n, int64_t k, const void* x,
                    int x_dtype, int64_t m, int64_t stride_x, void* y, int y_dtype, int64_t stride_y, void* scratch,
                    size_t scratch_bytes, void* stream, bool need_w = true, bool need_x = true, int wait_arrival = 0) {
@@ -101,7 +108,7 @@ static int mul_mat(const char* fn, bool mmq, const void* W, int type, int64_t n,
   if (rc) return rc;
   if (!need_w) {
     Q8Ptrs P = q8_ptrs(scratch, p.L, n);
-    if (!gemm_wanted(type, n, k, m)) P.xh = nullptr;
+    if (!prepare_writes_gemm_operands(m)) P.xh = nullptr;
     return launch_quantize(x, x_dtype, m, k, stride_x, &P, nullptr, p.L.kpad, (cudaStream_t)stream, wait_arrival);
   }
   if (mmq && (type == KQ_TYPE_IQ3_S || type == KQ_TYPE_IQ4_NL || type == KQ_TYPE_IQ4_XS)) {
@@ -214,7 +221,7 @@ static int prepare_common(const char* fn, int type, int64_t n, int64_t k, const 
   if (stride_x < min_stride) { set_error("%s: row stride %lld < %lld", fn, (long long)stride_x, (long long)min_stride); return KQ_EINVAL; }
   if (m > 80) { set_error("%s: the fused producers serve the decode path (m <= 80)", fn); return KQ_ELIMIT; }
   *P = q8_ptrs(scratch, p.L, n);
-  if (!gemm_wanted(type, n, k, m)) P->xh = nullptr;   // the GEMM's fp16 operands only where the projection will be a GEMM
+  if (!prepare_writes_gemm_operands(m)) P->xh = nullptr;   // the GEMM's fp16 operands only where some projection may be a GEMM
   return KQ_OK;
 }
 

@@ -145,6 +145,23 @@ def test_calls_of_17_to_80_tokens_take_the_gemm_where_it_is_faster(qt, n, k, m):
     assert rel_l2(to_np(y2)[:, rows], O.mul_mat(w[rows], qt, a.float().cpu().numpy(), "mmvq")) < GATE
 
 
+def test_one_preparation_serves_types_with_different_gemm_thresholds():
+    """A preparation made for a Q6_K tensor (GEMM from 49 tokens at this size) is then used by a Q4_K and a Q4_0 tensor
+    that take the GEMM at 40 tokens: the preparation writes the GEMM's operands whatever type it was told."""
+    n, k, m = 8192, 512, 40
+    x, xt = act(m, k, seed=11, dt="bf16")
+    ws = max(capi.workspace_bytes(qt, m, n, k) for qt in (14, 12, 2))
+    scratch = torch.full((ws,), 0xFF, dtype=torch.uint8, device=dev())
+    capi.prepare_q8(xt, 14, n, scratch)
+    rows = np.r_[0:64, n - 64:n]
+    for qt in (12, 2, 14):
+        w, wt = wire(qt, n, k, seed=qt)
+        y = torch.empty((m, n), dtype=torch.float32, device=dev())
+        capi.mul_mat_prepared(wt, qt, m, k, y, scratch)
+        assert capi.read_status(qt, m, n, k, scratch) == 0
+        assert rel_l2(to_np(y)[:, rows], O.mul_mat(w[rows], qt, x, "mmvq")) < GATE
+
+
 def test_gemm_and_gemv_paths_agree():
     qt, n, k, m = 14, 512, 2048, 96
     _, wt = wire(qt, n, k, seed=9)
