@@ -16,7 +16,8 @@ N = 1   decode GEMV at 27B-class shapes: a stack of 16 distinct MLP blocks, each
         Further blocks of the same JSON line: `decode_table` (per shape and M), `config3` (the decoder-stack workload
         of the multi-GPU runs on one GPU), `lowbit` (IQ3_S / Q2_K at M in {1, 16, 80} through the op API), `dequantize`
         (LM head), `prefill_gemm` (M in {256, 1024, 2048} and the LM head), `reference_cuda` (the reference's own CUDA
-        kernels, built unmodified into oracle/_ref, on the same inputs in the same run) and `cpu_baseline`.
+        kernels, built unmodified into oracle/_ref, on the same inputs in the same run), `moe` (the mixture-of-experts
+        ops, with the reference's beside them) and `cpu_baseline`.
 N > 1   the mixed-quant decoder stack: 64 layers, per layer merged q/k/v (Q8_0, N=8192), o (Q8_0, N=5120), merged
         gate/up (Q4_K, N=34816) and down (Q6_K, K=17408), batch 16, every projection sharded on its output rows over the
         ranks and all-gathered; each projection consumes the gathered output of the one before it (RMSNorm / SwiGLU /
@@ -664,6 +665,9 @@ def run_single(args, torch, dev, local):
             # ---- the reference's own CUDA kernels on the same GPU, same inputs, same run
             extra["reference_cuda"] = reference_cuda_leg(torch, tm, mats, xs, table, pf, dev, g, synth)
 
+            # ---- mixture-of-experts ops (32 experts of Q4_K 2816x2048, top-4), with the reference's kernels beside them
+            extra["moe"] = moe_leg(torch, tm, dev, synth)
+
     cpu = None
     if not args.no_cpu_baseline:
         cores = os.cpu_count() or 1
@@ -684,6 +688,49 @@ def run_single(args, torch, dev, local):
            "roofline": roof, "cpu_baseline": cpu}
     out.update(extra)
     print(json.dumps(out), flush=True)
+
+
+def moe_leg(torch, tm, dev, synth):
+    """ggml_moe_a8_vec (8 tokens) and ggml_moe_a8 (256 tokens, expert-sorted blocks) through torch.ops._C_gguf, and the
+    same calls on the reference's own build where it exists.  Synthetic routing: top_k distinct experts per token."""
+    from kaillm_b200 import linear
+    E, n, k, qt, top_k = 32, 2816, 2048, Q4_K, 4
+    try:
+        W = torch.stack([synth.wire_torch(qt, n, k, 500 + i, dev) for i in range(E)])
+        ref = None
+        path = os.path.join(ROOT, "oracle", "_ref", "_C_gguf_ref.so")
+        if os.path.exists(path):
+            torch.ops.load_library(path)
+            ref = torch.ops._C_gguf_ref
+        g = torch.Generator(device=dev)
+        rows = []
+        for tokens, which in ((8, "ggml_moe_a8_vec"), (256, "ggml_moe_a8")):
+            g.manual_seed(tokens)
+            x = torch.randn((tokens, k), device=dev, generator=g).to(torch.bfloat16)
+            ids = torch.stack([torch.randperm(E, device=dev, generator=g)[:top_k] for _ in range(tokens)]).to(torch.int32)
+            def call(ops_):
+                if which == "ggml_moe_a8_vec":
+                    return lambda: ops_.ggml_moe_a8_vec(x, W, ids, top_k, qt, n, tokens)
+                bs = int(ops_.ggml_moe_get_block_size(qt))
+                s_, e_, t_ = linear.moe_align_block_size(ids, bs, E)
+                used = int(t_.item())                  # only the blocks that hold slots (set-up, outside the timed region)
+                s_, e_ = s_[:used].contiguous(), e_[:used // bs].contiguous()
+                return lambda: ops_.ggml_moe_a8(x, W, s_, e_, t_, qt, n, top_k, tokens)
+            mine = call(torch.ops._C_gguf)
+            r, _ = tm.graph(mine)
+            us = tm.time(r, 10) * 1e3
+            row = {"op": which, "tokens": tokens, "pairs": tokens * top_k, "experts_hit": int(torch.unique(ids).numel()), "us_per_call": round(us, 1)}
+            if ref is not None:
+                theirs = call(ref)
+                a, b = mine().float(), theirs().float()
+                row["rel_l2_to_reference"] = float((a - b).norm() / b.norm().clamp_min(1e-30))
+                rr, _ = tm.graph(theirs)
+                rus = tm.time(rr, 3, warm=1) * 1e3
+                row.update({"reference_us": round(rus, 1), "speedup": round(rus / us, 2)})
+            rows.append(row)
+        return {"workload": f"{E} experts x Q4_K {n}x{k}, top-{top_k}, bf16 activations", "cases": rows}
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": f"{e!r}"[:300]}
 
 
 def reference_cuda_leg(torch, tm, mats, xs, table, pf, dev, g, synth):

@@ -108,7 +108,10 @@ def moe_align_block_size(topk_ids: torch.Tensor, block_size: int, num_experts: i
     nblocks = max_slots // block_size
     block_start = torch.arange(nblocks, device=topk_ids.device) * block_size
     ends = torch.cumsum(padded, 0)
-    expert_ids = torch.searchsorted(ends, block_start, right=True).to(torch.int32)   # blocks past the total: num_experts
+    expert_ids = torch.searchsorted(ends, block_start, right=True).to(torch.int32)
+    # blocks past the padded total belong to nobody: -1, which every kernel skips.  (An id equal to num_experts would be
+    # taken for a real expert by a kernel that only checks 0..255, as the reference's does, and read past the weights.)
+    expert_ids = torch.where(expert_ids >= num_experts, torch.full_like(expert_ids, -1), expert_ids)
     return sorted_ids, expert_ids, ends[-1:].to(torch.int32)
 
 

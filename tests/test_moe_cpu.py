@@ -30,6 +30,7 @@ def test_moe_align_block_size_layout(tokens, top_k, e, block):
     np.testing.assert_array_equal(s[:n].numpy(), ws)
     np.testing.assert_array_equal(ex[:n // block].numpy(), wex)
     assert bool((s[n:] == tokens * top_k).all())             # slots past the total are padding
+    assert bool((ex[n // block:] == -1).all())               # and their blocks belong to no expert
     assert s.numel() % block == 0 and ex.numel() == s.numel() // block
     # every (token, k) slot appears exactly once
     real = s[s < tokens * top_k].numpy()

@@ -157,7 +157,7 @@ def test_fused_moe_layer_and_align(tokens):
     ws, wex, wtot = align(ids, 8, e)
     n = int(tot.item())
     assert n == int(wtot[0]) and np.array_equal(s[:n].cpu().numpy(), ws) and np.array_equal(ex[:n // 8].cpu().numpy(), wex)
-    assert bool((s[n:] == tokens * top_k).all()) and bool((ex[n // 8:] >= e).all())
+    assert bool((s[n:] == tokens * top_k).all()) and bool((ex[n // 8:] == -1).all())   # unused blocks: no expert
     y = linear.fused_moe_gguf(xt, w1t, w2t, tw, idt, qt1, qt2)
     flavour = "mmq" if tokens > 64 else "mmvq"
     h1 = expected(w1, qt1, x, ids, flavour)
