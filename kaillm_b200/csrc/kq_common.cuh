@@ -445,14 +445,17 @@ __device__ __forceinline__ void decode_subblock(const uint8_t* __restrict__ row,
     const uint8_t* b = row + (size_t)(sb >> 3) * 110;
     const int ib = sb & 7;
     const float d = ld_h(b);
-    const uint8_t* qs = b + 2 + 8 * ib;
+    // blocks are 2-byte aligned: the sub-block's 8 index bytes and 4 sign bytes as 16-bit loads (6 instead of 12 byte loads)
+    const uint16_t* qs16 = reinterpret_cast<const uint16_t*>(b + 2 + 8 * ib);
     const uint32_t qh = b[66 + ib];
-    const uint8_t* sg = b + 74 + 4 * ib;
+    const uint16_t* sg16 = reinterpret_cast<const uint16_t*>(b + 74 + 4 * ib);
+    const uint32_t sgw = (uint32_t)sg16[0] | ((uint32_t)sg16[1] << 16);
 #pragma unroll
     for (int il = 0; il < 4; ++il) {
-      const uint32_t i1 = qs[2 * il] | ((qh << (8 - 2 * il)) & 256u);
-      const uint32_t i2 = qs[2 * il + 1] | ((qh << (7 - 2 * il)) & 256u);
-      const uint32_t s = sg[il];
+      const uint32_t q2 = qs16[il];
+      const uint32_t i1 = (q2 & 255u) | ((qh << (8 - 2 * il)) & 256u);
+      const uint32_t i2 = (q2 >> 8) | ((qh << (7 - 2 * il)) & 256u);
+      const uint32_t s = (sgw >> (8 * il)) & 255u;
       o.v[2 * il] = negate_bytes(grid[i1], nibble_to_bytemask(s & 15u));
       o.v[2 * il + 1] = negate_bytes(grid[i2], nibble_to_bytemask(s >> 4));
     }
