@@ -121,15 +121,17 @@ __global__ void __launch_bounds__(128) moe_dp4a_kernel(const MoeParams p) {
   }
 }
 
-// Block mode with the block's activations in shared memory: a CTA of eight warps copies the q8_1 codes and scales of its
-// KQ_MOE_BLOCK slots once and then walks MOE_ROWS_PER_CTA rows of the expert (warp = row), so the activations are read from
-// global memory once per 64 rows instead of once per row.  Same arithmetic, same order of additions per row as
-// moe_dp4a_kernel.  Measured on 32 experts x Q4_K 2816x2048, top-4, 256 tokens: 1005 -> see the note at run_moe.
+// The block's (vec mode: the pair's) activations in shared memory: a CTA of eight warps copies the q8_1 codes and scales of its
+// slots once and then walks MOE_ROWS_PER_CTA rows of the expert (a warp takes MOE_RW rows at a time), so the activations
+// are read from global memory once per 64 rows instead of once per row.  Same arithmetic, same order of additions per row
+// as moe_dp4a_kernel (bit-identical results).  Measured on 32 experts x Q4_K 2816x2048, top-4: block op at 256 tokens
+// 1005 -> 384 us (the reference's kernel: 581), vec op at 8 tokens 42 -> 38 us (reference: 63); four rows per warp were
+// slower than two (128 registers).
 constexpr int MOE_ROWS_PER_CTA = 64;
 #ifndef MOE_RW
 #define MOE_RW 2
 #endif
-template <int QT, int MT, bool MMQ, typename OutT>
+template <int QT, int MT, bool MMQ, bool BLOCK, typename OutT>
 __global__ void __launch_bounds__(256) moe_block_smem_kernel(const MoeParams p) {
   using F = Fmt<QT>;
   extern __shared__ __align__(16) uint8_t moe_smem[];
@@ -142,19 +144,27 @@ __global__ void __launch_bounds__(256) moe_block_smem_kernel(const MoeParams p) 
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t total = (int64_t)p.tokens * p.top_k;
-  const int64_t s0 = (int64_t)blockIdx.y * MT;
-  if (s0 > (int64_t)p.num_post_padded[0]) return;   // the reference's bound (moe.cuh:37)
-  const int expert = p.expert_ids[blockIdx.y];
-  if (expert < 0 || expert >= p.experts) return;
   int tok[MT], dst[MT];
+  int expert;
+  if constexpr (BLOCK) {
+    const int64_t s0 = (int64_t)blockIdx.y * MT;
+    if (s0 > (int64_t)p.num_post_padded[0]) return;   // the reference's bound (moe.cuh:37)
+    expert = p.expert_ids[blockIdx.y];
 #pragma unroll
-  for (int t = 0; t < MT; ++t) {
-    const int64_t s = s0 + t;
-    const int z = s < p.nslots ? p.ids[s] : -1;
-    const bool ok = z >= 0 && z < total;
-    dst[t] = ok ? z : -1;
-    tok[t] = ok ? z / p.top_k : 0;
+    for (int t = 0; t < MT; ++t) {
+      const int64_t s = s0 + t;
+      const int z = s < p.nslots ? p.ids[s] : -1;
+      const bool ok = z >= 0 && z < total;
+      dst[t] = ok ? z : -1;
+      tok[t] = ok ? z / p.top_k : 0;
+    }
+  } else {                                            // vec mode (MT = 1): the grid row is the (token, expert) pair
+    const int64_t z = blockIdx.y;
+    expert = p.ids[z];
+    dst[0] = (int)z;
+    tok[0] = (int)(z / p.top_k);
   }
+  if (expert < 0 || expert >= p.experts) return;
   {
     const int vec_per_row = p.kpad >> 4;             // 16-byte pieces of a token's codes
 #pragma unroll
@@ -244,7 +254,7 @@ int run_moe(const MoeParams& p, bool block, cudaStream_t st) {
     if (nblocks > 65535) { set_error("kq_moe_a8: more than 65535 blocks of sorted tokens"); return KQ_ELIMIT; }
     const size_t smem = (size_t)KQ_MOE_BLOCK * p.kpad + (size_t)KQ_MOE_BLOCK * (p.kpad >> 5) * 4;
     if (nblocks > 0 && smem <= 200 * 1024 && options().moe_smem) {
-      auto kern = moe_block_smem_kernel<QT, KQ_MOE_BLOCK, MMQ, OutT>;
+      auto kern = moe_block_smem_kernel<QT, KQ_MOE_BLOCK, MMQ, true, OutT>;
       static DeviceOnce attr_set;
       if (attr_set.first_time()) {
         KQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
@@ -257,7 +267,19 @@ int run_moe(const MoeParams& p, bool block, cudaStream_t st) {
     }
   } else {
     if (p.nslots > 65535) { set_error("kq_moe_a8_vec: more than 65535 (token, expert) pairs"); return KQ_ELIMIT; }
-    if (p.nslots > 0) moe_dp4a_kernel<QT, 1, MMQ, false, OutT><<<dim3(gx, (unsigned)p.nslots), 128, 0, st>>>(p);
+    const size_t smem = (size_t)p.kpad + (size_t)(p.kpad >> 5) * 4;
+    if (p.nslots > 0 && smem <= 200 * 1024 && options().moe_smem) {
+      auto kern = moe_block_smem_kernel<QT, 1, MMQ, false, OutT>;
+      static DeviceOnce attr_set;
+      if (attr_set.first_time()) {
+        KQ_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        attr_set.done();
+      }
+      const unsigned gr = (unsigned)((p.n + MOE_ROWS_PER_CTA - 1) / MOE_ROWS_PER_CTA);
+      kern<<<dim3(gr, (unsigned)p.nslots), 256, smem, st>>>(p);
+    } else if (p.nslots > 0) {
+      moe_dp4a_kernel<QT, 1, MMQ, false, OutT><<<dim3(gx, (unsigned)p.nslots), 128, 0, st>>>(p);
+    }
   }
   options().launches += 1;
   KQ_CUDA_TRY(cudaGetLastError());
