@@ -22,7 +22,7 @@ int cuda_fail(cudaError_t e, const char* what) {
 }
 
 Options& options() {
-  static Options o = {0, 3, 81, 2, 1, 0, 0, 1, 1, 0, 1, 1, 0, 1, 24, 1, 1};
+  static Options o = {0, 3, 81, 2, 1, 0, 0, 1, 1, 0, 1, 1, 0, 1, 24, 1, 1, 1};
   return o;
 }
 
@@ -532,6 +532,7 @@ int kq_set_option(const char* name, int value) {
   if (name && !strcmp(name, "no_fused_gather")) { options().no_fused_gather = value != 0; return KQ_OK; }
   if (name && !strcmp(name, "gemm_wide")) { options().gemm_wide = value; return KQ_OK; }
   if (name && !strcmp(name, "gemm_small_m")) { options().gemm_small_m = value != 0; return KQ_OK; }
+  if (name && !strcmp(name, "tile_two_stage")) { options().tile_two_stage = value != 0; return KQ_OK; }
   if (name && !strcmp(name, "moe_smem")) { options().moe_smem = value != 0; return KQ_OK; }
   if (name && !strcmp(name, "row_stage_kb")) { options().row_stage_kb = value < 4 ? 4 : (value > 96 ? 96 : value); return KQ_OK; }
   if (name && !strcmp(name, "umma")) { options().umma = value != 0; return KQ_OK; }
@@ -553,6 +554,7 @@ int kq_get_option(const char* name, int* value) {
   if (name && value && !strcmp(name, "no_fused_gather")) { *value = options().no_fused_gather; return KQ_OK; }
   if (name && value && !strcmp(name, "gemm_wide")) { *value = options().gemm_wide; return KQ_OK; }
   if (name && value && !strcmp(name, "gemm_small_m")) { *value = options().gemm_small_m; return KQ_OK; }
+  if (name && value && !strcmp(name, "tile_two_stage")) { *value = options().tile_two_stage; return KQ_OK; }
   if (name && value && !strcmp(name, "moe_smem")) { *value = options().moe_smem; return KQ_OK; }
   if (name && value && !strcmp(name, "row_stage_kb")) { *value = options().row_stage_kb; return KQ_OK; }
   if (name && value && !strcmp(name, "umma")) { *value = options().umma; return KQ_OK; }

@@ -55,6 +55,7 @@ struct Options {
   int gemm_wide;       // tcgen05 GEMM tile: 0 = 256 rows x 128 tokens, 2 = 128 rows x 256 tokens, 1 = the latter when m > 128
                        // or the format's wire bytes are staged through shared memory (where it is faster at every m)
   int row_stage_kb;    // Q4_K row-pair GEMV (1-2 tokens): target size of one ring stage (whole rows) in KB
+  int tile_two_stage;  // 1: the shared-stage GEMV may run on two whole-row stages of >= 32 KB instead of splitting K
   int moe_smem;        // 1: the MoE ops stage a block's / a pair's activations in shared memory (0: the one-warp-per-row kernel)
   int gemm_small_m;    // 1: calls of 17..gemm_min_m-1 tokens also go to the tcgen05 GEMM where it beats the 16-token
                        // GEMV passes (staged formats, enough 128-row tiles to fill the GPU)

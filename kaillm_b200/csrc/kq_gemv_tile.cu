@@ -741,10 +741,13 @@ bool make_tile_config(int type, int64_t n, int64_t k, int mtok, TileConfig& c) {
     const int fixed = TL_HEADER + (type == KQ_TYPE_IQ3_S ? TL_GRID_BYTES : 0) + a_bytes + d_bytes + z_bytes + TL_NRED * TL_CW * 512 + TL_TILE_BYTES;
     int stages = (TL_SMEM_LIMIT - fixed) / stage_bytes;
     if (stages > TL_MAX_STAGES) stages = TL_MAX_STAGES;
-    if (stages < 3) continue;
+    // two whole-row stages of >= 32 KB keep more bytes in flight, in far larger requests, than a split over K whose stages
+    // are row segments of a few KB (option tile_two_stage)
+    const bool two_ok = options().tile_two_stage && contig && stages == 2 && stage_bytes >= 32768;
+    if (stages < 3 && !two_ok) continue;
     if (ks > 1 && (int64_t)(n + TL_ROWS - 1) / TL_ROWS / (grid / ks) + 1 > TL_NRED * TL_CW * 512) continue;   // finish list
     if (ks > 1 && (n + TL_ROWS - 1) / TL_ROWS > KQ_CNT_SLOTS) continue;   // one arrival counter per 8-row tile
-    if (stages < 4 && ks < 4 && nblk >= 2 * ks) continue;   // a deeper ring with a finer split is better
+    if (stages < 4 && ks < 4 && nblk >= 2 * ks && !two_ok) continue;   // a deeper ring with a finer split is better
     c.ks = ks; c.grid = grid; c.stages = stages; c.row_stride = row_stride; c.stage_bytes = stage_bytes; c.contig = contig;
     c.a_stride = a_stride; c.a_bytes = a_bytes; c.d_bytes = d_bytes; c.z_bytes = z_bytes;
     c.smem = fixed + stages * stage_bytes;
