@@ -333,6 +333,10 @@ int kq_debug_copy_window(uint64_t base, int64_t n, int64_t rowbytes, int64_t row
  *                 integer path, inside the 1e-3 contract).  0 = m < gemm_min_m keeps exact integer dots.  Set it
  *                 BEFORE the activations are prepared (kq_prepare_q8* write the GEMM's operands only when wanted)
  *   "row_stage_kb" target size in KB of one shared-memory stage (whole rows) of the Q4_K 1-2-token kernel (default 24)
+ *   "tile_two_stage" 1 (default) = the shared-stage GEMV may run on two whole-row stages of >= 32 KB (Q8_0, K = 5120, 9-16
+ *                 tokens) instead of splitting K into row segments
+ *   "moe_smem"    1 (default) = the MoE ops stage a block's / a pair's activations in shared memory, 0 = one warp per row
+ *                 reading them from global memory (bit-identical results)
  *   "gemm_wide"   tile of the GEMM: 0 = 256 rows x 128 tokens, 2 = 128 rows x 256 tokens, 1 (default) = the latter
  *                 whenever more than 128 tokens come or the format's wire bytes are staged through shared memory
  *   "half_fma"    1 = K-quant dequantize contracts fp16 mul+sub into one fma (default), 0 = two roundings

@@ -47,6 +47,15 @@ def test_geometry_and_workspace():
     assert capi.workspace_bytes(12, 16, 17408, 5120) >= 16 * 5120 + 16 * 160 * 4
     assert capi.workspace_bytes(16, 1, 1, 256) == 0
     assert capi.workspace_bytes(12, 1, 64, 300) >= 512 + 64     # k padded to 512
+    # everything but the last region is independent of n and of the type; Q4_0 above 16 tokens adds its per-call table of
+    # -8 * d: fp16 [n][k / 32 rounded up to 128]
+    n, k = 4096, 5120
+    base = capi.workspace_bytes(8, 32, n, k)
+    assert capi.workspace_bytes(12, 32, n, k) == base == capi.workspace_bytes(14, 32, n, k)
+    assert capi.workspace_bytes(2, 16, n, k) == capi.workspace_bytes(8, 16, n, k)
+    extra = capi.workspace_bytes(2, 32, n, k) - base
+    assert n * 256 * 2 <= extra < n * 256 * 2 + 256
+    assert capi.workspace_bytes(8, 32, 2 * n, k) > base          # the split-K area grows with n
 
 
 def _mm(fn, W=0x1000, qt=12, n=8, k=256, x=0x2000, xdt=0, m=1, sx=256, y=0x3000, ydt=0, sy=8, scratch=0x4000, sb=1 << 30):
@@ -102,6 +111,10 @@ def test_options_roundtrip():
     capi.set_option("gemv_impl", old)
     with pytest.raises(capi.KqError):
         capi.set_option("nope", 1)
+    # the defaults of the dispatch options
+    for name, want in (("gemm_min_m", 81), ("gemm_small_m", 1), ("gemm_wide", 1), ("row_stage_kb", 24), ("tile_two_stage", 1),
+                       ("moe_smem", 1), ("umma", 0), ("no_fused_gather", 0)):
+        assert capi.get_option(name) == want, name
 
 
 def test_error_message_is_thread_local_text():
