@@ -2,7 +2,8 @@
 
     python -m kaillm_b200.probe --type 12 --n 17408 --k 5120 --m 16 [--opt gemv_impl=6 ...] [--mats 4] [--mmq] [--full]
 
-`--dequantize` runs kq_dequantize of each matrix instead.  `--mats` distinct weight matrices are generated from seeds (so the weights of a launch are never in L2 from the launch
+`--dequantize` runs kq_dequantize of each matrix instead; `--moe E` runs kq_moe_a8 (expert-sorted blocks) over E experts of
+n x k with `--m` tokens and `--topk` experts per token, `--mats` times.  `--mats` distinct weight matrices are generated from seeds (so the weights of a launch are never in L2 from the launch
 before), the activations are prepared once (`--full`: with every call, through kq_mul_mat_vec_a8 / kq_mul_mat_a8) and
 each matrix is multiplied once; the status word of the scratch is checked at the end.  Under `ncu` pick the kernel with
 `-k regex:...` and skip the first launch (`-s 1`).  Options are those of kq_set_option (gemv_impl, kres, umma, pdl ...).
@@ -27,6 +28,8 @@ def main(argv=None) -> int:
     ap.add_argument("--mmq", action="store_true", help="MMQ arithmetic (kq_mul_mat_a8)")
     ap.add_argument("--full", action="store_true", help="quantize the activations with every call")
     ap.add_argument("--dequantize", action="store_true", help="run kq_dequantize of the matrices (to bf16) instead of the product")
+    ap.add_argument("--moe", type=int, default=0, metavar="E", help="run kq_moe_a8 over E experts of n x k instead")
+    ap.add_argument("--topk", type=int, default=4)
     ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE")
     args = ap.parse_args(argv)
     dev = torch.device("cuda:0")
@@ -35,6 +38,20 @@ def main(argv=None) -> int:
         name, val = o.split("=")
         capi.set_option(name, int(val))
     qt, n, k, m = args.type, args.n, args.k, args.m
+    if args.moe:
+        from . import linear
+        e = args.moe
+        W = torch.stack([synth.wire_torch(qt, n, k, 100 + i, dev) for i in range(e)])
+        g = torch.Generator(device=dev)
+        g.manual_seed(m)
+        x = torch.randn((m, k), device=dev, generator=g).to(torch.bfloat16)
+        ids = torch.stack([torch.randperm(e, device=dev, generator=g)[:args.topk] for _ in range(m)]).to(torch.int32)
+        s_, e_, t_ = linear.moe_align_block_size(ids, capi.lib.kq_moe_block_size(qt), e)
+        ys = [capi.moe_a8(W, x, s_, e_, t_, args.topk, qt) for _ in range(args.mats)]
+        torch.cuda.synchronize()
+        ok = all(bool(torch.isfinite(y.float()).all()) for y in ys)
+        print(f"type {qt}: {e} experts of {n} x {k}, {m} tokens, top-{args.topk}: {args.mats} calls, finite {ok}")
+        return 0 if ok else 1
     ws = [synth.wire_torch(qt, n, k, 100 + i, dev) for i in range(args.mats)]
     if args.dequantize:
         outs = [capi.dequantize(w, qt, n * k, torch.bfloat16) for w in ws]
